@@ -1,0 +1,204 @@
+// Memory-bound row kernels: embedding gather, RMSNorm, rotary position encoding fused
+// with the write of K and V into cache pages, and the slot-ordered sum of routed-expert
+// outputs into the residual stream.  All statistics, angles and sums are float32.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding: out[t, :] = table[tokens[t], :] as float32 (the residual stream is float32).
+__global__ void embed_rows_kernel(const int* __restrict__ tokens, const void* __restrict__ table,
+                                  int table_dt, float* __restrict__ out, int H) {
+    const int t = blockIdx.x;
+    const size_t row = static_cast<size_t>(tokens[t]) * H;
+    float* o = out + static_cast<size_t>(t) * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = ld_dyn(table, table_dt, row + i);
+}
+
+extern "C" int locus_embed_rows(const int* tokens, const void* table, int table_dt, float* out,
+                                int T, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    embed_rows_kernel<<<T, 256, 0, stream>>>(tokens, table, table_dt, out, H);
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// RMSNorm of rows: out[i, :] = x[r, :] * rsqrt(mean(x[r]^2) + eps) * w, r = rows ? rows[i] : i.
+// The multiplication order (x * scale) * w follows the reference.  One block per row; the
+// sum of squares is reduced in an order that depends on H only.
+__global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void* __restrict__ w,
+                               int w_dt, float eps, void* __restrict__ out, int out_dt,
+                               const int* __restrict__ rows, int H) {
+    __shared__ float warp_part[32];
+    __shared__ float scale_s;
+    const int i = blockIdx.x;
+    const size_t src = static_cast<size_t>(rows ? rows[i] : i) * H;
+    const size_t dst = static_cast<size_t>(i) * H;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float v = ld_dyn(x, x_dt, src + j);
+        ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) warp_part[wid] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+        const int nw = blockDim.x >> 5;
+        for (int k = 0; k < nw; ++k) tot += warp_part[k];
+        scale_s = 1.0f / sqrtf(tot / static_cast<float>(H) + eps);
+    }
+    __syncthreads();
+    const float scale = scale_s;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        const float v = ld_dyn(x, x_dt, src + j);
+        st_dyn(out, out_dt, dst + j, v * scale * ld_dyn(w, w_dt, j));
+    }
+}
+
+extern "C" int locus_rmsnorm(const void* x, int x_dt, const void* w, int w_dt, float eps, void* out,
+                             int out_dt, const int* rows, int n_rows, int H, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    rmsnorm_kernel<<<n_rows, 256, 0, stream>>>(x, x_dt, w, w_dt, eps, out, out_dt, rows, H);
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Rotary encoding of q and k (angles = position * inv_freq[i], float32; sinf/cosf, no
+// fast-math) and write of the rotated K and the unrotated V into the page pool.
+//   qkv      [T, (nh + 2*nkv) * hd]   projections with bias already added
+//   q_out    [T, nh * hd]             rotated queries
+//   pool     one layer's pages: [n_pages][2 (K,V)][nkv][page_tokens][hd]
+//   slots    [T] page * page_tokens + offset of each token (from the block table)
+//   pairing  0: half-split pairs (i, i + rot/2); 1: interleaved pairs (2i, 2i+1)
+// Dimensions >= rot_dim of a head pass through unrotated.  inv_freq == nullptr applies
+// no rotation at all (a mixer without rotary encoding still uses the K/V write).
+// write_kv == 0 leaves the pages alone (a layer that reads another layer's cache).
+template <typename TA>
+__global__ void rope_kv_write_kernel(const TA* __restrict__ qkv, const int* __restrict__ positions,
+                                     const float* __restrict__ inv_freq, TA* __restrict__ q_out,
+                                     TA* __restrict__ pool, const int* __restrict__ slots, int nh,
+                                     int nkv, int hd, int rot_dim, int pairing, int page_tokens,
+                                     int write_kv) {
+    const int t = blockIdx.x;
+    const int half = rot_dim / 2;
+    const float pos = static_cast<float>(positions[t]);
+    const TA* src = qkv + static_cast<size_t>(t) * (nh + 2 * nkv) * hd;
+    const int slot = slots[t];
+    const int page = slot / page_tokens, off = slot % page_tokens;
+    const size_t page_base = static_cast<size_t>(page) * 2 * nkv * page_tokens * hd;
+    // rotated part of q and k heads: one work item per (head, pair)
+    const int n_rot_heads = nh + nkv;
+    if (inv_freq != nullptr) {
+        for (int it = threadIdx.x; it < n_rot_heads * half; it += blockDim.x) {
+            const int h = it / half, i = it % half;
+            const int d0 = pairing == 0 ? i : 2 * i;
+            const int d1 = pairing == 0 ? i + half : 2 * i + 1;
+            const float theta = pos * inv_freq[i];
+            const float c = cosf(theta), s = sinf(theta);
+            const float x0 = to_f(src[h * hd + d0]);
+            const float x1 = to_f(src[h * hd + d1]);
+            const float y0 = x0 * c - x1 * s;
+            const float y1 = x0 * s + x1 * c;
+            if (h < nh) {
+                TA* q = q_out + (static_cast<size_t>(t) * nh + h) * hd;
+                q[d0] = from_f<TA>(y0);
+                q[d1] = from_f<TA>(y1);
+            } else if (write_kv) {
+                TA* k = pool + page_base + (static_cast<size_t>(h - nh) * page_tokens + off) * hd;
+                k[d0] = from_f<TA>(y0);
+                k[d1] = from_f<TA>(y1);
+            }
+        }
+    }
+    // pass-through part of q and k heads, and all of v
+    const int rot = inv_freq != nullptr ? rot_dim : 0;
+    const int pass = hd - rot;
+    for (int it = threadIdx.x; it < n_rot_heads * pass; it += blockDim.x) {
+        const int h = it / pass, d = rot + it % pass;
+        const TA v = src[h * hd + d];
+        if (h < nh) {
+            q_out[(static_cast<size_t>(t) * nh + h) * hd + d] = v;
+        } else if (write_kv) {
+            pool[page_base + (static_cast<size_t>(h - nh) * page_tokens + off) * hd + d] = v;
+        }
+    }
+    if (!write_kv) return;
+    const TA* vsrc = src + static_cast<size_t>(nh + nkv) * hd;
+    TA* vdst = pool + page_base + static_cast<size_t>(nkv) * page_tokens * hd;
+    for (int it = threadIdx.x; it < nkv * hd; it += blockDim.x) {
+        const int h = it / hd, d = it % hd;
+        vdst[(static_cast<size_t>(h) * page_tokens + off) * hd + d] = vsrc[it];
+    }
+}
+
+extern "C" int locus_rope_kv_write(const void* qkv, int dt, const int* positions,
+                                   const float* inv_freq, void* q_out, void* pool,
+                                   const int* slots, int T, int nh, int nkv, int hd, int rot_dim,
+                                   int pairing, int page_tokens, int write_kv,
+                                   cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || (pairing != 0 && pairing != 1))
+        return LOCUS_ERR_UNSUPPORTED;
+    if (dt == LOCUS_DT_F32) {
+        rope_kv_write_kernel<float><<<T, 256, 0, stream>>>(
+            static_cast<const float*>(qkv), positions, inv_freq, static_cast<float*>(q_out),
+            static_cast<float*>(pool), slots, nh, nkv, hd, rot_dim, pairing, page_tokens, write_kv);
+    } else if (dt == LOCUS_DT_BF16) {
+        rope_kv_write_kernel<bf16><<<T, 256, 0, stream>>>(
+            static_cast<const bf16*>(qkv), positions, inv_freq, static_cast<bf16*>(q_out),
+            static_cast<bf16*>(pool), slots, nh, nkv, hd, rot_dim, pairing, page_tokens, write_kv);
+    } else {
+        return LOCUS_ERR_UNSUPPORTED;
+    }
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Routed-expert combine: x[t, :] += sum over slot = 0..k-1 (in that order) of
+// pair_out[pair_pos[t * k + slot], :].  The routing weight is already applied to
+// pair_out.  No atomics: the sum order is the selection order, for every batch.
+__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ pair_out,
+                                   const int* __restrict__ pair_pos, int k, int H) {
+    const int t = blockIdx.x;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < k; ++s) {
+            acc += pair_out[static_cast<size_t>(pair_pos[t * k + s]) * H + j];
+        }
+        x[static_cast<size_t>(t) * H + j] += acc;
+    }
+}
+
+extern "C" int locus_moe_combine(float* x, const float* pair_out, const int* pair_pos, int T,
+                                 int k, int H, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    moe_combine_kernel<<<T, 256, 0, stream>>>(x, pair_out, pair_pos, k, H);
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Row gather: out[i, :] = src[idx[i] / div, :]  (used to lay tokens out in expert order).
+template <typename TA>
+__global__ void gather_rows_kernel(const TA* __restrict__ src, const int* __restrict__ idx, int div,
+                                   TA* __restrict__ out, int W) {
+    const int i = blockIdx.x;
+    const TA* s = src + static_cast<size_t>(idx[i] / div) * W;
+    TA* o = out + static_cast<size_t>(i) * W;
+    for (int j = threadIdx.x; j < W; j += blockDim.x) o[j] = s[j];
+}
+
+extern "C" int locus_gather_rows(const void* src, int dt, const int* idx, int div, void* out,
+                                 int n, int W, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (div <= 0) return LOCUS_ERR_UNSUPPORTED;
+    if (dt == LOCUS_DT_F32) {
+        gather_rows_kernel<float><<<n, 256, 0, stream>>>(static_cast<const float*>(src), idx, div,
+                                                         static_cast<float*>(out), W);
+    } else if (dt == LOCUS_DT_BF16) {
+        gather_rows_kernel<bf16><<<n, 256, 0, stream>>>(static_cast<const bf16*>(src), idx, div,
+                                                        static_cast<bf16*>(out), W);
+    } else {
+        return LOCUS_ERR_UNSUPPORTED;
+    }
+    return locus_launch_status();
+}

@@ -1,0 +1,104 @@
+"""What a step hands to the parts: the runtime (device, element type, reusable buffers),
+the batch descriptors and a layer's view of the cache.
+
+A batch is ragged: ``n_seg`` segments, one per request in the step, each with ``seg_qn``
+new tokens that follow the ``seg_ctx`` tokens the request already has in the cache.  The
+tokens of all segments are laid end to end (``T`` rows).  Positions always come from
+these descriptors, never from a counter inside a kernel.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+
+class Runtime:
+    """Device, element type and the buffers that live across steps.
+
+    ``buf(key, shape, dtype)`` returns the same device tensor for the same key on every
+    call, allocated once at its first use (sized by the caller for the largest step), so a
+    step allocates nothing once every shape has been seen and CUDA graphs can hold the
+    addresses.
+    """
+
+    def __init__(self, device: torch.device, dtype: torch.dtype, max_tokens: int, max_segments: int,
+                 max_wanted: int) -> None:
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.max_tokens = max_tokens
+        self.max_segments = max_segments
+        self.max_wanted = max_wanted
+        self._bufs: Dict[Tuple, torch.Tensor] = {}
+        self._objects: Dict[Tuple, object] = {}
+
+    def buf(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        k = (key, tuple(shape), dtype)
+        t = self._bufs.get(k)
+        if t is None:
+            t = torch.empty(shape, dtype=dtype, device=self.device)
+            self._bufs[k] = t
+        return t
+
+    def rows(self, key: str, width: int, dtype: torch.dtype, n: int, per_token: int = 1) -> torch.Tensor:
+        """First ``n`` rows of a [max_tokens * per_token, width] buffer."""
+        return self.buf(key, (self.max_tokens * per_token, width), dtype)[:n]
+
+    def shared_object(self, key: Tuple, factory):
+        """One object per key for the whole model (for instance a routing layout that every
+        layer with the same expert count shares)."""
+        o = self._objects.get(key)
+        if o is None:
+            o = factory()
+            self._objects[key] = o
+        return o
+
+    def bytes_held(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._bufs.values())
+
+
+@dataclass
+class GroupBatch:
+    """Descriptors of one cache group for the step."""
+
+    block_table: torch.Tensor  # int32 [n_seg, table_width]
+    slots: torch.Tensor        # int32 [T]  page * page_tokens + offset of each new token
+    page_tokens: int
+
+
+@dataclass
+class StepBatch:
+    T: int
+    n_seg: int
+    tokens: torch.Tensor      # int32 [T]
+    positions: torch.Tensor   # int32 [T]
+    seg_q0: torch.Tensor      # int32 [n_seg] first row of each segment
+    seg_qn: torch.Tensor      # int32 [n_seg] new tokens
+    seg_ctx: torch.Tensor     # int32 [n_seg] tokens cached before the step
+    state_slots: torch.Tensor # int32 [n_seg] per-request state slot
+    want_rows: torch.Tensor   # int32 [n_want] rows whose logits are returned
+    n_want: int
+    chunk_items: torch.Tensor # int32 [n_chunk_items, 2] (segment, first query of a 16-token tile)
+    n_chunk_items: int
+    decode_items: torch.Tensor  # int32 [n_decode_items] segments with one new token
+    n_decode_items: int
+    max_splits: int           # split count that covers the longest context (decode kernel)
+    groups: Dict[int, GroupBatch] = field(default_factory=dict)
+    # host copies, for parts that plan on the host
+    host_seg_q0: List[int] = field(default_factory=list)
+    host_seg_qn: List[int] = field(default_factory=list)
+    host_seg_ctx: List[int] = field(default_factory=list)
+    host_state_slots: List[int] = field(default_factory=list)
+
+
+@dataclass
+class LayerCache:
+    """One layer call's view of the cache: its pages (if it keeps keys and values), the
+    descriptors of its group, and its per-request state (if it has any)."""
+
+    group: Optional[int]              # cache group id, key into StepBatch.groups
+    pool: Optional[torch.Tensor]      # [n_pages, 2, n_kv_heads, page_tokens, head_dim]
+    page_tokens: int
+    state: Optional[torch.Tensor]     # [n_state_slots, *StateSpec.shape]
+    writes: bool = True               # False: the call reads another call's cache

@@ -1,0 +1,372 @@
+"""Python entry points of the hand-written CUDA kernels.
+
+Each function takes torch tensors that already live on the GPU, checks what the C entry
+point cannot check (devices, contiguity, element types, shapes), and launches on torch's
+current stream through ctypes.  Nothing here allocates device memory or falls back to
+another implementation: a missing or failing kernel module raises.
+
+The functions are the only way the parts reach the GPU, so a test may replace them by
+plain torch functions of the same signature to exercise the engine's host logic.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc import build as _build
+
+ERR_UNSUPPORTED = 10001
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise KernelError(f"element type {dt} is not supported by the kernels (float32, bfloat16)") from None
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    return _build.load(name)
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(code: int, what: str, detail: str = "") -> None:
+    if code == 0:
+        return
+    if code == ERR_UNSUPPORTED:
+        raise KernelError(f"{what}: sizes or element types outside what the kernel takes {detail}")
+    raise KernelError(f"{what}: CUDA error {code} {detail}")
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda_c(t: torch.Tensor, name: str) -> None:
+    _need(t.is_cuda, f"{name} must be a CUDA tensor")
+    _need(t.is_contiguous(), f"{name} must be contiguous")
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    _cuda_c(t, name)
+    _need(t.dtype == torch.int32, f"{name} must be int32")
+
+
+LL = ctypes.c_longlong
+I = ctypes.c_int
+F = ctypes.c_float
+
+
+# ---------------------------------------------------------------------------
+def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = table[tokens[t], :] as float32."""
+    _i32(tokens, "tokens")
+    _cuda_c(table, "table")
+    _cuda_c(out, "out")
+    T, H = out.shape
+    _need(out.dtype == torch.float32, "embed_rows: out must be float32")
+    _need(tokens.numel() == T and table.shape[1] == H, "embed_rows: shape mismatch")
+    code = _lib("elementwise").locus_embed_rows(
+        _p(tokens), _p(table), I(dtype_code(table.dtype)), _p(out), I(T), I(H), _stream()
+    )
+    _check(code, "embed_rows")
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
+            rows: Optional[torch.Tensor] = None) -> None:
+    """out[i] = x[rows[i] if rows else i] * rsqrt(mean(x^2) + eps) * w  (statistics in float32)."""
+    _cuda_c(x, "x")
+    _cuda_c(w, "w")
+    _cuda_c(out, "out")
+    H = x.shape[-1]
+    n = out.shape[0]
+    _need(w.numel() == H and out.shape[-1] == H, "rmsnorm: width mismatch")
+    if rows is not None:
+        _i32(rows, "rows")
+        _need(rows.numel() == n, "rmsnorm: rows/out mismatch")
+    else:
+        _need(x.shape[0] == n, "rmsnorm: x/out mismatch")
+    code = _lib("elementwise").locus_rmsnorm(
+        _p(x), I(dtype_code(x.dtype)), _p(w), I(dtype_code(w.dtype)), F(eps), _p(out),
+        I(dtype_code(out.dtype)), _p(rows), I(n), I(H), _stream()
+    )
+    _check(code, "rmsnorm")
+
+
+class ExpertLayout:
+    """Device tensors that lay (token, slot) pairs out by expert (see :func:`moe_sort`)."""
+
+    def __init__(self, n_pairs_max: int, n_experts: int, tile_m: int, device) -> None:
+        self.tile_m = tile_m
+        self.n_experts = n_experts
+        self.max_tiles = (n_pairs_max + tile_m - 1) // tile_m + n_experts
+        i32 = dict(dtype=torch.int32, device=device)
+        self.counts = torch.zeros(n_experts, **i32)
+        self.offsets = torch.zeros(n_experts + 1, **i32)
+        self.sorted_pair = torch.zeros(n_pairs_max, **i32)
+        self.pair_pos = torch.zeros(n_pairs_max, **i32)
+        self.tile_expert = torch.zeros(self.max_tiles, **i32)
+        self.tile_row0 = torch.zeros(self.max_tiles, **i32)
+        self.tile_rows = torch.zeros(self.max_tiles, **i32)
+        self.n_tiles = torch.zeros(1, **i32)
+
+    def tiles_for(self, n_pairs: int) -> int:
+        """Upper bound of the number of row tiles when ``n_pairs`` pairs are routed."""
+        return min(self.max_tiles, n_pairs // self.tile_m + min(n_pairs, self.n_experts) + 1)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[torch.Tensor] = None,
+           bias: Optional[torch.Tensor] = None, accumulate: bool = False,
+           row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None,
+           x_rows: Optional[torch.Tensor] = None, x_row_div: int = 1, layout: Optional[ExpertLayout] = None, n_rows: Optional[int] = None) -> None:
+    """out = x . w^T with float32 accumulation on CUDA cores (see csrc/gemm_simt.cu).
+
+    ``w2``: out = silu(x . w^T) * (x . w2^T).  ``bias`` [N] is added, ``row_scale`` [M]
+    multiplies the row (``scale_rows``: row m uses row_scale[scale_rows[m]]), ``accumulate`` adds the result into the float32 ``out``.
+    ``x_rows``: logical row m reads x[x_rows[m] // x_row_div].  ``layout``: grouped product,
+    ``w`` is [E, N, K] and logical rows are the expert-sorted pairs of the layout.
+    ``n_rows``: number of logical rows (default: rows of ``out``).
+    """
+    _cuda_c(x, "x")
+    _cuda_c(w, "w")
+    _cuda_c(out, "out")
+    K = x.shape[-1]
+    N = w.shape[-2]
+    _need(w.shape[-1] == K, f"linear: x has width {K} but w has {w.shape[-1]}")
+    _need(out.shape[-1] == N, f"linear: out has width {out.shape[-1]} but w has {N} rows")
+    M = out.shape[0] if n_rows is None else n_rows
+    _need(M <= out.shape[0], "linear: more rows than out holds")
+    if x_rows is None and layout is None:
+        _need(x.shape[0] >= M, "linear: x has fewer rows than out")
+    if w2 is not None:
+        _need(w2.shape == w.shape and w2.dtype == w.dtype and w2.is_contiguous(), "linear: w2 must match w")
+    if accumulate:
+        _need(out.dtype == torch.float32, "linear: accumulate needs a float32 out")
+    if bias is not None:
+        _need(bias.numel() == N and bias.is_contiguous(), "linear: bias size")
+    if row_scale is not None:
+        _need(row_scale.dtype == torch.float32 and row_scale.is_contiguous(), "linear: row_scale must be float32")
+        if scale_rows is not None:
+            _i32(scale_rows, "scale_rows")
+        else:
+            _need(row_scale.numel() >= M, "linear: row_scale must hold M rows")
+    if x_rows is not None:
+        _i32(x_rows, "x_rows")
+    if layout is not None:
+        _need(w.dim() == 3 and w.shape[0] == layout.n_experts, "linear: grouped product needs w [E, N, K]")
+        _need(layout.tile_m == 64, "linear: the CUDA-core product uses 64-row tiles")
+        te, t0, tr, nt = layout.tile_expert, layout.tile_row0, layout.tile_rows, layout.n_tiles
+        max_tiles = layout.tiles_for(M)
+        stride = N * K
+    else:
+        _need(w.dim() == 2, "linear: w must be [N, K]")
+        te = t0 = tr = nt = None
+        max_tiles = 0
+        stride = 0
+    code = _lib("gemm_simt").locus_gemm_simt(
+        _p(x), I(dtype_code(x.dtype)), _p(w), _p(w2), I(dtype_code(w.dtype)), _p(bias),
+        I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
+        I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
+        LL(x.stride(0)), LL(out.stride(0)), _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), LL(stride),
+        _stream()
+    )
+    _check(code, "linear", f"(M={M}, N={N}, K={K}, x {x.dtype}, w {w.dtype})")
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
+                  q_out: torch.Tensor, pool: torch.Tensor, slots: torch.Tensor, *, n_heads: int,
+                  n_kv_heads: int, head_dim: int, rot_dim: int, interleaved: bool,
+                  page_tokens: int, write_kv: bool = True) -> None:
+    """Rotate q and k by position, write q to ``q_out`` and k, v into the layer's pages.
+
+    ``pool`` is one layer's pages [n_pages, 2, n_kv_heads, page_tokens, head_dim];
+    ``slots[t] = page * page_tokens + offset``.  ``inv_freq`` None: no rotation.
+    """
+    _cuda_c(qkv, "qkv")
+    _cuda_c(q_out, "q_out")
+    _cuda_c(pool, "pool")
+    _i32(positions, "positions")
+    _i32(slots, "slots")
+    T = qkv.shape[0]
+    _need(qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim, "rope_kv_write: qkv width")
+    _need(qkv.dtype == q_out.dtype == pool.dtype, "rope_kv_write: q, k, v and the cache share one element type")
+    _need(tuple(pool.shape[1:]) == (2, n_kv_heads, page_tokens, head_dim), "rope_kv_write: pool layout")
+    _need(positions.numel() >= T and slots.numel() >= T and q_out.shape[0] >= T, "rope_kv_write: T mismatch")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() == rot_dim // 2 and inv_freq.is_cuda,
+              "rope_kv_write: inv_freq must be float32 [rot_dim / 2]")
+    code = _lib("elementwise").locus_rope_kv_write(
+        _p(qkv), I(dtype_code(qkv.dtype)), _p(positions), _p(inv_freq), _p(q_out), _p(pool),
+        _p(slots), I(T), I(n_heads), I(n_kv_heads), I(head_dim), I(rot_dim),
+        I(1 if interleaved else 0), I(page_tokens), I(1 if write_kv else 0), _stream()
+    )
+    _check(code, "rope_kv_write")
+
+
+def attn_chunk(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
+               seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
+               items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
+               page_tokens: int, window: int, scale: float) -> None:
+    """Attention of portions of prompts: ``items`` [n_items, 2] = (segment, first query of a
+    16-query tile).  Keys come from the cache through ``block_table`` [n_seg, width]."""
+    _cuda_c(q, "q")
+    _cuda_c(out, "out")
+    _cuda_c(pool, "pool")
+    _i32(block_table, "block_table")
+    _i32(items, "items")
+    _need(q.dtype == pool.dtype == out.dtype, "attn_chunk: q, cache and out share one element type")
+    code = _lib("attention").locus_attn_chunk(
+        _p(q), I(dtype_code(q.dtype)), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
+        _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads),
+        I(head_dim), I(page_tokens), I(window), F(scale), _stream()
+    )
+    _check(code, "attn_chunk", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
+
+
+DECODE_SPLIT = 256
+
+
+def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
+                seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
+                items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                page_tokens: int, window: int, scale: float, part_o: torch.Tensor,
+                part_ml: torch.Tensor, max_splits: int) -> None:
+    """Attention of single new tokens: ``items`` [n_items] = segments with one new token.
+
+    ``part_o`` (float32, n_items * n_heads * max_splits * head_dim) and ``part_ml``
+    (float32, twice n_items * n_heads * max_splits) are scratch for the split results;
+    ``max_splits`` must be at least longest_position // 256 + 1.
+    """
+    _cuda_c(q, "q")
+    _cuda_c(out, "out")
+    _cuda_c(pool, "pool")
+    _i32(block_table, "block_table")
+    _i32(items, "items")
+    _need(q.dtype == pool.dtype == out.dtype, "attn_decode: q, cache and out share one element type")
+    _need(part_o.dtype == torch.float32 and part_o.numel() >= n_items * n_heads * max_splits * head_dim,
+          "attn_decode: part_o too small")
+    _need(part_ml.dtype == torch.float32 and part_ml.numel() >= 2 * n_items * n_heads * max_splits,
+          "attn_decode: part_ml too small")
+    code = _lib("attention").locus_attn_decode(
+        _p(q), I(dtype_code(q.dtype)), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
+        _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads),
+        I(head_dim), I(page_tokens), I(window), F(scale), _p(part_o), _p(part_ml), I(max_splits),
+        _stream()
+    )
+    _check(code, "attn_decode", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
+
+
+def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.Tensor],
+                ids: torch.Tensor, wts: torch.Tensor, gamma: Optional[torch.Tensor], *, top_k: int,
+                renorm: bool, scale: float = 1.0) -> None:
+    """Router: softmax over all experts, top-k by repeated arg-max, weights; and
+    gamma = sigmoid(w_gate . h) when the shared expert is gated.  All in float32."""
+    _cuda_c(h, "h")
+    _cuda_c(w_router, "w_router")
+    _i32(ids, "ids")
+    T, H = h.shape
+    E = w_router.shape[0]
+    _need(w_router.shape[1] == H, "router_topk: width mismatch")
+    _need(wts.dtype == torch.float32 and wts.numel() >= T * top_k and ids.numel() >= T * top_k,
+          "router_topk: ids / wts too small")
+    if w_gate is not None:
+        _need(w_gate.numel() == H and gamma is not None and gamma.dtype == torch.float32 and gamma.numel() >= T,
+              "router_topk: gate needs w_gate [H] and gamma [T] float32")
+    code = _lib("moe_route").locus_router_topk(
+        _p(h), I(dtype_code(h.dtype)), _p(w_router), I(dtype_code(w_router.dtype)), _p(w_gate),
+        I(dtype_code(w_gate.dtype) if w_gate is not None else 0), _p(ids), _p(wts), _p(gamma), I(T),
+        I(H), I(E), I(top_k), I(1 if renorm else 0), F(scale), _stream()
+    )
+    _check(code, "router_topk", f"(H={H}, E={E}, k={top_k})")
+
+
+def moe_sort(ids: torch.Tensor, n_pairs: int, layout: ExpertLayout) -> None:
+    """Fill ``layout`` from the picked experts ``ids`` (first ``n_pairs`` entries)."""
+    _i32(ids, "ids")
+    _need(n_pairs <= layout.sorted_pair.numel(), "moe_sort: layout too small")
+    code = _lib("moe_route").locus_moe_sort(
+        _p(ids), I(n_pairs), I(layout.n_experts), I(layout.tile_m), _p(layout.counts),
+        _p(layout.offsets), _p(layout.sorted_pair), _p(layout.pair_pos), _p(layout.tile_expert),
+        _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _stream()
+    )
+    _check(code, "moe_sort")
+
+
+def moe_combine(x: torch.Tensor, pair_out: torch.Tensor, pair_pos: torch.Tensor, top_k: int) -> None:
+    """x[t] += sum over slots (in slot order) of pair_out[pair_pos[t * k + slot]]."""
+    _cuda_c(x, "x")
+    _cuda_c(pair_out, "pair_out")
+    _i32(pair_pos, "pair_pos")
+    T, H = x.shape
+    _need(x.dtype == torch.float32 and pair_out.dtype == torch.float32, "moe_combine: float32 only")
+    _need(pair_out.shape[-1] == H, "moe_combine: width mismatch")
+    code = _lib("elementwise").locus_moe_combine(_p(x), _p(pair_out), _p(pair_pos), I(T), I(top_k), I(H),
+                                                 _stream())
+    _check(code, "moe_combine")
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor, div: int, out: torch.Tensor, n: int) -> None:
+    """out[i] = src[idx[i] // div] for i < n."""
+    _cuda_c(src, "src")
+    _cuda_c(out, "out")
+    _i32(idx, "idx")
+    _need(src.dtype == out.dtype and src.shape[-1] == out.shape[-1], "gather_rows: mismatch")
+    code = _lib("elementwise").locus_gather_rows(_p(src), I(dtype_code(src.dtype)), _p(idx), I(div), _p(out),
+                                                 I(n), I(src.shape[-1]), _stream())
+    _check(code, "gather_rows")
+
+
+def apply_penalties(logits: torch.Tensor, history: torch.Tensor, repeat: torch.Tensor,
+                    freq: torch.Tensor, presence: torch.Tensor) -> None:
+    """In place: repetition / frequency / presence penalties over ``history`` [R, n] (-1 = none)."""
+    _cuda_c(logits, "logits")
+    _i32(history, "history")
+    R, V = logits.shape
+    _need(logits.dtype == torch.float32, "apply_penalties: float32 logits")
+    _need(history.shape[0] == R, "apply_penalties: history rows")
+    code = _lib("sampling").locus_apply_penalties(
+        _p(logits), LL(logits.stride(0)), I(R), I(V), _p(history), I(history.shape[1]), _p(repeat),
+        _p(freq), _p(presence), _stream()
+    )
+    _check(code, "apply_penalties")
+
+
+def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, min_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
+           out: torch.Tensor, kept_count: Optional[torch.Tensor] = None) -> None:
+    """One token per row of ``logits`` [R, V] float32 (temperature <= 0: arg-max)."""
+    _need(logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1,
+          "sample: logits must be float32 CUDA rows")
+    R, V = logits.shape
+    _i32(out, "out")
+    _i32(top_k, "top_k")
+    for t, n in ((temperature, "temperature"), (top_p, "top_p"), (min_p, "min_p")):
+        _need(t.dtype == torch.float32 and t.numel() >= R and t.is_cuda, f"sample: {n} must be float32 [R]")
+    for t, n in ((seeds, "seeds"), (counters, "counters")):
+        _need(t.dtype == torch.int64 and t.numel() >= R and t.is_cuda, f"sample: {n} must be int64 [R]")
+    code = _lib("sampling").locus_sample(
+        _p(logits), LL(logits.stride(0)), I(R), I(V), _p(temperature), _p(top_k), _p(top_p), _p(min_p),
+        _p(seeds), _p(counters), _p(out), _p(kept_count), _stream()
+    )
+    _check(code, "sample")
+
+
+def modules_for(dtype: torch.dtype) -> list:
+    """Kernel modules that a model of element type ``dtype`` needs."""
+    return ["elementwise", "gemm_simt", "attention", "moe_route", "sampling"]

@@ -1,0 +1,109 @@
+"""Attention mixer over the paged cache: grouped-query attention with optional q/k/v bias,
+a position encoding, an optional window, and an output projection.
+
+Per token, as the reference computes it (``qwen2moe_attention``,
+src/locus/model/arch.cpp:596-696): q = Wq.h + bq, k = Wk.h + bk, v = Wv.h + bv
+(arch.cpp:618-620, 650-655); q and k rotated (arch.cpp:621-622, 656-657), v not; k and v
+written to the cache at the token's position; for head h with kv head h // (heads/kv_heads):
+scores = q.k * 1/sqrt(head_dim) over the keys 0..pos (arch.cpp:668-681), softmax
+(arch.cpp:682), weighted sum of v (arch.cpp:683-694); output = Wo.concat(heads), added to
+the residual stream (src/locus/model/llama.cpp:487-490).
+
+The three projections are one product against the stacked weight [(heads + 2 kv_heads) *
+head_dim, hidden]; that is layout only.  Scores, softmax and the weighted sum are float32.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import kernels as K
+from .base import Mixer, PagedKvSpec, PartSpec, TensorSource, make_part, register_mixer
+
+
+class Attention(Mixer):
+    def __init__(self, prefix: str, *, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 qkv_bias: bool, o_bias: bool = False, window: int = 0,
+                 position: PartSpec = PartSpec("none"), softmax_scale: Optional[float] = None) -> None:
+        super().__init__(prefix)
+        if n_heads % n_kv_heads:
+            raise ValueError(f"attention: {n_heads} heads are not a multiple of {n_kv_heads} kv heads")
+        if head_dim % 16 or not (16 <= head_dim <= 256):
+            raise ValueError(f"attention: head_dim {head_dim} is not a multiple of 16 in 16..256 "
+                             "(the attention kernels take no other head size)")
+        self.hidden, self.n_heads, self.n_kv_heads, self.head_dim = hidden, n_heads, n_kv_heads, head_dim
+        self.qkv_bias, self.o_bias, self.window = bool(qkv_bias), bool(o_bias), int(window)
+        self.scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(head_dim)
+        self.position = make_part("position", position, prefix + ".position")
+        self.q_dim = n_heads * head_dim
+        self.kv_dim = n_kv_heads * head_dim
+
+    def sub_parts(self):
+        return [self.position]
+
+    # -- weights ------------------------------------------------------------
+    def param_shapes(self):
+        shapes = {"wqkv": (self.q_dim + 2 * self.kv_dim, self.hidden), "wo": (self.hidden, self.q_dim)}
+        if self.qkv_bias:
+            shapes["bqkv"] = (self.q_dim + 2 * self.kv_dim,)
+        if self.o_bias:
+            shapes["bo"] = (self.hidden,)
+        return shapes
+
+    def sources(self):
+        p = self.prefix
+        rows = [("q_proj", 0, self.q_dim), ("k_proj", self.q_dim, self.kv_dim),
+                ("v_proj", self.q_dim + self.kv_dim, self.kv_dim)]
+        out = [TensorSource(f"{p}.{n}.weight", (size, self.hidden), "wqkv", row0) for n, row0, size in rows]
+        if self.qkv_bias:
+            out += [TensorSource(f"{p}.{n}.bias", (size,), "bqkv", row0, "bias") for n, row0, size in rows]
+        out.append(TensorSource(f"{p}.o_proj.weight", (self.hidden, self.q_dim), "wo"))
+        if self.o_bias:
+            out.append(TensorSource(f"{p}.o_proj.bias", (self.hidden,), "bo", 0, "bias"))
+        return out
+
+    def kernel_modules(self, dtype):
+        return ["elementwise", "gemm_simt", "attention"]
+
+    def cache_needs(self):
+        return PagedKvSpec(self.n_kv_heads, self.head_dim, self.window), None
+
+    # -- forward ------------------------------------------------------------
+    def forward(self, h, batch, cache, residual, rt) -> None:
+        T = batch.T
+        gb = batch.groups[cache.group]
+        qkv = rt.rows("attention.qkv", self.q_dim + 2 * self.kv_dim, rt.dtype, T)
+        K.linear(h, self.params["wqkv"], qkv, bias=self.params.get("bqkv"))
+        table = self.position.rotary_table()
+        if table is None:
+            # an encoding without a rotary table transforms q and k in place itself
+            self.position.apply(qkv[:, : self.q_dim], qkv[:, self.q_dim : self.q_dim + self.kv_dim],
+                                batch.positions)
+        q = rt.rows("attention.q", self.q_dim, rt.dtype, T)
+        K.rope_kv_write(
+            qkv, batch.positions, table.inv_freq if table else None, q, cache.pool, gb.slots,
+            n_heads=self.n_heads, n_kv_heads=self.n_kv_heads, head_dim=self.head_dim,
+            rot_dim=table.rot_dim if table else 0, interleaved=table.interleaved if table else False,
+            page_tokens=gb.page_tokens, write_kv=cache.writes,
+        )
+        o = rt.rows("attention.o", self.q_dim, rt.dtype, T)
+        common = dict(seg_q0=batch.seg_q0, seg_qn=batch.seg_qn, seg_ctx=batch.seg_ctx,
+                      block_table=gb.block_table, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
+                      head_dim=self.head_dim, page_tokens=gb.page_tokens, window=self.window,
+                      scale=self.scale)
+        if batch.n_chunk_items:
+            K.attn_chunk(q, cache.pool, o, items=batch.chunk_items, n_items=batch.n_chunk_items, **common)
+        if batch.n_decode_items:
+            n = batch.n_decode_items
+            part_o = rt.buf("attention.part_o", (rt.max_segments * self.n_heads * batch.max_splits * self.head_dim,),
+                            torch.float32)
+            part_ml = rt.buf("attention.part_ml", (2 * rt.max_segments * self.n_heads * batch.max_splits,),
+                             torch.float32)
+            K.attn_decode(q, cache.pool, o, items=batch.decode_items, n_items=n, part_o=part_o,
+                          part_ml=part_ml, max_splits=batch.max_splits, **common)
+        K.linear(o, self.params["wo"], residual, bias=self.params.get("bo"), accumulate=True)
+
+
+register_mixer("attention", Attention)

@@ -1,0 +1,252 @@
+"""Interfaces of the parts a model is put together from, and their registries.
+
+A model is data: a :class:`ModelPlan` names, layer by layer, which mixer, feed-forward,
+norm and block arrangement to use and with which sizes and constants, plus the order in
+which the layers run.  The parts themselves know nothing of the model they are in: they
+get their sizes as constructor arguments, declare the checkpoint tensors they want
+(:class:`TensorSource`), the cache they need (:class:`PagedKvSpec`, :class:`StateSpec`)
+and implement ``forward``.  New kinds are added with ``register_mixer`` and friends; the
+reference has one hook table per architecture instead (``ArchSpec``,
+src/locus/model/arch.hpp:19-53).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple
+
+import torch
+
+
+# ---------------------------------------------------------------------------
+# data that describes a model
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """A part chosen by kind, with its sizes and constants."""
+
+    kind: str
+    args: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    """One layer: the tensor-name prefix, the arrangement and the parts it arranges."""
+
+    prefix: str
+    arrangement: PartSpec
+    norm: PartSpec
+    mixer: PartSpec
+    feed_forward: PartSpec
+
+
+@dataclass(frozen=True)
+class LayerCall:
+    """One entry of the run order: run ``layer``; ``cache_of`` names an earlier entry of the
+    order (by its index) whose cache this call reads instead of keeping its own."""
+
+    layer: int
+    cache_of: Optional[int] = None
+
+
+@dataclass
+class ModelPlan:
+    architecture: str
+    hidden_size: int
+    vocab_size: int
+    max_positions: int
+    eos_token_id: int
+    embedding: PartSpec
+    layers: List[LayerSpec]
+    order: List[LayerCall]
+    final_norm: PartSpec
+    head: PartSpec
+    config: Any = None
+
+    def describe(self) -> Dict[str, Any]:
+        return {
+            "architecture": self.architecture,
+            "layers": len(self.layers),
+            "calls": len(self.order),
+            "hidden": self.hidden_size,
+            "vocab": self.vocab_size,
+        }
+
+
+# ---------------------------------------------------------------------------
+# what a part asks of the weight loader and the cache manager
+
+
+@dataclass(frozen=True)
+class TensorSource:
+    """A checkpoint tensor and where it goes: rows ``row0 .. row0 + shape[0]`` of the part's
+    parameter ``param`` (seen as [rows, cols], or as a vector when 1-D).  ``init`` names the
+    random distribution of the random-weights mode: "linear", "bias" or "norm"."""
+
+    name: str
+    shape: Tuple[int, ...]
+    param: str
+    row0: int = 0
+    init: str = "linear"
+
+
+@dataclass(frozen=True)
+class PagedKvSpec:
+    """Keys and values of every token, in pages; ``window`` > 0: only the last ``window``."""
+
+    n_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size (one tensor of ``shape`` per request), zero at start."""
+
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Part:
+    """Base of every part.  ``params`` holds the loaded device tensors by parameter name."""
+
+    def __init__(self, prefix: str) -> None:
+        self.prefix = prefix
+        self.params: Dict[str, torch.Tensor] = {}
+
+    # -- weights ------------------------------------------------------------
+    def param_shapes(self) -> Dict[str, Tuple[int, ...]]:
+        """Shape of every parameter this part owns."""
+        return {}
+
+    def sources(self) -> List[TensorSource]:
+        """Checkpoint tensors that fill the parameters."""
+        return []
+
+    # -- lifecycle ----------------------------------------------------------
+    def kernel_modules(self, dtype: torch.dtype) -> List[str]:
+        """CUDA modules (files of csrc/) this part launches."""
+        return []
+
+    def bind(self, rt: "Runtime") -> None:
+        """Called once after the parameters are on the device."""
+
+    def sub_parts(self) -> List["Part"]:
+        return []
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        """out = norm(x) (rows: gather of x rows); statistics in float32."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """How a mixer encodes positions.  A rotary encoding exposes its table so that the
+    mixer can fuse the rotation into its cache write; any encoding may instead implement
+    ``apply`` to transform q and k in place."""
+
+    def rotary_table(self) -> Optional["RotaryTable"]:
+        return None
+
+    def apply(self, q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+@dataclass
+class RotaryTable:
+    inv_freq: torch.Tensor  # float32 [rot_dim / 2] on the device
+    rot_dim: int
+    interleaved: bool
+
+
+class Mixer(Part):
+    """Mixes information across the tokens of a request (attention here)."""
+
+    def cache_needs(self) -> Tuple[Optional[PagedKvSpec], Optional[StateSpec]]:
+        return None, None
+
+    def forward(self, h: torch.Tensor, batch: "StepBatch", cache: "LayerCache",
+                residual: torch.Tensor, rt: "Runtime") -> None:
+        """Add the mixer's output for the ``batch.T`` rows of ``h`` into ``residual`` (float32)."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, batch: "StepBatch", residual: torch.Tensor, rt: "Runtime") -> None:
+        """Add the feed-forward output of ``h`` into ``residual`` (float32)."""
+        raise NotImplementedError
+
+
+class Arrangement(Part):
+    """How norm, mixer and feed-forward are arranged around the residual stream."""
+
+    def forward(self, x: torch.Tensor, batch: "StepBatch", cache: "LayerCache", rt: "Runtime") -> None:
+        raise NotImplementedError
+
+
+# ---------------------------------------------------------------------------
+# registries
+
+_REGISTRIES: Dict[str, Dict[str, Callable[..., Part]]] = {
+    "mixer": {},
+    "feed_forward": {},
+    "norm": {},
+    "position": {},
+    "arrangement": {},
+    "embedding": {},
+    "head": {},
+}
+
+
+def _register(family: str, kind: str, factory: Callable[..., Part]) -> None:
+    _REGISTRIES[family][kind] = factory
+
+
+def register_mixer(kind: str, factory: Callable[..., Part]) -> None:
+    _register("mixer", kind, factory)
+
+
+def register_feed_forward(kind: str, factory: Callable[..., Part]) -> None:
+    _register("feed_forward", kind, factory)
+
+
+def register_norm(kind: str, factory: Callable[..., Part]) -> None:
+    _register("norm", kind, factory)
+
+
+def register_position(kind: str, factory: Callable[..., Part]) -> None:
+    _register("position", kind, factory)
+
+
+def register_arrangement(kind: str, factory: Callable[..., Part]) -> None:
+    _register("arrangement", kind, factory)
+
+
+def register_embedding(kind: str, factory: Callable[..., Part]) -> None:
+    _register("embedding", kind, factory)
+
+
+def register_head(kind: str, factory: Callable[..., Part]) -> None:
+    _register("head", kind, factory)
+
+
+def make_part(family: str, spec: PartSpec, prefix: str, **extra) -> Part:
+    """Instantiate the part ``spec`` of ``family`` with tensor-name prefix ``prefix``."""
+    try:
+        factory = _REGISTRIES[family][spec.kind]
+    except KeyError:
+        known = ", ".join(sorted(_REGISTRIES[family])) or "(none)"
+        raise ValueError(f"unknown {family} kind {spec.kind!r} (registered: {known})") from None
+    return factory(prefix, **spec.args, **extra)
+
+
+def registered(family: str) -> List[str]:
+    return sorted(_REGISTRIES[family])
+
+
+def iter_parts(part: Part):
+    """The part and every part nested in it."""
+    yield part
+    for s in part.sub_parts():
+        yield from iter_parts(s)

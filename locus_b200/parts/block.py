@@ -1,0 +1,84 @@
+"""Block arrangements and the parts at the two ends of the model.
+
+``PreNorm``: x += mixer(norm1(x)); x += feed_forward(norm2(x)) -- the residual placement
+of the reference's forward (src/locus/model/llama.cpp:485-509).  The residual stream x is
+float32 in every mode; the normed activations have the model's element type.
+
+``Embedding``: x = table[token] (llama.cpp:450).  ``LmHead``: logits = W . h in float32,
+W being the embedding table when the head is tied (llama.cpp:292-297, 512-513).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels as K
+from .base import (Arrangement, Part, PartSpec, TensorSource, make_part, register_arrangement,
+                   register_embedding, register_head)
+
+
+class PreNorm(Arrangement):
+    def __init__(self, prefix: str, *, hidden: int, norm: PartSpec, mixer: PartSpec,
+                 feed_forward: PartSpec, mixer_prefix: str = "self_attn", ff_prefix: str = "mlp",
+                 norm1_name: str = "input_layernorm", norm2_name: str = "post_attention_layernorm") -> None:
+        super().__init__(prefix)
+        self.hidden = hidden
+        self.norm1 = make_part("norm", norm, f"{prefix}.{norm1_name}")
+        self.mixer = make_part("mixer", mixer, f"{prefix}.{mixer_prefix}")
+        self.norm2 = make_part("norm", norm, f"{prefix}.{norm2_name}")
+        self.ff = make_part("feed_forward", feed_forward, f"{prefix}.{ff_prefix}")
+
+    def sub_parts(self):
+        return [self.norm1, self.mixer, self.norm2, self.ff]
+
+    def forward(self, x, batch, cache, rt) -> None:
+        T = batch.T
+        h = rt.rows("block.h", self.hidden, rt.dtype, T)
+        self.norm1.forward(x, h)
+        self.mixer.forward(h, batch, cache, x, rt)
+        self.norm2.forward(x, h)
+        self.ff.forward(h, batch, x, rt)
+
+
+class Embedding(Part):
+    def __init__(self, prefix: str, *, vocab: int, hidden: int) -> None:
+        super().__init__(prefix)
+        self.vocab, self.hidden = int(vocab), int(hidden)
+
+    def param_shapes(self):
+        return {"table": (self.vocab, self.hidden)}
+
+    def sources(self):
+        return [TensorSource(self.prefix + ".weight", (self.vocab, self.hidden), "table")]
+
+    def kernel_modules(self, dtype):
+        return ["elementwise"]
+
+    def forward(self, tokens: torch.Tensor, out: torch.Tensor) -> None:
+        K.embed_rows(tokens, self.params["table"], out)
+
+
+class LmHead(Part):
+    """``tied``: no tensor of its own; the model hands it the embedding table."""
+
+    def __init__(self, prefix: str, *, vocab: int, hidden: int, tied: bool) -> None:
+        super().__init__(prefix)
+        self.vocab, self.hidden, self.tied = int(vocab), int(hidden), bool(tied)
+
+    def param_shapes(self):
+        return {} if self.tied else {"weight": (self.vocab, self.hidden)}
+
+    def sources(self):
+        if self.tied:
+            return []
+        return [TensorSource(self.prefix + ".weight", (self.vocab, self.hidden), "weight")]
+
+    def kernel_modules(self, dtype):
+        return ["gemm_simt"]
+
+    def forward(self, h: torch.Tensor, logits: torch.Tensor) -> None:
+        K.linear(h, self.params["weight"], logits)
+
+
+register_arrangement("pre_norm", PreNorm)
+register_embedding("embedding", Embedding)
+register_head("linear", LmHead)

@@ -1,0 +1,127 @@
+"""Feed-forward parts: the dense SwiGLU MLP and the sparse mixture of experts.
+
+Dense (src/locus/model/llama.cpp:493-503 of the reference):
+    out = Wdown . (silu(Wgate . h) * (Wup . h)),  silu(g) = g / (1 + exp(-g))
+    (``silu_mul``, src/locus/backend/cpu_ops.cpp:1736-1743).
+
+Sparse (``moe_ffn`` llama.cpp:992-1077, ``moe_select`` llama.cpp:900-980):
+    r = Wr . h; p = softmax(r) over all experts; pick top-k by k rounds of arg-max with
+    strict '>' (ties to the lowest index); weight w_e = p_e / wsum * scale with
+    wsum = sum of picked p_e when ``norm_topk`` else 1; out = sum over picked e, in pick
+    order, of w_e * SwiGLU_e(h); then the shared expert, scaled by
+    sigmoid(w_shared_gate . h) when it is gated (llama.cpp:1062-1076), is added.
+
+The batched form lays the (token, slot) pairs out by expert, runs each expert over its
+tokens, and sums each token's pairs in slot order without atomics (the reference's
+``moe_ffn_batch``, llama.cpp:1079-1235, does the same to stay byte-identical).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels as K
+from .base import FeedForward, TensorSource, register_feed_forward
+
+
+class DenseMlp(FeedForward):
+    def __init__(self, prefix: str, *, hidden: int, intermediate: int) -> None:
+        super().__init__(prefix)
+        self.hidden, self.inter = int(hidden), int(intermediate)
+
+    def param_shapes(self):
+        return {"w_gate": (self.inter, self.hidden), "w_up": (self.inter, self.hidden),
+                "w_down": (self.hidden, self.inter)}
+
+    def sources(self):
+        p = self.prefix
+        return [
+            TensorSource(f"{p}.gate_proj.weight", (self.inter, self.hidden), "w_gate"),
+            TensorSource(f"{p}.up_proj.weight", (self.inter, self.hidden), "w_up"),
+            TensorSource(f"{p}.down_proj.weight", (self.hidden, self.inter), "w_down"),
+        ]
+
+    def kernel_modules(self, dtype):
+        return ["gemm_simt"]
+
+    def forward(self, h, batch, residual, rt, row_scale=None) -> None:
+        T = h.shape[0]
+        act = rt.rows(f"dense_mlp.act{self.inter}", self.inter, rt.dtype, T)
+        K.linear(h, self.params["w_gate"], act, w2=self.params["w_up"])
+        K.linear(act, self.params["w_down"], residual, accumulate=True, row_scale=row_scale)
+
+
+class SparseMoe(FeedForward):
+    """Softmax top-k routed SwiGLU experts plus an optional (gated) shared SwiGLU expert."""
+
+    def __init__(self, prefix: str, *, hidden: int, n_experts: int, top_k: int, norm_topk: bool,
+                 expert_intermediate: int, shared_intermediate: int = 0, shared_gate: bool = True,
+                 weight_scale: float = 1.0) -> None:
+        super().__init__(prefix)
+        if not (1 <= top_k <= n_experts):
+            raise ValueError(f"sparse_moe: top_k {top_k} must be within 1..{n_experts}")
+        self.hidden, self.E, self.k = int(hidden), int(n_experts), int(top_k)
+        self.norm_topk, self.I, self.Is = bool(norm_topk), int(expert_intermediate), int(shared_intermediate)
+        self.shared_gate = bool(shared_gate) and self.Is > 0
+        self.weight_scale = float(weight_scale)
+        self.shared = (DenseMlp(prefix + ".shared_expert", hidden=hidden, intermediate=self.Is)
+                       if self.Is > 0 else None)
+        self._layout = None
+
+    def sub_parts(self):
+        return [self.shared] if self.shared is not None else []
+
+    def param_shapes(self):
+        s = {
+            "router": (self.E, self.hidden),
+            "gate_exps": (self.E, self.I, self.hidden),
+            "up_exps": (self.E, self.I, self.hidden),
+            "down_exps": (self.E, self.hidden, self.I),
+        }
+        if self.shared_gate:
+            s["shared_gate"] = (1, self.hidden)
+        return s
+
+    def sources(self):
+        p = self.prefix
+        out = [TensorSource(f"{p}.gate.weight", (self.E, self.hidden), "router")]
+        for e in range(self.E):
+            out.append(TensorSource(f"{p}.experts.{e}.gate_proj.weight", (self.I, self.hidden), "gate_exps", e * self.I))
+            out.append(TensorSource(f"{p}.experts.{e}.up_proj.weight", (self.I, self.hidden), "up_exps", e * self.I))
+            out.append(TensorSource(f"{p}.experts.{e}.down_proj.weight", (self.hidden, self.I), "down_exps",
+                                    e * self.hidden))
+        if self.shared_gate:
+            out.append(TensorSource(f"{p}.shared_expert_gate.weight", (1, self.hidden), "shared_gate"))
+        return out
+
+    def kernel_modules(self, dtype):
+        return ["gemm_simt", "moe_route", "elementwise"]
+
+    def bind(self, rt) -> None:
+        self._layout = rt.shared_object(
+            ("expert_layout", self.E, self.k),
+            lambda: K.ExpertLayout(rt.max_tokens * self.k, self.E, 64, rt.device),
+        )
+
+    def forward(self, h, batch, residual, rt) -> None:
+        T = h.shape[0]
+        n_pairs = T * self.k
+        ids = rt.buf("moe.ids", (rt.max_tokens * self.k,), torch.int32)
+        wts = rt.buf("moe.wts", (rt.max_tokens * self.k,), torch.float32)
+        gamma = rt.buf("moe.gamma", (rt.max_tokens,), torch.float32) if self.shared_gate else None
+        K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,
+                      top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale)
+        lay = self._layout
+        K.moe_sort(ids, n_pairs, lay)
+        act = rt.rows(f"moe.act{self.I}", self.I, rt.dtype, n_pairs, per_token=self.k)
+        K.linear(h, self.params["gate_exps"], act, w2=self.params["up_exps"], x_rows=lay.sorted_pair,
+                 x_row_div=self.k, layout=lay, n_rows=n_pairs)
+        pair_out = rt.rows("moe.pair_out", self.hidden, torch.float32, n_pairs, per_token=self.k)
+        K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts,
+                 scale_rows=lay.sorted_pair)
+        K.moe_combine(residual, pair_out, lay.pair_pos, self.k)
+        if self.shared is not None:
+            self.shared.forward(h, batch, residual, rt, row_scale=gamma)
+
+
+register_feed_forward("dense_mlp", DenseMlp)
+register_feed_forward("sparse_moe", SparseMoe)
