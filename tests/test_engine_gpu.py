@@ -1,0 +1,382 @@
+"""The engine on the GPU against the plain implementation (float64 oracle), in float32 and
+in bfloat16, for three tiny configurations: every request alone and whole; most of it in
+one step and the last 32 tokens one by one; in portions of changing size down to two
+tokens; mixed batches of up to four live requests with so few pages that pages are used
+again; long decoding across the split boundary of the decode kernel; the first tokens of
+a sequence; greedy and temperature generation through the entry point; trace replay as a
+program.  Pages are poisoned with NaN when created and when given back, so a read of a
+stale or unwritten slot shows in the logits.
+"""
+import json
+import math
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen2moe as plain
+from tiny_configs import config, make_model_dir, random_tokens
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# max |error| and mean |error| of the logits, relative to the largest |logit| of the request.
+# float32: rounding of float32 sums over a few hundred terms and a few layers.
+# bfloat16: activations, keys and values are rounded to 8 bits of mantissa between kernels.
+TOL = {torch.float32: (5e-5, 1e-5), torch.bfloat16: (2e-2, 4e-3)}
+# The router of the engine sees rounded activations; where two experts' probabilities are
+# this close (relative) in the oracle, either choice is right and the oracle follows the engine.
+NEAR_TIE = {torch.float32: 1e-5, torch.bfloat16: 1e-2}
+
+REQUESTS = {  # name -> (length, seed); lengths straddle page edges (16 and 64) and the 256-key split
+    "A": [(5, 1), (17, 2), (33, 3), (64, 4), (200, 5)],
+    "B": [(1, 1), (7, 2), (64, 3), (100, 4), (129, 5), (300, 6)],
+    "C": [(2, 1), (25, 2), (49, 3), (130, 4), (290, 5)],
+}
+
+
+class Case:
+    def __init__(self, name, tmp):
+        self.name = name
+        self.dir = make_model_dir(tmp, name, torch.bfloat16)
+        self.cfg, self.weights = plain.load_folder(self.dir)
+        self.tokens = {f"r{i}": random_tokens(n, self.cfg["vocab_size"], 100 * s + n)
+                       for i, (n, s) in enumerate(REQUESTS[name])}
+        self._ref = {}
+
+    def ref(self, rid):
+        """(logits, aux) of the oracle with its own routing."""
+        if rid not in self._ref:
+            aux = {}
+            lg = plain.forward(self.cfg, self.weights, self.tokens[rid], torch.float64, aux=aux)
+            self._ref[rid] = (lg, aux)
+        return self._ref[rid][0]
+
+    def near_ties(self, rid, near_tie):
+        """Positions where, in some layer, the k-th and (k+1)-th expert are within ``near_tie``."""
+        self.ref(rid)
+        k = self.cfg["num_experts_per_tok"]
+        out = set()
+        for prefix, rows in self._ref[rid][1].items():
+            for pos, (ids, probs) in enumerate(rows):
+                top = torch.sort(probs, descending=True).values
+                if k < top.shape[0] and float(top[k]) >= float(top[k - 1]) * (1 - near_tie):
+                    out.add(pos)
+        return out
+
+    def ref_following(self, rid, routed, near_tie):
+        """Oracle logits when the engine's routing is followed.  The engine's router sees
+        rounded activations, so at a near-tie it may pick the other expert; that is allowed
+        only where the oracle's own probabilities of the swapped experts are within
+        ``near_tie`` (relative) of each other.  Returns (logits, number of tokens that differ)."""
+        base = self.ref(rid)
+        aux = self._ref[rid][1]
+        forced, n_diff = {}, 0
+        for prefix, per_pos in (routed or {}).items():
+            own = aux[prefix]
+            rows = []
+            for pos in range(len(self.tokens[rid])):
+                ids, probs = own[pos]
+                eng = per_pos.get(pos, ids)
+                if sorted(eng) != sorted(ids):
+                    n_diff += 1
+                    kth = min(float(probs[e]) for e in ids)
+                    for e in eng:
+                        assert float(probs[e]) >= kth * (1 - near_tie), (
+                            f"{self.name}/{rid} {prefix} position {pos}: the engine picked expert {e} "
+                            f"(p={float(probs[e]):.6f}) although the k-th best has p={kth:.6f}")
+                rows.append(eng)
+            forced[prefix] = rows
+        if n_diff == 0:
+            return base, 0
+        return plain.forward(self.cfg, self.weights, self.tokens[rid], torch.float64, forced_routing=forced), n_diff
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def case(request, tmp_path_factory):
+    return Case(request.param, tmp_path_factory.mktemp("models"))
+
+
+def make_runner(case, dtype, *, page_tokens=16, n_pages=64, max_tokens=320, use_graphs=False, max_seq=None):
+    from locus_b200.cache import CacheManager
+    from locus_b200.engine.step import ModelRunner
+    from locus_b200.models import load_model
+
+    model = load_model(case.dir, dtype, "cuda:0")
+    cache = CacheManager(model.cache_needs(), page_tokens=page_tokens, n_pages=n_pages, n_state_slots=4,
+                         max_seq_tokens=max_seq or case.cfg["max_position_embeddings"], dtype=dtype, device="cuda:0",
+                         poison=True)
+    return ModelRunner(model, cache, max_tokens=max_tokens, max_segments=4, use_graphs=use_graphs), cache
+
+
+def run_trace(runner, cache, case, steps, observe=True):
+    """steps: list of lists of (request id, n tokens).  Every fed position's logits are wanted.
+    A request is released after its last token.  Returns {rid: [T, V] logits}."""
+    from locus_b200.engine.step import StepEntry
+
+    fed = {}
+    got = {}
+    routed = {}   # rid -> {moe prefix: {position: [experts]}}
+    seen = []     # this step's (prefix, ids) in layer order
+
+    for part in runner.model.all_parts():
+        if hasattr(part, "observer"):
+            part.observer = (lambda prefix, ids, wts: seen.append((prefix, ids.cpu().tolist()))) if observe else None
+    if observe:
+        case.routed = routed
+    for step in steps:
+        seen.clear()
+        entries, spans = [], []
+        for rid, n in step:
+            a = fed.get(rid, 0)
+            seq = cache.get(rid) or cache.open(rid)
+            assert cache.ensure_capacity(seq, n), f"out of pages for {rid}"
+            entries.append(StepEntry(seq, case.tokens[rid][a : a + n], list(range(n))))
+            spans.append((rid, a, n))
+            fed[rid] = a + n
+        logits = runner.step(entries).float().cpu()
+        row = 0
+        for rid, a, n in spans:
+            got.setdefault(rid, []).append((a, logits[row : row + n].clone()))
+            for prefix, ids in seen:
+                d = routed.setdefault(rid, {}).setdefault(prefix, {})
+                for i in range(n):
+                    d[a + i] = ids[row + i]
+            row += n
+        for rid, a, n in spans:
+            if fed[rid] == len(case.tokens[rid]):
+                cache.release(cache.get(rid))
+        cache.check_invariants()
+    out = {}
+    for rid, parts in got.items():
+        parts.sort(key=lambda p: p[0])
+        out[rid] = torch.cat([p[1] for p in parts])
+        assert out[rid].shape[0] == len(case.tokens[rid])
+    return out
+
+
+def check(case, got, dtype, what):
+    tol_max, tol_mean = TOL[dtype]
+    for rid, lg in got.items():
+        ref, _ = case.ref_following(rid, getattr(case, "routed", {}).get(rid), NEAR_TIE[dtype])
+        scale = float(ref.abs().max())
+        err = (lg.double() - ref).abs()
+        assert torch.isfinite(lg).all(), f"{what} {case.name}/{rid}: logits are not finite"
+        worst = int(err.max(dim=1).values.argmax())
+        assert float(err.max()) <= tol_max * scale, (
+            f"{what} {case.name}/{rid}: max error {float(err.max()):.3e} > {tol_max * scale:.3e}; "
+            f"first position above the bound: {int((err.max(dim=1).values > tol_max * scale).nonzero()[0])}, worst {worst}")
+        assert float(err.mean()) <= tol_mean * scale, f"{what} {case.name}/{rid}: mean error {float(err.mean()):.3e}"
+
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_whole_requests_alone(case, dtype):
+    runner, cache = make_runner(case, dtype)
+    got = run_trace(runner, cache, case, [[(rid, len(t))] for rid, t in case.tokens.items()])
+    check(case, got, dtype, "whole")
+    assert cache.free_pages() == cache.total_pages()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_last_32_tokens_one_by_one(case, dtype):
+    runner, cache = make_runner(case, dtype)
+    steps = []
+    for rid, t in case.tokens.items():
+        head = max(0, len(t) - 32)
+        if head:
+            steps.append([(rid, head)])
+        steps += [[(rid, 1)] for _ in range(len(t) - head)]
+    got = run_trace(runner, cache, case, steps)
+    check(case, got, dtype, "prefill then decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_portions_of_changing_size(case, dtype):
+    runner, cache = make_runner(case, dtype)
+    sizes = [2, 16, 3, 17, 2, 31, 64, 5, 2, 15, 33, 1, 2, 48]
+    steps = []
+    for rid, t in case.tokens.items():
+        a, i = 0, 0
+        while a < len(t):
+            n = min(sizes[i % len(sizes)], len(t) - a)
+            steps.append([(rid, n)])
+            a += n
+            i += 1
+    got = run_trace(runner, cache, case, steps)
+    check(case, got, dtype, "portions")
+
+
+def mixed_steps(case, max_live=4):
+    """Up to four live requests: portions of some beside single tokens of others.  Each
+    request is fed in portions up to 32 tokens before its last 8 tokens go one by one."""
+    todo = list(case.tokens.items())
+    live, fed, steps = [], {}, []
+    sizes = [7, 32, 2, 19, 16, 5]
+    k = 0
+    while todo or live:
+        while todo and len(live) < max_live:
+            live.append(todo.pop(0)[0])
+        step = []
+        for rid in list(live):
+            n_total = len(case.tokens[rid])
+            a = fed.get(rid, 0)
+            left = n_total - a
+            n = 1 if left <= 8 else min(sizes[k % len(sizes)], left - 8)
+            k += 1
+            step.append((rid, n))
+            fed[rid] = a + n
+            if fed[rid] == n_total:
+                live.remove(rid)
+        steps.append(step)
+    return steps
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mixed_batches_with_pages_used_again(case, dtype):
+    longest = max(len(t) for t in case.tokens.values())
+    steps = mixed_steps(case)
+    # just enough pages for the four largest live requests: pages of finished requests are reused
+    lens = sorted((len(t) for t in case.tokens.values()), reverse=True)
+    n_pages = sum(-(-n // 16) for n in lens[:4])
+    runner, cache = make_runner(case, dtype, page_tokens=16, n_pages=n_pages)
+    got = run_trace(runner, cache, case, steps)
+    check(case, got, dtype, "mixed")
+    assert cache.free_pages() == cache.total_pages()
+    # once more in the same pool, other order: every page has been used before
+    order = list(reversed(list(case.tokens)))
+    got = run_trace(runner, cache, case, [[(rid, len(case.tokens[rid]))] for rid in order])
+    check(case, got, dtype, "whole after reuse")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_and_first_tokens(case, dtype):
+    """A request decoded token by token from its very first token (positions 0, 1, 2, ...),
+    with 64-token pages and the CUDA graph of single-token steps, beside a second request."""
+    runner, cache = make_runner(case, dtype, page_tokens=64, n_pages=12)
+    rids = list(case.tokens)
+    long_rid, other = rids[-1], rids[-2]
+    steps = []
+    n_long, n_other = len(case.tokens[long_rid]), len(case.tokens[other])
+    for i in range(max(n_long, n_other)):
+        step = []
+        if i < n_long:
+            step.append((long_rid, 1))
+        if i < n_other:
+            step.append((other, 1))
+        steps.append(step)
+    got = run_trace(runner, cache, case, steps)
+    check(case, got, dtype, "token by token")
+    # the same steps replayed from CUDA graphs give the same bits
+    grunner, gcache = make_runner(case, dtype, page_tokens=64, n_pages=12, use_graphs=True)
+    ggot = run_trace(grunner, gcache, case, steps, observe=False)
+    assert grunner.stats["graph_replays"] > 0
+    for rid in got:
+        assert torch.equal(got[rid], ggot[rid]), f"graph replay differs for {rid}"
+
+
+def test_weights_stored_in_32_bit_stay_so(case, tmp_path):
+    """A folder stored in float32, run as a bfloat16 model: matrices stay float32."""
+    d = make_model_dir(tmp_path, case.name, torch.float32)
+    from locus_b200.models import load_model
+
+    model = load_model(d, torch.bfloat16, "cuda:0")
+    assert all(p.dtype == torch.float32 for part in model.all_parts() for p in part.params.values())
+    c32 = Case.__new__(Case)
+    c32.name, c32.dir = case.name, d
+    c32.cfg, c32.weights = plain.load_folder(d)
+    c32.tokens = {"r": random_tokens(70, c32.cfg["vocab_size"], 9)}
+    c32._ref, c32.routed = {}, {}
+    runner, cache = make_runner(c32, torch.bfloat16)
+    got = run_trace(runner, cache, c32, [[("r", 37)], [("r", 2)]] + [[("r", 1)]] * 31)
+    check(c32, got, torch.bfloat16, "float32 weights in a bfloat16 model")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generate_greedy_and_sampled(case, dtype):
+    from locus_b200.engine.engine import Engine
+
+    eng = Engine.from_model_dir(case.dir, dtype=dtype, ctx=1024, page_tokens=16, max_batch_tokens=48, chunk=16,
+                                max_running=4)
+    prompts = [case.tokens[r][:n] for r, n in zip(list(case.tokens)[-3:], (5, 17, 33))]
+    out = eng.generate(prompts, max_new_tokens=16)
+    assert eng.cache.free_pages() == eng.cache.total_pages()
+    for p, o in zip(prompts, out):
+        assert len(o) == 16
+        # every generated token must be the arg-max of the oracle's logits, unless the two
+        # best logits are closer than the rounding of this element type
+        full = p + o
+        ref = plain.forward(case.cfg, case.weights, full, torch.float64)
+        for i, tok in enumerate(o):
+            row = ref[len(p) + i - 1]
+            top2 = torch.topk(row, 2).values
+            margin = float(top2[0] - row[tok])
+            assert margin <= TOL[torch.float32 if dtype == "float32" else torch.bfloat16][0] * float(ref.abs().max()) * 2, \
+                f"token {i}: picked {tok}, margin to the best {margin:.3e}"
+    # the same prompts in one batch, one by one, and in another order give the same tokens
+    again = [eng.generate([p], max_new_tokens=16)[0] for p in reversed(prompts)]
+    if dtype == "float32":
+        assert again == list(reversed(out))
+    # temperature sampling: reproducible for a seed, independent of the batch
+    s1 = eng.generate(prompts, max_new_tokens=12, temperature=0.8, seed=1)
+    s2 = eng.generate(prompts, max_new_tokens=12, temperature=0.8, seed=1)
+    assert s1 == s2
+    s3 = eng.generate(prompts, max_new_tokens=12, temperature=0.8, seed=2)
+    assert s3 != s1
+    assert eng.cache.free_pages() == eng.cache.total_pages()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(case, dtype, tmp_path):
+    """bin/trace_run as a program: a mixed trace with a pool of 4 x 64-token pages short of
+    what all requests together need, so pages are used again."""
+    if case.name == "C":
+        pytest.skip("one windowed and two plain configurations are enough for the program test")
+    out = tmp_path / "out"
+    rids = list(case.tokens)[:4]
+    lens = {r: len(case.tokens[r]) for r in rids}
+    max_tokens = sum(sorted((-(-n // 64) * 64 for n in lens.values()), reverse=True)[:2])
+    steps, fed = [], {}
+    # two requests at a time, portions beside single tokens
+    pairs = [rids[:2], rids[2:]]
+    step_no = 0
+    lines = []
+    expect = {}
+    for pair in pairs:
+        live = list(pair)
+        while live:
+            entries, end = [], []
+            for j, rid in enumerate(list(live)):
+                a = fed.get(rid, 0)
+                n = min(lens[rid] - a, 1 if (step_no + j) % 3 == 0 else 11)
+                want = list(range(n)) if n <= 2 else [0, n - 1]
+                entries.append({"id": rid, "tokens": case.tokens[rid][a : a + n], "want": want})
+                expect.setdefault(step_no, []).extend((rid, a + w) for w in want)
+                fed[rid] = a + n
+                if fed[rid] == lens[rid]:
+                    end.append(rid)
+                    live.remove(rid)
+            lines.append(json.dumps({"step": step_no, "entries": entries, "end": end}))
+            step_no += 1
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", case.dir, "--dtype", dtype,
+                           "--out", str(out), "--max-tokens", str(max_tokens)], input="\n".join(lines) + "\n",
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(step_no)]
+    import numpy as np
+    V = case.cfg["vocab_size"]
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    for s, wants in expect.items():
+        arr = torch.from_numpy(np.fromfile(out / f"{s}.f32", dtype="<f4").reshape(-1, V).copy())
+        assert arr.shape[0] == len(wants)
+        for row, (rid, pos) in enumerate(wants):
+            ref = case.ref(rid)
+            if pos in case.near_ties(rid, NEAR_TIE[tdt]):
+                continue  # either expert is right there; the program cannot tell us which it took
+            scale = float(ref.abs().max())
+            err = float((arr[row].double() - ref[pos]).abs().max())
+            assert err <= TOL[tdt][0] * scale, f"step {s} {rid}@{pos}: {err:.3e}"

@@ -1,0 +1,371 @@
+"""Each CUDA kernel alone against its plain torch reference (tests/emulated_kernels.py, in
+float64), at sizes other than the tiny models': odd widths, head sizes in steps of 16,
+group ratios, page sizes, windows.  float32 kernels must agree to float32 rounding;
+bfloat16 kernels to the rounding of their bfloat16 outputs (inputs are shared exactly)."""
+import math
+
+import pytest
+import torch
+
+import emulated_kernels as EK
+import locus_b200.kernels as K
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(autouse=True)
+def _precise():
+    EK.PRECISE = True
+    yield
+    EK.PRECISE = False
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+def close(got, ref, dtype, what, scale=None):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    s = float(ref.abs().max()) if scale is None else scale
+    tol = (2e-5 if dtype == torch.float32 else 1.2e-2) * max(s, 1e-6)
+    err = float((got - ref).abs().max())
+    assert math.isfinite(err) and err <= tol, f"{what}: max error {err:.3e} > {tol:.3e} (scale {s:.3e})"
+
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_rows(dtype):
+    table = rnd(37, 50, dtype=dtype)
+    toks = torch.tensor([0, 36, 5, 5, 17], dtype=torch.int32)
+    out = torch.empty(5, 50, device=DEV)
+    K.embed_rows(toks.to(DEV), table.to(DEV), out)
+    assert torch.equal(out.cpu(), table[toks.long()].float())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H", [8, 200, 2048 + 24])
+def test_rmsnorm(dtype, H):
+    x = rnd(7, H, seed=1, scale=3.0)
+    w = rnd(H, dtype=dtype, seed=2) + 1
+    out = torch.empty(7, H, dtype=dtype, device=DEV)
+    K.rmsnorm(x.to(DEV), w.to(DEV), 1e-5, out)
+    ref = torch.empty(7, H, dtype=torch.float64)
+    EK.rmsnorm(x, w, 1e-5, ref)
+    close(out, ref, dtype, "rmsnorm")
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    out2 = torch.empty(3, H, dtype=dtype, device=DEV)
+    K.rmsnorm(x.to(DEV), w.to(DEV), 1e-5, out2, rows.to(DEV))
+    close(out2, ref[rows.long()], dtype, "rmsnorm rows")
+
+
+@pytest.mark.parametrize("xdt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M,N,K_", [(1, 1, 8), (5, 331, 120), (70, 130, 72), (129, 64, 2048)])
+def test_linear_plain_bias_scale_accumulate(xdt, wdt, M, N, K_):
+    x, w = rnd(M, K_, dtype=xdt, seed=3), rnd(N, K_, dtype=wdt, seed=4, scale=0.1)
+    bias, rs = rnd(N, dtype=wdt, seed=5), rnd(M, seed=6)
+    for use_bias, use_rs, acc in [(False, False, False), (True, False, False), (True, True, True)]:
+        odt = torch.float32 if acc else xdt
+        out0 = rnd(M, N, dtype=odt, seed=7)
+        out = out0.clone().to(DEV)
+        K.linear(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV) if use_bias else None,
+                 row_scale=rs.to(DEV) if use_rs else None, accumulate=acc)
+        ref = out0.clone().double()
+        EK.linear(x, w, ref, bias=bias if use_bias else None, row_scale=rs if use_rs else None, accumulate=acc)
+        close(out, ref, odt, f"linear bias={use_bias} scale={use_rs} acc={acc}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_linear_swiglu(dtype):
+    x, wg, wu = rnd(33, 120, dtype=dtype, seed=1), rnd(77, 120, dtype=dtype, seed=2, scale=0.2), \
+        rnd(77, 120, dtype=dtype, seed=3, scale=0.2)
+    out = torch.empty(33, 77, dtype=dtype, device=DEV)
+    K.linear(x.to(DEV), wg.to(DEV), out, w2=wu.to(DEV))
+    ref = torch.empty(33, 77, dtype=torch.float64)
+    EK.linear(x, wg, ref, w2=wu)
+    close(out, ref, dtype, "swiglu")
+
+
+def _route(T, E, k, seed):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).reshape(-1)
+    return ids
+
+
+@pytest.mark.parametrize("T,E,k", [(1, 4, 2), (50, 7, 3), (300, 60, 4), (9, 5, 5)])
+def test_moe_sort_layout(T, E, k):
+    ids = _route(T, E, k, T)
+    if T == 9:
+        ids[:] = 2  # every pair on one expert; others empty
+    lay = K.ExpertLayout(T * k, E, 64, DEV)
+    K.moe_sort(ids.to(DEV), T * k, lay)
+    ref = EK.ExpertLayout(T * k, E, 64, "cpu")
+    EK.moe_sort(ids, T * k, ref)
+    n_tiles = int(ref.n_tiles)
+    assert int(lay.n_tiles.cpu()) == n_tiles
+    assert n_tiles <= lay.tiles_for(T * k)
+    for name in ("counts", "offsets", "sorted_pair", "pair_pos"):
+        assert torch.equal(getattr(lay, name).cpu(), getattr(ref, name)), name
+    for name in ("tile_expert", "tile_row0", "tile_rows"):
+        assert torch.equal(getattr(lay, name).cpu()[:n_tiles], getattr(ref, name)[:n_tiles]), name
+
+
+@pytest.mark.parametrize("xdt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+def test_linear_grouped_experts(xdt, wdt):
+    T, E, k, H, I = 150, 6, 2, 72, 40
+    ids = _route(T, E, k, 11)
+    ids[: 2 * 70] = 1  # one expert with more than two row tiles
+    h = rnd(T, H, dtype=xdt, seed=1)
+    wg, wu = rnd(E, I, H, dtype=wdt, seed=2, scale=0.2), rnd(E, I, H, dtype=wdt, seed=3, scale=0.2)
+    wd = rnd(E, H, I, dtype=wdt, seed=4, scale=0.2)
+    wts = torch.rand(T * k, generator=torch.Generator().manual_seed(5))
+    lay, ref_lay = K.ExpertLayout(T * k, E, 64, DEV), EK.ExpertLayout(T * k, E, 64, "cpu")
+    K.moe_sort(ids.to(DEV), T * k, lay)
+    EK.moe_sort(ids, T * k, ref_lay)
+    act = torch.empty(T * k, I, dtype=xdt, device=DEV)
+    K.linear(h.to(DEV), wg.to(DEV), act, w2=wu.to(DEV), x_rows=lay.sorted_pair, x_row_div=k, layout=lay,
+             n_rows=T * k)
+    ref_act = torch.empty(T * k, I, dtype=torch.float64)
+    EK.linear(h, wg, ref_act, w2=wu, x_rows=ref_lay.sorted_pair, x_row_div=k, layout=ref_lay, n_rows=T * k)
+    close(act, ref_act, xdt, "grouped swiglu")
+    pair_out = torch.empty(T * k, H, device=DEV)
+    K.linear(act, wd.to(DEV), pair_out, layout=lay, n_rows=T * k, row_scale=wts.to(DEV), scale_rows=lay.sorted_pair)
+    ref_out = torch.empty(T * k, H, dtype=torch.float64)
+    EK.linear(act.cpu(), wd, ref_out, layout=ref_lay, n_rows=T * k, row_scale=wts, scale_rows=ref_lay.sorted_pair)
+    close(pair_out, ref_out, torch.float32 if xdt == torch.float32 else torch.bfloat16, "grouped down")
+    x = rnd(T, H, seed=9)
+    xd = x.clone().to(DEV)
+    K.moe_combine(xd, pair_out, lay.pair_pos, k)
+    xr = x.clone().double()
+    EK.moe_combine(xr, pair_out.cpu().double(), ref_lay.pair_pos, k)
+    close(xd, xr, torch.float32, "combine")
+
+
+@pytest.mark.parametrize("xdt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("T,H,E,k,renorm", [(1, 64, 8, 2, False), (19, 200, 60, 4, False), (40, 72, 12, 3, True),
+                                            (3, 2048, 5, 5, True)])
+def test_router_topk(xdt, wdt, T, H, E, k, renorm):
+    h, wr, wg = rnd(T, H, dtype=xdt, seed=1), rnd(E, H, dtype=wdt, seed=2, scale=0.3), rnd(1, H, dtype=wdt, seed=3, scale=0.3)
+    ids = torch.zeros(T * k, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(T * k, device=DEV)
+    gamma = torch.zeros(T, device=DEV)
+    K.router_topk(h.to(DEV), wr.to(DEV), wg.to(DEV), ids, wts, gamma, top_k=k, renorm=renorm, scale=1.5)
+    rids, rw, rg = torch.zeros(T * k, dtype=torch.int32), torch.zeros(T * k, dtype=torch.float64), \
+        torch.zeros(T, dtype=torch.float64)
+    EK.router_topk(h, wr, wg, rids, rw, rg, top_k=k, renorm=renorm, scale=1.5)
+    assert torch.equal(ids.cpu(), rids), "picked experts (and their order) differ"
+    close(wts, rw, torch.float32, "router weights")
+    close(gamma, rg, torch.float32, "shared gate")
+
+
+def test_router_ties_go_to_lowest_index():
+    h = torch.ones(2, 16)
+    wr = torch.zeros(6, 16)
+    wr[4] = 0.5  # expert 4 wins, the others tie
+    ids = torch.zeros(6, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(6, device=DEV)
+    K.router_topk(h.to(DEV), wr.to(DEV), None, ids, wts, None, top_k=3, renorm=False)
+    assert ids.cpu().tolist() == [4, 0, 1, 4, 0, 1]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,rot,inter", [(4, 4, 16, 16, False), (6, 2, 32, 32, False), (5, 1, 48, 24, False),
+                                                 (2, 1, 64, 64, True)])
+def test_rope_kv_write(dtype, nh, nkv, hd, rot, inter):
+    T, P, pages = 9, 16, 5
+    qkv = rnd(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=1)
+    pos = torch.tensor([0, 1, 2, 40, 41, 1000, 7, 8, 9], dtype=torch.int32)
+    slots = torch.tensor([3 * P + 0, 3 * P + 1, 3 * P + 15, 0, 1, 4 * P + 7, 2 * P + 3, 2 * P + 4, 2 * P + 5],
+                         dtype=torch.int32)
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot).float()
+    pool0 = rnd(pages, 2, nkv, P, hd, dtype=dtype, seed=2)
+    pool, q = pool0.clone().to(DEV), torch.empty(T, nh * hd, dtype=dtype, device=DEV)
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, rot_dim=rot, interleaved=inter, page_tokens=P)
+    K.rope_kv_write(qkv.to(DEV), pos.to(DEV), inv.to(DEV), q, pool, slots.to(DEV), **kw)
+    rpool, rq = pool0.clone().double(), torch.empty(T, nh * hd, dtype=torch.float64)
+    EK.rope_kv_write(qkv, pos, inv, rq, rpool, slots, **kw)
+    close(q, rq, dtype, "rotated q")
+    close(pool, rpool, dtype, "pages")
+    # a layer that reads another layer's cache leaves the pages alone; no table: no rotation
+    pool2 = pool0.clone().to(DEV)
+    K.rope_kv_write(qkv.to(DEV), pos.to(DEV), None, q, pool2, slots.to(DEV), write_kv=False, **{**kw, "rot_dim": 0})
+    assert torch.equal(pool2.cpu(), pool0)
+    assert torch.equal(q.cpu(), qkv[:, : nh * hd])
+
+
+def _paged_case(dtype, nh, nkv, hd, P, segs, seed=0, n_pages=40):
+    """segs: list of (ctx, qn).  Random pool, shuffled page tables."""
+    g = torch.Generator().manual_seed(seed)
+    pool = rnd(n_pages, 2, nkv, P, hd, dtype=dtype, seed=seed + 1)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max((c + n + P - 1) // P for c, n in segs)
+    table = torch.full((len(segs), width), -1, dtype=torch.int32)
+    used = 0
+    q0s, T = [], 0
+    for s, (c, n) in enumerate(segs):
+        need = (c + n + P - 1) // P
+        table[s, :need] = torch.tensor(perm[used : used + need], dtype=torch.int32)
+        used += need
+        q0s.append(T)
+        T += n
+    assert used <= n_pages
+    q = rnd(T, nh * hd, dtype=dtype, seed=seed + 2)
+    meta = dict(seg_q0=torch.tensor(q0s, dtype=torch.int32), seg_qn=torch.tensor([n for _, n in segs], dtype=torch.int32),
+                seg_ctx=torch.tensor([c for c, _ in segs], dtype=torch.int32), block_table=table)
+    return pool, q, meta, T
+
+
+def _dev(meta):
+    return {k: v.to(DEV) for k, v in meta.items()}
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 4, 16, 16, 0), (6, 2, 32, 16, 0), (5, 1, 48, 64, 0),
+                                                (2, 2, 128, 64, 0), (3, 1, 256, 16, 0), (4, 2, 64, 16, 20),
+                                                (2, 1, 32, 64, 1)])
+def test_attn_chunk(dtype, nh, nkv, hd, P, window):
+    segs = [(0, 5), (33, 17), (100, 2), (15, 40), (64, 16)]
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=hd)
+    items = []
+    for s, (c, n) in enumerate(segs):
+        items += [(s, o) for o in range(0, n, 16)]
+    items_t = torch.tensor(items, dtype=torch.int32)
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=window, scale=1 / math.sqrt(hd))
+    out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
+    K.attn_chunk(q.to(DEV), pool.to(DEV), out, items=items_t.to(DEV), n_items=len(items), **_dev(meta), **kw)
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.attn_chunk(q, pool, ref, items=items_t, n_items=len(items), **meta, **kw)
+    close(out, ref, dtype, "attn_chunk")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 4, 16, 16, 0), (6, 2, 32, 64, 0), (5, 1, 48, 16, 0),
+                                                (16, 16, 128, 64, 0), (2, 1, 256, 64, 0), (4, 2, 64, 16, 300),
+                                                (4, 4, 80, 16, 7)])
+def test_attn_decode(dtype, nh, nkv, hd, P, window):
+    segs = [(0, 1), (255, 1), (256, 1), (700, 1), (31, 1)]
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=hd + 1, n_pages=100)
+    items = torch.arange(len(segs), dtype=torch.int32)
+    max_splits = 700 // K.DECODE_SPLIT + 1 + 2  # more splits than needed must not matter
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=window, scale=1 / math.sqrt(hd))
+    out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
+    part_o = torch.full((len(segs) * nh * max_splits * hd,), float("nan"), device=DEV)
+    part_ml = torch.full((2 * len(segs) * nh * max_splits,), float("nan"), device=DEV)
+    K.attn_decode(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=len(segs), part_o=part_o,
+                  part_ml=part_ml, max_splits=max_splits, **_dev(meta), **kw)
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.attn_decode(q, pool, ref, items=items, n_items=len(segs), part_o=None, part_ml=None, max_splits=max_splits,
+                   **meta, **kw)
+    close(out, ref, dtype, "attn_decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
+    """One key among hundreds carries a large score: the output must be (nearly) its value.
+    With a window that ends one key short of it, the output must not contain it."""
+    nh = nkv = 2
+    hd, P, ctx = 64, 16, 600
+    far = 3  # position of the marked key
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, [(ctx, 1), (ctx - 7, 8)], seed=5, n_pages=90)
+    pool *= 0.05
+    q *= 0.05
+    for s in range(2):
+        page, off = int(meta["block_table"][s, far // P]), far % P
+        pool[page, 0, :, off] = 0
+        pool[page, 0, :, off, 0] = 30.0
+        pool[page, 1, :, off] = 0
+        pool[page, 1, :, off, 1] = 7.0
+    q.view(T, nh, hd)[:, :, 0] = 8.0  # score 8 * 30 / sqrt(64) = 30 on the marked key
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, scale=1 / math.sqrt(hd))
+    for window, seen in [(0, True), (ctx - far + 1, True), (ctx - far, False)]:
+        out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
+        K.attn_decode(q.to(DEV), pool.to(DEV), out, items=torch.tensor([0], dtype=torch.int32, device=DEV), n_items=1,
+                      part_o=torch.zeros(nh * 4 * hd, device=DEV), part_ml=torch.zeros(2 * nh * 4, device=DEV),
+                      max_splits=4, window=window, **_dev(meta), **kw)
+        items = torch.tensor([[1, 0]], dtype=torch.int32)
+        w2 = window - 7 if window else 0  # segment 1's last query sits at the same position as segment 0's
+        K.attn_chunk(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=1, window=window, **_dev(meta), **kw)
+        o = out.float().cpu().view(T, nh, hd)
+        for row in (0, T - 1):
+            v = float(o[row, 0, 1])
+            if seen:
+                assert abs(v - 7.0) < 0.1, (window, row, v)
+            else:
+                assert abs(v) < 0.5, (window, row, v)
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    x = torch.zeros(4, 16, device=DEV)
+    with pytest.raises(K.KernelError):
+        K.linear(x, torch.zeros(8, 16, device=DEV), torch.zeros(4, 8, dtype=torch.bfloat16, device=DEV), accumulate=True)
+    with pytest.raises(K.KernelError):
+        K.linear(x.half(), torch.zeros(8, 16, device=DEV), torch.zeros(4, 8, device=DEV))
+    meta = dict(seg_q0=torch.zeros(1, dtype=torch.int32, device=DEV), seg_qn=torch.ones(1, dtype=torch.int32, device=DEV),
+                seg_ctx=torch.zeros(1, dtype=torch.int32, device=DEV),
+                block_table=torch.zeros(1, 1, dtype=torch.int32, device=DEV))
+    with pytest.raises(K.KernelError):  # head size 24 is not a multiple of 16
+        K.attn_chunk(torch.zeros(1, 24, device=DEV), torch.zeros(1, 2, 1, 16, 24, device=DEV),
+                     torch.zeros(1, 24, device=DEV), items=torch.zeros(1, 2, dtype=torch.int32, device=DEV), n_items=1,
+                     n_heads=1, n_kv_heads=1, head_dim=24, page_tokens=16, window=0, scale=1.0, **meta)
+
+
+@pytest.mark.parametrize("V", [331, 4096, 151936])
+def test_sample_greedy_and_filters(V):
+    R = 6
+    logits = rnd(R, V, seed=V, scale=2.0)
+    logits[1, 17] = logits[1, 99] = logits[1].max() + 1  # a tie: the first maximum wins
+    dl = logits.to(DEV)
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)
+    out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    kept = torch.zeros(R, dtype=torch.int32, device=DEV)
+    temp = f32([0.0, 0.0, 0.8, 1.0, 1.3, 0.7])
+    top_k = torch.tensor([0, 0, 1, 50, 0, 40], dtype=torch.int32, device=DEV)
+    top_p = f32([1.0, 1.0, 1.0, 1.0, 0.6, 0.9])
+    min_p = f32([0.0, 0.0, 0.0, 0.0, 0.0, 0.05])
+    seeds = torch.arange(R, dtype=torch.int64, device=DEV) + 5
+    import plain_qwen2moe as plain
+    dists = [None, None] + [plain.kept_distribution(logits[r], float(temp[r]), int(top_k[r]), float(top_p[r]), float(min_p[r]))
+                            for r in range(2, R)]
+    counts = [dict() for _ in range(R)]
+    n_draws = 300
+    for c in range(n_draws):
+        K.sample(dl, temperature=temp, top_k=top_k, top_p=top_p, min_p=min_p, seeds=seeds,
+                 counters=torch.full((R,), c, dtype=torch.int64, device=DEV), out=out, kept_count=kept)
+        o = out.cpu().tolist()
+        for r in range(R):
+            counts[r][o[r]] = counts[r].get(o[r], 0) + 1
+        if c == 0:
+            first, kept0 = o, kept.cpu().tolist()
+    assert first[0] == int(torch.argmax(logits[0])) and first[1] == 17
+    assert set(counts[0]) == {first[0]} and set(counts[2]) == {int(torch.argmax(logits[2]))}  # top_k = 1
+    for r in range(3, R):
+        assert kept0[r] == len(dists[r]), (r, kept0[r], len(dists[r]))
+        assert set(counts[r]) <= set(dists[r]), "a token outside the kept set was drawn"
+        # the most probable kept token is drawn about as often as it should be
+        tok = max(dists[r], key=dists[r].get)
+        p = dists[r][tok]
+        sd = math.sqrt(p * (1 - p) / n_draws)
+        assert abs(counts[r].get(tok, 0) / n_draws - p) < 5 * sd + 0.01, (r, p, counts[r].get(tok, 0) / n_draws)
+    # same seed and counter: same token
+    K.sample(dl, temperature=temp, top_k=top_k, top_p=top_p, min_p=min_p, seeds=seeds,
+             counters=torch.zeros(R, dtype=torch.int64, device=DEV), out=out)
+    assert out.cpu().tolist() == first
+
+
+def test_penalties():
+    import plain_qwen2moe as plain
+    V, R = 50, 3
+    logits = rnd(R, V, seed=3, scale=2.0)
+    hist = torch.tensor([[1, 2, 2, 2, -1, -1], [5, 5, 7, 49, 0, 0], [-1] * 6], dtype=torch.int32)
+    rep, fr, pr = torch.tensor([1.3, 1.0, 1.2]), torch.tensor([0.0, 0.5, 0.1]), torch.tensor([0.2, 0.0, 0.1])
+    d = logits.clone().to(DEV)
+    K.apply_penalties(d, hist.to(DEV), rep.to(DEV), fr.to(DEV), pr.to(DEV))
+    for r in range(R):
+        h = [t for t in hist[r].tolist() if t >= 0]
+        ref = plain.apply_penalties(logits[r], h, float(rep[r]), float(fr[r]), float(pr[r]), 64)
+        close(d[r], ref, torch.float32, f"penalties row {r}")
