@@ -92,7 +92,7 @@ def test_groups_have_pages_of_their_own_and_windows_give_pages_back():
     for _ in range(30):
         assert c.ensure_capacity(s, 1)
         c.commit(s, 1)
-    assert s.n_tokens == 100 and c.pages_held_ok(s) if hasattr(c, "pages_held_ok") else True
+    assert s.n_tokens == 100
     assert s.pages_held(1) <= 3  # a window of 20 never holds more than ceil(20/16)+1 pages
     c.check_invariants()
     c.release(s)
@@ -108,7 +108,7 @@ def test_state_slots_follow_requests_and_start_at_zero():
     st[a.state_slot] = 7.0
     c.release(a)
     d = c.open("d")
-    assert d.state_slot == a.state_slot if False else True
+    assert d.state_slot == 0  # the slot that was just given back is used again
     assert float(c.layer_caches()[0].state[d.state_slot].abs().sum()) == 0.0  # zeroed on open
     c.open("e")
     with pytest.raises(CacheError, match="no free state slot"):

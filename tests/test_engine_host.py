@@ -1,0 +1,120 @@
+"""The engine's host logic on the CPU (no GPU): with the CUDA entry points replaced by their
+torch twins, the real model, parts, cache manager, step function, scheduler and sampler
+front end run whole prompts, portions, mixed batches with reused pages and generation, and
+must agree with the plain implementation.  What this does not cover -- the kernels
+themselves -- is covered by the gpu tests."""
+import pytest
+import torch
+
+import emulated_kernels as EK
+import plain_qwen2moe as plain
+from locus_b200.cache import CacheError, CacheManager
+from locus_b200.engine.engine import Engine
+from locus_b200.engine.scheduler import SchedulerConfig
+from locus_b200.engine.step import ModelRunner, StepEntry, StepError
+from locus_b200.models import load_model
+from locus_b200.sampling.sampler import Sampler
+from tiny_configs import make_model_dir, random_tokens
+
+
+@pytest.fixture(autouse=True)
+def _emulate(monkeypatch):
+    EK.install(monkeypatch)
+
+
+def setup(name, tmp_path, n_pages=12, page=16, max_tokens=64):
+    d = make_model_dir(tmp_path, name, torch.float32)
+    cfg, W = plain.load_folder(d)
+    model = load_model(d, torch.float32, "cpu")
+    cache = CacheManager(model.cache_needs(), page_tokens=page, n_pages=n_pages, n_state_slots=4,
+                         max_seq_tokens=cfg["max_position_embeddings"], dtype=torch.float32, device="cpu", poison=True)
+    return cfg, W, model, cache, ModelRunner(model, cache, max_tokens=max_tokens, max_segments=4)
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_cuts_and_mixed_batches_agree_with_plain(name, tmp_path):
+    cfg, W, model, cache, runner = setup(name, tmp_path, n_pages=7)
+    toks = {r: random_tokens(n, cfg["vocab_size"], n) for r, n in (("a", 45), ("b", 33), ("c", 18), ("d", 30))}
+    ref = {r: plain.forward(cfg, W, t, torch.float64) for r, t in toks.items()}
+    # a and b start; c joins; b ends and d takes its pages (7 pages: never room for all four)
+    steps = [[("a", 20), ("b", 2)], [("a", 1), ("b", 31)], [("a", 5), ("c", 16)], [("a", 1), ("c", 1), ("d", 17)],
+             [("a", 18), ("c", 1), ("d", 13)]]
+    fed, got = {}, {r: [] for r in toks}
+    for step in steps:
+        entries = []
+        for r, n in step:
+            a = fed.get(r, 0)
+            seq = cache.get(r) or cache.open(r)
+            assert cache.ensure_capacity(seq, n), (r, n)
+            entries.append(StepEntry(seq, toks[r][a : a + n], list(range(n))))
+            fed[r] = a + n
+        lg = runner.step(entries)
+        row = 0
+        for r, n in step:
+            got[r].append(lg[row : row + n].clone())
+            row += n
+        for r, n in step:
+            if fed[r] == len(toks[r]):
+                cache.release(cache.get(r))
+        cache.check_invariants()
+    for r in toks:
+        out = torch.cat(got[r]).double()
+        assert out.shape == ref[r].shape
+        assert float((out - ref[r]).abs().max()) <= 2e-5 * float(ref[r].abs().max()), r
+    assert cache.free_pages() == cache.total_pages()
+
+
+def test_step_refuses_bad_batches(tmp_path):
+    cfg, W, model, cache, runner = setup("A", tmp_path)
+    s = cache.open("a")
+    with pytest.raises(CacheError, match="not ensured"):
+        runner.step([StepEntry(s, [1, 2, 3], [2])])
+    assert cache.ensure_capacity(s, 3)
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        runner.step([StepEntry(s, [1, 256, 3], [])])
+    with pytest.raises(StepError, match="wanted place"):
+        runner.step([StepEntry(s, [1, 2, 3], [3])])
+    with pytest.raises(StepError, match="twice"):
+        runner.step([StepEntry(s, [1], []), StepEntry(s, [2], [])])
+    with pytest.raises(StepError, match="no tokens"):
+        runner.step([StepEntry(s, [], [])])
+    with pytest.raises(StepError, match="at least one entry"):
+        runner.step([])
+    other = CacheManager(model.cache_needs(), page_tokens=16, n_pages=2, n_state_slots=1, max_seq_tokens=32, device="cpu")
+    foreign = other.open("x")
+    other.ensure_capacity(foreign, 2)
+    with pytest.raises(CacheError, match="not open in the runner's cache"):
+        runner.step([StepEntry(foreign, [1, 2], [])])
+    assert s.n_tokens == 0  # nothing ran
+    big = cache.open("big")
+    assert cache.ensure_capacity(big, 70)
+    with pytest.raises(StepError, match="built for 64"):
+        runner.step([StepEntry(big, list(range(70)), [])])
+    # context overflow is refused before launch
+    cfg2, W2, model2, cache2, runner2 = setup("A", tmp_path, n_pages=20, max_tokens=300)
+    s2 = cache2.open("long")
+    assert cache2.ensure_capacity(s2, 256)
+    runner2.step([StepEntry(s2, [1] * 256, [])])
+    with pytest.raises((StepError, CacheError), match="overflow|exceed"):
+        cache2.ensure_capacity(s2, 1)
+        runner2.step([StepEntry(s2, [1], [0])])
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_generation_through_the_engine_matches_plain_greedy(name, tmp_path):
+    cfg, W, model, cache, runner = setup(name, tmp_path, n_pages=16)
+    eng = Engine(runner, cache, Sampler("cpu", 4), max_positions=cfg["max_position_embeddings"],
+                 config=SchedulerConfig(max_batch_tokens=24, chunk=16, max_running=4, decode_headroom=4))
+    prompts = [random_tokens(n, cfg["vocab_size"], 7 * n) for n in (5, 17, 33)]
+    out = eng.generate(prompts, max_new_tokens=6)
+    for p, o in zip(prompts, out):
+        assert o == plain.greedy_generate(cfg, W, p, 6, torch.float64)
+    assert cache.free_pages() == cache.total_pages()
+    # temperature sampling goes through the same path and is reproducible
+    a = eng.generate(prompts[:2], max_new_tokens=5, temperature=0.8, seed=1)
+    b = eng.generate(prompts[:2], max_new_tokens=5, temperature=0.8, seed=1)
+    assert a == b and all(len(x) == 5 for x in a)
+    # penalties reach the sampler with the request's history
+    from locus_b200.sampling.sampler import SamplingParams
+    c = eng.generate(prompts[:1], max_new_tokens=5, sampling=SamplingParams(repeat_penalty=1.5, presence_penalty=0.5))
+    assert len(c[0]) == 5
