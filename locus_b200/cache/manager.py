@@ -205,6 +205,15 @@ class CacheManager:
                     self._give_back(g, table[i])
                     table[i] = -1
 
+    def adopt(self, seq: SeqCache, n: int) -> bool:
+        """Declare ``n`` more tokens as cached without writing them: takes the pages and
+        advances the count.  For measurements on synthetic cache contents only; the keys
+        and values are whatever the pages hold."""
+        if not self.ensure_capacity(seq, n):
+            return False
+        self.commit(seq, n)
+        return True
+
     def release(self, seq: SeqCache) -> None:
         """The request ends (or is preempted): everything it holds goes back."""
         self._check_open(seq)

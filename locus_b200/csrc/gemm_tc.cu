@@ -1,0 +1,343 @@
+// bfloat16 matrix products on the Blackwell tensor cores (tcgen05.mma, accumulators in
+// tensor memory), operands staged in shared memory by TMA through a multi-stage mbarrier
+// pipeline:  out = x . W^T  with the same fused epilogues as the CUDA-core kernel.
+//
+// Roles are swapped so that the WEIGHT rows are the 128-row M side of the MMA and the
+// tokens are its N side (16..256 columns): a decode step with a handful of tokens streams
+// each weight tile once at full tile height, and a prefill step uses 128- or 256-token tiles.
+//
+//   D[n, t] (tensor memory, lane n, column t) = sum_k W[n0 + n, k] * x[t0 + t, k]
+//
+// One CTA computes one 128 x TN output tile over the whole K (no split of K: the order of
+// the sum for an element depends on K only).  Warp 0 issues TMA loads (one elected thread),
+// warp 1 allocates tensor memory and issues the MMAs (one elected thread), warps 2-5 read
+// the accumulators back (tcgen05.ld, each warp its own 32 lanes) and run the epilogue:
+// bias, SwiGLU of two accumulators, per-row scale, store as bfloat16 / float32 or add into
+// a float32 tensor.  Grouped products (experts) take the tile list that moe_sort built.
+//
+// Every wait on an mbarrier is bounded (about a second of clock cycles); when a wait runs
+// out the kernel records a code in the module's error word, stops waiting and finishes, so
+// a fault in the pipeline shows as an error on the host, never as a hang.  No load uses
+// cluster multicast.
+#include <cuda.h>
+
+#include "common.cuh"
+
+#define TILE_W 128      // weight rows per tile (MMA M)
+#define TILE_K 64       // k elements per stage: 128 bytes of bfloat16, one swizzle row
+#define A_BYTES (TILE_W * TILE_K * 2)
+#define WAIT_LIMIT 2000000000LL
+
+__device__ int g_tc_error = 0;
+
+struct TcArgs {
+    int M, N, K, TN, dual, stages, tmem_cols;
+    int accumulate;
+    void* out;
+    int out_dt;
+    long long ldo;
+    const void* bias;
+    int bias_dt;
+    const float* row_scale;
+    const int* scale_rows;
+    const int* tile_expert;
+    const int* tile_row0;
+    const int* tile_rows;
+    const int* n_tiles;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: false (and the error word set to `code`) when the limit runs out.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > WAIT_LIMIT) {
+            atomicCAS(&g_tc_error, 0, code);
+            return false;
+        }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {
+    // K-major, 128-byte swizzle: 8 rows of 128 bytes per swizzle atom, atoms 1024 bytes apart
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);   // start address
+    d |= static_cast<uint64_t>(1) << 16;                   // leading byte offset (unused with swizzle)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;           // stride byte offset between 8-row groups
+    d |= static_cast<uint64_t>(1) << 46;                   // descriptor version of sm_100
+    d |= static_cast<uint64_t>(2) << 61;                   // SWIZZLE_128B
+    return d;
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr));
+}
+
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
+               const __grid_constant__ CUtensorMap map_x, TcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    int x_row0, rows_valid;
+    long long w_row0 = static_cast<long long>(blockIdx.x) * TILE_W;
+    if (a.tile_expert != nullptr) {
+        const int tile = blockIdx.y;
+        if (tile >= *a.n_tiles) return;  // uniform for the whole block
+        x_row0 = a.tile_row0[tile];
+        rows_valid = a.tile_rows[tile];
+        w_row0 += static_cast<long long>(a.tile_expert[tile]) * a.N;
+    } else {
+        x_row0 = blockIdx.y * a.TN;
+        rows_valid = min(a.TN, a.M - x_row0);
+    }
+
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
+    const uint32_t x_bytes = static_cast<uint32_t>(a.TN) * TILE_K * 2;
+    const uint32_t stage_bytes = A_BYTES * (1 + a.dual) + x_bytes;
+    const uint32_t bars = base + a.stages * stage_bytes;
+    // barriers: full[s] at bars + 8 s, empty[s] at bars + 8 (stages + s), accumulator-ready, then the TMEM slot
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * a.stages, bar_acc = bars + 16 * a.stages;
+    const uint32_t slot = bar_acc + 8;
+    volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (slot - smem_u32(smem_raw)));
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < a.stages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *slot_ptr;
+    const int nkb = (a.K + TILE_K - 1) / TILE_K;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % a.stages;
+                mbar_wait(bar_empty + 8 * s, ((kb / a.stages) & 1) ^ 1, 1);
+                const uint32_t st = base + s * stage_bytes;
+                mbar_expect_tx(bar_full + 8 * s, stage_bytes);
+                tma_load_2d(st, &map_w, kb * TILE_K, static_cast<int>(w_row0), bar_full + 8 * s);
+                if (a.dual) tma_load_2d(st + A_BYTES, &map_w2, kb * TILE_K, static_cast<int>(w_row0), bar_full + 8 * s);
+                tma_load_2d(st + A_BYTES * (1 + a.dual), &map_x, kb * TILE_K, x_row0, bar_full + 8 * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major, N = TN, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a.TN >> 3) << 17) |
+                                   (static_cast<uint32_t>(TILE_W >> 4) << 24);
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % a.stages;
+                mbar_wait(bar_full + 8 * s, (kb / a.stages) & 1, 2);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t st = base + s * stage_bytes;
+                const uint64_t dw = make_desc(st), dw2 = make_desc(st + A_BYTES);
+                const uint64_t dx = make_desc(st + A_BYTES * (1 + a.dual));
+#pragma unroll
+                for (int k4 = 0; k4 < TILE_K / 16; ++k4) {
+                    const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+                    umma_bf16(tmem, dw + 2 * k4, dx + 2 * k4, idesc, acc);  // 16 elements = 32 bytes = 2 units
+                    if (a.dual) umma_bf16(tmem + a.TN, dw2 + 2 * k4, dx + 2 * k4, idesc, acc);
+                }
+                umma_commit(bar_empty + 8 * s);  // the stage is free when these MMAs have read it
+            }
+            umma_commit(bar_acc);
+        }
+    } else {
+        const int quarter = warp & 3;  // tensor-memory lanes this warp may read
+        const int row = quarter * 32 + lane;
+        const long long n = static_cast<long long>(blockIdx.x) * TILE_W + row;  // output column
+        const bool n_ok = n < a.N;
+        mbar_wait(bar_acc, 0, 3);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const float bias = (a.bias && n_ok) ? ld_dyn(a.bias, a.bias_dt, n) : 0.f;
+        const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+        for (int c0 = 0; c0 < a.TN; c0 += 16) {
+            if (c0 >= rows_valid) break;  // uniform
+            uint32_t v[16], u[16];
+            tmem_ld16(lane_addr + c0, v);
+            if (a.dual) tmem_ld16(lane_addr + a.TN + c0, u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                if (c0 + j >= rows_valid || !n_ok) continue;
+                const int r = x_row0 + c0 + j;
+                float val = __uint_as_float(v[j]);
+                if (a.dual) {
+                    const float g = val;
+                    val = g / (1.0f + expf(-g)) * __uint_as_float(u[j]);
+                }
+                val += bias;
+                if (a.row_scale) val *= a.row_scale[a.scale_rows ? a.scale_rows[r] : r];
+                const size_t o = static_cast<size_t>(r) * a.ldo + n;
+                if (a.accumulate) {
+                    static_cast<float*>(a.out)[o] += val;
+                } else {
+                    st_dyn(a.out, a.out_dt, o, val);
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess) {
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        }
+    }
+    return fn;
+}
+
+// rows x K bfloat16 matrix, row stride ld elements; box = box_rows x 64 elements, 128-byte swizzle.
+// Rows and k beyond the matrix read as zero.
+static bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, long long ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    cuuint32_t box[2] = {TILE_K, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static int pow2_at_least(int v) {
+    int p = 32;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+// x [x_rows_total, K] bfloat16 (row stride ldx), w (and w2) [w_rows_total, K] bfloat16 contiguous.
+// Plain product: M rows of x, N = w_rows_total.  Grouped: w holds E experts of N rows each,
+// x rows are the expert-sorted pairs, the tile list has tiles of TN rows.
+// TN: token tile, a multiple of 16 in 16..256 (dual: at most 128... 256 columns of tensor memory each).
+extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ldx, const void* w, const void* w2,
+                             long long w_rows_total, const void* bias, int bias_dt, void* out, int out_dt,
+                             int accumulate, const float* row_scale, const int* scale_rows, int M, int N, int K,
+                             long long ldo, int TN, const int* tile_expert, const int* tile_row0,
+                             const int* tile_rows, const int* n_tiles, int max_tiles, cudaStream_t stream) {
+    const int dual = w2 != nullptr ? 1 : 0;
+    if (N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
+    if (TN < 16 || TN > 256 || TN % 16 != 0 || (dual && TN > 256)) return LOCUS_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2)) & 15)
+        return LOCUS_ERR_UNSUPPORTED;
+    if (accumulate && out_dt != LOCUS_DT_F32) return LOCUS_ERR_UNSUPPORTED;
+    if (w_rows_total >= (1LL << 31) || x_rows_total >= (1LL << 31)) return LOCUS_ERR_UNSUPPORTED;
+    CUtensorMap map_w, map_w2, map_x;
+    if (!make_map(&map_w, w, w_rows_total, K, K, TILE_W)) return LOCUS_ERR_UNSUPPORTED;
+    if (!make_map(&map_w2, dual ? w2 : w, w_rows_total, K, K, TILE_W)) return LOCUS_ERR_UNSUPPORTED;
+    if (!make_map(&map_x, x, x_rows_total, K, ldx, TN)) return LOCUS_ERR_UNSUPPORTED;
+    TcArgs a;
+    a.M = M; a.N = N; a.K = K; a.TN = TN; a.dual = dual;
+    const int stage_bytes = A_BYTES * (1 + dual) + TN * TILE_K * 2;
+    int stages = (200 * 1024) / stage_bytes;
+    if (stages > 12) stages = 12;
+    const int nkb = (K + TILE_K - 1) / TILE_K;
+    if (stages > nkb) stages = nkb;
+    if (stages < 1) return LOCUS_ERR_UNSUPPORTED;
+    a.stages = stages;
+    a.tmem_cols = pow2_at_least(TN * (1 + dual));
+    if (a.tmem_cols > 512) return LOCUS_ERR_UNSUPPORTED;
+    a.accumulate = accumulate; a.out = out; a.out_dt = out_dt; a.ldo = ldo; a.bias = bias; a.bias_dt = bias_dt;
+    a.row_scale = row_scale; a.scale_rows = scale_rows; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
+    a.tile_rows = tile_rows; a.n_tiles = n_tiles;
+    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 16 * stages + 16 + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+            return static_cast<int>(cudaGetLastError());
+        attr_set = true;
+    }
+    const int tiles_y = tile_expert ? max_tiles : ceil_div(M, TN);
+    if (tiles_y <= 0) return 0;
+    if (tiles_y > 65535) return LOCUS_ERR_UNSUPPORTED;
+    dim3 grid(ceil_div(N, TILE_W), tiles_y);
+    gemm_tc_kernel<<<grid, 192, smem, stream>>>(map_w, map_w2, map_x, a);
+    return locus_launch_status();
+}
+
+// Reads and clears the module's error word (0 = no bounded wait ran out).  Synchronises.
+extern "C" int locus_gemm_tc_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) cudaMemcpyToSymbol(g_tc_error, &zero, sizeof(int));
+    return v;
+}

@@ -25,6 +25,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheError, CacheManager, SeqCache
+from .. import kernels as K
 from ..kernels import DECODE_SPLIT
 from .batch import GroupBatch, Runtime, StepBatch
 
@@ -59,12 +60,17 @@ class ModelRunner:
         W = cache.table_width
         items_max = max_tokens // CHUNK_TILE + max_segments + 1
         size = (max_tokens * (2 + G) + max_segments * (5 + G * W) + self.max_wanted + 2 * items_max)
-        self._host = torch.empty(size, dtype=torch.int32,
-                                 pin_memory=self.device.type == "cuda")
-        self._host_np = self._host.numpy()
+        # two pinned staging buffers, used in turn: a buffer is rewritten only after the copy
+        # that read it has finished (its event), so steps may be queued without a host sync
+        on_gpu = self.device.type == "cuda"
+        self._hosts = [torch.empty(size, dtype=torch.int32, pin_memory=on_gpu) for _ in range(2)]
+        self._host_events = [torch.cuda.Event() if on_gpu else None for _ in range(2)]
+        self._host_used = [False, False]
+        self._host_turn = 0
         self._dev = torch.empty(size, dtype=torch.int32, device=self.device)
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._graph_logits: Dict[int, torch.Tensor] = {}
+        self._graph_launches: Dict[int, int] = {}
         self.launch_counter = 0
         self.stats = {"steps": 0, "tokens": 0, "graph_replays": 0, "h2d_bytes": 0}
 
@@ -152,14 +158,22 @@ class ModelRunner:
             fields.extend((slots, table))
         off = 0
         views = []
-        hn = self._host_np
+        turn = self._host_turn
+        self._host_turn ^= 1
+        if self._host_used[turn] and self._host_events[turn] is not None:
+            self._host_events[turn].synchronize()
+        host = self._hosts[turn]
+        hn = host.numpy()
         for f in fields:
             n = len(f)
             if n:
                 hn[off : off + n] = f
             views.append((off, n))
             off += n
-        self._dev[:off].copy_(self._host[:off], non_blocking=True)
+        self._dev[:off].copy_(host[:off], non_blocking=True)
+        if self._host_events[turn] is not None:
+            self._host_events[turn].record()
+            self._host_used[turn] = True
         self.stats["h2d_bytes"] += off * 4
 
         def dv(i):
@@ -188,23 +202,28 @@ class ModelRunner:
         decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         graphed = self.use_graphs and decode_only and self.device.type == "cuda"
         batch = self._build(entries, fixed_splits=graphed)
+        before = K.launches
         if graphed:
             key = len(entries)
             g = self._graphs.get(key)
             if g is None:
                 logits = self.model.forward(batch, self.layer_caches)  # also allocates every buffer
+                self._graph_launches[key] = K.launches - before
                 torch.cuda.synchronize(self.device)
                 g = torch.cuda.CUDAGraph()
                 with torch.cuda.graph(g):
                     out = self.model.forward(batch, self.layer_caches)
                 self._graphs[key] = g
                 self._graph_logits[key] = out
+                self.launch_counter += self._graph_launches[key]
             else:
                 g.replay()
                 self.stats["graph_replays"] += 1
                 logits = self._graph_logits[key]
+                self.launch_counter += self._graph_launches[key]
         else:
             logits = self.model.forward(batch, self.layer_caches)
+            self.launch_counter += K.launches - before
         for e in entries:
             self.cache.commit(e.seq, len(e.tokens))
         self.stats["steps"] += 1

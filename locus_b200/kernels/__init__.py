@@ -45,8 +45,15 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+# kernels launched through this module since import (several entry points launch two)
+launches = 0
+_LAUNCHES_OF = {"moe_sort": 2, "attn_decode": 2}
+
+
 def _check(code: int, what: str, detail: str = "") -> None:
+    global launches
     if code == 0:
+        launches += _LAUNCHES_OF.get(what, 1)
         return
     if code == ERR_UNSUPPORTED:
         raise KernelError(f"{what}: sizes or element types outside what the kernel takes {detail}")
@@ -112,10 +119,14 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
 class ExpertLayout:
     """Device tensors that lay (token, slot) pairs out by expert (see :func:`moe_sort`)."""
 
+    MIN_TILE = 16
+
     def __init__(self, n_pairs_max: int, n_experts: int, tile_m: int, device) -> None:
+        """``tile_m``: rows of a tile; :func:`moe_sort` may be given another one per call
+        (at least ``MIN_TILE``), the buffers are sized for the smallest."""
         self.tile_m = tile_m
         self.n_experts = n_experts
-        self.max_tiles = (n_pairs_max + tile_m - 1) // tile_m + n_experts
+        self.max_tiles = (n_pairs_max + self.MIN_TILE - 1) // self.MIN_TILE + n_experts
         i32 = dict(dtype=torch.int32, device=device)
         self.counts = torch.zeros(n_experts, **i32)
         self.offsets = torch.zeros(n_experts + 1, **i32)
@@ -129,6 +140,45 @@ class ExpertLayout:
     def tiles_for(self, n_pairs: int) -> int:
         """Upper bound of the number of row tiles when ``n_pairs`` pairs are routed."""
         return min(self.max_tiles, n_pairs // self.tile_m + min(n_pairs, self.n_experts) + 1)
+
+
+# Tests switch this off to run the CUDA-core product on bfloat16 inputs.
+USE_TENSOR_CORES = True
+
+
+def tensor_cores_take(x: torch.Tensor, w: torch.Tensor, x_rows: Optional[torch.Tensor] = None) -> bool:
+    """Whether :func:`linear` runs this product on the tensor cores: bfloat16 activations and
+    weights, rows that TMA can address (width and row stride multiples of 8 elements,
+    16-byte aligned base), and no row gather (gather into a buffer first)."""
+    K = x.shape[-1]
+    return (USE_TENSOR_CORES and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x_rows is None
+            and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def token_tile(m: int, dual: bool = False) -> int:
+    """Token tile (the N side of the MMA) for ``m`` rows."""
+    for t in (16, 32, 64, 128):
+        if m <= t:
+            return t
+    return 128 if dual else 256
+
+
+def expert_tile(n_pairs: int, n_experts: int) -> int:
+    """Row tile of a grouped product from the mean number of rows per expert."""
+    mean = n_pairs / max(1, n_experts)
+    if mean >= 96:
+        return 128
+    if mean >= 40:
+        return 64
+    if mean >= 12:
+        return 32
+    return 16
+
+
+def tc_error() -> int:
+    """Error word of the tensor-core module (0 = fine); reading it synchronises the device.
+    Non-zero: a bounded wait inside a kernel ran out (1 producer, 2 MMA, 3 epilogue)."""
+    return int(_lib("gemm_tc").locus_gemm_tc_error())
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[torch.Tensor] = None,
@@ -170,6 +220,26 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         _i32(x_rows, "x_rows")
     if layout is not None:
         _need(w.dim() == 3 and w.shape[0] == layout.n_experts, "linear: grouped product needs w [E, N, K]")
+    if tensor_cores_take(x, w, x_rows):
+        # bfloat16 x bfloat16: tcgen05 kernel (csrc/gemm_tc.cu)
+        if layout is not None:
+            TN = layout.tile_m
+            te, t0, tr, nt = layout.tile_expert, layout.tile_row0, layout.tile_rows, layout.n_tiles
+            max_tiles = layout.tiles_for(M)
+        else:
+            _need(w.dim() == 2, "linear: w must be [N, K]")
+            TN = token_tile(M, w2 is not None)
+            te = t0 = tr = nt = None
+            max_tiles = 0
+        code = _lib("gemm_tc").locus_gemm_tc(
+            _p(x), LL(M), LL(x.stride(0)), _p(w), _p(w2), LL(w.numel() // K), _p(bias),
+            I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
+            I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), I(M), I(N), I(K), LL(out.stride(0)), I(TN),
+            _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), _stream()
+        )
+        _check(code, "linear", f"(tensor cores; M={M}, N={N}, K={K}, token tile {TN})")
+        return
+    if layout is not None:
         _need(layout.tile_m == 64, "linear: the CUDA-core product uses 64-row tiles")
         te, t0, tr, nt = layout.tile_expert, layout.tile_row0, layout.tile_rows, layout.n_tiles
         max_tiles = layout.tiles_for(M)
@@ -296,10 +366,14 @@ def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.
     _check(code, "router_topk", f"(H={H}, E={E}, k={top_k})")
 
 
-def moe_sort(ids: torch.Tensor, n_pairs: int, layout: ExpertLayout) -> None:
-    """Fill ``layout`` from the picked experts ``ids`` (first ``n_pairs`` entries)."""
+def moe_sort(ids: torch.Tensor, n_pairs: int, layout: ExpertLayout, tile_m: Optional[int] = None) -> None:
+    """Fill ``layout`` from the picked experts ``ids`` (first ``n_pairs`` entries), with row
+    tiles of ``tile_m`` rows (default: the layout's)."""
     _i32(ids, "ids")
     _need(n_pairs <= layout.sorted_pair.numel(), "moe_sort: layout too small")
+    if tile_m is not None:
+        _need(tile_m >= layout.MIN_TILE, f"moe_sort: tiles of at least {layout.MIN_TILE} rows")
+        layout.tile_m = tile_m
     code = _lib("moe_route").locus_moe_sort(
         _p(ids), I(n_pairs), I(layout.n_experts), I(layout.tile_m), _p(layout.counts),
         _p(layout.offsets), _p(layout.sorted_pair), _p(layout.pair_pos), _p(layout.tile_expert),
@@ -369,4 +443,4 @@ def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tens
 
 def modules_for(dtype: torch.dtype) -> list:
     """Kernel modules that a model of element type ``dtype`` needs."""
-    return ["elementwise", "gemm_simt", "attention", "moe_route", "sampling"]
+    return ["elementwise", "gemm_simt", "gemm_tc", "attention", "moe_route", "sampling"]

@@ -41,7 +41,7 @@ class DenseMlp(FeedForward):
         ]
 
     def kernel_modules(self, dtype):
-        return ["gemm_simt"]
+        return ["gemm_simt"] + (["gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def forward(self, h, batch, residual, rt, row_scale=None) -> None:
         T = h.shape[0]
@@ -97,7 +97,7 @@ class SparseMoe(FeedForward):
         return out
 
     def kernel_modules(self, dtype):
-        return ["gemm_simt", "moe_route", "elementwise"]
+        return ["gemm_simt", "moe_route", "elementwise"] + (["gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def bind(self, rt) -> None:
         self._layout = rt.shared_object(
@@ -116,10 +116,18 @@ class SparseMoe(FeedForward):
         if self.observer is not None:
             self.observer(self.prefix, ids[:n_pairs].view(T, self.k), wts[:n_pairs].view(T, self.k))
         lay = self._layout
-        K.moe_sort(ids, n_pairs, lay)
         act = rt.rows(f"moe.act{self.I}", self.I, rt.dtype, n_pairs, per_token=self.k)
-        K.linear(h, self.params["gate_exps"], act, w2=self.params["up_exps"], x_rows=lay.sorted_pair,
-                 x_row_div=self.k, layout=lay, n_rows=n_pairs)
+        if (K.tensor_cores_take(h, self.params["gate_exps"]) and self.I % 8 == 0
+                and self.params["down_exps"].dtype == torch.bfloat16):
+            # tensor cores: TMA reads whole row ranges, so lay the tokens out in expert order first
+            K.moe_sort(ids, n_pairs, lay, K.expert_tile(n_pairs, self.E))
+            xs = rt.rows("moe.x_sorted", self.hidden, rt.dtype, n_pairs, per_token=self.k)
+            K.gather_rows(h, lay.sorted_pair, self.k, xs, n_pairs)
+            K.linear(xs, self.params["gate_exps"], act, w2=self.params["up_exps"], layout=lay, n_rows=n_pairs)
+        else:
+            K.moe_sort(ids, n_pairs, lay, 64)
+            K.linear(h, self.params["gate_exps"], act, w2=self.params["up_exps"], x_rows=lay.sorted_pair,
+                     x_row_div=self.k, layout=lay, n_rows=n_pairs)
         pair_out = rt.rows("moe.pair_out", self.hidden, torch.float32, n_pairs, per_token=self.k)
         K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts,
                  scale_rows=lay.sorted_pair)

@@ -163,7 +163,9 @@ def router_topk(h, w_router, w_gate, ids, wts, gamma, *, top_k, renorm, scale=1.
         gamma[:T] = (1.0 / (1.0 + torch.exp(-z))).to(gamma.dtype)
 
 
-def moe_sort(ids, n_pairs, layout):
+def moe_sort(ids, n_pairs, layout, tile_m=None):
+    if tile_m is not None:
+        layout.tile_m = tile_m
     E, tm = layout.n_experts, layout.tile_m
     idl = ids[:n_pairs].tolist()
     pos = 0

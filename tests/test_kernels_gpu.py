@@ -369,3 +369,91 @@ def test_penalties():
         h = [t for t in hist[r].tolist() if t >= 0]
         ref = plain.apply_penalties(logits[r], h, float(rep[r]), float(fr[r]), float(pr[r]), 64)
         close(d[r], ref, torch.float32, f"penalties row {r}")
+
+
+# ---------------------------------------------------------------------------
+# tensor-core products (csrc/gemm_tc.cu): every bfloat16 x bfloat16 call of K.linear above
+# already runs on them; these add the large tiles, every grouped tile size, and the
+# CUDA-core product on the same bfloat16 inputs.
+
+@pytest.fixture
+def cuda_cores_only():
+    K.USE_TENSOR_CORES = False
+    yield
+    K.USE_TENSOR_CORES = True
+
+
+def test_tensor_cores_are_what_runs_for_bfloat16():
+    x, w = torch.zeros(4, 64, dtype=torch.bfloat16, device=DEV), torch.zeros(8, 64, dtype=torch.bfloat16, device=DEV)
+    assert K.tensor_cores_take(x, w)
+    assert not K.tensor_cores_take(x.float(), w.float()) and not K.tensor_cores_take(x, w.float())
+    assert not K.tensor_cores_take(x[:, :60], w[:, :60])  # width 60: no 16-byte rows for TMA
+    assert K.tc_error() == 0
+
+
+@pytest.mark.parametrize("M,N,K_", [(300, 260, 1408), (2048, 384, 2048), (17, 2048, 5632), (64, 128, 64)])
+def test_linear_tensor_cores_large_tiles(M, N, K_):
+    dt = torch.bfloat16
+    x, w = rnd(M, K_, dtype=dt, seed=3), rnd(N, K_, dtype=dt, seed=4, scale=0.05)
+    bias, rs = rnd(N, dtype=dt, seed=5), rnd(M, seed=6)
+    ref = torch.empty(M, N, dtype=torch.float64)
+    EK.linear(x, w, ref, bias=bias)
+    out = torch.empty(M, N, dtype=dt, device=DEV)
+    K.linear(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV))
+    close(out, ref, dt, "tensor-core linear + bias")
+    res0 = rnd(M, N, seed=7)
+    res = res0.clone().to(DEV)
+    K.linear(x.to(DEV), w.to(DEV), res, row_scale=rs.to(DEV), accumulate=True)
+    ref2 = res0.clone().double()
+    EK.linear(x, w, ref2, row_scale=rs, accumulate=True)
+    close(res, ref2, dt, "tensor-core linear accumulate")
+    w2 = rnd(N, K_, dtype=dt, seed=8, scale=0.05)
+    act = torch.empty(M, N, dtype=dt, device=DEV)
+    K.linear(x.to(DEV), w.to(DEV), act, w2=w2.to(DEV))
+    ref3 = torch.empty(M, N, dtype=torch.float64)
+    EK.linear(x, w, ref3, w2=w2)
+    close(act, ref3, dt, "tensor-core swiglu")
+    assert K.tc_error() == 0
+
+
+@pytest.mark.parametrize("tile", [16, 32, 64, 128])
+def test_linear_grouped_tensor_cores_every_tile(tile):
+    T, E, k, H, I = 210, 7, 3, 136, 72
+    dt = torch.bfloat16
+    ids = _route(T, E, k, 3)
+    ids[: 3 * 60] = 4   # one crowded expert (several tiles), expert 0 possibly small
+    ids[ids == 2] = 5   # expert 2 gets nothing
+    h = rnd(T, H, dtype=dt, seed=1)
+    wg, wu = rnd(E, I, H, dtype=dt, seed=2, scale=0.2), rnd(E, I, H, dtype=dt, seed=3, scale=0.2)
+    wd = rnd(E, H, I, dtype=dt, seed=4, scale=0.2)
+    wts = torch.rand(T * k, generator=torch.Generator().manual_seed(5))
+    lay, ref_lay = K.ExpertLayout(T * k, E, 64, DEV), EK.ExpertLayout(T * k, E, 64, "cpu")
+    K.moe_sort(ids.to(DEV), T * k, lay, tile)
+    EK.moe_sort(ids, T * k, ref_lay, tile)
+    assert int(lay.n_tiles.cpu()) == int(ref_lay.n_tiles) <= lay.tiles_for(T * k)
+    xs = torch.empty(T * k, H, dtype=dt, device=DEV)
+    K.gather_rows(h.to(DEV), lay.sorted_pair, k, xs, T * k)
+    assert torch.equal(xs.cpu(), h[(ref_lay.sorted_pair.long() // k)])
+    act = torch.full((T * k, I), float("nan"), dtype=dt, device=DEV)
+    K.linear(xs, wg.to(DEV), act, w2=wu.to(DEV), layout=lay, n_rows=T * k)
+    ref_act = torch.empty(T * k, I, dtype=torch.float64)
+    EK.linear(xs.cpu(), wg, ref_act, w2=wu, layout=ref_lay, n_rows=T * k)
+    close(act, ref_act, dt, f"grouped swiglu, tile {tile}")
+    pair_out = torch.full((T * k, H), float("nan"), device=DEV)
+    K.linear(act, wd.to(DEV), pair_out, layout=lay, n_rows=T * k, row_scale=wts.to(DEV), scale_rows=lay.sorted_pair)
+    ref_out = torch.empty(T * k, H, dtype=torch.float64)
+    EK.linear(act.cpu(), wd, ref_out, layout=ref_lay, n_rows=T * k, row_scale=wts, scale_rows=ref_lay.sorted_pair)
+    close(pair_out, ref_out, dt, f"grouped down, tile {tile}")
+    assert K.tc_error() == 0
+
+
+def test_cuda_core_product_on_bfloat16(cuda_cores_only):
+    dt = torch.bfloat16
+    x, w = rnd(70, 120, dtype=dt, seed=3), rnd(130, 120, dtype=dt, seed=4, scale=0.1)
+    out = torch.empty(70, 130, dtype=dt, device=DEV)
+    before = K.launches
+    K.linear(x.to(DEV), w.to(DEV), out)
+    ref = torch.empty(70, 130, dtype=torch.float64)
+    EK.linear(x, w, ref)
+    close(out, ref, dt, "cuda-core bf16")
+    assert K.launches == before + 1
