@@ -382,3 +382,49 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
     }
     return locus_launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// Decode attention with the scratch inside the library (see attention_static.h for who this
+// is for, what it costs and the rules of use).  The kernels are the ones above; only the
+// home of the partial results differs.
+#include "attention_static.h"
+
+// The scratch itself.  On the host this name is only a handle for cudaGetSymbolAddress; the
+// device address it stands for is looked up once per device below.
+static __device__ __align__(256) float g_attn_static_scratch[LOCUS_ATTN_STATIC_SCRATCH_FLOATS];
+
+#define LOCUS_MAX_DEVICES 64
+static float* g_attn_static_ptr[LOCUS_MAX_DEVICES];  // device address of the array, per device
+
+extern "C" int locus_attn_decode_static(const void* q, int dt, const void* pool, void* out,
+                                        const int* seg_q0, const int* seg_qn, const int* seg_ctx,
+                                        const int* block_table, int table_stride, const int* items,
+                                        int n_items, int nh, int nkv, int hd, int page_tokens,
+                                        int window, float scale, int max_splits, cudaStream_t stream) {
+    if (n_items <= 0) return 0;
+    if (int e = check_common(nh, nkv, hd, page_tokens, window)) return e;
+    if (max_splits <= 0) return LOCUS_ERR_UNSUPPORTED;
+    // part_o: n_items * nh * max_splits * hd floats, then part_ml: 2 floats per (item, head, split)
+    const long long units = static_cast<long long>(n_items) * nh * max_splits;
+    const long long need = units * (hd + 2);
+    if (need > LOCUS_ATTN_STATIC_SCRATCH_FLOATS) return LOCUS_ERR_SCRATCH_TOO_SMALL;
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    if (dev < 0 || dev >= LOCUS_MAX_DEVICES) return LOCUS_ERR_UNSUPPORTED;
+    if (g_attn_static_ptr[dev] == nullptr) {
+        // first call on this device (it is the current one): resolve the array's device address
+        void* p = nullptr;
+        err = cudaGetSymbolAddress(&p, g_attn_static_scratch);
+        if (err != cudaSuccess) return static_cast<int>(err);
+        if (p == nullptr) return LOCUS_ERR_UNSUPPORTED;
+        g_attn_static_ptr[dev] = static_cast<float*>(p);
+    }
+    float* part_o = g_attn_static_ptr[dev];
+    float* part_ml = part_o + units * hd;  // units * hd is a multiple of 16 floats: stays aligned
+    // Nothing to clear: the split kernel writes m and l for every (item, head, split) of the
+    // grid and the sums of every split the merge kernel reads.
+    return locus_attn_decode(q, dt, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride,
+                             items, n_items, nh, nkv, hd, page_tokens, window, scale, part_o, part_ml,
+                             max_splits, stream);
+}

@@ -35,6 +35,9 @@ NVCC_FLAGS = [
 
 HEADERS = ["common.cuh"]
 
+# module name -> further headers its library depends on
+MODULE_HEADERS: Dict[str, List[str]] = {"attention": ["attention_static.h"]}
+
 # module name -> extra nvcc flags
 MODULE_FLAGS: Dict[str, List[str]] = {}
 
@@ -78,7 +81,7 @@ def module_names() -> List[str]:
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for f in [name + ".cu"] + HEADERS:
+    for f in [name + ".cu"] + HEADERS + MODULE_HEADERS.get(name, []):
         with open(os.path.join(CSRC_DIR, f), "rb") as fh:
             h.update(fh.read())
     h.update(" ".join(NVCC_FLAGS + MODULE_FLAGS.get(name, [])).encode())
