@@ -1,0 +1,219 @@
+// bfloat16 products for a few dozen rows (decode steps, the router): out = x . W^T with at
+// most 32 rows of x per tile.  Reading W once from HBM is what bounds this work, so a block
+// takes only 16 rows of W and streams them with 16-byte loads straight from global memory
+// into tensor-core fragments (mma.sync m16n8k16, bfloat16 in, float32 accumulate): the 16
+// weight rows are the M side, up to 32 tokens (four 8-wide tiles) the N side.  The eight
+// warps of a block split K between them in interleaved 32-element steps, so a block of 16
+// weight rows keeps 8 x 4 x 16 bytes per lane in flight, and N / 16 blocks cover the GPU even
+// for a 2048-row matrix.  Partial sums of the warps are added in warp order through shared
+// memory, then the usual epilogue runs (bias, SwiGLU of two weight matrices, per-row scale,
+// store or add into float32); gathered and grouped (expert tile list) forms as elsewhere.
+//
+// Within a k-step the 32 k-values are handed to the two MMAs in a permuted order (lane
+// quad q takes the 8 consecutive elements 8q..8q+7 of every row), the same for W and x, so
+// every load is a full 16-byte vector of one row.  The order of the sum of an element
+// depends on K only.
+#include "common.cuh"
+
+#define SK_WARPS 8
+#define SK_ROWS 16
+
+struct SkinnyArgs {
+    const bf16* x;
+    const bf16* w;
+    const bf16* w2;
+    const void* bias;
+    int bias_dt;
+    void* out;
+    int out_dt;
+    int accumulate;
+    const float* row_scale;
+    const int* scale_rows;
+    const int* x_rows;
+    int x_row_div;
+    int M, N, K;
+    long long ldx, ldo;
+    const int* tile_expert;
+    const int* tile_row0;
+    const int* tile_rows;
+    const int* n_tiles;
+    long long w_expert_stride;
+};
+
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 ld_stream(const bf16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
+
+template <int NT, bool DUAL>
+__global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
+    extern __shared__ float red[];  // [SK_WARPS][(DUAL ? 2 : 1)][NT][16 * 8]
+    int tok0, ntok;
+    const bf16* W = a.w;
+    const bf16* W2 = a.w2;
+    if (a.tile_expert != nullptr) {
+        const int tile = blockIdx.y;
+        if (tile >= *a.n_tiles) return;
+        const long long e = a.tile_expert[tile];
+        tok0 = a.tile_row0[tile];
+        ntok = a.tile_rows[tile];
+        W += e * a.w_expert_stride;
+        if (DUAL) W2 += e * a.w_expert_stride;
+    } else {
+        tok0 = blockIdx.y * (NT * 8);
+        ntok = min(NT * 8, a.M - tok0);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, q = lane & 3;
+    const int n0 = blockIdx.x * SK_ROWS;
+    const int K = a.K;
+    // weight rows of this lane (clamped: rows past N are computed and dropped)
+    const long long r_lo = min(n0 + g, a.N - 1), r_hi = min(n0 + g + 8, a.N - 1);
+    const bf16* wl = W + r_lo * K;
+    const bf16* wh = W + r_hi * K;
+    const bf16* ul = DUAL ? W2 + r_lo * K : nullptr;
+    const bf16* uh = DUAL ? W2 + r_hi * K : nullptr;
+    // token rows of this lane, one per 8-wide tile
+    const bf16* xr[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int t = j * 8 + g;
+        if (t < ntok) {
+            const int r = tok0 + t;
+            const long long xrow = a.x_rows ? a.x_rows[r] / a.x_row_div : r;
+            xr[j] = a.x + xrow * a.ldx;
+        } else {
+            xr[j] = nullptr;
+        }
+    }
+    float c[NT][4], c2[DUAL ? NT : 1][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            c[j][i] = 0.f;
+            if (DUAL) c2[j][i] = 0.f;
+        }
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    // this warp's k-steps: 32 elements each, interleaved with the other warps'; four steps at a time
+    constexpr int STEP = 32, STRIDE = STEP * SK_WARPS, UNROLL = 4;
+    for (int kb = warp * STEP; kb < K; kb += STRIDE * UNROLL) {
+        uint4 al[UNROLL], ah[UNROLL], bl[DUAL ? UNROLL : 1], bh[DUAL ? UNROLL : 1];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = kb + u * STRIDE + q * 8;
+            const bool in = k < K;  // K is a multiple of 8: a chunk is inside or outside as a whole
+            al[u] = in ? ld_stream(wl + k) : zero;
+            ah[u] = in ? ld_stream(wh + k) : zero;
+            if (DUAL) {
+                bl[u] = in ? ld_stream(ul + k) : zero;
+                bh[u] = in ? ld_stream(uh + k) : zero;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = kb + u * STRIDE + q * 8;
+            if (kb + u * STRIDE >= K) break;  // uniform in the warp
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const uint4 xv = (xr[j] != nullptr && k < K) ? *reinterpret_cast<const uint4*>(xr[j] + k) : zero;
+                mma_bf16(c[j], al[u].x, ah[u].x, al[u].y, ah[u].y, xv.x, xv.y);
+                mma_bf16(c[j], al[u].z, ah[u].z, al[u].w, ah[u].w, xv.z, xv.w);
+                if (DUAL) {
+                    mma_bf16(c2[j], bl[u].x, bh[u].x, bl[u].y, bh[u].y, xv.x, xv.y);
+                    mma_bf16(c2[j], bl[u].z, bh[u].z, bl[u].w, bh[u].w, xv.z, xv.w);
+                }
+            }
+        }
+    }
+    // partial sums of the warps -> shared memory; element (row r, token col) of tile j at [j][col * 16 + r]
+    constexpr int SETS = DUAL ? 2 : 1;
+    float* mine = red + static_cast<size_t>(warp) * SETS * NT * 128;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        float* d = mine + j * 128;
+        d[(2 * q) * 16 + g] = c[j][0];
+        d[(2 * q + 1) * 16 + g] = c[j][1];
+        d[(2 * q) * 16 + g + 8] = c[j][2];
+        d[(2 * q + 1) * 16 + g + 8] = c[j][3];
+        if (DUAL) {
+            float* d2 = mine + (NT + j) * 128;
+            d2[(2 * q) * 16 + g] = c2[j][0];
+            d2[(2 * q + 1) * 16 + g] = c2[j][1];
+            d2[(2 * q) * 16 + g + 8] = c2[j][2];
+            d2[(2 * q + 1) * 16 + g + 8] = c2[j][3];
+        }
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < NT * 128; idx += blockDim.x) {
+        const int j = idx / 128, col = (idx % 128) / 16, r = idx % 16;
+        const int t = j * 8 + col, n = n0 + r;
+        if (t >= ntok || n >= a.N) continue;
+        float v = 0.f, u = 0.f;
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) {
+            v += red[static_cast<size_t>(w) * SETS * NT * 128 + idx];
+            if (DUAL) u += red[static_cast<size_t>(w) * SETS * NT * 128 + NT * 128 + idx];
+        }
+        if (DUAL) v = v / (1.0f + expf(-v)) * u;
+        if (a.bias) v += ld_dyn(a.bias, a.bias_dt, n);
+        const int row = tok0 + t;
+        if (a.row_scale) v *= a.row_scale[a.scale_rows ? a.scale_rows[row] : row];
+        const size_t o = static_cast<size_t>(row) * a.ldo + n;
+        if (a.accumulate) {
+            static_cast<float*>(a.out)[o] += v;
+        } else {
+            st_dyn(a.out, a.out_dt, o, v);
+        }
+    }
+}
+
+template <int NT>
+static int launch(const SkinnyArgs& a, int tiles, bool dual, cudaStream_t stream) {
+    dim3 grid(ceil_div(a.N, SK_ROWS), tiles);
+    if (grid.x == 0 || grid.y == 0) return 0;
+    if (grid.y > 65535) return LOCUS_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * SK_WARPS * (dual ? 2 : 1) * NT * 128;
+    if (dual) {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(skinny_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        skinny_kernel<NT, true><<<grid, 32 * SK_WARPS, smem, stream>>>(a);
+    } else {
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(skinny_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        skinny_kernel<NT, false><<<grid, 32 * SK_WARPS, smem, stream>>>(a);
+    }
+    return locus_launch_status();
+}
+
+// tile_tokens: 8, 16 or 32 rows of x per tile (for a grouped product: the tile size of the
+// tile list).  x and W bfloat16; K a multiple of 8; 16-byte aligned rows.
+extern "C" int locus_gemm_skinny(const void* x, const void* w, const void* w2, const void* bias, int bias_dt,
+                                 void* out, int out_dt, int accumulate, const float* row_scale,
+                                 const int* scale_rows, const int* x_rows, int x_row_div, int M, int N, int K,
+                                 long long ldx, long long ldo, int tile_tokens, const int* tile_expert,
+                                 const int* tile_row0, const int* tile_rows, const int* n_tiles, int max_tiles,
+                                 long long w_expert_stride, cudaStream_t stream) {
+    if (N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2)) & 15)
+        return LOCUS_ERR_UNSUPPORTED;
+    if (accumulate && out_dt != LOCUS_DT_F32) return LOCUS_ERR_UNSUPPORTED;
+    if (x_rows != nullptr && x_row_div <= 0) return LOCUS_ERR_UNSUPPORTED;
+    if (tile_tokens != 8 && tile_tokens != 16 && tile_tokens != 32) return LOCUS_ERR_UNSUPPORTED;
+    SkinnyArgs a;
+    a.x = static_cast<const bf16*>(x); a.w = static_cast<const bf16*>(w); a.w2 = static_cast<const bf16*>(w2);
+    a.bias = bias; a.bias_dt = bias_dt; a.out = out; a.out_dt = out_dt; a.accumulate = accumulate;
+    a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows; a.x_row_div = x_row_div;
+    a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldo = ldo; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
+    a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.w_expert_stride = w_expert_stride;
+    const int tiles = tile_expert ? max_tiles : ceil_div(M, tile_tokens);
+    const bool dual = w2 != nullptr;
+    if (tile_tokens == 8) return launch<1>(a, tiles, dual, stream);
+    if (tile_tokens == 16) return launch<2>(a, tiles, dual, stream);
+    return launch<4>(a, tiles, dual, stream);
+}

@@ -5,69 +5,134 @@
 // depend on what else is in the batch.
 #include "common.cuh"
 
-// One block per token.
+#define RT_TOK 8    // tokens per block
+#define RT_WARPS 8  // experts per block, one per warp
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float* o);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* o) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w; o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<bf16>(const bf16* p, float* o) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        o[2 * i] = f.x;
+        o[2 * i + 1] = f.y;
+    }
+}
+
+// Grid (token tiles of RT_TOK, expert groups of RT_WARPS).  A block stages its tokens'
+// activations in shared memory; each warp computes the router logit of one expert (the shared
+// gate counts as expert E) for all tokens of the tile, every weight read once per tile, and
+// writes it to `logits` [T, E (+1)].  The block that finishes a tile last (a counter per tile,
+// reset for the next launch) runs softmax, selection and weights for the tile, one warp per token.
 //   h        [T, H]   normed activations (float32 or bfloat16)
 //   wr       [E, H]   router weight; wg [H] weight of the shared-expert gate (or null)
 //   ids      [T, k]   picked experts in pick order; wts [T, k] their weights
 //   gamma    [T]      sigmoid(wg . h) (written only when wg != null)
-// Selection: k rounds of arg-max over softmax probabilities with strict '>' (ties go to
-// the lowest index).  weight = p / wsum * scale with wsum = sum of picked p when renorm,
-// else 1.
+// Selection: k rounds of arg-max over softmax probabilities with strict '>' (ties go to the
+// lowest index).  weight = p / wsum * scale with wsum = sum of picked p when renorm, else 1.
+// The order in which a logit is summed depends on H only (8-element chunks per lane when H
+// is a multiple of 8, single elements else), not on the tile or its other tokens.
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(256) router_topk_kernel(
     const TX* __restrict__ h, const TW* __restrict__ wr, const void* __restrict__ wg, int wg_dt,
-    int* __restrict__ ids, float* __restrict__ wts, float* __restrict__ gamma, int H, int E, int k,
-    int renorm, float scale) {
-    extern __shared__ float smem[];
-    float* hs = smem;           // [H]
-    float* logit = smem + H;    // [E]
-    const int t = blockIdx.x;
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    const TX* hrow = h + static_cast<size_t>(t) * H;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) hs[j] = to_f(hrow[j]);
+    float* __restrict__ logits, int* __restrict__ counters, int* __restrict__ ids,
+    float* __restrict__ wts, float* __restrict__ gamma, int T, int H, int E, int k, int renorm,
+    float scale) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    TX* hs = reinterpret_cast<TX*>(smem_raw);                                        // [RT_TOK][H]
+    float* probs = reinterpret_cast<float*>(smem_raw + sizeof(TX) * RT_TOK * H);     // [RT_TOK][E1]
+    __shared__ int is_last;
+    const int E1 = E + (wg != nullptr ? 1 : 0);
+    const int tile = blockIdx.x, grp = blockIdx.y;
+    const int t0 = tile * RT_TOK, nt = min(RT_TOK, T - t0);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const TX* hsrc = h + static_cast<size_t>(t0) * H;
+    for (int i = threadIdx.x; i < nt * H; i += blockDim.x) hs[i] = hsrc[i];
     __syncthreads();
-    for (int e = wid; e < E + (wg != nullptr ? 1 : 0); e += nw) {
-        float acc = 0.f;
-        if (e < E) {
-            const TW* w = wr + static_cast<size_t>(e) * H;
-            for (int j = lane; j < H; j += 32) acc = fmaf(hs[j], to_f(w[j]), acc);
+    const int e = grp * RT_WARPS + wid;
+    if (e < E1) {
+        float acc[RT_TOK];
+#pragma unroll
+        for (int t = 0; t < RT_TOK; ++t) acc[t] = 0.f;
+        const bool gate = e >= E;
+        const bool vec = (H % 8 == 0) && (!gate || wg_dt == (sizeof(TW) == 4 ? LOCUS_DT_F32 : LOCUS_DT_BF16));
+        if (vec) {
+            const TW* w = gate ? static_cast<const TW*>(wg) : wr + static_cast<size_t>(e) * H;
+            for (int j = lane * 8; j < H; j += 256) {
+                float wv[8];
+                load8<TW>(w + j, wv);
+#pragma unroll
+                for (int t = 0; t < RT_TOK; ++t) {
+                    if (t < nt) {
+                        float hv[8];
+                        load8<TX>(hs + t * H + j, hv);
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) acc[t] = fmaf(hv[u], wv[u], acc[t]);
+                    }
+                }
+            }
         } else {
-            for (int j = lane; j < H; j += 32) acc = fmaf(hs[j], ld_dyn(wg, wg_dt, j), acc);
+            for (int j = lane; j < H; j += 32) {
+                const float wv = gate ? ld_dyn(wg, wg_dt, j) : to_f(wr[static_cast<size_t>(e) * H + j]);
+#pragma unroll
+                for (int t = 0; t < RT_TOK; ++t)
+                    if (t < nt) acc[t] = fmaf(to_f(hs[t * H + j]), wv, acc[t]);
+            }
         }
-        acc = warp_sum(acc);
-        if (lane == 0) {
-            if (e < E) {
-                logit[e] = acc;
-            } else {
-                gamma[t] = 1.0f / (1.0f + expf(-acc));
+#pragma unroll
+        for (int t = 0; t < RT_TOK; ++t) {
+            if (t < nt) {
+                const float s = warp_sum(acc[t]);
+                if (lane == 0) logits[static_cast<size_t>(t0 + t) * E1 + e] = s;
             }
         }
     }
+    // the last block of the tile to get here selects
+    __threadfence();
     __syncthreads();
-    if (wid != 0) return;
-    // softmax over all E experts
+    if (threadIdx.x == 0) is_last = atomicAdd(&counters[tile], 1) == static_cast<int>(gridDim.y) - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) counters[tile] = 0;
+    if (wid >= nt) return;
+    const int t = t0 + wid;
+    const float* lg = logits + static_cast<size_t>(t) * E1;
+    float* p = probs + wid * E1;
     float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, logit[e]);
+    for (int x = lane; x < E; x += 32) {
+        const float v = __ldcg(lg + x);
+        p[x] = v;
+        mx = fmaxf(mx, v);
+    }
+    if (wg != nullptr && lane == 0) gamma[t] = 1.0f / (1.0f + expf(-__ldcg(lg + E)));
     mx = warp_max(mx);
     float sum = 0.f;
-    for (int e = lane; e < E; e += 32) {
-        const float v = expf(logit[e] - mx);
-        logit[e] = v;
+    for (int x = lane; x < E; x += 32) {
+        const float v = expf(p[x] - mx);
+        p[x] = v;
         sum += v;
     }
     sum = warp_sum(sum);
-    __syncwarp();
-    for (int e = lane; e < E; e += 32) logit[e] = logit[e] / sum;
+    for (int x = lane; x < E; x += 32) p[x] = p[x] / sum;
     __syncwarp();
     float wsum = 0.f;
     for (int r = 0; r < k; ++r) {
         float best = -1.f;
         int best_e = 0x7fffffff;
-        for (int e = lane; e < E; e += 32) {
-            const float v = logit[e];
-            if (v > best) {  // taken experts hold -2; ascending e keeps the lowest index on ties
+        for (int x = lane; x < E; x += 32) {
+            const float v = p[x];
+            if (v > best) {  // taken experts hold -2; ascending x keeps the lowest index on ties
                 best = v;
-                best_e = e;
+                best_e = x;
             }
         }
 #pragma unroll
@@ -82,7 +147,7 @@ __global__ void __launch_bounds__(256) router_topk_kernel(
         if (lane == 0) {
             ids[t * k + r] = best_e;
             wts[t * k + r] = best;
-            logit[best_e] = -2.f;
+            p[best_e] = -2.f;
         }
         wsum += best;
         __syncwarp();
@@ -93,21 +158,28 @@ __global__ void __launch_bounds__(256) router_topk_kernel(
     }
 }
 
+// logits: scratch [T, E (+1 with a gate)] floats; counters: ceil(T / 8) ints, zero before the
+// first launch (every launch leaves them zero again).
 extern "C" int locus_router_topk(const void* h, int x_dt, const void* wr, int w_dt, const void* wg,
-                                 int wg_dt, int* ids, float* wts, float* gamma, int T, int H,
-                                 int E, int k, int renorm, float scale, cudaStream_t stream) {
+                                 int wg_dt, float* logits, int* counters, int* ids, float* wts,
+                                 float* gamma, int T, int H, int E, int k, int renorm, float scale,
+                                 cudaStream_t stream) {
     if (T <= 0) return 0;
     if (E <= 0 || k <= 0 || k > E) return LOCUS_ERR_UNSUPPORTED;
-    const size_t smem = static_cast<size_t>(H + E) * sizeof(float);
+    const int E1 = E + (wg != nullptr ? 1 : 0);
+    const size_t xsize = x_dt == LOCUS_DT_F32 ? 4 : 2;
+    const size_t smem = xsize * RT_TOK * H + sizeof(float) * RT_TOK * E1;
     if (smem > 200 * 1024) return LOCUS_ERR_UNSUPPORTED;
+    dim3 grid(ceil_div(T, RT_TOK), ceil_div(E1, RT_WARPS));
+    if (grid.y > 65535) return LOCUS_ERR_UNSUPPORTED;
 #define ROUTER_LAUNCH(TX, TW)                                                                    \
     do {                                                                                         \
         if (smem > 48 * 1024)                                                                    \
             cudaFuncSetAttribute(router_topk_kernel<TX, TW>,                                     \
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        router_topk_kernel<TX, TW><<<T, 256, smem, stream>>>(                                    \
-            static_cast<const TX*>(h), static_cast<const TW*>(wr), wg, wg_dt, ids, wts, gamma,   \
-            H, E, k, renorm, scale);                                                             \
+        router_topk_kernel<TX, TW><<<grid, 256, smem, stream>>>(                                 \
+            static_cast<const TX*>(h), static_cast<const TW*>(wr), wg, wg_dt, logits, counters,  \
+            ids, wts, gamma, T, H, E, k, renorm, scale);                                         \
     } while (0)
     if (x_dt == LOCUS_DT_F32 && w_dt == LOCUS_DT_F32) ROUTER_LAUNCH(float, float);
     else if (x_dt == LOCUS_DT_BF16 && w_dt == LOCUS_DT_BF16) ROUTER_LAUNCH(bf16, bf16);

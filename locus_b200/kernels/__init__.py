@@ -119,7 +119,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
 class ExpertLayout:
     """Device tensors that lay (token, slot) pairs out by expert (see :func:`moe_sort`)."""
 
-    MIN_TILE = 16
+    MIN_TILE = 8
 
     def __init__(self, n_pairs_max: int, n_experts: int, tile_m: int, device) -> None:
         """``tile_m``: rows of a tile; :func:`moe_sort` may be given another one per call
@@ -153,6 +153,33 @@ def tensor_cores_take(x: torch.Tensor, w: torch.Tensor, x_rows: Optional[torch.T
     K = x.shape[-1]
     return (USE_TENSOR_CORES and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x_rows is None
             and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+FEW_ROWS = 8  # rows of x per tile of the row-streaming kernel
+
+
+def few_rows_take(x: torch.Tensor, w: torch.Tensor, m: int, layout: Optional["ExpertLayout"] = None) -> bool:
+    """Whether :func:`linear` runs this product with the row-streaming kernel: at most 8 rows
+    (per expert tile when grouped), width a multiple of 8, 32-byte aligned rows."""
+    K = x.shape[-1]
+    rows_ok = layout.tile_m <= FEW_ROWS if layout is not None else m <= FEW_ROWS
+    return (rows_ok and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 32 == 0 and w.data_ptr() % 32 == 0)
+
+
+SKINNY_ROWS = 32      # most rows of x per tile of the weight-streaming tensor-core kernel
+SKINNY_MIN_ROWS = 2   # a single row goes to the row-streaming kernel
+
+
+def skinny_takes(x: torch.Tensor, w: torch.Tensor, m: int, layout: Optional["ExpertLayout"] = None) -> bool:
+    """Whether :func:`linear` runs this product with the weight-streaming tensor-core kernel:
+    bfloat16 x bfloat16, at most 32 rows (per expert tile of 8, 16 or 32 rows when grouped)."""
+    K = x.shape[-1]
+    if layout is not None:
+        rows_ok = layout.tile_m in (8, 16, 32)
+    else:
+        rows_ok = SKINNY_MIN_ROWS <= m <= SKINNY_ROWS
+    return (USE_TENSOR_CORES and rows_ok and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def token_tile(m: int, dual: bool = False) -> int:
@@ -220,6 +247,42 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         _i32(x_rows, "x_rows")
     if layout is not None:
         _need(w.dim() == 3 and w.shape[0] == layout.n_experts, "linear: grouped product needs w [E, N, K]")
+    if skinny_takes(x, w, M, layout):
+        # bfloat16, up to 32 rows per tile: weight-streaming tensor-core kernel (csrc/gemm_skinny.cu)
+        if layout is not None:
+            tile = layout.tile_m
+            te, t0, tr, nt = layout.tile_expert, layout.tile_row0, layout.tile_rows, layout.n_tiles
+            max_tiles, stride = layout.tiles_for(M), N * K
+        else:
+            _need(w.dim() == 2, "linear: w must be [N, K]")
+            tile = 8 if M <= 8 else (16 if M <= 16 else 32)
+            te = t0 = tr = nt = None
+            max_tiles = stride = 0
+        code = _lib("gemm_skinny").locus_gemm_skinny(
+            _p(x), _p(w), _p(w2), _p(bias), I(dtype_code(bias.dtype) if bias is not None else 0), _p(out),
+            I(dtype_code(out.dtype)), I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), _p(x_rows),
+            I(x_row_div), I(M), I(N), I(K), LL(x.stride(0)), LL(out.stride(0)), I(tile), _p(te), _p(t0), _p(tr),
+            _p(nt), I(max_tiles), LL(stride), _stream()
+        )
+        _check(code, "linear", f"(skinny; M={M}, N={N}, K={K}, tile {tile})")
+        return
+    if few_rows_take(x, w, M, layout):
+        # a handful of rows: bandwidth-bound row-streaming kernel (csrc/gemv.cu)
+        if layout is not None:
+            te, t0, tr, nt = layout.tile_expert, layout.tile_row0, layout.tile_rows, layout.n_tiles
+            max_tiles, stride = layout.tiles_for(M), N * K
+        else:
+            _need(w.dim() == 2, "linear: w must be [N, K]")
+            te = t0 = tr = nt = None
+            max_tiles = stride = 0
+        code = _lib("gemv").locus_gemv(
+            _p(x), I(dtype_code(x.dtype)), _p(w), _p(w2), I(dtype_code(w.dtype)), _p(bias),
+            I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
+            I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), _p(x_rows), I(x_row_div), I(M), I(N), I(K),
+            LL(x.stride(0)), LL(out.stride(0)), _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), LL(stride), _stream()
+        )
+        _check(code, "linear", f"(few rows; M={M}, N={N}, K={K}, x {x.dtype}, w {w.dtype})")
+        return
     if tensor_cores_take(x, w, x_rows):
         # bfloat16 x bfloat16: tcgen05 kernel (csrc/gemm_tc.cu)
         if layout is not None:
@@ -342,11 +405,22 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
     _check(code, "attn_decode", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
 
+class RouterScratch:
+    """Scratch of :func:`router_topk`: the router logits of a step and one counter per tile of
+    8 tokens (zero between launches)."""
+
+    def __init__(self, max_tokens: int, n_logits: int, device) -> None:
+        self.max_tokens, self.n_logits = max_tokens, n_logits
+        self.logits = torch.empty(max_tokens * n_logits, dtype=torch.float32, device=device)
+        self.counters = torch.zeros((max_tokens + 7) // 8, dtype=torch.int32, device=device)
+
+
 def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.Tensor],
                 ids: torch.Tensor, wts: torch.Tensor, gamma: Optional[torch.Tensor], *, top_k: int,
-                renorm: bool, scale: float = 1.0) -> None:
+                renorm: bool, scale: float = 1.0, scratch: Optional[RouterScratch] = None) -> None:
     """Router: softmax over all experts, top-k by repeated arg-max, weights; and
-    gamma = sigmoid(w_gate . h) when the shared expert is gated.  All in float32."""
+    gamma = sigmoid(w_gate . h) when the shared expert is gated.  All in float32.
+    ``scratch`` must hold T tokens of E (+1 with a gate) logits (made on the fly when None)."""
     _cuda_c(h, "h")
     _cuda_c(w_router, "w_router")
     _i32(ids, "ids")
@@ -358,10 +432,14 @@ def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.
     if w_gate is not None:
         _need(w_gate.numel() == H and gamma is not None and gamma.dtype == torch.float32 and gamma.numel() >= T,
               "router_topk: gate needs w_gate [H] and gamma [T] float32")
+    e1 = E + (1 if w_gate is not None else 0)
+    if scratch is None:
+        scratch = RouterScratch(T, e1, h.device)
+    _need(scratch.n_logits >= e1 and scratch.max_tokens >= T, "router_topk: scratch too small")
     code = _lib("moe_route").locus_router_topk(
         _p(h), I(dtype_code(h.dtype)), _p(w_router), I(dtype_code(w_router.dtype)), _p(w_gate),
-        I(dtype_code(w_gate.dtype) if w_gate is not None else 0), _p(ids), _p(wts), _p(gamma), I(T),
-        I(H), I(E), I(top_k), I(1 if renorm else 0), F(scale), _stream()
+        I(dtype_code(w_gate.dtype) if w_gate is not None else 0), _p(scratch.logits), _p(scratch.counters),
+        _p(ids), _p(wts), _p(gamma), I(T), I(H), I(E), I(top_k), I(1 if renorm else 0), F(scale), _stream()
     )
     _check(code, "router_topk", f"(H={H}, E={E}, k={top_k})")
 
@@ -443,4 +521,4 @@ def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tens
 
 def modules_for(dtype: torch.dtype) -> list:
     """Kernel modules that a model of element type ``dtype`` needs."""
-    return ["elementwise", "gemm_simt", "gemm_tc", "attention", "moe_route", "sampling"]
+    return ["elementwise", "gemm_simt", "gemv", "gemm_skinny", "gemm_tc", "attention", "moe_route", "sampling"]

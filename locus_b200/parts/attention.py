@@ -65,7 +65,7 @@ class Attention(Mixer):
         return out
 
     def kernel_modules(self, dtype):
-        return ["elementwise", "gemm_simt", "attention"] + (["gemm_tc"] if dtype == torch.bfloat16 else [])
+        return ["elementwise", "gemm_simt", "gemv", "attention"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def cache_needs(self):
         return PagedKvSpec(self.n_kv_heads, self.head_dim, self.window), None

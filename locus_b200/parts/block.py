@@ -73,7 +73,7 @@ class LmHead(Part):
         return [TensorSource(self.prefix + ".weight", (self.vocab, self.hidden), "weight")]
 
     def kernel_modules(self, dtype):
-        return ["gemm_simt"] + (["gemm_tc"] if dtype == torch.bfloat16 else [])
+        return ["gemm_simt", "gemv"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def forward(self, h: torch.Tensor, logits: torch.Tensor) -> None:
         K.linear(h, self.params["weight"], logits)

@@ -41,7 +41,7 @@ class DenseMlp(FeedForward):
         ]
 
     def kernel_modules(self, dtype):
-        return ["gemm_simt"] + (["gemm_tc"] if dtype == torch.bfloat16 else [])
+        return ["gemm_simt", "gemv"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def forward(self, h, batch, residual, rt, row_scale=None) -> None:
         T = h.shape[0]
@@ -66,6 +66,7 @@ class SparseMoe(FeedForward):
         self.shared = (DenseMlp(prefix + ".shared_expert", hidden=hidden, intermediate=self.Is)
                        if self.Is > 0 else None)
         self._layout = None
+        self._scratch = None
         # telemetry hook: called with (prefix, ids [T, k], weights [T, k]) after routing; the
         # reference counts expert hits per layer the same way (src/locus/model/moe_stats.cpp:23-78)
         self.observer = None
@@ -97,12 +98,16 @@ class SparseMoe(FeedForward):
         return out
 
     def kernel_modules(self, dtype):
-        return ["gemm_simt", "moe_route", "elementwise"] + (["gemm_tc"] if dtype == torch.bfloat16 else [])
+        return ["gemm_simt", "gemv", "moe_route", "elementwise"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])
 
     def bind(self, rt) -> None:
         self._layout = rt.shared_object(
             ("expert_layout", self.E, self.k),
             lambda: K.ExpertLayout(rt.max_tokens * self.k, self.E, 64, rt.device),
+        )
+        self._scratch = rt.shared_object(
+            ("router_scratch", self.E + 1),
+            lambda: K.RouterScratch(rt.max_tokens, self.E + 1, rt.device),
         )
 
     def forward(self, h, batch, residual, rt) -> None:
@@ -112,15 +117,23 @@ class SparseMoe(FeedForward):
         wts = rt.buf("moe.wts", (rt.max_tokens * self.k,), torch.float32)
         gamma = rt.buf("moe.gamma", (rt.max_tokens,), torch.float32) if self.shared_gate else None
         K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,
-                      top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale)
+                      top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale, scratch=self._scratch)
         if self.observer is not None:
             self.observer(self.prefix, ids[:n_pairs].view(T, self.k), wts[:n_pairs].view(T, self.k))
         lay = self._layout
         act = rt.rows(f"moe.act{self.I}", self.I, rt.dtype, n_pairs, per_token=self.k)
-        if (K.tensor_cores_take(h, self.params["gate_exps"]) and self.I % 8 == 0
-                and self.params["down_exps"].dtype == torch.bfloat16):
-            # tensor cores: TMA reads whole row ranges, so lay the tokens out in expert order first
-            K.moe_sort(ids, n_pairs, lay, K.expert_tile(n_pairs, self.E))
+        tile = K.FEW_ROWS if T <= K.FEW_ROWS else K.expert_tile(n_pairs, self.E)
+        widths_ok = self.I % 8 == 0 and self.hidden % 8 == 0
+        all_bf16 = (K.tensor_cores_take(h, self.params["gate_exps"]) and widths_ok
+                    and self.params["down_exps"].dtype == torch.bfloat16)
+        if (all_bf16 and tile <= K.SKINNY_ROWS) or (widths_ok and tile <= K.FEW_ROWS):
+            # few rows per expert: the weight-streaming kernels gather the token rows themselves
+            K.moe_sort(ids, n_pairs, lay, tile)
+            K.linear(h, self.params["gate_exps"], act, w2=self.params["up_exps"], x_rows=lay.sorted_pair,
+                     x_row_div=self.k, layout=lay, n_rows=n_pairs)
+        elif all_bf16:
+            # tcgen05 kernel: TMA reads whole row ranges, so lay the tokens out in expert order first
+            K.moe_sort(ids, n_pairs, lay, tile)
             xs = rt.rows("moe.x_sorted", self.hidden, rt.dtype, n_pairs, per_token=self.k)
             K.gather_rows(h, lay.sorted_pair, self.k, xs, n_pairs)
             K.linear(xs, self.params["gate_exps"], act, w2=self.params["up_exps"], layout=lay, n_rows=n_pairs)

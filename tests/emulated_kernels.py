@@ -139,7 +139,7 @@ def attn_decode(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_
           scale=scale)
 
 
-def router_topk(h, w_router, w_gate, ids, wts, gamma, *, top_k, renorm, scale=1.0):
+def router_topk(h, w_router, w_gate, ids, wts, gamma, *, top_k, renorm, scale=1.0, scratch=None):
     T = h.shape[0]
     r = _f(h) @ _f(w_router).T
     p = torch.softmax(r, dim=-1)

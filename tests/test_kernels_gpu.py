@@ -416,7 +416,7 @@ def test_linear_tensor_cores_large_tiles(M, N, K_):
     assert K.tc_error() == 0
 
 
-@pytest.mark.parametrize("tile", [16, 32, 64, 128])
+@pytest.mark.parametrize("tile", [8, 16, 32, 64, 128])  # 8: the row-streaming kernel
 def test_linear_grouped_tensor_cores_every_tile(tile):
     T, E, k, H, I = 210, 7, 3, 136, 72
     dt = torch.bfloat16
@@ -445,6 +445,37 @@ def test_linear_grouped_tensor_cores_every_tile(tile):
     EK.linear(act.cpu(), wd, ref_out, layout=ref_lay, n_rows=T * k, row_scale=wts, scale_rows=ref_lay.sorted_pair)
     close(pair_out, ref_out, dt, f"grouped down, tile {tile}")
     assert K.tc_error() == 0
+
+
+@pytest.mark.parametrize("M,N,K_", [(2, 61, 2048), (8, 2048, 1408), (9, 100, 72), (17, 331, 120), (32, 6144, 2048)])
+def test_linear_skinny_rows(M, N, K_):
+    """2..32 rows of bfloat16: the weight-streaming tensor-core kernel, every epilogue."""
+    dt = torch.bfloat16
+    x, w = rnd(M, K_, dtype=dt, seed=3), rnd(N, K_, dtype=dt, seed=4, scale=0.05)
+    assert K.skinny_takes(x.to(DEV), w.to(DEV), M)
+    bias, rs = rnd(N, dtype=dt, seed=5), rnd(M, seed=6)
+    ref = torch.empty(M, N, dtype=torch.float64)
+    EK.linear(x, w, ref, bias=bias)
+    out = torch.empty(M, N, dtype=dt, device=DEV)
+    K.linear(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV))
+    close(out, ref, dt, "skinny linear + bias")
+    logits = torch.empty(M, N, device=DEV)  # float32 out, as the head and the router want it
+    K.linear(x.to(DEV), w.to(DEV), logits)
+    ref_l = torch.empty(M, N, dtype=torch.float64)
+    EK.linear(x, w, ref_l)
+    close(logits, ref_l, torch.float32, "skinny linear float32 out")
+    res0 = rnd(M, N, seed=7)
+    res = res0.clone().to(DEV)
+    K.linear(x.to(DEV), w.to(DEV), res, row_scale=rs.to(DEV), accumulate=True)
+    ref2 = res0.clone().double()
+    EK.linear(x, w, ref2, row_scale=rs, accumulate=True)
+    close(res, ref2, dt, "skinny accumulate")
+    w2 = rnd(N, K_, dtype=dt, seed=8, scale=0.05)
+    act = torch.empty(M, N, dtype=dt, device=DEV)
+    K.linear(x.to(DEV), w.to(DEV), act, w2=w2.to(DEV))
+    ref3 = torch.empty(M, N, dtype=torch.float64)
+    EK.linear(x, w, ref3, w2=w2)
+    close(act, ref3, dt, "skinny swiglu")
 
 
 def test_cuda_core_product_on_bfloat16(cuda_cores_only):
