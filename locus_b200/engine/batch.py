@@ -81,6 +81,8 @@ class StepBatch:
     n_want: int
     chunk_items: torch.Tensor # int32 [n_chunk_items, 2] (segment, first query of a 16-token tile)
     n_chunk_items: int
+    chunk_items64: torch.Tensor  # the same portions cut into 64-token tiles (tensor-core kernel)
+    n_chunk_items64: int
     decode_items: torch.Tensor  # int32 [n_decode_items] segments with one new token
     n_decode_items: int
     max_splits: int           # split count that covers the longest context (decode kernel)

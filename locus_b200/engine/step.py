@@ -59,7 +59,7 @@ class ModelRunner:
         G = len(cache.groups)
         W = cache.table_width
         items_max = max_tokens // CHUNK_TILE + max_segments + 1
-        size = (max_tokens * (2 + G) + max_segments * (5 + G * W) + self.max_wanted + 2 * items_max)
+        size = (max_tokens * (2 + G) + max_segments * (5 + G * W) + self.max_wanted + 4 * items_max)
         # two pinned staging buffers, used in turn: a buffer is rewritten only after the copy
         # that read it has finished (its event), so steps may be queued without a host sync
         on_gpu = self.device.type == "cuda"
@@ -120,6 +120,7 @@ class ModelRunner:
         positions: List[int] = []
         seg_q0, seg_qn, seg_ctx, slots_state, want_rows = [], [], [], [], []
         chunk_items: List[int] = []
+        chunk_items64: List[int] = []
         decode_items: List[int] = []
         longest = 0
         for s, e in enumerate(entries):
@@ -138,8 +139,11 @@ class ModelRunner:
             else:
                 for q in range(0, n, CHUNK_TILE):
                     chunk_items.extend((s, q))
+                for q in range(0, n, K.MMA_QUERY_TILE):
+                    chunk_items64.extend((s, q))
         T, n_seg = len(tokens), len(entries)
-        fields = [tokens, positions, seg_q0, seg_qn, seg_ctx, slots_state, want_rows, chunk_items, decode_items]
+        fields = [tokens, positions, seg_q0, seg_qn, seg_ctx, slots_state, want_rows, chunk_items, decode_items,
+                  chunk_items64]
         group_fields = []
         for g in cache.groups:
             slots: List[int] = []
@@ -185,11 +189,12 @@ class ModelRunner:
             T=T, n_seg=n_seg, tokens=dv(0), positions=dv(1), seg_q0=dv(2), seg_qn=dv(3), seg_ctx=dv(4),
             state_slots=dv(5), want_rows=dv(6), n_want=len(want_rows),
             chunk_items=dv(7).view(-1, 2), n_chunk_items=len(chunk_items) // 2,
+            chunk_items64=dv(9).view(-1, 2), n_chunk_items64=len(chunk_items64) // 2,
             decode_items=dv(8), n_decode_items=len(decode_items), max_splits=max_splits,
             host_seg_q0=seg_q0, host_seg_qn=seg_qn, host_seg_ctx=seg_ctx, host_state_slots=slots_state,
         )
         for gi, g in enumerate(cache.groups):
-            batch.groups[g.gid] = GroupBatch(block_table=dv(9 + 2 * gi + 1).view(n_seg, W), slots=dv(9 + 2 * gi),
+            batch.groups[g.gid] = GroupBatch(block_table=dv(10 + 2 * gi + 1).view(n_seg, W), slots=dv(10 + 2 * gi),
                                              page_tokens=P)
         return batch
 

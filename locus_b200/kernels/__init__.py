@@ -372,6 +372,35 @@ def attn_chunk(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0
     _check(code, "attn_chunk", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
 
+MMA_HEAD_DIMS = (16, 32, 48, 64, 96, 128)
+MMA_QUERY_TILE = 64
+
+
+def attn_chunk_mma_takes(q: torch.Tensor, head_dim: int) -> bool:
+    """Whether the tensor-core kernel of prompt portions takes this case (bfloat16, head size
+    in ``MMA_HEAD_DIMS``); otherwise :func:`attn_chunk` does it on the CUDA cores."""
+    return USE_TENSOR_CORES and q.dtype == torch.bfloat16 and head_dim in MMA_HEAD_DIMS
+
+
+def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
+                   seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
+                   items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                   page_tokens: int, window: int, scale: float) -> None:
+    """Attention of portions of prompts on the tensor cores: ``items`` [n_items, 2] =
+    (segment, first query of a 64-query tile); otherwise as :func:`attn_chunk`."""
+    _cuda_c(q, "q")
+    _cuda_c(out, "out")
+    _cuda_c(pool, "pool")
+    _i32(block_table, "block_table")
+    _i32(items, "items")
+    _need(q.dtype == pool.dtype == out.dtype == torch.bfloat16, "attn_chunk_mma: bfloat16 only")
+    code = _lib("attention_mma").locus_attn_chunk_mma(
+        _p(q), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx), _p(block_table), I(block_table.shape[1]),
+        _p(items), I(n_items), I(n_heads), I(n_kv_heads), I(head_dim), I(page_tokens), I(window), F(scale), _stream()
+    )
+    _check(code, "attn_chunk_mma", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
+
+
 DECODE_SPLIT = 256
 
 
@@ -521,4 +550,4 @@ def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tens
 
 def modules_for(dtype: torch.dtype) -> list:
     """Kernel modules that a model of element type ``dtype`` needs."""
-    return ["elementwise", "gemm_simt", "gemv", "gemm_skinny", "gemm_tc", "attention", "moe_route", "sampling"]
+    return ["elementwise", "gemm_simt", "gemv", "gemm_skinny", "gemm_tc", "attention", "attention_mma", "moe_route", "sampling"]

@@ -129,6 +129,13 @@ def attn_chunk(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_i
           scale=scale)
 
 
+def attn_chunk_mma(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_items, n_heads, n_kv_heads,
+                   head_dim, page_tokens, window, scale):
+    attn_chunk(q, pool, out, seg_q0=seg_q0, seg_qn=seg_qn, seg_ctx=seg_ctx, block_table=block_table, items=items,
+               n_items=n_items, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, page_tokens=page_tokens,
+               window=window, scale=scale)
+
+
 def attn_decode(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_items, n_heads, n_kv_heads,
                 head_dim, page_tokens, window, scale, part_o, part_ml, max_splits):
     segs = [int(items[i]) for i in range(n_items)]
@@ -249,7 +256,7 @@ def sample(logits, *, temperature, top_k, top_p, min_p, seeds, counters, out, ke
             kept_count[r] = int(keep.sum())
 
 
-_NAMES = ["embed_rows", "rmsnorm", "linear", "rope_kv_write", "attn_chunk", "attn_decode", "router_topk",
+_NAMES = ["embed_rows", "rmsnorm", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk",
           "moe_sort", "moe_combine", "gather_rows", "apply_penalties", "sample"]
 
 

@@ -243,6 +243,27 @@ def test_attn_chunk(dtype, nh, nkv, hd, P, window):
     close(out, ref, dtype, "attn_chunk")
 
 
+@pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 4, 16, 16, 0), (6, 2, 32, 16, 0), (5, 1, 48, 64, 0),
+                                                (2, 2, 64, 16, 0), (3, 1, 96, 64, 0), (4, 2, 128, 64, 0),
+                                                (4, 2, 64, 16, 20), (2, 1, 32, 64, 1), (2, 2, 128, 16, 100)])
+def test_attn_chunk_tensor_cores(nh, nkv, hd, P, window):
+    """Portions of 2 to 200 tokens at contexts that straddle the 64-key tiles and the pages."""
+    dtype = torch.bfloat16
+    segs = [(0, 5), (33, 17), (100, 2), (15, 140), (64, 64), (190, 200), (63, 1 + 64)]
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=hd + 7, n_pages=120)
+    items = []
+    for s, (c, n) in enumerate(segs):
+        items += [(s, o) for o in range(0, n, K.MMA_QUERY_TILE)]
+    items_t = torch.tensor(items, dtype=torch.int32)
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=window, scale=1 / math.sqrt(hd))
+    assert K.attn_chunk_mma_takes(q.to(DEV), hd)
+    out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    K.attn_chunk_mma(q.to(DEV), pool.to(DEV), out, items=items_t.to(DEV), n_items=len(items), **_dev(meta), **kw)
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.attn_chunk(q, pool, ref, items=items_t, n_items=len(items), **meta, **kw)
+    close(out, ref, dtype, "attn_chunk_mma")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 4, 16, 16, 0), (6, 2, 32, 64, 0), (5, 1, 48, 16, 0),
                                                 (16, 16, 128, 64, 0), (2, 1, 256, 64, 0), (4, 2, 64, 16, 300),
@@ -290,6 +311,12 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
         items = torch.tensor([[1, 0]], dtype=torch.int32)
         w2 = window - 7 if window else 0  # segment 1's last query sits at the same position as segment 0's
         K.attn_chunk(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=1, window=window, **_dev(meta), **kw)
+        if dtype == torch.bfloat16:  # the tensor-core kernel must see (or not see) the marked key as well
+            out_tc = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
+            K.attn_chunk_mma(q.to(DEV), pool.to(DEV), out_tc, items=items.to(DEV), n_items=1, window=window,
+                             **_dev(meta), **kw)
+            v = float(out_tc.float().cpu().view(T, nh, hd)[T - 1, 0, 1])
+            assert (abs(v - 7.0) < 0.1) if seen else (abs(v) < 0.5), (window, v)
         o = out.float().cpu().view(T, nh, hd)
         for row in (0, T - 1):
             v = float(o[row, 0, 1])
