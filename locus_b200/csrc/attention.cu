@@ -3,7 +3,7 @@
 //
 //   * chunk:  a tile of up to 16 consecutive new tokens of one request against every key
 //             it may see (earlier pages plus the causal triangle inside the portion);
-//   * decode: one new token of a request, its keys split into fixed ranges of 256
+//   * decode: one new token of a request, its keys split into fixed ranges of 128
 //             absolute positions, partial results merged in ascending order.
 //
 // Both read K and V through the request's block table, honour an optional window (a query
@@ -33,7 +33,7 @@ struct AttnArgs {
 
 #define CHUNK_BQ 16
 #define CHUNK_TK 32
-#define DEC_SPLIT 256
+#define DEC_SPLIT 128
 
 template <typename T>
 __device__ __forceinline__ const T* kv_row(const AttnArgs& a, const int* table, int t, int kvh,
@@ -217,13 +217,30 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
     for (int d = tid; d < hd; d += 128)
         qs[d] = to_f(static_cast<const T*>(a.q)[(static_cast<size_t>(row) * a.nh + h) * hd + d]);
-    __syncthreads();
     const int nk = k1 - k0 + 1;
+    // where each key row of the split starts (elements from the pool base), looked up once
+    // (in units of 16 elements: rows start at multiples of hd, a multiple of 16, and the pool may hold
+    // more than 2^32 elements)
+    __shared__ unsigned int krow[DEC_SPLIT];
+    for (int j = tid; j < nk; j += 128)
+        krow[j] = static_cast<unsigned int>((kv_row<T>(a, table, k0 + j, kvh, 0) - static_cast<const T*>(a.pool)) >> 4);
+    const size_t v_off = static_cast<size_t>(a.nkv) * a.page_tokens * hd;  // V row = K row + v_off
+    __syncthreads();
     float mx = -INFINITY;
     for (int j = tid; j < nk; j += 128) {
-        const T* kr = kv_row<T>(a, table, k0 + j, kvh, 0);
+        const T* kr = static_cast<const T*>(a.pool) + (static_cast<size_t>(krow[j]) << 4);
         float dot = 0.f;
-        for (int d = 0; d < hd; d += VEC) {
+        int d = 0;
+        for (; d + 4 * VEC <= hd; d += 4 * VEC) {  // four loads in flight
+            float kv[4][VEC];
+#pragma unroll
+            for (int u4 = 0; u4 < 4; ++u4) Vec<T>::load(kr + d + u4 * VEC, kv[u4]);
+#pragma unroll
+            for (int u4 = 0; u4 < 4; ++u4)
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) dot = fmaf(qs[d + u4 * VEC + u], kv[u4][u], dot);
+        }
+        for (; d < hd; d += VEC) {
             float kv[VEC];
             Vec<T>::load(kr + d, kv);
 #pragma unroll
@@ -258,10 +275,22 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
 #pragma unroll
     for (int u = 0; u < VEC; ++u) acc[u] = 0.f;
     if (g < kpp) {
-        for (int j = g; j < nk; j += kpp) {
-            const T* vr = kv_row<T>(a, table, k0 + j, kvh, 1);
+        const T* vbase = static_cast<const T*>(a.pool) + v_off + dv;
+        int j = g;
+        for (; j + 3 * kpp < nk; j += 4 * kpp) {  // four rows in flight
+            float vv[4][VEC];
+#pragma unroll
+            for (int u4 = 0; u4 < 4; ++u4) Vec<T>::load(vbase + (static_cast<size_t>(krow[j + u4 * kpp]) << 4), vv[u4]);
+#pragma unroll
+            for (int u4 = 0; u4 < 4; ++u4) {
+                const float pj = sc[j + u4 * kpp];
+#pragma unroll
+                for (int u = 0; u < VEC; ++u) acc[u] = fmaf(pj, vv[u4][u], acc[u]);
+            }
+        }
+        for (; j < nk; j += kpp) {
             float vv[VEC];
-            Vec<T>::load(vr + dv, vv);
+            Vec<T>::load(vbase + (static_cast<size_t>(krow[j]) << 4), vv);
             const float pj = sc[j];
 #pragma unroll
             for (int u = 0; u < VEC; ++u) acc[u] = fmaf(pj, vv[u], acc[u]);
@@ -351,7 +380,7 @@ extern "C" int locus_attn_chunk(const void* q, int dt, const void* pool, void* o
 
 // Scratch: part_o needs n_items * nh * max_splits * hd floats, part_ml twice
 // n_items * nh * max_splits.  max_splits must cover the longest context:
-// max_splits >= (longest position) / 256 + 1.
+// max_splits >= (longest position) / DEC_SPLIT + 1.
 extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* out,
                                  const int* seg_q0, const int* seg_qn, const int* seg_ctx,
                                  const int* block_table, int table_stride, const int* items,

@@ -39,7 +39,8 @@
 extern "C" {
 #endif
 
-// Same arguments and results as locus_attn_decode, without part_o / part_ml.
+// Same arguments and results as locus_attn_decode, without part_o / part_ml (max_splits must
+// cover the longest context: at least longest position / 128 + 1).
 // Returns 0, a cudaError_t, LOCUS_ERR_UNSUPPORTED (10001) or LOCUS_ERR_SCRATCH_TOO_SMALL.
 int locus_attn_decode_static(const void* q, int dt, const void* pool, void* out, const int* seg_q0,
                              const int* seg_qn, const int* seg_ctx, const int* block_table,

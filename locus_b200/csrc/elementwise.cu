@@ -55,9 +55,68 @@ __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void*
     }
 }
 
+// The common case (float32 in, width a multiple of 4): 16-byte loads, the row kept in registers.
+template <typename TW, typename TO>
+__global__ void __launch_bounds__(256) rmsnorm_f32_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+                                                          float eps, TO* __restrict__ out,
+                                                          const int* __restrict__ rows, int H) {
+    __shared__ float warp_part[8];
+    __shared__ float scale_s;
+    const int i = blockIdx.x;
+    const float4* src = reinterpret_cast<const float4*>(x + static_cast<size_t>(rows ? rows[i] : i) * H);
+    const int n4 = H >> 2;
+    float4 v[4];  // up to 4096 elements per row in registers; wider rows re-read
+    float ss = 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int j = threadIdx.x + u * 256;
+        if (j < n4) {
+            v[u] = src[j];
+            ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss);
+            ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
+        }
+    }
+    for (int j = threadIdx.x + 1024; j < n4; j += 256) {
+        const float4 t = src[j];
+        ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float tot = 0.f;
+        for (int k = 0; k < 8; ++k) tot += warp_part[k];
+        scale_s = 1.0f / sqrtf(tot / static_cast<float>(H) + eps);
+    }
+    __syncthreads();
+    const float scale = scale_s;
+    TO* dst = out + static_cast<size_t>(i) * H;
+    for (int j = threadIdx.x; j < n4; j += 256) {
+        const int u = j >> 8;
+        const float4 t = u < 4 ? v[u] : src[j];
+        const int c = j << 2;
+        dst[c] = from_f<TO>(t.x * scale * to_f(w[c]));
+        dst[c + 1] = from_f<TO>(t.y * scale * to_f(w[c + 1]));
+        dst[c + 2] = from_f<TO>(t.z * scale * to_f(w[c + 2]));
+        dst[c + 3] = from_f<TO>(t.w * scale * to_f(w[c + 3]));
+    }
+}
+
 extern "C" int locus_rmsnorm(const void* x, int x_dt, const void* w, int w_dt, float eps, void* out,
                              int out_dt, const int* rows, int n_rows, int H, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
+    if (x_dt == LOCUS_DT_F32 && H % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        const float* xf = static_cast<const float*>(x);
+#define NORM_LAUNCH(TW, TO)                                                                             \
+        rmsnorm_f32_kernel<TW, TO><<<n_rows, 256, 0, stream>>>(xf, static_cast<const TW*>(w), eps,          \
+                                                               static_cast<TO*>(out), rows, H)
+        if (w_dt == LOCUS_DT_BF16 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(bf16, bf16);
+        else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_F32) NORM_LAUNCH(float, float);
+        else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(float, bf16);
+        else NORM_LAUNCH(bf16, float);
+#undef NORM_LAUNCH
+        return locus_launch_status();
+    }
     rmsnorm_kernel<<<n_rows, 256, 0, stream>>>(x, x_dt, w, w_dt, eps, out, out_dt, rows, H);
     return locus_launch_status();
 }
@@ -88,13 +147,22 @@ __global__ void rope_kv_write_kernel(const TA* __restrict__ qkv, const int* __re
     const size_t page_base = static_cast<size_t>(page) * 2 * nkv * page_tokens * hd;
     // rotated part of q and k heads: one work item per (head, pair)
     const int n_rot_heads = nh + nkv;
+    // sine and cosine once per pair index, shared by all heads of the token
+    __shared__ float cs_c[256], cs_s[256];
+    if (inv_freq != nullptr) {
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float theta = pos * inv_freq[i];
+            cs_c[i] = cosf(theta);
+            cs_s[i] = sinf(theta);
+        }
+    }
+    __syncthreads();
     if (inv_freq != nullptr) {
         for (int it = threadIdx.x; it < n_rot_heads * half; it += blockDim.x) {
             const int h = it / half, i = it % half;
             const int d0 = pairing == 0 ? i : 2 * i;
             const int d1 = pairing == 0 ? i + half : 2 * i + 1;
-            const float theta = pos * inv_freq[i];
-            const float c = cosf(theta), s = sinf(theta);
+            const float c = cs_c[i], s = cs_s[i];
             const float x0 = to_f(src[h * hd + d0]);
             const float x1 = to_f(src[h * hd + d1]);
             const float y0 = x0 * c - x1 * s;
@@ -137,7 +205,7 @@ extern "C" int locus_rope_kv_write(const void* qkv, int dt, const int* positions
                                    int pairing, int page_tokens, int write_kv,
                                    cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || (pairing != 0 && pairing != 1))
+    if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || (pairing != 0 && pairing != 1) || rot_dim > 512)
         return LOCUS_ERR_UNSUPPORTED;
     if (dt == LOCUS_DT_F32) {
         rope_kv_write_kernel<float><<<T, 256, 0, stream>>>(

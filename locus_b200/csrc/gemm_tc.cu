@@ -122,7 +122,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
         : "r"(taddr));
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                const __grid_constant__ CUtensorMap map_x, TcArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -208,30 +208,48 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int row = quarter * 32 + lane;
         const long long n = static_cast<long long>(blockIdx.x) * TILE_W + row;  // output column
         const bool n_ok = n < a.N;
+        // while the MMAs run: the scale of every token row of the tile -> shared memory
+        float* scales = reinterpret_cast<float*>(smem_raw + (slot + 16 - smem_u32(smem_raw)));
+        if (a.row_scale) {
+            for (int c = threadIdx.x - 64; c < a.TN; c += 128) {
+                const int r = x_row0 + c;
+                scales[c] = c < rows_valid ? a.row_scale[a.scale_rows ? a.scale_rows[r] : r] : 0.f;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
+        }
+        const float bias = (a.bias && n_ok) ? ld_dyn(a.bias, a.bias_dt, n) : 0.f;
         mbar_wait(bar_acc, 0, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const float bias = (a.bias && n_ok) ? ld_dyn(a.bias, a.bias_dt, n) : 0.f;
         const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+        float* outf = static_cast<float*>(a.out);
         for (int c0 = 0; c0 < a.TN; c0 += 16) {
             if (c0 >= rows_valid) break;  // uniform
             uint32_t v[16], u[16];
             tmem_ld16(lane_addr + c0, v);
             if (a.dual) tmem_ld16(lane_addr + a.TN + c0, u);
+            // for an add-into epilogue, fetch the 16 old values while the accumulators arrive
+            float old[16];
+            if (a.accumulate) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const bool ok = n_ok && c0 + j < rows_valid;
+                    old[j] = ok ? outf[static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n] : 0.f;
+                }
+            }
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
                 if (c0 + j >= rows_valid || !n_ok) continue;
-                const int r = x_row0 + c0 + j;
                 float val = __uint_as_float(v[j]);
                 if (a.dual) {
                     const float g = val;
                     val = g / (1.0f + expf(-g)) * __uint_as_float(u[j]);
                 }
                 val += bias;
-                if (a.row_scale) val *= a.row_scale[a.scale_rows ? a.scale_rows[r] : r];
-                const size_t o = static_cast<size_t>(r) * a.ldo + n;
+                if (a.row_scale) val *= scales[c0 + j];
+                const size_t o = static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n;
                 if (a.accumulate) {
-                    static_cast<float*>(a.out)[o] += val;
+                    outf[o] = old[j] + val;
                 } else {
                     st_dyn(a.out, a.out_dt, o, val);
                 }
@@ -279,6 +297,10 @@ static bool make_map(CUtensorMap* map, const void* ptr, long long rows, long lon
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Shared-memory budget of the pipeline in KiB; 0 = chosen from the grid size (see below).
+static int g_budget_kb = 0;
+extern "C" void locus_gemm_tc_set_budget_kb(int kb) { g_budget_kb = kb; }
+
 static int pow2_at_least(int v) {
     int p = 32;
     while (p < v) p <<= 1;
@@ -308,8 +330,14 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     TcArgs a;
     a.M = M; a.N = N; a.K = K; a.TN = TN; a.dual = dual;
     const int stage_bytes = A_BYTES * (1 + dual) + TN * TILE_K * 2;
-    int stages = (200 * 1024) / stage_bytes;
+    const int tiles_y = tile_expert ? max_tiles : ceil_div(M, TN);
+    const long long n_blocks = static_cast<long long>(ceil_div(N, TILE_W)) * tiles_y;
+    // A grid of more than one block per SM runs two blocks per SM (the epilogue of one overlaps
+    // the MMAs of the other): half the shared memory each.  A small grid gets deep pipelines.
+    const int budget = g_budget_kb > 0 ? g_budget_kb * 1024 : (n_blocks > 160 ? 108 * 1024 : 200 * 1024);
+    int stages = budget / stage_bytes;
     if (stages > 12) stages = 12;
+    if (stages < 2) stages = 2;
     const int nkb = (K + TILE_K - 1) / TILE_K;
     if (stages > nkb) stages = nkb;
     if (stages < 1) return LOCUS_ERR_UNSUPPORTED;
@@ -319,14 +347,13 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     a.accumulate = accumulate; a.out = out; a.out_dt = out_dt; a.ldo = ldo; a.bias = bias; a.bias_dt = bias_dt;
     a.row_scale = row_scale; a.scale_rows = scale_rows; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles;
-    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 16 * stages + 16 + 1024;
+    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 16 * stages + 32 + 4 * TN + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
             return static_cast<int>(cudaGetLastError());
         attr_set = true;
     }
-    const int tiles_y = tile_expert ? max_tiles : ceil_div(M, TN);
     if (tiles_y <= 0) return 0;
     if (tiles_y > 65535) return LOCUS_ERR_UNSUPPORTED;
     dim3 grid(ceil_div(N, TILE_W), tiles_y);

@@ -191,6 +191,82 @@ extern "C" int locus_router_topk(const void* h, int x_dt, const void* wr, int w_
 }
 
 // ---------------------------------------------------------------------------
+// Selection alone, from router logits that another kernel produced (the bfloat16 path computes
+// them on the tensor cores): one warp per token.  logits [T, E (+1)] float32; column E, when
+// has_gate, is the logit of the shared-expert gate.  Same softmax, selection and weights as above.
+__global__ void __launch_bounds__(256) router_select_kernel(const float* __restrict__ logits, int ld,
+                                                            int* __restrict__ ids, float* __restrict__ wts,
+                                                            float* __restrict__ gamma, int T, int E, int k,
+                                                            int has_gate, int renorm, float scale) {
+    extern __shared__ float probs_all[];  // [warps][E]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + wid;
+    if (t >= T) return;
+    const float* lg = logits + static_cast<size_t>(t) * ld;
+    float* p = probs_all + wid * E;
+    float mx = -INFINITY;
+    for (int x = lane; x < E; x += 32) {
+        const float v = lg[x];
+        p[x] = v;
+        mx = fmaxf(mx, v);
+    }
+    if (has_gate && lane == 0) gamma[t] = 1.0f / (1.0f + expf(-lg[E]));
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int x = lane; x < E; x += 32) {
+        const float v = expf(p[x] - mx);
+        p[x] = v;
+        sum += v;
+    }
+    sum = warp_sum(sum);
+    for (int x = lane; x < E; x += 32) p[x] = p[x] / sum;
+    __syncwarp();
+    float wsum = 0.f;
+    for (int r = 0; r < k; ++r) {
+        float best = -1.f;
+        int best_e = 0x7fffffff;
+        for (int x = lane; x < E; x += 32) {
+            const float v = p[x];
+            if (v > best) {
+                best = v;
+                best_e = x;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+            if (ov > best || (ov == best && oe < best_e)) {
+                best = ov;
+                best_e = oe;
+            }
+        }
+        if (lane == 0) {
+            ids[t * k + r] = best_e;
+            wts[t * k + r] = best;
+            p[best_e] = -2.f;
+        }
+        wsum += best;
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float div = renorm ? wsum : 1.0f;
+        for (int r = 0; r < k; ++r) wts[t * k + r] = wts[t * k + r] / div * scale;
+    }
+}
+
+extern "C" int locus_router_select(const float* logits, int ld, int* ids, float* wts, float* gamma, int T, int E,
+                                   int k, int has_gate, int renorm, float scale, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || k <= 0 || k > E || ld < E + (has_gate ? 1 : 0)) return LOCUS_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * 8 * E;
+    if (smem > 48 * 1024) return LOCUS_ERR_UNSUPPORTED;
+    router_select_kernel<<<ceil_div(T, 8), 256, smem, stream>>>(logits, ld, ids, wts, gamma, T, E, k, has_gate,
+                                                                renorm, scale);
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
 // Bookkeeping.  A "pair" is p = token * k + slot.  Pairs are laid out by expert, pairs of
 // one expert in ascending p (a stable order that does not depend on thread timing):
 //   counts[e], offsets[e] (offsets[E] = n_pairs), sorted_pair[i] = p, pair_pos[p] = i,

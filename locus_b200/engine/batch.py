@@ -32,6 +32,21 @@ class Runtime:
         self.max_wanted = max_wanted
         self._bufs: Dict[Tuple, torch.Tensor] = {}
         self._objects: Dict[Tuple, object] = {}
+        # a second stream for work that does not depend on the main chain (forked and joined
+        # with events, also inside a CUDA graph capture)
+        self.side_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        self._fork_event = torch.cuda.Event() if self.side_stream is not None else None
+        self._join_event = torch.cuda.Event() if self.side_stream is not None else None
+
+    def side(self):
+        """Context in which launches go to the side stream, ordered after everything launched so
+        far on the main stream; :meth:`join` makes the main stream wait for it.  On a device
+        without streams (tests on the CPU) it is a no-op."""
+        return _SideScope(self)
+
+    def join(self) -> None:
+        if self.side_stream is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._join_event)
 
     def buf(self, key: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         k = (key, tuple(shape), dtype)
@@ -56,6 +71,34 @@ class Runtime:
 
     def bytes_held(self) -> int:
         return sum(t.numel() * t.element_size() for t in self._bufs.values())
+
+
+class _SideScope:
+    def __init__(self, rt: "Runtime") -> None:
+        self.rt = rt
+
+    def __enter__(self):
+        rt = self.rt
+        if rt.side_stream is None:
+            return self
+        from .. import kernels as K
+
+        rt._fork_event.record(torch.cuda.current_stream(rt.device))
+        rt.side_stream.wait_event(rt._fork_event)
+        self._ctx = torch.cuda.stream(rt.side_stream)
+        self._ctx.__enter__()
+        self._scope = K.stream_scope()
+        self._scope.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        rt = self.rt
+        if rt.side_stream is None:
+            return False
+        rt._join_event.record(rt.side_stream)
+        self._scope.__exit__(*exc)
+        self._ctx.__exit__(*exc)
+        return False
 
 
 @dataclass

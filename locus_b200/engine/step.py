@@ -212,11 +212,12 @@ class ModelRunner:
             key = len(entries)
             g = self._graphs.get(key)
             if g is None:
-                logits = self.model.forward(batch, self.layer_caches)  # also allocates every buffer
+                with K.stream_scope():
+                    logits = self.model.forward(batch, self.layer_caches)  # also allocates every buffer
                 self._graph_launches[key] = K.launches - before
                 torch.cuda.synchronize(self.device)
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
+                with torch.cuda.graph(g), K.stream_scope():
                     out = self.model.forward(batch, self.layer_caches)
                 self._graphs[key] = g
                 self._graph_logits[key] = out
@@ -227,7 +228,8 @@ class ModelRunner:
                 logits = self._graph_logits[key]
                 self.launch_counter += self._graph_launches[key]
         else:
-            logits = self.model.forward(batch, self.layer_caches)
+            with K.stream_scope():
+                logits = self.model.forward(batch, self.layer_caches)
             self.launch_counter += K.launches - before
         for e in entries:
             self.cache.commit(e.seq, len(e.tokens))

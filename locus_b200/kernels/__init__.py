@@ -33,16 +33,43 @@ def dtype_code(dt: torch.dtype) -> int:
         raise KernelError(f"element type {dt} is not supported by the kernels (float32, bfloat16)") from None
 
 
+_LIBS = {}
+
+
 def _lib(name: str) -> ctypes.CDLL:
-    return _build.load(name)
+    lib = _LIBS.get(name)
+    if lib is None:
+        lib = _LIBS[name] = _build.load(name)
+    return lib
 
 
 def _p(t: Optional[torch.Tensor]):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+_stream_override = None
+
+
 def _stream():
+    if _stream_override is not None:
+        return _stream_override
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class stream_scope:
+    """Within the scope every launch goes to the stream that is torch's current stream when
+    the scope is entered (looked up once instead of once per launch)."""
+
+    def __enter__(self):
+        global _stream_override
+        self._saved = _stream_override
+        _stream_override = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream) if torch.cuda.is_available() else None
+        return self
+
+    def __exit__(self, *exc):
+        global _stream_override
+        _stream_override = self._saved
+        return False
 
 
 # kernels launched through this module since import (several entry points launch two)
@@ -167,7 +194,7 @@ def few_rows_take(x: torch.Tensor, w: torch.Tensor, m: int, layout: Optional["Ex
 
 
 SKINNY_ROWS = 32      # most rows of x per tile of the weight-streaming tensor-core kernel
-SKINNY_MIN_ROWS = 2   # a single row goes to the row-streaming kernel
+SKINNY_MIN_ROWS = 1
 
 
 def skinny_takes(x: torch.Tensor, w: torch.Tensor, m: int, layout: Optional["ExpertLayout"] = None) -> bool:
@@ -401,7 +428,7 @@ def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, se
     _check(code, "attn_chunk_mma", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
 
-DECODE_SPLIT = 256
+DECODE_SPLIT = 128
 
 
 def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
@@ -471,6 +498,42 @@ def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.
         _p(ids), _p(wts), _p(gamma), I(T), I(H), I(E), I(top_k), I(1 if renorm else 0), F(scale), _stream()
     )
     _check(code, "router_topk", f"(H={H}, E={E}, k={top_k})")
+
+
+def router_logits(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor) -> None:
+    """logits[t, e] = w_all[e] . h[t] in float32 with the weight-streaming tensor-core kernel,
+    for ANY number of tokens (tiles of up to 32): one kernel, and one order of the sum, for
+    every batch shape.  bfloat16 ``h`` [T, H] and ``w_all`` [E (+1), H]; ``logits`` [T, >= E (+1)]."""
+    _cuda_c(h, "h")
+    _cuda_c(w_all, "w_all")
+    T, H = h.shape
+    n = w_all.shape[0]
+    _need(h.dtype == torch.bfloat16 and w_all.dtype == torch.bfloat16 and H % 8 == 0, "router_logits: bfloat16, H % 8 == 0")
+    _need(logits.dtype == torch.float32 and logits.shape[0] >= T and logits.shape[1] >= n and logits.stride(1) == 1,
+          "router_logits: logits must be float32 [T, >= rows of w_all]")
+    tile = 8 if T <= 8 else (16 if T <= 16 else 32)
+    code = _lib("gemm_skinny").locus_gemm_skinny(
+        _p(h), _p(w_all), None, None, I(0), _p(logits), I(0), I(0), None, None, None, I(1), I(T), I(n), I(H),
+        LL(h.stride(0)), LL(logits.stride(0)), I(tile), None, None, None, None, I(0), LL(0), _stream()
+    )
+    _check(code, "router_logits", f"(T={T}, H={H}, rows {n})")
+
+
+def router_select(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch.Tensor, wts: torch.Tensor,
+                  gamma: Optional[torch.Tensor], *, n_tokens: int, top_k: int, renorm: bool, scale: float = 1.0) -> None:
+    """Softmax over the first ``n_experts`` columns of ``logits``, top-k by repeated arg-max,
+    weights; gamma = sigmoid(column n_experts) when ``has_gate``."""
+    _need(logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1, "router_select: float32 logits")
+    _i32(ids, "ids")
+    _need(wts.dtype == torch.float32 and wts.numel() >= n_tokens * top_k and ids.numel() >= n_tokens * top_k,
+          "router_select: ids / wts too small")
+    if has_gate:
+        _need(gamma is not None and gamma.dtype == torch.float32 and gamma.numel() >= n_tokens, "router_select: gamma")
+    code = _lib("moe_route").locus_router_select(
+        _p(logits), I(logits.stride(0)), _p(ids), _p(wts), _p(gamma), I(n_tokens), I(n_experts), I(top_k),
+        I(1 if has_gate else 0), I(1 if renorm else 0), F(scale), _stream()
+    )
+    _check(code, "router_select", f"(E={n_experts}, k={top_k})")
 
 
 def moe_sort(ids: torch.Tensor, n_pairs: int, layout: ExpertLayout, tile_m: Optional[int] = None) -> None:

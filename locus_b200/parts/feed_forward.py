@@ -67,6 +67,7 @@ class SparseMoe(FeedForward):
                        if self.Is > 0 else None)
         self._layout = None
         self._scratch = None
+        self._router_all = None
         # telemetry hook: called with (prefix, ids [T, k], weights [T, k]) after routing; the
         # reference counts expert hits per layer the same way (src/locus/model/moe_stats.cpp:23-78)
         self.observer = None
@@ -109,6 +110,12 @@ class SparseMoe(FeedForward):
             ("router_scratch", self.E + 1),
             lambda: K.RouterScratch(rt.max_tokens, self.E + 1, rt.device),
         )
+        self._router_all = None
+        r, g = self.params["router"], self.params.get("shared_gate")
+        if (rt.dtype == torch.bfloat16 and r.dtype == torch.bfloat16 and self.hidden % 8 == 0
+                and (g is None or g.dtype == torch.bfloat16)):
+            # router rows and the gate row as one matrix (a copy of a few hundred KB)
+            self._router_all = torch.cat([r, g.view(1, -1)], 0).contiguous() if g is not None else r
 
     def forward(self, h, batch, residual, rt) -> None:
         T = h.shape[0]
@@ -116,10 +123,24 @@ class SparseMoe(FeedForward):
         ids = rt.buf("moe.ids", (rt.max_tokens * self.k,), torch.int32)
         wts = rt.buf("moe.wts", (rt.max_tokens * self.k,), torch.float32)
         gamma = rt.buf("moe.gamma", (rt.max_tokens,), torch.float32) if self.shared_gate else None
-        K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,
-                      top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale, scratch=self._scratch)
+        if self._router_all is not None and K.USE_TENSOR_CORES:
+            # bfloat16: router (and gate) logits on the tensor cores, one kernel for every batch shape
+            logits = self._scratch.logits.view(rt.max_tokens, self.E + 1)
+            K.router_logits(h, self._router_all, logits)
+            K.router_select(logits, self.E, self.shared_gate, ids, wts, gamma, n_tokens=T, top_k=self.k,
+                            renorm=self.norm_topk, scale=self.weight_scale)
+        else:
+            K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,
+                          top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale, scratch=self._scratch)
         if self.observer is not None:
             self.observer(self.prefix, ids[:n_pairs].view(T, self.k), wts[:n_pairs].view(T, self.k))
+        # The shared expert needs only h and gamma: for a few tokens, where no kernel fills the
+        # GPU, it runs beside the routed experts on the side stream and is joined before the combine
+        # (both add into the residual, so they must not overlap there).
+        overlap = self.shared is not None and T <= 64
+        if overlap:
+            with rt.side():
+                self.shared.forward(h, batch, residual, rt, row_scale=gamma)
         lay = self._layout
         act = rt.rows(f"moe.act{self.I}", self.I, rt.dtype, n_pairs, per_token=self.k)
         tile = K.FEW_ROWS if T <= K.FEW_ROWS else K.expert_tile(n_pairs, self.E)
@@ -144,8 +165,10 @@ class SparseMoe(FeedForward):
         pair_out = rt.rows("moe.pair_out", self.hidden, torch.float32, n_pairs, per_token=self.k)
         K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts,
                  scale_rows=lay.sorted_pair)
+        if overlap:
+            rt.join()
         K.moe_combine(residual, pair_out, lay.pair_pos, self.k)
-        if self.shared is not None:
+        if self.shared is not None and not overlap:
             self.shared.forward(h, batch, residual, rt, row_scale=gamma)
 
 

@@ -170,6 +170,32 @@ def router_topk(h, w_router, w_gate, ids, wts, gamma, *, top_k, renorm, scale=1.
         gamma[:T] = (1.0 / (1.0 + torch.exp(-z))).to(gamma.dtype)
 
 
+def router_logits(h, w_all, logits):
+    T, n = h.shape[0], w_all.shape[0]
+    logits[:T, :n] = (_f(h) @ _f(w_all).T).to(logits.dtype)
+
+
+def router_select(logits, n_experts, has_gate, ids, wts, gamma, *, n_tokens, top_k, renorm, scale=1.0):
+    p = torch.softmax(_f(logits[:n_tokens, :n_experts]), dim=-1)
+    for t in range(n_tokens):
+        picked = []
+        for _ in range(top_k):
+            best = -1
+            for e in range(n_experts):
+                if e in picked:
+                    continue
+                if best < 0 or p[t, e] > p[t, best]:
+                    best = e
+            picked.append(best)
+        wsum = sum(p[t, e] for e in picked) if renorm else 1.0
+        for j, e in enumerate(picked):
+            ids[t * top_k + j] = e
+            wts[t * top_k + j] = float(p[t, e] / wsum * scale)
+    if has_gate:
+        z = _f(logits[:n_tokens, n_experts])
+        gamma[:n_tokens] = (1.0 / (1.0 + torch.exp(-z))).to(gamma.dtype)
+
+
 def moe_sort(ids, n_pairs, layout, tile_m=None):
     if tile_m is not None:
         layout.tile_m = tile_m
@@ -256,7 +282,7 @@ def sample(logits, *, temperature, top_k, top_p, min_p, seeds, counters, out, ke
             kept_count[r] = int(keep.sum())
 
 
-_NAMES = ["embed_rows", "rmsnorm", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk",
+_NAMES = ["embed_rows", "rmsnorm", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
           "moe_sort", "moe_combine", "gather_rows", "apply_penalties", "sample"]
 
 

@@ -163,6 +163,33 @@ def test_router_topk(xdt, wdt, T, H, E, k, renorm):
     close(gamma, rg, torch.float32, "shared gate")
 
 
+@pytest.mark.parametrize("T,H,E,k,renorm", [(1, 64, 8, 2, False), (19, 200, 60, 4, False), (40, 72, 12, 3, True),
+                                            (300, 2048, 60, 4, False)])
+def test_router_on_tensor_cores(T, H, E, k, renorm):
+    """bfloat16 path: logits by the weight-streaming kernel (any number of tokens), then selection."""
+    dt = torch.bfloat16
+    h, wr, wg = rnd(T, H, dtype=dt, seed=1), rnd(E, H, dtype=dt, seed=2, scale=0.3), rnd(1, H, dtype=dt, seed=3, scale=0.3)
+    w_all = torch.cat([wr, wg], 0).to(DEV)
+    logits = torch.full((T + 3, E + 1), float("nan"), device=DEV)
+    K.router_logits(h.to(DEV), w_all, logits)
+    ref_logits = h.double() @ torch.cat([wr, wg], 0).double().T
+    close(logits[:T], ref_logits, torch.float32, "router logits")
+    ids = torch.zeros(T * k, dtype=torch.int32, device=DEV)
+    wts, gamma = torch.zeros(T * k, device=DEV), torch.zeros(T, device=DEV)
+    K.router_select(logits, E, True, ids, wts, gamma, n_tokens=T, top_k=k, renorm=renorm, scale=1.5)
+    rids, rw, rg = torch.zeros(T * k, dtype=torch.int32), torch.zeros(T * k, dtype=torch.float64), \
+        torch.zeros(T, dtype=torch.float64)
+    EK.router_topk(h, wr, wg, rids, rw, rg, top_k=k, renorm=renorm, scale=1.5)
+    assert torch.equal(ids.cpu(), rids), "picked experts (and their order) differ"
+    close(wts, rw, torch.float32, "router weights")
+    close(gamma, rg, torch.float32, "shared gate")
+    # the logits of a token do not depend on the other tokens of the batch: bit for bit
+    one = torch.full((1, E + 1), float("nan"), device=DEV)
+    for t in (0, T // 2, T - 1):
+        K.router_logits(h[t : t + 1].to(DEV), w_all, one)
+        assert torch.equal(one[0], logits[t]), f"token {t} alone differs from token {t} in the batch"
+
+
 def test_router_ties_go_to_lowest_index():
     h = torch.ones(2, 16)
     wr = torch.zeros(6, 16)

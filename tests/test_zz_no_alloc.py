@@ -62,7 +62,9 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice(dtype):
     assert hasattr(lib, "locus_attn_decode_static")
     nh, nkv, hd, P = 8, 2, 64, 16
     ctxs = [[0, 255, 256, 700], [513, 31, 1023, 300]]
-    max_splits = 4
+    from locus_b200.kernels import DECODE_SPLIT
+
+    max_splits = 1023 // DECODE_SPLIT + 1  # the longest context below is 1023
     n = 4
     scratch = (torch.empty(n * nh * max_splits * hd, device=DEV), torch.empty(2 * n * nh * max_splits, device=DEV))
     # first call on this device resolves the array's address; it is made outside any capture
