@@ -1,0 +1,154 @@
+"""Runs one kernel of the engine on synthetic inputs, for timing and for profiler captures.
+
+    python -m locus_b200.tools.kernel_bench linear --m 2048 --n 6144 --k 2048 [--dual] [--accumulate] [--iters 20]
+    python -m locus_b200.tools.kernel_bench attn_decode --batch 8 --ctx 4000 [--heads 16 --kv-heads 16 --head-dim 128]
+    python -m locus_b200.tools.kernel_bench attn_chunk --tokens 2048 --ctx 0
+
+Times with CUDA events after warm-up.  Weights rotate through enough copies that the L2
+cannot hold them (``linear``); attention reads a cache larger than the L2 at the default
+sizes.  Prints one line with microseconds per call, TFLOP/s and GB/s.  Under ``ncu`` use a
+small ``--iters`` and ``-k regex:<kernel>``.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+import sys
+
+import torch
+
+from .. import kernels as K
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def _time(fn, iters: int, graph: bool) -> float:
+    """Microseconds per call.  ``graph``: replay the calls from a CUDA graph so that the
+    host's launch cost does not hide a short kernel's time."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    if graph:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g), K.stream_scope():
+            for _ in range(iters):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = _events()
+        a.record()
+        g.replay()
+        b.record()
+    else:
+        a, b = _events()
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / iters
+
+
+def bench_linear(args) -> None:
+    dev = "cuda:0"
+    dt = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    M, N, Kd = args.m, args.n, args.k
+    wbytes = N * Kd * (2 if dt == torch.bfloat16 else 4) * (2 if args.dual else 1)
+    copies = max(1, min(40, int(400e6 // wbytes)))
+    ws = [(torch.randn(N, Kd, device=dev) * 0.02).to(dt) for _ in range(copies)]
+    w2s = [(torch.randn(N, Kd, device=dev) * 0.02).to(dt) for _ in range(copies)] if args.dual else None
+    x = torch.randn(M, Kd, device=dev).to(dt)
+    out = torch.zeros(M, N, device=dev, dtype=torch.float32 if args.accumulate else dt)
+    state = {"i": 0}
+
+    def fn():
+        i = state["i"] % copies
+        state["i"] += 1
+        K.linear(x, ws[i], out, w2=w2s[i] if args.dual else None, accumulate=args.accumulate)
+
+    us = _time(fn, args.iters, args.graph)
+    flops = 2.0 * M * N * Kd * (2 if args.dual else 1)
+    print(f"linear M={M} N={N} K={Kd} dual={int(args.dual)} accumulate={int(args.accumulate)} {args.dtype}: "
+          f"{us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s  weights {wbytes / us / 1e3:.1f} GB/s  "
+          f"(tensor-core error word {K.tc_error() if dt == torch.bfloat16 else 0})")
+
+
+def _paged(args, B: int, ctx: int, new: int):
+    dev = "cuda:0"
+    dt = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    P, nh, nkv, hd = args.page_tokens, args.heads, args.kv_heads, args.head_dim
+    per = -(-(ctx + new) // P)
+    pool = torch.randn(B * per, 2, nkv, P, hd, device=dev).to(dt)
+    table = torch.arange(B * per, dtype=torch.int32, device=dev).view(B, per).contiguous()
+    q = torch.randn(B * new, nh * hd, device=dev).to(dt)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    meta = dict(seg_q0=i32([i * new for i in range(B)]), seg_qn=i32([new] * B), seg_ctx=i32([ctx] * B), block_table=table)
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=args.window, scale=1 / math.sqrt(hd))
+    return pool, q, torch.empty_like(q), meta, kw, i32
+
+
+def bench_attn_decode(args) -> None:
+    B, ctx = args.batch, args.ctx
+    pool, q, out, meta, kw, i32 = _paged(args, B, ctx, 1)
+    ms = ctx // K.DECODE_SPLIT + 1
+    po = torch.empty(B * args.heads * ms * args.head_dim, device="cuda:0")
+    pm = torch.empty(2 * B * args.heads * ms, device="cuda:0")
+    items = i32(list(range(B)))
+
+    def fn():
+        K.attn_decode(q, pool, out, items=items, n_items=B, part_o=po, part_ml=pm, max_splits=ms, **meta, **kw)
+
+    us = _time(fn, args.iters, args.graph)
+    byts = B * (ctx + 1) * 2 * args.kv_heads * args.head_dim * pool.element_size()
+    print(f"attn_decode batch={B} ctx={ctx} heads={args.heads}/{args.kv_heads} head_dim={args.head_dim} {args.dtype}: "
+          f"{us:.1f} us/call  cache read {byts / us / 1e3:.1f} GB/s")
+
+
+def bench_attn_chunk(args) -> None:
+    T, ctx = args.tokens, args.ctx
+    pool, q, out, meta, kw, i32 = _paged(args, 1, ctx, T)
+    mma = K.attn_chunk_mma_takes(q, args.head_dim) and not args.cuda_cores
+    tile = K.MMA_QUERY_TILE if mma else 16
+    items = torch.tensor([(0, o) for o in range(0, T, tile)], dtype=torch.int32, device="cuda:0")
+
+    def fn():
+        (K.attn_chunk_mma if mma else K.attn_chunk)(q, pool, out, items=items, n_items=items.shape[0], **meta, **kw)
+
+    us = _time(fn, args.iters, args.graph)
+    flops = 4.0 * args.heads * args.head_dim * (T * ctx + T * (T + 1) / 2)
+    print(f"attn_chunk tokens={T} ctx={ctx} heads={args.heads}/{args.kv_heads} head_dim={args.head_dim} "
+          f"{'tensor cores' if mma else 'cuda cores'}: {us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="kernel_bench")
+    ap.add_argument("kernel", choices=["linear", "attn_decode", "attn_chunk"])
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--graph", action="store_true", help="time a CUDA graph of the calls")
+    ap.add_argument("--m", type=int, default=2048)
+    ap.add_argument("--n", type=int, default=2048)
+    ap.add_argument("--k", type=int, default=2048)
+    ap.add_argument("--dual", action="store_true", help="SwiGLU of two weight matrices")
+    ap.add_argument("--accumulate", action="store_true", help="add into a float32 output")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--ctx", type=int, default=4000)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=16)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--page-tokens", type=int, default=64)
+    ap.add_argument("--window", type=int, default=0)
+    ap.add_argument("--cuda-cores", action="store_true", help="attn_chunk: the CUDA-core kernel")
+    args = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("kernel_bench: no CUDA device", file=sys.stderr)
+        return 1
+    {"linear": bench_linear, "attn_decode": bench_attn_decode, "attn_chunk": bench_attn_chunk}[args.kernel](args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
