@@ -84,6 +84,7 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     const int t_hi = p0 + nq - 1;
     const int t_lo = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
     const int P = a.page_tokens;
+    const float scale_log2 = a.scale * 1.4426950408889634f;
 
     // ---- Q tile -> shared (rows past nq are zero)
     for (int i = tid; i < MQ * CH; i += 128) {
@@ -169,19 +170,36 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
                 mma16816(s[2 * jp + 1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
             }
         }
-        // ---- scale, mask, online softmax (rows g and g + 8 of the warp's 16)
+        // ---- scale, mask, online softmax (rows g and g + 8 of the warp's 16), in the base-2 domain:
+        // exp(x * scale - m) = exp2(x * scale * log2(e) - m').  The mask test runs only on tiles that
+        // can hold a masked key for one of this warp's rows (the diagonal, the window's edge, the start).
         float mx[2] = {m_run[0], m_run[1]};
+        const int p_first = p0 + warp * 16;
+        const bool need_mask = tile0 + MK - 1 > p_first || tile0 < t_lo ||
+                               (a.window > 0 && tile0 <= p_first + 15 - a.window);
+        if (need_mask) {
 #pragma unroll
-        for (int j = 0; j < MK / 8; ++j) {
+            for (int j = 0; j < MK / 8; ++j) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const int rr = i >> 1;
-                const int t = tile0 + j * 8 + qd * 2 + (i & 1);
-                const int p = pq[rr];
-                const bool ok = t <= p && t >= t_lo && (a.window == 0 || t > p - a.window);
-                const float v = ok ? s[j][i] * a.scale : -INFINITY;
-                s[j][i] = v;
-                mx[rr] = fmaxf(mx[rr], v);
+                for (int i = 0; i < 4; ++i) {
+                    const int rr = i >> 1;
+                    const int t = tile0 + j * 8 + qd * 2 + (i & 1);
+                    const int p = pq[rr];
+                    const bool ok = t <= p && t >= t_lo && (a.window == 0 || t > p - a.window);
+                    const float v = ok ? s[j][i] * scale_log2 : -INFINITY;
+                    s[j][i] = v;
+                    mx[rr] = fmaxf(mx[rr], v);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < MK / 8; ++j) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float v = s[j][i] * scale_log2;
+                    s[j][i] = v;
+                    mx[i >> 1] = fmaxf(mx[i >> 1], v);
+                }
             }
         }
         float alpha[2];
@@ -189,18 +207,18 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
         for (int rr = 0; rr < 2; ++rr) {
             mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
             mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
-            alpha[rr] = (mx[rr] == -INFINITY) ? 1.f : expf(m_run[rr] - mx[rr]);
+            alpha[rr] = (mx[rr] == -INFINITY) ? 1.f : exp2f(m_run[rr] - mx[rr]);
             m_run[rr] = mx[rr];
         }
         float sum[2] = {0.f, 0.f};
+        const float m0 = mx[0] == -INFINITY ? 0.f : mx[0], m1 = mx[1] == -INFINITY ? 0.f : mx[1];  // exp2(-inf - 0) = 0
 #pragma unroll
         for (int j = 0; j < MK / 8; ++j) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const int rr = i >> 1;
-                const float e = (mx[rr] == -INFINITY) ? 0.f : expf(s[j][i] - mx[rr]);
+                const float e = exp2f(s[j][i] - ((i >> 1) ? m1 : m0));
                 s[j][i] = e;
-                sum[rr] += e;
+                sum[i >> 1] += e;
             }
         }
 #pragma unroll

@@ -184,7 +184,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major, N = TN, M = 128
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(a.TN >> 3) << 17) |
+            // N covers only the valid token rows of this tile, rounded up to 16: a ragged last tile
+            // (or an expert with few rows) costs MMA time for its rows, not for the whole tile
+            const int n_mma = min(a.TN, (rows_valid + 15) & ~15);
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n_mma >> 3) << 17) |
                                    (static_cast<uint32_t>(TILE_W >> 4) << 24);
             for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % a.stages;
@@ -218,6 +221,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
         }
         const float bias = (a.bias && n_ok) ? ld_dyn(a.bias, a.bias_dt, n) : 0.f;
+        // Wide stores: the warp's 32 output columns x 16 token rows go through a small transpose in
+        // shared memory so that a lane writes 8 consecutive columns of one token (16 or 32 bytes).
+        // Needs rows of out that start on 16-byte boundaries and a full 32-column stripe.
+        float* stage = reinterpret_cast<float*>(smem_raw + ((slot + 16 + 4 * a.TN + 15) & ~15u) - smem_u32(smem_raw)) +
+                       (warp - 2) * (16 * 36);
+        const long long n_warp = static_cast<long long>(blockIdx.x) * TILE_W + quarter * 32;
+        const int esize = a.out_dt == LOCUS_DT_F32 ? 4 : 2;
+        const bool wide = n_warp + 32 <= a.N && (a.ldo * esize) % 16 == 0 &&
+                          (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
         mbar_wait(bar_acc, 0, 3);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -227,9 +239,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t v[16], u[16];
             tmem_ld16(lane_addr + c0, v);
             if (a.dual) tmem_ld16(lane_addr + a.TN + c0, u);
-            // for an add-into epilogue, fetch the 16 old values while the accumulators arrive
+            // narrow add-into epilogue: fetch the 16 old values while the accumulators arrive
             float old[16];
-            if (a.accumulate) {
+            if (a.accumulate && !wide) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const bool ok = n_ok && c0 + j < rows_valid;
@@ -237,21 +249,63 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
             }
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float val[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                if (c0 + j >= rows_valid || !n_ok) continue;
-                float val = __uint_as_float(v[j]);
+                float x = __uint_as_float(v[j]);
                 if (a.dual) {
-                    const float g = val;
-                    val = g / (1.0f + expf(-g)) * __uint_as_float(u[j]);
+                    const float g = x;
+                    x = g / (1.0f + expf(-g)) * __uint_as_float(u[j]);
                 }
-                val += bias;
-                if (a.row_scale) val *= scales[c0 + j];
-                const size_t o = static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n;
-                if (a.accumulate) {
-                    outf[o] = old[j] + val;
-                } else {
-                    st_dyn(a.out, a.out_dt, o, val);
+                x += bias;
+                if (a.row_scale) x *= scales[c0 + j];
+                val[j] = x;
+            }
+            if (wide) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) stage[j * 36 + lane] = val[j];
+                __syncwarp();
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int j = (lane >> 2) + 8 * half;
+                    if (c0 + j < rows_valid) {
+                        const int c = (lane & 3) * 8;
+                        const float4 lo = *reinterpret_cast<const float4*>(stage + j * 36 + c);
+                        const float4 hi = *reinterpret_cast<const float4*>(stage + j * 36 + c + 4);
+                        const size_t o = static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n_warp + c;
+                        if (a.out_dt == LOCUS_DT_F32) {
+                            float4* dst = reinterpret_cast<float4*>(outf + o);
+                            if (a.accumulate) {
+                                const float4 p0 = dst[0], p1 = dst[1];
+                                dst[0] = make_float4(p0.x + lo.x, p0.y + lo.y, p0.z + lo.z, p0.w + lo.w);
+                                dst[1] = make_float4(p1.x + hi.x, p1.y + hi.y, p1.z + hi.z, p1.w + hi.w);
+                            } else {
+                                dst[0] = lo;
+                                dst[1] = hi;
+                            }
+                        } else {
+                            __nv_bfloat162 b0 = __floats2bfloat162_rn(lo.x, lo.y), b1 = __floats2bfloat162_rn(lo.z, lo.w);
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(hi.x, hi.y), b3 = __floats2bfloat162_rn(hi.z, hi.w);
+                            uint4 pk;
+                            pk.x = *reinterpret_cast<uint32_t*>(&b0);
+                            pk.y = *reinterpret_cast<uint32_t*>(&b1);
+                            pk.z = *reinterpret_cast<uint32_t*>(&b2);
+                            pk.w = *reinterpret_cast<uint32_t*>(&b3);
+                            *reinterpret_cast<uint4*>(static_cast<bf16*>(a.out) + o) = pk;
+                        }
+                    }
+                }
+                __syncwarp();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    if (c0 + j >= rows_valid || !n_ok) continue;
+                    const size_t o = static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n;
+                    if (a.accumulate) {
+                        outf[o] = old[j] + val[j];
+                    } else {
+                        st_dyn(a.out, a.out_dt, o, val[j]);
+                    }
                 }
             }
         }
@@ -334,7 +388,7 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     const long long n_blocks = static_cast<long long>(ceil_div(N, TILE_W)) * tiles_y;
     // A grid of more than one block per SM runs two blocks per SM (the epilogue of one overlaps
     // the MMAs of the other): half the shared memory each.  A small grid gets deep pipelines.
-    const int budget = g_budget_kb > 0 ? g_budget_kb * 1024 : (n_blocks > 160 ? 108 * 1024 : 200 * 1024);
+    const int budget = g_budget_kb > 0 ? g_budget_kb * 1024 : (n_blocks > 160 ? 100 * 1024 : 200 * 1024);
     int stages = budget / stage_bytes;
     if (stages > 12) stages = 12;
     if (stages < 2) stages = 2;
@@ -347,7 +401,7 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     a.accumulate = accumulate; a.out = out; a.out_dt = out_dt; a.ldo = ldo; a.bias = bias; a.bias_dt = bias_dt;
     a.row_scale = row_scale; a.scale_rows = scale_rows; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles;
-    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 16 * stages + 32 + 4 * TN + 1024;
+    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 16 * stages + 64 + 4 * TN + 4 * 16 * 36 * 4 + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
