@@ -274,8 +274,12 @@ def main() -> int:
         eng = Engine(runner, cache, sampler, max_positions=cfg.max_position_embeddings,
                      config=SchedulerConfig(max_batch_tokens=PREFILL_TOKENS, chunk=PREFILL_TOKENS, max_running=max_b,
                                             decode_headroom=16))
-        n_prompt = ctx - (K_steps + W) - 2
-        rids = [eng.submit(torch.randint(0, V, (n_prompt,), generator=gen).tolist(), K_steps + W + 1, GREEDY, 0)
+        # Requests that finish their prompt early decode while the others still prefill; nobody may
+        # reach its length limit (or the context limit) inside the timed steps, or the batch would shrink.
+        prefill_steps = -(-(B * ctx) // PREFILL_TOKENS) + 2
+        n_new = K_steps + W + prefill_steps + 2
+        n_prompt = ctx - n_new - 1
+        rids = [eng.submit(torch.randint(0, V, (n_prompt,), generator=gen).tolist(), n_new, GREEDY, 0)
                 for _ in range(B)]
         while any(eng.get(r).n_fed < n_prompt for r in rids):
             eng.step()
@@ -288,8 +292,8 @@ def main() -> int:
             eng.step()
         torch.cuda.synchronize()
         sec = time.perf_counter() - t1
-        done = sum(len(eng.get(r).generated) for r in rids)
-        assert done >= B * (K_steps + W), "the requests did not decode through the timed steps"
+        assert all(eng.get(r).status.value == "running" and len(eng.get(r).generated) >= K_steps + W for r in rids), \
+            "a request left the batch inside the timed steps"
         e2e = {"value": B * K_steps / sec, "unit": "tokens/s",
                "h2d_bytes_per_step": (runner.stats["h2d_bytes"] - h0 + sampler.h2d_bytes - s0) / K_steps,
                "d2h_bytes_per_step": (sampler.d2h_bytes - d0) / K_steps, "ms_per_step": sec * 1e3 / K_steps}
