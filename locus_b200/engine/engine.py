@@ -114,6 +114,8 @@ class Engine:
                     if self.on_token is not None:
                         self.on_token(r, int(tok))
             self.timing["steps"] += 1
+            if self.timing["steps"] % 256 == 1 and hasattr(self.runner, "check_device_errors"):
+                self.runner.check_device_errors()  # the first step and every 256th
             self.timing["step_seconds"] += time.perf_counter() - t0
             for p in planned:
                 self.timing["decode_tokens" if p.n == 1 and p.start >= len(p.request.prompt) else "prefill_tokens"] += p.n

@@ -198,6 +198,15 @@ class ModelRunner:
                                              page_tokens=P)
         return batch
 
+    def check_device_errors(self) -> None:
+        """Raise if a kernel recorded a fault since the last check (a bounded wait of the
+        tensor-core pipeline that ran out).  Synchronises the device."""
+        if self.device.type == "cuda" and "gemm_tc" in K._LIBS:
+            code = K.tc_error()
+            if code:
+                raise RuntimeError(f"tensor-core kernel fault: a pipeline wait ran out (code {code}: "
+                                   "1 = loader, 2 = MMA issuer, 3 = epilogue); results since the last check are invalid")
+
     # ------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Run the entries' tokens; returns logits [n_wanted, vocab] (float32, on the device,
