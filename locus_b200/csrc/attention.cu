@@ -320,16 +320,36 @@ __global__ void attn_decode_merge_kernel(AttnArgs a) {
     const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
     const int s0 = t_lo / DEC_SPLIT, s1 = p / DEC_SPLIT;
     const size_t base = (static_cast<size_t>(item) * a.nh + h) * a.max_splits;
-    float M = -INFINITY;
-    for (int s = s0; s <= s1; ++s) M = fmaxf(M, a.part_ml[2 * (base + s)]);
-    float L = 0.f;
-    for (int s = s0; s <= s1; ++s)
-        L += a.part_ml[2 * (base + s) + 1] * expf(a.part_ml[2 * (base + s)] - M);
-    const float inv = 1.0f / L;
+    // weight of every split, exp(m_s - M), computed once (threads in parallel) into shared memory;
+    // the sums over splits stay in ascending order
+    extern __shared__ float wsplit[];  // [s1 - s0 + 1]
+    __shared__ float M_sh, inv_sh;
+    const int ns = s1 - s0 + 1;
+    float mloc = -INFINITY;
+    for (int i = threadIdx.x; i < ns; i += blockDim.x) mloc = fmaxf(mloc, a.part_ml[2 * (base + s0 + i)]);
+    mloc = warp_max(mloc);
+    __shared__ float wm[8];
+    if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = mloc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float M = wm[0];
+        for (int w = 1; w < static_cast<int>((blockDim.x + 31) >> 5); ++w) M = fmaxf(M, wm[w]);
+        M_sh = M;
+    }
+    __syncthreads();
+    const float M = M_sh;
+    for (int i = threadIdx.x; i < ns; i += blockDim.x) wsplit[i] = expf(a.part_ml[2 * (base + s0 + i)] - M);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float L = 0.f;
+        for (int i = 0; i < ns; ++i) L += a.part_ml[2 * (base + s0 + i) + 1] * wsplit[i];
+        inv_sh = 1.0f / L;
+    }
+    __syncthreads();
+    const float inv = inv_sh;
     for (int d = threadIdx.x; d < a.hd; d += blockDim.x) {
         float o = 0.f;
-        for (int s = s0; s <= s1; ++s)
-            o += a.part_o[(base + s) * a.hd + d] * expf(a.part_ml[2 * (base + s)] - M);
+        for (int i = 0; i < ns; ++i) o += a.part_o[(base + s0 + i) * a.hd + d] * wsplit[i];
         static_cast<T*>(a.out)[(static_cast<size_t>(row) * a.nh + h) * a.hd + d] = from_f<T>(o * inv);
     }
 }
@@ -400,12 +420,12 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
         const int kpp = 128 / (hd / 4);
         const size_t smem = sizeof(float) * (hd + DEC_SPLIT + kpp * hd);
         attn_decode_split_kernel<float><<<grid, 128, smem, stream>>>(a);
-        attn_decode_merge_kernel<float><<<mgrid, mthreads, 0, stream>>>(a);
+        attn_decode_merge_kernel<float><<<mgrid, mthreads, sizeof(float) * max_splits, stream>>>(a);
     } else if (dt == LOCUS_DT_BF16) {
         const int kpp = 128 / (hd / 8);
         const size_t smem = sizeof(float) * (hd + DEC_SPLIT + kpp * hd);
         attn_decode_split_kernel<bf16><<<grid, 128, smem, stream>>>(a);
-        attn_decode_merge_kernel<bf16><<<mgrid, mthreads, 0, stream>>>(a);
+        attn_decode_merge_kernel<bf16><<<mgrid, mthreads, sizeof(float) * max_splits, stream>>>(a);
     } else {
         return LOCUS_ERR_UNSUPPORTED;
     }

@@ -199,6 +199,58 @@ __global__ void rope_kv_write_kernel(const TA* __restrict__ qkv, const int* __re
     }
 }
 
+// bfloat16, half-split pairs over the whole head: 16-byte loads and stores, eight pairs per thread.
+__global__ void __launch_bounds__(256) rope_kv_write_bf16_kernel(
+    const bf16* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+    bf16* __restrict__ q_out, bf16* __restrict__ pool, const int* __restrict__ slots, int nh, int nkv, int hd,
+    int page_tokens, int write_kv) {
+    __shared__ float cs_c[128], cs_s[128];
+    const int t = blockIdx.x;
+    const int half = hd / 2;
+    const float pos = static_cast<float>(positions[t]);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        const float theta = pos * inv_freq[i];
+        cs_c[i] = cosf(theta);
+        cs_s[i] = sinf(theta);
+    }
+    __syncthreads();
+    const bf16* src = qkv + static_cast<size_t>(t) * (nh + 2 * nkv) * hd;
+    const int slot = slots[t];
+    const int page = slot / page_tokens, off = slot % page_tokens;
+    bf16* kbase = pool + static_cast<size_t>(page) * 2 * nkv * page_tokens * hd + static_cast<size_t>(off) * hd;
+    const int cpb = half / 8;  // 16-byte chunks per half head
+    for (int it = threadIdx.x; it < (nh + nkv) * cpb; it += blockDim.x) {
+        const int h = it / cpb, i0 = (it % cpb) * 8;
+        if (h >= nh && !write_kv) continue;
+        const uint4 lo = *reinterpret_cast<const uint4*>(src + h * hd + i0);
+        const uint4 hi = *reinterpret_cast<const uint4*>(src + h * hd + half + i0);
+        const __nv_bfloat162* l2 = reinterpret_cast<const __nv_bfloat162*>(&lo);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&hi);
+        uint4 olo, ohi;
+        __nv_bfloat162* ol = reinterpret_cast<__nv_bfloat162*>(&olo);
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&ohi);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float2 x0 = __bfloat1622float2(l2[u]), x1 = __bfloat1622float2(h2[u]);
+            const float c0 = cs_c[i0 + 2 * u], s0 = cs_s[i0 + 2 * u], c1 = cs_c[i0 + 2 * u + 1], s1 = cs_s[i0 + 2 * u + 1];
+            ol[u] = __floats2bfloat162_rn(x0.x * c0 - x1.x * s0, x0.y * c1 - x1.y * s1);
+            oh[u] = __floats2bfloat162_rn(x0.x * s0 + x1.x * c0, x0.y * s1 + x1.y * c1);
+        }
+        bf16* dst = h < nh ? q_out + (static_cast<size_t>(t) * nh + h) * hd
+                           : kbase + static_cast<size_t>(h - nh) * page_tokens * hd;
+        *reinterpret_cast<uint4*>(dst + i0) = olo;
+        *reinterpret_cast<uint4*>(dst + half + i0) = ohi;
+    }
+    if (!write_kv) return;
+    const bf16* vsrc = src + static_cast<size_t>(nh + nkv) * hd;
+    bf16* vbase = kbase + static_cast<size_t>(nkv) * page_tokens * hd;
+    for (int it = threadIdx.x; it < nkv * (hd / 8); it += blockDim.x) {
+        const int h = it / (hd / 8), d = (it % (hd / 8)) * 8;
+        *reinterpret_cast<uint4*>(vbase + static_cast<size_t>(h) * page_tokens * hd + d) =
+            *reinterpret_cast<const uint4*>(vsrc + h * hd + d);
+    }
+}
+
 extern "C" int locus_rope_kv_write(const void* qkv, int dt, const int* positions,
                                    const float* inv_freq, void* q_out, void* pool,
                                    const int* slots, int T, int nh, int nkv, int hd, int rot_dim,
@@ -207,6 +259,13 @@ extern "C" int locus_rope_kv_write(const void* qkv, int dt, const int* positions
     if (T <= 0) return 0;
     if (rot_dim < 0 || rot_dim > hd || (rot_dim & 1) || (pairing != 0 && pairing != 1) || rot_dim > 512)
         return LOCUS_ERR_UNSUPPORTED;
+    if (dt == LOCUS_DT_BF16 && inv_freq != nullptr && pairing == 0 && rot_dim == hd && hd % 16 == 0 && hd <= 256 &&
+        ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pool)) & 15) == 0) {
+        rope_kv_write_bf16_kernel<<<T, 256, 0, stream>>>(
+            static_cast<const bf16*>(qkv), positions, inv_freq, static_cast<bf16*>(q_out), static_cast<bf16*>(pool),
+            slots, nh, nkv, hd, page_tokens, write_kv);
+        return locus_launch_status();
+    }
     if (dt == LOCUS_DT_F32) {
         rope_kv_write_kernel<float><<<T, 256, 0, stream>>>(
             static_cast<const float*>(qkv), positions, inv_freq, static_cast<float*>(q_out),

@@ -271,32 +271,42 @@ extern "C" int locus_router_select(const float* logits, int ld, int* ids, float*
 // one expert in ascending p (a stable order that does not depend on thread timing):
 //   counts[e], offsets[e] (offsets[E] = n_pairs), sorted_pair[i] = p, pair_pos[p] = i,
 // and a list of row tiles of tile_m rows: tile_expert[], tile_row0[], tile_rows[], *n_tiles.
-__global__ void moe_count_kernel(const int* __restrict__ ids, int n_pairs, int* __restrict__ counts) {
-    __shared__ int warp_part[32];
+__global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ ids, int n_pairs,
+                                                         int* __restrict__ counts) {
+    __shared__ int warp_part[8];
     const int e = blockIdx.x;
     int c = 0;
-    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) c += (ids[p] == e);
+    const int n4 = n_pairs >> 2;
+    const int4* ids4 = reinterpret_cast<const int4*>(ids);
+    for (int p = threadIdx.x; p < n4; p += blockDim.x) {
+        const int4 v = ids4[p];
+        c += (v.x == e) + (v.y == e) + (v.z == e) + (v.w == e);
+    }
+    for (int p = (n4 << 2) + threadIdx.x; p < n_pairs; p += blockDim.x) c += (ids[p] == e);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
     if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = c;
     __syncthreads();
     if (threadIdx.x == 0) {
         int tot = 0;
-        for (int w = 0; w < (blockDim.x >> 5); ++w) tot += warp_part[w];
+        for (int w = 0; w < 8; ++w) tot += warp_part[w];
         counts[e] = tot;
     }
 }
 
-__global__ void moe_fill_kernel(const int* __restrict__ ids, int n_pairs, int E,
-                                const int* __restrict__ counts, int tile_m,
-                                int* __restrict__ offsets, int* __restrict__ sorted_pair,
-                                int* __restrict__ pair_pos, int* __restrict__ tile_expert,
-                                int* __restrict__ tile_row0, int* __restrict__ tile_rows,
-                                int* __restrict__ n_tiles) {
-    __shared__ int s_off, s_tile, s_base;
-    __shared__ int warp_cnt[32];
+// One block per expert.  Each of the 8 warps takes a contiguous eighth of the pairs: it counts its
+// matches, the block adds the warps' counts in order, then every warp ranks its own matches with
+// ballots -- no block-wide barrier inside the loops.  Positions are ascending in p (stable).
+__global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ ids, int n_pairs, int E,
+                                                        const int* __restrict__ counts, int tile_m,
+                                                        int* __restrict__ offsets, int* __restrict__ sorted_pair,
+                                                        int* __restrict__ pair_pos, int* __restrict__ tile_expert,
+                                                        int* __restrict__ tile_row0, int* __restrict__ tile_rows,
+                                                        int* __restrict__ n_tiles) {
+    __shared__ int s_off;
+    __shared__ int warp_cnt[8];
     const int e = blockIdx.x;
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
         int off = 0, tile = 0;
         for (int j = 0; j < e; ++j) {
@@ -304,7 +314,6 @@ __global__ void moe_fill_kernel(const int* __restrict__ ids, int n_pairs, int E,
             tile += (counts[j] + tile_m - 1) / tile_m;
         }
         s_off = off;
-        s_tile = tile;
         offsets[e] = off;
         const int mine = counts[e];
         const int nt = (mine + tile_m - 1) / tile_m;
@@ -317,30 +326,27 @@ __global__ void moe_fill_kernel(const int* __restrict__ ids, int n_pairs, int E,
             offsets[E] = off + mine;
             *n_tiles = tile + nt;
         }
-        s_base = 0;
     }
+    const int per = ((n_pairs + 7) / 8 + 31) & ~31;  // pairs per warp, a multiple of 32
+    const int p_begin = wid * per, p_end = min(n_pairs, p_begin + per);
+    int c = 0;
+    for (int p = p_begin + lane; p < p_end; p += 32) c += (ids[p] == e);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+    if (lane == 0) warp_cnt[wid] = c;
     __syncthreads();
-    const int off = s_off;
-    for (int p0 = 0; p0 < n_pairs; p0 += blockDim.x) {
-        const int p = p0 + threadIdx.x;
-        const bool hit = p < n_pairs && ids[p] == e;
+    int pos = s_off;
+    for (int w = 0; w < wid; ++w) pos += warp_cnt[w];
+    for (int p0 = p_begin; p0 < p_end; p0 += 32) {
+        const int p = p0 + lane;
+        const bool hit = p < p_end && ids[p] == e;
         const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0) warp_cnt[wid] = __popc(ballot);
-        __syncthreads();
-        int before = s_base;
-        for (int w = 0; w < wid; ++w) before += warp_cnt[w];
         if (hit) {
-            const int pos = off + before + __popc(ballot & ((1u << lane) - 1u));
-            sorted_pair[pos] = p;
-            pair_pos[p] = pos;
+            const int at = pos + __popc(ballot & ((1u << lane) - 1u));
+            sorted_pair[at] = p;
+            pair_pos[p] = at;
         }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            int tot = 0;
-            for (int w = 0; w < nw; ++w) tot += warp_cnt[w];
-            s_base += tot;
-        }
-        __syncthreads();
+        pos += __popc(ballot);
     }
 }
 
