@@ -188,6 +188,7 @@ struct Vec<bf16> {
 // running maximum m and denominator l; a split outside the key range writes l = 0.
 template <typename T>
 __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
+    pdl_entry();
     extern __shared__ float smem[];
     constexpr int VEC = Vec<T>::N;
     const int hd = a.hd;
@@ -313,6 +314,7 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
 // grid (n_items, nh); merges the splits of one (request, head) in ascending order.
 template <typename T>
 __global__ void attn_decode_merge_kernel(AttnArgs a) {
+    pdl_entry();
     const int item = blockIdx.x, h = blockIdx.y;
     const int seg = a.items[item];
     const int p = a.seg_ctx[seg];
@@ -419,13 +421,13 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
     if (dt == LOCUS_DT_F32) {
         const int kpp = 128 / (hd / 4);
         const size_t smem = sizeof(float) * (hd + DEC_SPLIT + kpp * hd);
-        attn_decode_split_kernel<float><<<grid, 128, smem, stream>>>(a);
-        attn_decode_merge_kernel<float><<<mgrid, mthreads, sizeof(float) * max_splits, stream>>>(a);
+        locus_launch(attn_decode_split_kernel<float>, grid, 128, smem, stream, a);
+        locus_launch(attn_decode_merge_kernel<float>, mgrid, mthreads, sizeof(float) * max_splits, stream, a);
     } else if (dt == LOCUS_DT_BF16) {
         const int kpp = 128 / (hd / 8);
         const size_t smem = sizeof(float) * (hd + DEC_SPLIT + kpp * hd);
-        attn_decode_split_kernel<bf16><<<grid, 128, smem, stream>>>(a);
-        attn_decode_merge_kernel<bf16><<<mgrid, mthreads, sizeof(float) * max_splits, stream>>>(a);
+        locus_launch(attn_decode_split_kernel<bf16>, grid, 128, smem, stream, a);
+        locus_launch(attn_decode_merge_kernel<bf16>, mgrid, mthreads, sizeof(float) * max_splits, stream, a);
     } else {
         return LOCUS_ERR_UNSUPPORTED;
     }

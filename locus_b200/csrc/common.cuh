@@ -58,4 +58,34 @@ __device__ __forceinline__ float warp_max(float v) {
 
 static inline int locus_launch_status() { return static_cast<int>(cudaGetLastError()); }
 
+// Programmatic dependent launch.  A kernel launched with the attribute may be scheduled before the
+// kernel in front of it in the stream has drained; its blocks wait in pdl_entry() until that grid has
+// finished and its writes are visible.  No kernel here signals early (an early signal let waiting
+// blocks take SM slots from the running kernel and measured slower), so what is saved is launch
+// processing between the many short kernels of a decode step.  Launches go through locus_launch();
+// the attribute is only set while the module's switch is on (locus_set_pdl), otherwise the wait is
+// a no-op and the launch an ordinary one.
+static int g_locus_pdl = 0;
+extern "C" void locus_set_pdl(int on) { g_locus_pdl = on; }
+
+__device__ __forceinline__ void pdl_entry() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+static inline void locus_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_locus_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

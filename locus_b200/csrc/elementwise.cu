@@ -7,6 +7,7 @@
 // Embedding: out[t, :] = table[tokens[t], :] as float32 (the residual stream is float32).
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const void* __restrict__ table,
                                   int table_dt, float* __restrict__ out, int H) {
+    pdl_entry();
     const int t = blockIdx.x;
     const size_t row = static_cast<size_t>(tokens[t]) * H;
     float* o = out + static_cast<size_t>(t) * H;
@@ -16,7 +17,7 @@ __global__ void embed_rows_kernel(const int* __restrict__ tokens, const void* __
 extern "C" int locus_embed_rows(const int* tokens, const void* table, int table_dt, float* out,
                                 int T, int H, cudaStream_t stream) {
     if (T <= 0) return 0;
-    embed_rows_kernel<<<T, 256, 0, stream>>>(tokens, table, table_dt, out, H);
+    locus_launch(embed_rows_kernel, T, 256, 0, stream, tokens, table, table_dt, out, H);
     return locus_launch_status();
 }
 
@@ -60,6 +61,7 @@ template <typename TW, typename TO>
 __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(const float* __restrict__ x, const TW* __restrict__ w,
                                                           float eps, TO* __restrict__ out,
                                                           const int* __restrict__ rows, int H) {
+    pdl_entry();
     __shared__ float warp_part[8];
     __shared__ float scale_s;
     const int i = blockIdx.x;
@@ -108,8 +110,8 @@ extern "C" int locus_rmsnorm(const void* x, int x_dt, const void* w, int w_dt, f
     if (x_dt == LOCUS_DT_F32 && H % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
         const float* xf = static_cast<const float*>(x);
 #define NORM_LAUNCH(TW, TO)                                                                             \
-        rmsnorm_f32_kernel<TW, TO><<<n_rows, 256, 0, stream>>>(xf, static_cast<const TW*>(w), eps,          \
-                                                               static_cast<TO*>(out), rows, H)
+        locus_launch(rmsnorm_f32_kernel<TW, TO>, n_rows, 256, 0, stream, xf, static_cast<const TW*>(w), eps,      \
+                     static_cast<TO*>(out), rows, H)
         if (w_dt == LOCUS_DT_BF16 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(bf16, bf16);
         else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_F32) NORM_LAUNCH(float, float);
         else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(float, bf16);
@@ -204,6 +206,7 @@ __global__ void __launch_bounds__(256) rope_kv_write_bf16_kernel(
     const bf16* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
     bf16* __restrict__ q_out, bf16* __restrict__ pool, const int* __restrict__ slots, int nh, int nkv, int hd,
     int page_tokens, int write_kv) {
+    pdl_entry();
     __shared__ float cs_c[128], cs_s[128];
     const int t = blockIdx.x;
     const int half = hd / 2;
@@ -261,9 +264,8 @@ extern "C" int locus_rope_kv_write(const void* qkv, int dt, const int* positions
         return LOCUS_ERR_UNSUPPORTED;
     if (dt == LOCUS_DT_BF16 && inv_freq != nullptr && pairing == 0 && rot_dim == hd && hd % 16 == 0 && hd <= 256 &&
         ((reinterpret_cast<uintptr_t>(qkv) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(pool)) & 15) == 0) {
-        rope_kv_write_bf16_kernel<<<T, 256, 0, stream>>>(
-            static_cast<const bf16*>(qkv), positions, inv_freq, static_cast<bf16*>(q_out), static_cast<bf16*>(pool),
-            slots, nh, nkv, hd, page_tokens, write_kv);
+        locus_launch(rope_kv_write_bf16_kernel, T, 256, 0, stream, static_cast<const bf16*>(qkv), positions, inv_freq,
+                     static_cast<bf16*>(q_out), static_cast<bf16*>(pool), slots, nh, nkv, hd, page_tokens, write_kv);
         return locus_launch_status();
     }
     if (dt == LOCUS_DT_F32) {
@@ -286,6 +288,7 @@ extern "C" int locus_rope_kv_write(const void* qkv, int dt, const int* positions
 // pair_out.  No atomics: the sum order is the selection order, for every batch.
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ pair_out,
                                    const int* __restrict__ pair_pos, int k, int H) {
+    pdl_entry();
     const int t = blockIdx.x;
     for (int j = threadIdx.x; j < H; j += blockDim.x) {
         float acc = 0.f;
@@ -299,7 +302,7 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restric
 extern "C" int locus_moe_combine(float* x, const float* pair_out, const int* pair_pos, int T,
                                  int k, int H, cudaStream_t stream) {
     if (T <= 0) return 0;
-    moe_combine_kernel<<<T, 256, 0, stream>>>(x, pair_out, pair_pos, k, H);
+    locus_launch(moe_combine_kernel, T, 256, 0, stream, x, pair_out, pair_pos, k, H);
     return locus_launch_status();
 }
 

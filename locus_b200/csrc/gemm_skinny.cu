@@ -52,6 +52,7 @@ __device__ __forceinline__ uint4 ld_stream(const bf16* p) { return __ldcs(reinte
 
 template <int NT, bool DUAL>
 __global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
+    pdl_entry();
     extern __shared__ float red[];  // [SK_WARPS][(DUAL ? 2 : 1)][NT][16 * 8]
     int tok0, ntok;
     const bf16* W = a.w;
@@ -182,11 +183,11 @@ static int launch(const SkinnyArgs& a, int tiles, bool dual, cudaStream_t stream
     if (dual) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(skinny_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        skinny_kernel<NT, true><<<grid, 32 * SK_WARPS, smem, stream>>>(a);
+        locus_launch(skinny_kernel<NT, true>, grid, 32 * SK_WARPS, smem, stream, a);
     } else {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(skinny_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        skinny_kernel<NT, false><<<grid, 32 * SK_WARPS, smem, stream>>>(a);
+        locus_launch(skinny_kernel<NT, false>, grid, 32 * SK_WARPS, smem, stream, a);
     }
     return locus_launch_status();
 }

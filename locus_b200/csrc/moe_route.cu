@@ -198,6 +198,7 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
                                                             int* __restrict__ ids, float* __restrict__ wts,
                                                             float* __restrict__ gamma, int T, int E, int k,
                                                             int has_gate, int renorm, float scale) {
+    pdl_entry();
     extern __shared__ float probs_all[];  // [warps][E]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int t = blockIdx.x * (blockDim.x >> 5) + wid;
@@ -261,8 +262,8 @@ extern "C" int locus_router_select(const float* logits, int ld, int* ids, float*
     if (E <= 0 || k <= 0 || k > E || ld < E + (has_gate ? 1 : 0)) return LOCUS_ERR_UNSUPPORTED;
     const size_t smem = sizeof(float) * 8 * E;
     if (smem > 48 * 1024) return LOCUS_ERR_UNSUPPORTED;
-    router_select_kernel<<<ceil_div(T, 8), 256, smem, stream>>>(logits, ld, ids, wts, gamma, T, E, k, has_gate,
-                                                                renorm, scale);
+    locus_launch(router_select_kernel, ceil_div(T, 8), 256, smem, stream, logits, ld, ids, wts, gamma, T, E, k, has_gate,
+                 renorm, scale);
     return locus_launch_status();
 }
 
@@ -273,6 +274,7 @@ extern "C" int locus_router_select(const float* logits, int ld, int* ids, float*
 // and a list of row tiles of tile_m rows: tile_expert[], tile_row0[], tile_rows[], *n_tiles.
 __global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ ids, int n_pairs,
                                                          int* __restrict__ counts) {
+    pdl_entry();
     __shared__ int warp_part[8];
     const int e = blockIdx.x;
     int c = 0;
@@ -303,6 +305,7 @@ __global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ i
                                                         int* __restrict__ pair_pos, int* __restrict__ tile_expert,
                                                         int* __restrict__ tile_row0, int* __restrict__ tile_rows,
                                                         int* __restrict__ n_tiles) {
+    pdl_entry();
     __shared__ int s_off;
     __shared__ int warp_cnt[8];
     const int e = blockIdx.x;
@@ -355,8 +358,8 @@ extern "C" int locus_moe_sort(const int* ids, int n_pairs, int E, int tile_m, in
                               int* tile_row0, int* tile_rows, int* n_tiles, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
     if (E <= 0 || tile_m <= 0) return LOCUS_ERR_UNSUPPORTED;
-    moe_count_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, counts);
-    moe_fill_kernel<<<E, 256, 0, stream>>>(ids, n_pairs, E, counts, tile_m, offsets, sorted_pair,
-                                           pair_pos, tile_expert, tile_row0, tile_rows, n_tiles);
+    locus_launch(moe_count_kernel, E, 256, 0, stream, ids, n_pairs, counts);
+    locus_launch(moe_fill_kernel, E, 256, 0, stream, ids, n_pairs, E, counts, tile_m, offsets, sorted_pair, pair_pos,
+                 tile_expert, tile_row0, tile_rows, n_tiles);
     return locus_launch_status();
 }

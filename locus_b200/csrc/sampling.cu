@@ -99,6 +99,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
     const float* __restrict__ top_p, const float* __restrict__ min_p,
     const u64* __restrict__ seeds, const u64* __restrict__ counters, int* __restrict__ out_token,
     int* __restrict__ kept_count) {
+    pdl_entry();
     __shared__ u64 scratch[SAMPLE_THREADS / 32];
     __shared__ u64 hist[256];
     __shared__ float wmax[32];
@@ -304,8 +305,7 @@ extern "C" int locus_sample(const float* logits, long long row_stride, int R, in
                             int* out_token, int* kept_count, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return LOCUS_ERR_UNSUPPORTED;
-    sample_kernel<<<R, SAMPLE_THREADS, 0, stream>>>(logits, row_stride, V, temperature, top_k,
-                                                    top_p, min_p, seeds, counters, out_token,
-                                                    kept_count);
+    locus_launch(sample_kernel, R, SAMPLE_THREADS, 0, stream, logits, row_stride, V, temperature, top_k, top_p, min_p,
+                 seeds, counters, out_token, kept_count);
     return locus_launch_status();
 }

@@ -226,7 +226,7 @@ class ModelRunner:
                 self._graph_launches[key] = K.launches - before
                 torch.cuda.synchronize(self.device)
                 g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g), K.stream_scope():
+                with torch.cuda.graph(g), K.stream_scope(), K.pdl_scope():
                     out = self.model.forward(batch, self.layer_caches)
                 self._graphs[key] = g
                 self._graph_logits[key] = out

@@ -56,6 +56,24 @@ def _stream():
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class pdl_scope:
+    """Within the scope, kernels that support it are launched with programmatic dependent
+    launch (see csrc/common.cuh): the next kernel's blocks are scheduled while the previous
+    kernel still runs.  Used for the CUDA graphs of decode steps."""
+
+    def __enter__(self):
+        for lib in _LIBS.values():
+            if hasattr(lib, "locus_set_pdl"):
+                lib.locus_set_pdl(1)
+        return self
+
+    def __exit__(self, *exc):
+        for lib in _LIBS.values():
+            if hasattr(lib, "locus_set_pdl"):
+                lib.locus_set_pdl(0)
+        return False
+
+
 class stream_scope:
     """Within the scope every launch goes to the stream that is torch's current stream when
     the scope is entered (looked up once instead of once per launch)."""
