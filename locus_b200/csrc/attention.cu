@@ -28,6 +28,7 @@ struct AttnArgs {
     // decode only
     float* part_o;            // [n_items, nh, max_splits, hd]
     float* part_ml;           // [n_items, nh, max_splits, 2]
+    int* counters;            // [n_items, nh], zero between launches
     int max_splits;
 };
 
@@ -167,12 +168,15 @@ struct Vec<float> {
         const float4 v = *reinterpret_cast<const float4*>(p);
         o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
     }
+    __device__ static void unpack(const uint4& v, float* o) {
+        o[0] = __uint_as_float(v.x); o[1] = __uint_as_float(v.y);
+        o[2] = __uint_as_float(v.z); o[3] = __uint_as_float(v.w);
+    }
 };
 template <>
 struct Vec<bf16> {
     static constexpr int N = 8;
-    __device__ static void load(const bf16* p, float* o) {
-        const uint4 v = *reinterpret_cast<const uint4*>(p);
+    __device__ static void unpack(const uint4& v, float* o) {
         const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -181,11 +185,12 @@ struct Vec<bf16> {
             o[2 * i + 1] = f.y;
         }
     }
+    __device__ static void load(const bf16* p, float* o) { unpack(*reinterpret_cast<const uint4*>(p), o); }
 };
 
 // grid (n_items, nh, max_splits); split s covers absolute key positions
 // [s * DEC_SPLIT, (s + 1) * DEC_SPLIT).  Writes unnormalised partial sums with their
-// running maximum m and denominator l; a split outside the key range writes l = 0.
+// running maximum m and denominator l, then the last block of a (request, head) merges its splits.
 template <typename T>
 __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     pdl_entry();
@@ -208,13 +213,7 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     const int k1 = min(p, (split + 1) * DEC_SPLIT - 1);  // inclusive
     const int tid = threadIdx.x;
     const size_t part = (static_cast<size_t>(item) * a.nh + h) * a.max_splits + split;
-    if (k0 > k1) {
-        if (tid == 0) {
-            a.part_ml[2 * part] = -INFINITY;
-            a.part_ml[2 * part + 1] = 0.f;
-        }
-        return;
-    }
+    if (k0 > k1) return;  // a split without keys: neither written nor read
     const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
     for (int d = tid; d < hd; d += 128)
         qs[d] = to_f(static_cast<const T*>(a.q)[(static_cast<size_t>(row) * a.nh + h) * hd + d]);
@@ -309,50 +308,325 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
         a.part_ml[2 * part] = m_sh;
         a.part_ml[2 * part + 1] = l_sh;
     }
-}
-
-// grid (n_items, nh); merges the splits of one (request, head) in ascending order.
-template <typename T>
-__global__ void attn_decode_merge_kernel(AttnArgs a) {
-    pdl_entry();
-    const int item = blockIdx.x, h = blockIdx.y;
-    const int seg = a.items[item];
-    const int p = a.seg_ctx[seg];
-    const int row = a.seg_q0[seg];
-    const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-    const int s0 = t_lo / DEC_SPLIT, s1 = p / DEC_SPLIT;
+    // The block that finishes last among the splits of this (request, head) merges them: a counter per
+    // (request, head), zero before the launch and zero again after it.  The merge adds the splits in
+    // ascending order whichever block runs it.
+    const int s0 = t_lo / DEC_SPLIT, s1 = p / DEC_SPLIT;  // the splits that hold keys: all of them count
+    __shared__ int last_sh;
+    __syncthreads();  // every thread's partial results are written ...
+    if (tid == 0) {
+        __threadfence();  // ... and visible to the other blocks before this block counts itself done
+        int* counter = a.counters + static_cast<size_t>(item) * a.nh + h;
+        const int done = atomicAdd(counter, 1);
+        last_sh = done == s1 - s0;
+        if (last_sh) *counter = 0;
+    }
+    __syncthreads();
+    if (!last_sh) return;
+    __threadfence();
     const size_t base = (static_cast<size_t>(item) * a.nh + h) * a.max_splits;
-    // weight of every split, exp(m_s - M), computed once (threads in parallel) into shared memory;
-    // the sums over splits stay in ascending order
-    extern __shared__ float wsplit[];  // [s1 - s0 + 1]
+    // weight of every split, exp(m_s - M), computed once (threads in parallel) into shared memory
+    float* wsplit = red + kpp * hd;  // [s1 - s0 + 1]
     __shared__ float M_sh, inv_sh;
     const int ns = s1 - s0 + 1;
     float mloc = -INFINITY;
-    for (int i = threadIdx.x; i < ns; i += blockDim.x) mloc = fmaxf(mloc, a.part_ml[2 * (base + s0 + i)]);
+    for (int i = tid; i < ns; i += 128) mloc = fmaxf(mloc, __ldcg(a.part_ml + 2 * (base + s0 + i)));
     mloc = warp_max(mloc);
-    __shared__ float wm[8];
-    if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = mloc;
+    if ((tid & 31) == 0) wred[tid >> 5] = mloc;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        float M = wm[0];
-        for (int w = 1; w < static_cast<int>((blockDim.x + 31) >> 5); ++w) M = fmaxf(M, wm[w]);
-        M_sh = M;
-    }
+    if (tid == 0) M_sh = fmaxf(fmaxf(wred[0], wred[1]), fmaxf(wred[2], wred[3]));
     __syncthreads();
     const float M = M_sh;
-    for (int i = threadIdx.x; i < ns; i += blockDim.x) wsplit[i] = expf(a.part_ml[2 * (base + s0 + i)] - M);
+    for (int i = tid; i < ns; i += 128) wsplit[i] = expf(__ldcg(a.part_ml + 2 * (base + s0 + i)) - M);
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (tid == 0) {
         float L = 0.f;
-        for (int i = 0; i < ns; ++i) L += a.part_ml[2 * (base + s0 + i) + 1] * wsplit[i];
+        for (int i = 0; i < ns; ++i) L += __ldcg(a.part_ml + 2 * (base + s0 + i) + 1) * wsplit[i];
         inv_sh = 1.0f / L;
     }
     __syncthreads();
     const float inv = inv_sh;
-    for (int d = threadIdx.x; d < a.hd; d += blockDim.x) {
+    for (int d = tid; d < hd; d += 128) {
         float o = 0.f;
-        for (int i = 0; i < ns; ++i) o += a.part_o[(base + s0 + i) * a.hd + d] * wsplit[i];
-        static_cast<T*>(a.out)[(static_cast<size_t>(row) * a.nh + h) * a.hd + d] = from_f<T>(o * inv);
+        for (int i = 0; i < ns; ++i) o += __ldcg(a.part_o + (base + s0 + i) * hd + d) * wsplit[i];
+        static_cast<T*>(a.out)[(static_cast<size_t>(row) * a.nh + h) * hd + d] = from_f<T>(o * inv);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Streaming decode attention: the form for head sizes whose rows are 128, 256 or 512 bytes and pages
+// that are a multiple of a chunk (8, 16 or 32 keys for those rows).
+//
+// Reading the cache is all there is to this work, so the kernel is built to keep loads in flight
+// without pause.  The unit of work is a range of keys of one (request, head), done by ONE warp with
+// no shared memory and no block barrier: LPK lanes share a key row (16 bytes each), 32 / LPK rows per
+// load instruction, eight load instructions per chunk.  While the scores of a chunk are computed its
+// V rows are already on their way, and the K rows of the next chunk are requested before the chunk's
+// softmax update and weighted sum run.  Every lane group keeps its own running maximum, denominator
+// and sum (online softmax, base 2); the groups are merged by shuffles at the end of the range.
+//
+// The grid is fixed (a few blocks per SM): every block first decides, from the batch's context
+// lengths, how long a range is, so that the ranges fill the warps of the grid in as few rounds as
+// possible (cost = rounds x (range length + a constant for the overhead of a range) + a term for the
+// merge of the longest request); warps then take
+// ranges in a fixed stride.  The warp that finishes last among the ranges of a (request, head) merges
+// them in ascending order.  The range length depends on the batch, so a request's result can differ
+// from batch to batch, in rounding only.
+#define DS_WARPS 4        // warps of a block
+#define DS_LOADS 8        // load instructions per chunk
+#define DS_OVERHEAD 64    // fixed cost of a range, in keys
+#define DS_MERGE 2        // cost of merging one more range, in keys
+#define DS_CAND 256       // candidate range lengths looked at
+#define DS_MAX_ITEMS 1024
+
+// a 16-byte load of cache data that is read once: no line of L1 is spent on it
+__device__ __forceinline__ uint4 ld_once(const uint4* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+template <typename T, int LPK>
+__global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(AttnArgs a, int n_items, int max_units) {
+    pdl_entry();
+    constexpr int VEC = 16 / sizeof(T);   // elements of a lane
+    constexpr int KPL = 32 / LPK;         // key rows of a load instruction
+    constexpr int CHUNK = DS_LOADS * KPL; // keys of a chunk
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int hd = a.hd, P = a.page_tokens;
+
+    // ---- how the batch is cut into ranges (the same result in every block) ----
+    __shared__ int s_first[DS_MAX_ITEMS];   // first key of item i, rounded down to 32
+    __shared__ int s_nkeys[DS_MAX_ITEMS];   // keys from there to the query's own position
+    __shared__ int s_pref[DS_MAX_ITEMS + 1];  // ranges of the items before i
+    __shared__ unsigned long long s_best[DS_WARPS];
+    __shared__ int s_len;
+    int longest = 0;
+    for (int i = tid; i < n_items; i += blockDim.x) {
+        const int p = a.seg_ctx[a.items[i]];
+        const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+        const int first = t_lo & ~31;
+        s_first[i] = first;
+        s_nkeys[i] = p - first + 1;
+    }
+    __syncthreads();
+    for (int i = 0; i < n_items; ++i) longest = max(longest, s_nkeys[i]);
+    const int n_warps = gridDim.x * DS_WARPS;
+    {
+        // candidates: multiples of `step` keys; a thread looks at two of them
+        const int step = 32 * ((longest + 32 * DS_CAND - 1) / (32 * DS_CAND));
+        unsigned long long best = ~0ull;
+        for (int c = tid; c < DS_CAND; c += blockDim.x) {
+            const int len = step * (c + 1);
+            if (len - step >= longest && c > 0) break;  // longer than any context: same cut as the one before
+            long long units = 0;
+            for (int i = 0; i < n_items; ++i) units += (s_nkeys[i] + len - 1) / len;
+            units *= a.nh;
+            if (units > max_units) continue;  // the scratch does not hold that many partial results
+            const long long rounds = (units + n_warps - 1) / n_warps;
+            // the merge of a (request, head) runs in one warp and grows with its number of ranges
+            const unsigned long long cost = static_cast<unsigned long long>(rounds) * (len + DS_OVERHEAD) +
+                                            DS_MERGE * static_cast<unsigned long long>((longest + len - 1) / len);
+            best = min(best, (cost << 24) | static_cast<unsigned>(c));  // ties: the shorter range
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
+        if (lane == 0) s_best[warp] = best;
+        __syncthreads();
+        if (tid == 0) {
+            unsigned long long b = s_best[0];
+            for (int w = 1; w < DS_WARPS; ++w) b = min(b, s_best[w]);
+            // nothing fits (a scratch smaller than one range per (request, head)): refused on the host
+            s_len = b == ~0ull ? 0 : step * (static_cast<int>(b & 0xffffff) + 1);
+            int acc = 0;
+            const int len = max(32, s_len);
+            for (int i = 0; i < n_items; ++i) {
+                s_pref[i] = acc;
+                acc += (s_nkeys[i] + len - 1) / len;
+            }
+            s_pref[n_items] = acc;
+        }
+        __syncthreads();
+    }
+    const int len = s_len;
+    if (len == 0) return;
+    const int n_ranges = s_pref[n_items];
+    const long long n_units = static_cast<long long>(n_ranges) * a.nh;
+
+    const int grp = lane / LPK, sub = lane % LPK;  // which row of a load, which 16 bytes of the row
+    const int d0 = sub * VEC;
+    const float qscale = a.scale * 1.4426950408889634f;  // scores in base 2
+    const int pshift = (P & (P - 1)) == 0 ? __ffs(P) - 1 : -1;  // pages of 2^k tokens: shifts instead of divisions
+    const size_t v_off = static_cast<size_t>(a.nkv) * P * hd;  // V row = K row + v_off
+    const size_t v_units = v_off / VEC;
+    const unsigned page_units = static_cast<unsigned>(2 * v_off / VEC), row_units = hd / VEC;
+
+    for (long long u = static_cast<long long>(blockIdx.x) * DS_WARPS + warp; u < n_units; u += n_warps) {
+        const int h = static_cast<int>(u % a.nh);
+        const int r = static_cast<int>(u / a.nh);  // range index over the batch
+        int item = 0;
+        while (s_pref[item + 1] <= r) ++item;  // few items: a linear search
+        const int split = r - s_pref[item];
+        const int seg = a.items[item];
+        const int p = a.seg_ctx[seg];
+        const int row = a.seg_q0[seg];
+        const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
+        const int k_begin = s_first[item] + split * len;           // a multiple of 32: chunks do not straddle pages
+        const int k_end = min(p + 1, k_begin + len);               // exclusive
+        const int kvh = h / (a.nh / a.nkv);
+        const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
+        const T* pool = static_cast<const T*>(a.pool) + static_cast<size_t>(kvh) * P * hd + d0;
+
+        float q[VEC];
+        {
+            float raw[VEC];
+            Vec<T>::load(static_cast<const T*>(a.q) + (static_cast<size_t>(row) * a.nh + h) * hd + d0, raw);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) q[i] = raw[i] * qscale;
+        }
+        float m = -INFINITY, l = 0.f, acc[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+
+        // A chunk lies inside one page (chunks start at multiples of their size, which divides the page
+        // size), so one block-table entry serves it; entries are fetched two chunks ahead.  Row starts are
+        // kept in 16-byte units from the pool's base (the host refuses pools of 64 GiB or more).
+        const uint4* pool4 = reinterpret_cast<const uint4*>(pool);
+        auto page_of = [&](int k0) -> int {
+            if (k0 >= k_end) return 0;
+            return table[pshift >= 0 ? k0 >> pshift : k0 / P];
+        };
+        auto chunk_base = [&](int k0, int page) -> unsigned {
+            const int po = pshift >= 0 ? k0 & (P - 1) : k0 % P;
+            return static_cast<unsigned>(page) * page_units + static_cast<unsigned>(po + grp) * row_units;
+        };
+        auto live = [&](int k0, int g) -> bool {
+            const int t = k0 + g * KPL + grp;
+            return t >= t_lo && t < k_end;
+        };
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
+        uint4 kreg[DS_LOADS], vreg[DS_LOADS];
+        int page_next = page_of(k_begin + CHUNK), page_next2 = page_of(k_begin + 2 * CHUNK);
+        unsigned base = chunk_base(k_begin, page_of(k_begin));
+#pragma unroll
+        for (int g = 0; g < DS_LOADS; ++g)
+            kreg[g] = live(k_begin, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+        for (int k0 = k_begin; k0 < k_end; k0 += CHUNK) {
+            // V of this chunk
+#pragma unroll
+            for (int g = 0; g < DS_LOADS; ++g)
+                vreg[g] = live(k0, g) ? ld_once(pool4 + v_units + base + g * KPL * row_units) : zero4;
+            // scores of this chunk
+            float sc[DS_LOADS];
+#pragma unroll
+            for (int g = 0; g < DS_LOADS; ++g) {
+                float kf[VEC];
+                Vec<T>::unpack(kreg[g], kf);
+                float dot = 0.f;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) dot = fmaf(q[i], kf[i], dot);
+#pragma unroll
+                for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                sc[g] = live(k0, g) ? dot : -INFINITY;
+            }
+            // K of the next chunk, and the block-table entry of the chunk after the next two
+            base = chunk_base(k0 + CHUNK, page_next);
+            page_next = page_next2;
+            page_next2 = page_of(k0 + 3 * CHUNK);
+#pragma unroll
+            for (int g = 0; g < DS_LOADS; ++g)
+                kreg[g] = live(k0 + CHUNK, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+            // running softmax of this lane group, then the weighted sum
+            float mx = m;
+#pragma unroll
+            for (int g = 0; g < DS_LOADS; ++g) mx = fmaxf(mx, sc[g]);
+            if (mx != -INFINITY) {
+                const float corr = exp2f(m - mx);  // 0 on the first live chunk
+                l *= corr;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) acc[i] *= corr;
+#pragma unroll
+                for (int g = 0; g < DS_LOADS; ++g) {
+                    const float pr = exp2f(sc[g] - mx);  // 0 for a key that is not there
+                    l += pr;
+                    float vf[VEC];
+                    Vec<T>::unpack(vreg[g], vf);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(pr, vf[i], acc[i]);
+                }
+                m = mx;
+            }
+        }
+        // merge the lane groups (ascending group order is kept by always putting the lower group first)
+#pragma unroll
+        for (int o = LPK; o < 32; o <<= 1) {
+            const float m_o = __shfl_xor_sync(0xffffffffu, m, o);
+            const float l_o = __shfl_xor_sync(0xffffffffu, l, o);
+            float acc_o[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc_o[i] = __shfl_xor_sync(0xffffffffu, acc[i], o);
+            const float mx = fmaxf(m, m_o);
+            const float wa = mx == -INFINITY ? 0.f : exp2f(m - mx), wb = mx == -INFINITY ? 0.f : exp2f(m_o - mx);
+            const bool low = (lane & o) == 0;
+            // the same expression in both lanes of a pair: (lower group) + (upper group)
+            l = low ? l * wa + l_o * wb : l_o * wb + l * wa;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] = low ? acc[i] * wa + acc_o[i] * wb : acc_o[i] * wb + acc[i] * wa;
+            m = mx;
+        }
+        if (grp == 0) {
+            float* po = a.part_o + static_cast<size_t>(u) * hd + d0;
+#pragma unroll
+            for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4*>(po + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+            if (sub == 0) {
+                a.part_ml[2 * u] = m;
+                a.part_ml[2 * u + 1] = l;
+            }
+        }
+        // the warp that finishes the last range of this (request, head) merges them
+        __syncwarp();
+        int last = 0;
+        const int n_splits = s_pref[item + 1] - s_pref[item];
+        if (lane == 0) {
+            __threadfence();
+            int* counter = a.counters + static_cast<size_t>(item) * a.nh + h;
+            last = atomicAdd(counter, 1) == n_splits - 1;
+            if (last) *counter = 0;
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (!last) continue;
+        __threadfence();
+        const long long u0 = static_cast<long long>(s_pref[item]) * a.nh + h;  // range s of this head: u0 + s * nh
+        float M = -INFINITY;
+        for (int sidx = lane; sidx < n_splits; sidx += 32) M = fmaxf(M, __ldcg(a.part_ml + 2 * (u0 + static_cast<long long>(sidx) * a.nh)));
+        M = warp_max(M);
+        float L = 0.f;  // lanes take the ranges in turn, then a fixed tree of shuffles adds the lanes
+        for (int sidx = lane; sidx < n_splits; sidx += 32) {
+            const long long us = u0 + static_cast<long long>(sidx) * a.nh;
+            L += __ldcg(a.part_ml + 2 * us + 1) * exp2f(__ldcg(a.part_ml + 2 * us) - M);
+        }
+        L = warp_sum(L);
+        const float inv = 1.0f / L;
+        for (int d = lane * 4; d < hd; d += 128) {
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 16
+            for (int sidx = 0; sidx < n_splits; ++sidx) {
+                const long long us = u0 + static_cast<long long>(sidx) * a.nh;
+                const float w = exp2f(__ldcg(a.part_ml + 2 * us) - M);
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(a.part_o + us * hd + d));
+                o.x = fmaf(v.x, w, o.x);
+                o.y = fmaf(v.y, w, o.y);
+                o.z = fmaf(v.z, w, o.z);
+                o.w = fmaf(v.w, w, o.w);
+            }
+            T* dst = static_cast<T*>(a.out) + (static_cast<size_t>(row) * a.nh + h) * hd + d;
+            dst[0] = from_f<T>(o.x * inv);
+            dst[1] = from_f<T>(o.y * inv);
+            dst[2] = from_f<T>(o.z * inv);
+            dst[3] = from_f<T>(o.w * inv);
+        }
     }
 }
 
@@ -371,7 +645,7 @@ static AttnArgs make_args(const void* q, const void* pool, void* out, const int*
     a.q = q; a.pool = pool; a.out = out; a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx;
     a.block_table = block_table; a.table_stride = table_stride; a.items = items; a.nh = nh;
     a.nkv = nkv; a.hd = hd; a.page_tokens = page_tokens; a.window = window; a.scale = scale;
-    a.part_o = nullptr; a.part_ml = nullptr; a.max_splits = 0;
+    a.part_o = nullptr; a.part_ml = nullptr; a.counters = nullptr; a.max_splits = 0;
     return a;
 }
 
@@ -400,34 +674,64 @@ extern "C" int locus_attn_chunk(const void* q, int dt, const void* pool, void* o
     return locus_launch_status();
 }
 
-// Scratch: part_o needs n_items * nh * max_splits * hd floats, part_ml twice
-// n_items * nh * max_splits.  max_splits must cover the longest context:
-// max_splits >= (longest position) / DEC_SPLIT + 1.
+// Scratch: part_o holds max_units partial results of hd floats, part_ml two floats for each, counters
+// n_items * nh ints that are zero before the call (the call leaves them zero).  The streaming kernel
+// cuts the batch into at most max_units ranges (at least n_items * nh; a few thousand more let short
+// batches fill the GPU); the kernel for other head sizes needs n_items * nh * max_splits units, where
+// max_splits must cover the longest context: max_splits >= (longest position) / DEC_SPLIT + 1.
 extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* out,
                                  const int* seg_q0, const int* seg_qn, const int* seg_ctx,
                                  const int* block_table, int table_stride, const int* items,
                                  int n_items, int nh, int nkv, int hd, int page_tokens, int window,
-                                 float scale, float* part_o, float* part_ml, int max_splits,
-                                 cudaStream_t stream) {
+                                 float scale, float* part_o, float* part_ml, int* counters, int max_splits,
+                                 long long max_units, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (int e = check_common(nh, nkv, hd, page_tokens, window)) return e;
     if (nh > 65535 || max_splits <= 0 || max_splits > 65535) return LOCUS_ERR_UNSUPPORTED;
     AttnArgs a = make_args(q, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride, items,
                            nh, nkv, hd, page_tokens, window, scale);
-    a.part_o = part_o; a.part_ml = part_ml; a.max_splits = max_splits;
+    a.part_o = part_o; a.part_ml = part_ml; a.counters = counters; a.max_splits = max_splits;
+    if (counters == nullptr) return LOCUS_ERR_UNSUPPORTED;
+    if (max_units < static_cast<long long>(n_items) * nh) return LOCUS_ERR_UNSUPPORTED;
+    // rows of 128, 256 or 512 bytes: the streaming kernel on a fixed grid
+    const int lpk = hd * (dt == LOCUS_DT_F32 ? 4 : 2) / 16;
+    const int chunk_keys = lpk > 0 ? DS_LOADS * 32 / lpk : 1;
+    if ((dt == LOCUS_DT_F32 || dt == LOCUS_DT_BF16) && (lpk == 8 || lpk == 16 || lpk == 32) && n_items <= DS_MAX_ITEMS &&
+        page_tokens % chunk_keys == 0) {
+        static int n_sm = 0;
+        if (n_sm == 0) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess ||
+                cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0) {
+                n_sm = 0;
+                return static_cast<int>(cudaGetLastError());
+            }
+        }
+        const dim3 sgrid(n_sm * 4);
+        const int units = static_cast<int>(max_units < (1 << 30) ? max_units : (1 << 30));
+        if (dt == LOCUS_DT_F32) {
+            if (lpk == 8) locus_launch(attn_decode_stream_kernel<float, 8>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
+            else if (lpk == 16) locus_launch(attn_decode_stream_kernel<float, 16>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
+            else locus_launch(attn_decode_stream_kernel<float, 32>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
+        } else {
+            if (lpk == 8) locus_launch(attn_decode_stream_kernel<bf16, 8>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
+            else if (lpk == 16) locus_launch(attn_decode_stream_kernel<bf16, 16>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
+            else locus_launch(attn_decode_stream_kernel<bf16, 32>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
+        }
+        return locus_launch_status();
+    }
+    if (max_units < static_cast<long long>(n_items) * nh * max_splits) return LOCUS_ERR_UNSUPPORTED;
     dim3 grid(n_items, nh, max_splits);
-    dim3 mgrid(n_items, nh);
-    const int mthreads = hd <= 32 ? 32 : (hd <= 64 ? 64 : 128);
     if (dt == LOCUS_DT_F32) {
         const int kpp = 128 / (hd / 4);
-        const size_t smem = sizeof(float) * (hd + DEC_SPLIT + kpp * hd);
+        const size_t smem = sizeof(float) * (hd + DEC_SPLIT + kpp * hd + max_splits);
+        if (smem > 48 * 1024) return LOCUS_ERR_UNSUPPORTED;
         locus_launch(attn_decode_split_kernel<float>, grid, 128, smem, stream, a);
-        locus_launch(attn_decode_merge_kernel<float>, mgrid, mthreads, sizeof(float) * max_splits, stream, a);
     } else if (dt == LOCUS_DT_BF16) {
         const int kpp = 128 / (hd / 8);
-        const size_t smem = sizeof(float) * (hd + DEC_SPLIT + kpp * hd);
+        const size_t smem = sizeof(float) * (hd + DEC_SPLIT + kpp * hd + max_splits);
+        if (smem > 48 * 1024) return LOCUS_ERR_UNSUPPORTED;
         locus_launch(attn_decode_split_kernel<bf16>, grid, 128, smem, stream, a);
-        locus_launch(attn_decode_merge_kernel<bf16>, mgrid, mthreads, sizeof(float) * max_splits, stream, a);
     } else {
         return LOCUS_ERR_UNSUPPORTED;
     }
@@ -443,9 +747,12 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
 // The scratch itself.  On the host this name is only a handle for cudaGetSymbolAddress; the
 // device address it stands for is looked up once per device below.
 static __device__ __align__(256) float g_attn_static_scratch[LOCUS_ATTN_STATIC_SCRATCH_FLOATS];
+// One counter per (request, head): zero when the library is loaded, and every call leaves them zero.
+static __device__ int g_attn_static_counters[LOCUS_ATTN_STATIC_COUNTERS];
 
 #define LOCUS_MAX_DEVICES 64
 static float* g_attn_static_ptr[LOCUS_MAX_DEVICES];  // device address of the array, per device
+static int* g_attn_static_cnt_ptr[LOCUS_MAX_DEVICES];
 
 extern "C" int locus_attn_decode_static(const void* q, int dt, const void* pool, void* out,
                                         const int* seg_q0, const int* seg_qn, const int* seg_ctx,
@@ -459,6 +766,8 @@ extern "C" int locus_attn_decode_static(const void* q, int dt, const void* pool,
     const long long units = static_cast<long long>(n_items) * nh * max_splits;
     const long long need = units * (hd + 2);
     if (need > LOCUS_ATTN_STATIC_SCRATCH_FLOATS) return LOCUS_ERR_SCRATCH_TOO_SMALL;
+    const long long cap = LOCUS_ATTN_STATIC_SCRATCH_FLOATS / (hd + 2);  // partial results that the array holds
+    if (static_cast<long long>(n_items) * nh > LOCUS_ATTN_STATIC_COUNTERS) return LOCUS_ERR_SCRATCH_TOO_SMALL;
     int dev = -1;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return static_cast<int>(err);
@@ -469,13 +778,18 @@ extern "C" int locus_attn_decode_static(const void* q, int dt, const void* pool,
         err = cudaGetSymbolAddress(&p, g_attn_static_scratch);
         if (err != cudaSuccess) return static_cast<int>(err);
         if (p == nullptr) return LOCUS_ERR_UNSUPPORTED;
+        void* c = nullptr;
+        err = cudaGetSymbolAddress(&c, g_attn_static_counters);
+        if (err != cudaSuccess) return static_cast<int>(err);
+        if (c == nullptr) return LOCUS_ERR_UNSUPPORTED;
+        g_attn_static_cnt_ptr[dev] = static_cast<int*>(c);
         g_attn_static_ptr[dev] = static_cast<float*>(p);
     }
     float* part_o = g_attn_static_ptr[dev];
-    float* part_ml = part_o + units * hd;  // units * hd is a multiple of 16 floats: stays aligned
-    // Nothing to clear: the split kernel writes m and l for every (item, head, split) of the
-    // grid and the sums of every split the merge kernel reads.
+    float* part_ml = part_o + cap * hd;  // hd is a multiple of 16 floats: stays aligned
+    // Nothing to clear: the kernel writes the sums, m and l of every split that it later reads,
+    // and the counters are zero between calls.
     return locus_attn_decode(q, dt, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride,
                              items, n_items, nh, nkv, hd, page_tokens, window, scale, part_o, part_ml,
-                             max_splits, stream);
+                             g_attn_static_cnt_ptr[dev], max_splits, cap, stream);
 }

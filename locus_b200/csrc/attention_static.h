@@ -10,22 +10,24 @@
 // inside the library, in a file-scope device array of fixed size.
 //
 // What it costs.  Every GPU on which the library is loaded holds
-// LOCUS_ATTN_STATIC_SCRATCH_FLOATS * 4 bytes (4 MiB) for that array until the process ends,
+// LOCUS_ATTN_STATIC_SCRATCH_FLOATS * 4 bytes (4 MiB) for that array, and 64 KiB of counters, until the process ends,
 // whether this entry point is ever called or not.
 //
-// Limit.  A call needs  n_items * n_heads * max_splits * (head_dim + 2)  floats of scratch.
-// Calls that need more than LOCUS_ATTN_STATIC_SCRATCH_FLOATS are refused with
-// LOCUS_ERR_SCRATCH_TOO_SMALL before anything is launched; use locus_attn_decode with
-// buffers of your own for those.
+// Limit.  A call needs  n_items * n_heads * max_splits * (head_dim + 2)  floats of scratch and
+// n_items * n_heads  counters.  Calls that need more than LOCUS_ATTN_STATIC_SCRATCH_FLOATS
+// floats or LOCUS_ATTN_STATIC_COUNTERS counters are refused with LOCUS_ERR_SCRATCH_TOO_SMALL
+// before anything is launched; use locus_attn_decode with buffers of your own for those.
 //
 // Rules of use.
 //  * The first call on each device looks up the array's device address
 //    (cudaGetSymbolAddress) with that device current.  Make that first call outside of any
 //    stream capture.
 //  * All calls share the one array, and it keeps whatever the last call left in it.  Nothing
-//    in it has to start at zero: a call writes every element before it reads it.  Because
-//    the array is shared, two calls whose kernels can overlap on the GPU (different streams,
-//    or different host threads) race; order them on one stream or with events.
+//    in it has to start at zero: a call writes every element before it reads it.  The
+//    counters (a second, small array) are zero when the library is loaded and every call
+//    that completes leaves them zero.  Because the arrays are shared, two calls whose
+//    kernels can overlap on the GPU (different streams, or different host threads) race;
+//    order them on one stream or with events.
 //  * It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs
 //    are the caller's.
 #pragma once
@@ -33,6 +35,7 @@
 #include <cuda_runtime.h>
 
 #define LOCUS_ATTN_STATIC_SCRATCH_FLOATS (1 << 20)
+#define LOCUS_ATTN_STATIC_COUNTERS (1 << 14)
 #define LOCUS_ERR_SCRATCH_TOO_SMALL 10002
 
 #ifdef __cplusplus

@@ -194,17 +194,12 @@ extern "C" int locus_router_topk(const void* h, int x_dt, const void* wr, int w_
 // Selection alone, from router logits that another kernel produced (the bfloat16 path computes
 // them on the tensor cores): one warp per token.  logits [T, E (+1)] float32; column E, when
 // has_gate, is the logit of the shared-expert gate.  Same softmax, selection and weights as above.
-__global__ void __launch_bounds__(256) router_select_kernel(const float* __restrict__ logits, int ld,
-                                                            int* __restrict__ ids, float* __restrict__ wts,
-                                                            float* __restrict__ gamma, int T, int E, int k,
-                                                            int has_gate, int renorm, float scale) {
-    pdl_entry();
-    extern __shared__ float probs_all[];  // [warps][E]
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int t = blockIdx.x * (blockDim.x >> 5) + wid;
-    if (t >= T) return;
-    const float* lg = logits + static_cast<size_t>(t) * ld;
-    float* p = probs_all + wid * E;
+// Softmax, selection and weights of one token by one warp.  lg: the token's logits; p: E floats of
+// shared memory of this warp; s_ids (or null): where the picks are also kept for the block.
+__device__ __forceinline__ void select_token(const float* __restrict__ lg, float* p, int t, int lane,
+                                             int* __restrict__ ids, float* __restrict__ wts,
+                                             float* __restrict__ gamma, int* s_ids, int E, int k, int has_gate,
+                                             int renorm, float scale) {
     float mx = -INFINITY;
     for (int x = lane; x < E; x += 32) {
         const float v = lg[x];
@@ -244,6 +239,7 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
         }
         if (lane == 0) {
             ids[t * k + r] = best_e;
+            if (s_ids != nullptr) s_ids[t * k + r] = best_e;
             wts[t * k + r] = best;
             p[best_e] = -2.f;
         }
@@ -254,6 +250,19 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
         const float div = renorm ? wsum : 1.0f;
         for (int r = 0; r < k; ++r) wts[t * k + r] = wts[t * k + r] / div * scale;
     }
+}
+
+__global__ void __launch_bounds__(256) router_select_kernel(const float* __restrict__ logits, int ld,
+                                                            int* __restrict__ ids, float* __restrict__ wts,
+                                                            float* __restrict__ gamma, int T, int E, int k,
+                                                            int has_gate, int renorm, float scale) {
+    pdl_entry();
+    extern __shared__ float probs_all[];  // [warps][E]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + wid;
+    if (t >= T) return;
+    select_token(logits + static_cast<size_t>(t) * ld, probs_all + wid * E, t, lane, ids, wts, gamma, nullptr, E, k,
+                 has_gate, renorm, scale);
 }
 
 extern "C" int locus_router_select(const float* logits, int ld, int* ids, float* wts, float* gamma, int T, int E,
@@ -361,5 +370,110 @@ extern "C" int locus_moe_sort(const int* ids, int n_pairs, int E, int tile_m, in
     locus_launch(moe_count_kernel, E, 256, 0, stream, ids, n_pairs, counts);
     locus_launch(moe_fill_kernel, E, 256, 0, stream, ids, n_pairs, E, counts, tile_m, offsets, sorted_pair, pair_pos,
                  tile_expert, tile_row0, tile_rows, n_tiles);
+    return locus_launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Selection and bookkeeping of a decode-sized batch in one launch: one block selects the experts of
+// every token (a warp per token, the arithmetic of router_select_kernel) and then lays the pairs out
+// by expert (the result of moe_count_kernel and moe_fill_kernel), all through shared memory.
+// Limits: n_pairs = T * k <= RS_MAX_PAIRS, E <= RS_MAX_E.
+#define RS_MAX_PAIRS 1024
+#define RS_MAX_E 512
+
+__global__ void __launch_bounds__(256) route_small_kernel(const float* __restrict__ logits, int ld,
+                                                          int* __restrict__ ids, float* __restrict__ wts,
+                                                          float* __restrict__ gamma, int T, int E, int k, int has_gate,
+                                                          int renorm, float scale, int tile_m, int* __restrict__ counts,
+                                                          int* __restrict__ offsets, int* __restrict__ sorted_pair,
+                                                          int* __restrict__ pair_pos, int* __restrict__ tile_expert,
+                                                          int* __restrict__ tile_row0, int* __restrict__ tile_rows,
+                                                          int* __restrict__ n_tiles) {
+    pdl_entry();
+    extern __shared__ float rs_smem[];  // probabilities [8][E], then the ints below
+    int* s_ids = reinterpret_cast<int*>(rs_smem + 8 * E);  // [T * k]
+    int* s_cnt = s_ids + T * k;                             // [E]
+    int* s_off = s_cnt + E;                                 // [E + 1]
+    int* s_tile = s_off + E + 1;                            // [E + 1]
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int n_pairs = T * k;
+    for (int t = wid; t < T; t += 8)
+        select_token(logits + static_cast<size_t>(t) * ld, rs_smem + wid * E, t, lane, ids, wts, gamma, s_ids, E, k,
+                     has_gate, renorm, scale);
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int c = 0;
+        for (int p = 0; p < n_pairs; ++p) c += (s_ids[p] == e);
+        s_cnt[e] = c;
+        counts[e] = c;
+    }
+    __syncthreads();
+    if (wid == 0) {
+        // exclusive prefix sums of rows and of tiles over the experts: a contiguous run of experts per lane
+        const int per = (E + 31) / 32;
+        const int e0 = min(E, lane * per), e1 = min(E, e0 + per);
+        int rows = 0, tiles = 0;
+        for (int e = e0; e < e1; ++e) {
+            rows += s_cnt[e];
+            tiles += (s_cnt[e] + tile_m - 1) / tile_m;
+        }
+        int rows_before = rows, tiles_before = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int r = __shfl_up_sync(0xffffffffu, rows_before, o);
+            const int tl = __shfl_up_sync(0xffffffffu, tiles_before, o);
+            if (lane >= o) {
+                rows_before += r;
+                tiles_before += tl;
+            }
+        }
+        rows_before -= rows;
+        tiles_before -= tiles;
+        for (int e = e0; e < e1; ++e) {
+            s_off[e] = rows_before;
+            s_tile[e] = tiles_before;
+            rows_before += s_cnt[e];
+            tiles_before += (s_cnt[e] + tile_m - 1) / tile_m;
+        }
+        if (e1 == E && e0 < E) {
+            s_off[E] = rows_before;
+            s_tile[E] = tiles_before;
+        }
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        const int off = s_off[e], mine = s_cnt[e], tile = s_tile[e];
+        offsets[e] = off;
+        if (e == E - 1) {
+            offsets[E] = s_off[E];
+            *n_tiles = s_tile[E];
+        }
+        const int nt = (mine + tile_m - 1) / tile_m;
+        for (int i = 0; i < nt; ++i) {
+            tile_expert[tile + i] = e;
+            tile_row0[tile + i] = off + i * tile_m;
+            tile_rows[tile + i] = min(tile_m, mine - i * tile_m);
+        }
+        int at = off;
+        for (int p = 0; p < n_pairs && at < off + mine; ++p) {
+            if (s_ids[p] == e) {
+                sorted_pair[at] = p;
+                pair_pos[p] = at;
+                ++at;
+            }
+        }
+    }
+}
+
+extern "C" int locus_route_small(const float* logits, int ld, int* ids, float* wts, float* gamma, int T, int E,
+                                 int k, int has_gate, int renorm, float scale, int tile_m, int* counts,
+                                 int* offsets, int* sorted_pair, int* pair_pos, int* tile_expert, int* tile_row0,
+                                 int* tile_rows, int* n_tiles, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (E <= 0 || k <= 0 || k > E || ld < E + (has_gate ? 1 : 0) || tile_m <= 0) return LOCUS_ERR_UNSUPPORTED;
+    if (E > RS_MAX_E || static_cast<long long>(T) * k > RS_MAX_PAIRS) return LOCUS_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * 8 * E + sizeof(int) * (static_cast<size_t>(T) * k + 3 * E + 2);
+    locus_launch(route_small_kernel, 1, 256, smem, stream, logits, ld, ids, wts, gamma, T, E, k, has_gate, renorm,
+                 scale, tile_m, counts, offsets, sorted_pair, pair_pos, tile_expert, tile_row0, tile_rows, n_tiles);
     return locus_launch_status();
 }

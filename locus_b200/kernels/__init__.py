@@ -92,7 +92,7 @@ class stream_scope:
 
 # kernels launched through this module since import (several entry points launch two)
 launches = 0
-_LAUNCHES_OF = {"moe_sort": 2, "attn_decode": 2}
+_LAUNCHES_OF = {"moe_sort": 2}
 
 
 def _check(code: int, what: str, detail: str = "") -> None:
@@ -449,16 +449,32 @@ def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, se
 DECODE_SPLIT = 128
 
 
+def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype, max_splits: int, device) -> int:
+    """How many partial results the scratch of :func:`attn_decode` should hold for batches of up to
+    ``max_items`` requests: for the streaming kernel (rows of 128, 256 or 512 bytes) one per
+    (request, head) plus eight rounds of the grid's warps, so that short batches can be cut finely;
+    for other head sizes one per (request, head, split)."""
+    row_bytes = head_dim * (4 if dtype == torch.float32 else 2)
+    if row_bytes in (128, 256, 512) and max_items <= 1024:
+        try:
+            n_sm = torch.cuda.get_device_properties(device).multi_processor_count
+        except Exception:  # no GPU (host tests with emulated kernels)
+            n_sm = 148
+        return max_items * n_heads + 8 * 16 * n_sm
+    return max_items * n_heads * max_splits
+
+
 def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
                 seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
                 items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
                 page_tokens: int, window: int, scale: float, part_o: torch.Tensor,
-                part_ml: torch.Tensor, max_splits: int) -> None:
+                part_ml: torch.Tensor, counters: torch.Tensor, max_splits: int) -> None:
     """Attention of single new tokens: ``items`` [n_items] = segments with one new token.
 
-    ``part_o`` (float32, n_items * n_heads * max_splits * head_dim) and ``part_ml``
-    (float32, twice n_items * n_heads * max_splits) are scratch for the split results;
-    ``max_splits`` must be at least longest_position // 256 + 1.
+    ``part_o`` (float32, units * head_dim) and ``part_ml`` (float32, 2 * units) are scratch for
+    partial results, ``units`` as :func:`decode_units` gives it (at least n_items * n_heads);
+    ``counters`` (int32, n_items * n_heads) must be zero before the call and is zero after it;
+    ``max_splits`` must be at least longest_position // DECODE_SPLIT + 1.
     """
     _cuda_c(q, "q")
     _cuda_c(out, "out")
@@ -466,15 +482,17 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
     _i32(block_table, "block_table")
     _i32(items, "items")
     _need(q.dtype == pool.dtype == out.dtype, "attn_decode: q, cache and out share one element type")
-    _need(part_o.dtype == torch.float32 and part_o.numel() >= n_items * n_heads * max_splits * head_dim,
-          "attn_decode: part_o too small")
-    _need(part_ml.dtype == torch.float32 and part_ml.numel() >= 2 * n_items * n_heads * max_splits,
-          "attn_decode: part_ml too small")
+    _need(part_o.dtype == torch.float32 and part_ml.dtype == torch.float32, "attn_decode: float32 scratch")
+    max_units = min(part_o.numel() // head_dim, part_ml.numel() // 2)
+    _need(max_units >= n_items * n_heads, "attn_decode: scratch too small")
+    _need(pool.numel() * pool.element_size() < (64 << 30), "attn_decode: a layer's cache pool of 64 GiB or more")
+    _i32(counters, "counters")
+    _need(counters.numel() >= n_items * n_heads, "attn_decode: counters too small")
     code = _lib("attention").locus_attn_decode(
         _p(q), I(dtype_code(q.dtype)), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
         _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads),
-        I(head_dim), I(page_tokens), I(window), F(scale), _p(part_o), _p(part_ml), I(max_splits),
-        _stream()
+        I(head_dim), I(page_tokens), I(window), F(scale), _p(part_o), _p(part_ml), _p(counters), I(max_splits),
+        ctypes.c_longlong(max_units), _stream()
     )
     _check(code, "attn_decode", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
@@ -568,6 +586,42 @@ def moe_sort(ids: torch.Tensor, n_pairs: int, layout: ExpertLayout, tile_m: Opti
         _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _stream()
     )
     _check(code, "moe_sort")
+
+
+ROUTE_SMALL_PAIRS = 1024  # limits of the one-launch selection + layout
+ROUTE_SMALL_EXPERTS = 512
+
+
+def route_small_takes(n_tokens: int, top_k: int, n_experts: int) -> bool:
+    """Whether ``route_small`` handles this batch (a decode-sized batch: its single block would be
+    slow for more tokens)."""
+    return n_tokens <= 16 and n_tokens * top_k <= ROUTE_SMALL_PAIRS and n_experts <= ROUTE_SMALL_EXPERTS
+
+
+def route_small(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch.Tensor, wts: torch.Tensor,
+                gamma: Optional[torch.Tensor], layout: ExpertLayout, *, n_tokens: int, top_k: int, renorm: bool,
+                scale: float = 1.0, tile_m: Optional[int] = None) -> None:
+    """``router_select`` followed by ``moe_sort`` in one launch, for batches that
+    ``route_small_takes``: same picks, weights and layout."""
+    _need(route_small_takes(n_tokens, top_k, n_experts), "route_small: batch too large")
+    _need(logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1, "route_small: float32 logits")
+    _i32(ids, "ids")
+    _need(wts.dtype == torch.float32 and wts.numel() >= n_tokens * top_k and ids.numel() >= n_tokens * top_k,
+          "route_small: ids / wts too small")
+    _need(n_tokens * top_k <= layout.sorted_pair.numel() and layout.n_experts == n_experts,
+          "route_small: layout does not fit")
+    if has_gate:
+        _need(gamma is not None and gamma.dtype == torch.float32 and gamma.numel() >= n_tokens, "route_small: gamma")
+    if tile_m is not None:
+        _need(tile_m >= layout.MIN_TILE, f"route_small: tiles of at least {layout.MIN_TILE} rows")
+        layout.tile_m = tile_m
+    code = _lib("moe_route").locus_route_small(
+        _p(logits), I(logits.stride(0)), _p(ids), _p(wts), _p(gamma), I(n_tokens), I(n_experts), I(top_k),
+        I(1 if has_gate else 0), I(1 if renorm else 0), F(scale), I(layout.tile_m), _p(layout.counts),
+        _p(layout.offsets), _p(layout.sorted_pair), _p(layout.pair_pos), _p(layout.tile_expert),
+        _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _stream()
+    )
+    _check(code, "route_small", f"(T={n_tokens}, E={n_experts}, k={top_k})")
 
 
 def moe_combine(x: torch.Tensor, pair_out: torch.Tensor, pair_pos: torch.Tensor, top_k: int) -> None:

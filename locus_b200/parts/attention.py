@@ -100,12 +100,15 @@ class Attention(Mixer):
                 K.attn_chunk(q, cache.pool, o, items=batch.chunk_items, n_items=batch.n_chunk_items, **common)
         if batch.n_decode_items:
             n = batch.n_decode_items
-            part_o = rt.buf("attention.part_o", (rt.max_segments * self.n_heads * batch.max_splits * self.head_dim,),
-                            torch.float32)
-            part_ml = rt.buf("attention.part_ml", (2 * rt.max_segments * self.n_heads * batch.max_splits,),
-                             torch.float32)
+            units = K.decode_units(rt.max_segments, self.n_heads, self.head_dim, q.dtype, batch.max_splits, rt.device)
+            part_o = rt.buf("attention.part_o", (units * self.head_dim,), torch.float32)
+            part_ml = rt.buf("attention.part_ml", (2 * units,), torch.float32)
+            counters = rt.shared_object(
+                ("attention.counters", rt.max_segments * self.n_heads),
+                lambda: torch.zeros(rt.max_segments * self.n_heads, dtype=torch.int32, device=rt.device),
+            )
             K.attn_decode(q, cache.pool, o, items=batch.decode_items, n_items=n, part_o=part_o,
-                          part_ml=part_ml, max_splits=batch.max_splits, **common)
+                          part_ml=part_ml, counters=counters, max_splits=batch.max_splits, **common)
         K.linear(o, self.params["wo"], residual, bias=self.params.get("bo"), accumulate=True)
 
 

@@ -123,12 +123,28 @@ class SparseMoe(FeedForward):
         ids = rt.buf("moe.ids", (rt.max_tokens * self.k,), torch.int32)
         wts = rt.buf("moe.wts", (rt.max_tokens * self.k,), torch.float32)
         gamma = rt.buf("moe.gamma", (rt.max_tokens,), torch.float32) if self.shared_gate else None
+        lay = self._layout
+        # which kernels the expert products run on decides the row tile of the expert layout
+        tile = K.FEW_ROWS if T <= K.FEW_ROWS else K.expert_tile(n_pairs, self.E)
+        widths_ok = self.I % 8 == 0 and self.hidden % 8 == 0
+        all_bf16 = (K.tensor_cores_take(h, self.params["gate_exps"]) and widths_ok
+                    and self.params["down_exps"].dtype == torch.bfloat16)
+        streamed = (all_bf16 and tile <= K.SKINNY_ROWS) or (widths_ok and tile <= K.FEW_ROWS)
+        if not streamed and not all_bf16:
+            tile = 64
+        sorted_already = False
         if self._router_all is not None and K.USE_TENSOR_CORES:
             # bfloat16: router (and gate) logits on the tensor cores, one kernel for every batch shape
             logits = self._scratch.logits.view(rt.max_tokens, self.E + 1)
             K.router_logits(h, self._router_all, logits)
-            K.router_select(logits, self.E, self.shared_gate, ids, wts, gamma, n_tokens=T, top_k=self.k,
-                            renorm=self.norm_topk, scale=self.weight_scale)
+            if K.route_small_takes(T, self.k, self.E):
+                # a decode-sized batch: selection and the expert layout in one launch
+                K.route_small(logits, self.E, self.shared_gate, ids, wts, gamma, lay, n_tokens=T, top_k=self.k,
+                              renorm=self.norm_topk, scale=self.weight_scale, tile_m=tile)
+                sorted_already = True
+            else:
+                K.router_select(logits, self.E, self.shared_gate, ids, wts, gamma, n_tokens=T, top_k=self.k,
+                                renorm=self.norm_topk, scale=self.weight_scale)
         else:
             K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,
                           top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale, scratch=self._scratch)
@@ -141,27 +157,18 @@ class SparseMoe(FeedForward):
         if overlap:
             with rt.side():
                 self.shared.forward(h, batch, residual, rt, row_scale=gamma)
-        lay = self._layout
         act = rt.rows(f"moe.act{self.I}", self.I, rt.dtype, n_pairs, per_token=self.k)
-        tile = K.FEW_ROWS if T <= K.FEW_ROWS else K.expert_tile(n_pairs, self.E)
-        widths_ok = self.I % 8 == 0 and self.hidden % 8 == 0
-        all_bf16 = (K.tensor_cores_take(h, self.params["gate_exps"]) and widths_ok
-                    and self.params["down_exps"].dtype == torch.bfloat16)
-        if (all_bf16 and tile <= K.SKINNY_ROWS) or (widths_ok and tile <= K.FEW_ROWS):
-            # few rows per expert: the weight-streaming kernels gather the token rows themselves
+        if not sorted_already:
             K.moe_sort(ids, n_pairs, lay, tile)
+        if streamed or not all_bf16:
+            # few rows per expert (or no tensor-core form): the kernels gather the token rows themselves
             K.linear(h, self.params["gate_exps"], act, w2=self.params["up_exps"], x_rows=lay.sorted_pair,
                      x_row_div=self.k, layout=lay, n_rows=n_pairs)
-        elif all_bf16:
+        else:
             # tcgen05 kernel: TMA reads whole row ranges, so lay the tokens out in expert order first
-            K.moe_sort(ids, n_pairs, lay, tile)
             xs = rt.rows("moe.x_sorted", self.hidden, rt.dtype, n_pairs, per_token=self.k)
             K.gather_rows(h, lay.sorted_pair, self.k, xs, n_pairs)
             K.linear(xs, self.params["gate_exps"], act, w2=self.params["up_exps"], layout=lay, n_rows=n_pairs)
-        else:
-            K.moe_sort(ids, n_pairs, lay, 64)
-            K.linear(h, self.params["gate_exps"], act, w2=self.params["up_exps"], x_rows=lay.sorted_pair,
-                     x_row_div=self.k, layout=lay, n_rows=n_pairs)
         pair_out = rt.rows("moe.pair_out", self.hidden, torch.float32, n_pairs, per_token=self.k)
         K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts,
                  scale_rows=lay.sorted_pair)

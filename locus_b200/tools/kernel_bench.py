@@ -96,9 +96,11 @@ def bench_attn_decode(args) -> None:
     po = torch.empty(B * args.heads * ms * args.head_dim, device="cuda:0")
     pm = torch.empty(2 * B * args.heads * ms, device="cuda:0")
     items = i32(list(range(B)))
+    cnt = torch.zeros(B * args.heads, dtype=torch.int32, device="cuda:0")
 
     def fn():
-        K.attn_decode(q, pool, out, items=items, n_items=B, part_o=po, part_ml=pm, max_splits=ms, **meta, **kw)
+        K.attn_decode(q, pool, out, items=items, n_items=B, part_o=po, part_ml=pm, counters=cnt, max_splits=ms,
+                      **meta, **kw)
 
     us = _time(fn, args.iters, args.graph)
     byts = B * (ctx + 1) * 2 * args.kv_heads * args.head_dim * pool.element_size()

@@ -137,7 +137,7 @@ def attn_chunk_mma(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items,
 
 
 def attn_decode(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_items, n_heads, n_kv_heads,
-                head_dim, page_tokens, window, scale, part_o, part_ml, max_splits):
+                head_dim, page_tokens, window, scale, part_o, part_ml, counters, max_splits):
     segs = [int(items[i]) for i in range(n_items)]
     for s in segs:
         assert int(seg_ctx[s]) // K.DECODE_SPLIT + 1 <= max_splits
@@ -194,6 +194,17 @@ def router_select(logits, n_experts, has_gate, ids, wts, gamma, *, n_tokens, top
     if has_gate:
         z = _f(logits[:n_tokens, n_experts])
         gamma[:n_tokens] = (1.0 / (1.0 + torch.exp(-z))).to(gamma.dtype)
+
+
+def route_small_takes(n_tokens, top_k, n_experts):
+    return n_tokens <= 16 and n_tokens * top_k <= 1024 and n_experts <= 512
+
+
+def route_small(logits, n_experts, has_gate, ids, wts, gamma, layout, *, n_tokens, top_k, renorm, scale=1.0,
+                tile_m=None):
+    router_select(logits, n_experts, has_gate, ids, wts, gamma, n_tokens=n_tokens, top_k=top_k, renorm=renorm,
+                  scale=scale)
+    moe_sort(ids, n_tokens * top_k, layout, tile_m)
 
 
 def moe_sort(ids, n_pairs, layout, tile_m=None):
@@ -283,7 +294,7 @@ def sample(logits, *, temperature, top_k, top_p, min_p, seeds, counters, out, ke
 
 
 _NAMES = ["embed_rows", "rmsnorm", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
-          "moe_sort", "moe_combine", "gather_rows", "apply_penalties", "sample"]
+          "moe_sort", "route_small", "route_small_takes", "moe_combine", "gather_rows", "apply_penalties", "sample"]
 
 
 def install(monkeypatch) -> None:

@@ -190,6 +190,40 @@ def test_router_on_tensor_cores(T, H, E, k, renorm):
         assert torch.equal(one[0], logits[t]), f"token {t} alone differs from token {t} in the batch"
 
 
+@pytest.mark.parametrize("T,E,k,tile,gate,renorm", [(1, 4, 2, 8, True, True), (8, 60, 4, 8, True, False),
+                                                     (13, 7, 3, 16, False, True), (16, 33, 16, 32, True, True),
+                                                     (5, 512, 6, 8, False, False)])
+def test_route_small_is_select_then_sort(T, E, k, tile, gate, renorm):
+    """One launch for a decode-sized batch gives, bit for bit, what the two kernels give."""
+    g = torch.Generator().manual_seed(T * 1000 + E)
+    logits = (torch.randn(T, E + 1, generator=g) * 2).to(DEV)
+    if T > 4:
+        logits[3, : min(E, 5)] = 1.25  # ties: the lowest index wins in both
+    assert K.route_small_takes(T, k, E)
+    out = {}
+    for name in ("two", "one"):
+        ids = torch.full((T * k,), -1, dtype=torch.int32, device=DEV)
+        wts, gamma = torch.zeros(T * k, device=DEV), torch.zeros(T, device=DEV)
+        lay = K.ExpertLayout(T * k, E, 64, DEV)
+        if name == "two":
+            K.router_select(logits, E, gate, ids, wts, gamma if gate else None, n_tokens=T, top_k=k, renorm=renorm,
+                            scale=0.75)
+            K.moe_sort(ids, T * k, lay, tile)
+        else:
+            K.route_small(logits, E, gate, ids, wts, gamma if gate else None, lay, n_tokens=T, top_k=k,
+                          renorm=renorm, scale=0.75, tile_m=tile)
+        out[name] = (ids, wts, gamma, lay)
+    (ids2, wts2, gamma2, lay2), (ids1, wts1, gamma1, lay1) = out["two"], out["one"]
+    assert torch.equal(ids1, ids2) and torch.equal(wts1, wts2) and torch.equal(gamma1, gamma2)
+    n_tiles = int(lay2.n_tiles.cpu())
+    assert int(lay1.n_tiles.cpu()) == n_tiles
+    for name in ("counts", "offsets", "sorted_pair", "pair_pos"):
+        assert torch.equal(getattr(lay1, name), getattr(lay2, name)), name
+    for name in ("tile_expert", "tile_row0", "tile_rows"):
+        assert torch.equal(getattr(lay1, name)[:n_tiles], getattr(lay2, name)[:n_tiles]), name
+    assert not K.route_small_takes(17, k, E) and not K.route_small_takes(T, k, 513)
+
+
 def test_router_ties_go_to_lowest_index():
     h = torch.ones(2, 16)
     wr = torch.zeros(6, 16)
@@ -304,12 +338,16 @@ def test_attn_decode(dtype, nh, nkv, hd, P, window):
     out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
     part_o = torch.full((len(segs) * nh * max_splits * hd,), float("nan"), device=DEV)
     part_ml = torch.full((2 * len(segs) * nh * max_splits,), float("nan"), device=DEV)
-    K.attn_decode(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=len(segs), part_o=part_o,
-                  part_ml=part_ml, max_splits=max_splits, **_dev(meta), **kw)
+    counters = torch.zeros(len(segs) * nh, dtype=torch.int32, device=DEV)
     ref = torch.zeros(T, nh * hd, dtype=torch.float64)
-    EK.attn_decode(q, pool, ref, items=items, n_items=len(segs), part_o=None, part_ml=None, max_splits=max_splits,
-                   **meta, **kw)
-    close(out, ref, dtype, "attn_decode")
+    EK.attn_decode(q, pool, ref, items=items, n_items=len(segs), part_o=None, part_ml=None, counters=None,
+                   max_splits=max_splits, **meta, **kw)
+    for again in range(2):  # the second call finds the counters as the first left them: zero
+        out.zero_()
+        K.attn_decode(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=len(segs), part_o=part_o,
+                      part_ml=part_ml, counters=counters, max_splits=max_splits, **_dev(meta), **kw)
+        close(out, ref, dtype, "attn_decode")
+        assert int(counters.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -330,11 +368,12 @@ def test_attention_finds_a_far_key_and_respects_the_window_edge(dtype):
         pool[page, 1, :, off, 1] = 7.0
     q.view(T, nh, hd)[:, :, 0] = 8.0  # score 8 * 30 / sqrt(64) = 30 on the marked key
     kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, scale=1 / math.sqrt(hd))
+    ms = ctx // K.DECODE_SPLIT + 1
     for window, seen in [(0, True), (ctx - far + 1, True), (ctx - far, False)]:
         out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
         K.attn_decode(q.to(DEV), pool.to(DEV), out, items=torch.tensor([0], dtype=torch.int32, device=DEV), n_items=1,
-                      part_o=torch.zeros(nh * 4 * hd, device=DEV), part_ml=torch.zeros(2 * nh * 4, device=DEV),
-                      max_splits=4, window=window, **_dev(meta), **kw)
+                      part_o=torch.zeros(nh * ms * hd, device=DEV), part_ml=torch.zeros(2 * nh * ms, device=DEV),
+                      counters=torch.zeros(nh, dtype=torch.int32, device=DEV), max_splits=ms, window=window, **_dev(meta), **kw)
         items = torch.tensor([[1, 0]], dtype=torch.int32)
         w2 = window - 7 if window else 0  # segment 1's last query sits at the same position as segment 0's
         K.attn_chunk(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=1, window=window, **_dev(meta), **kw)

@@ -50,8 +50,10 @@ def _call(lib, static, c, out, nh, nkv, hd, P, window, max_splits, scratch=None)
             F(1.0 / math.sqrt(hd))]
     if static:
         return lib.locus_attn_decode_static(*head, I(max_splits), stream)
-    part_o, part_ml = scratch
-    return lib.locus_attn_decode(*head, p(part_o), p(part_ml), I(max_splits), stream)
+    part_o, part_ml, counters = scratch
+    units = min(part_o.numel() // hd, part_ml.numel() // 2)
+    return lib.locus_attn_decode(*head, p(part_o), p(part_ml), p(counters), I(max_splits), ctypes.c_longlong(units),
+                                 stream)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -66,7 +68,8 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice(dtype):
 
     max_splits = 1023 // DECODE_SPLIT + 1  # the longest context below is 1023
     n = 4
-    scratch = (torch.empty(n * nh * max_splits * hd, device=DEV), torch.empty(2 * n * nh * max_splits, device=DEV))
+    scratch = (torch.empty(n * nh * max_splits * hd, device=DEV), torch.empty(2 * n * nh * max_splits, device=DEV),
+               torch.zeros(n * nh, dtype=torch.int32, device=DEV))
     # first call on this device resolves the array's address; it is made outside any capture
     cases = [_case(dtype, 11 + i, n, nh, nkv, hd, P, ctxs[i]) for i in range(2)]
     outs = [torch.zeros(n, nh * hd, dtype=dtype, device=DEV) for _ in range(2)]
