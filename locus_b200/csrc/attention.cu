@@ -391,6 +391,7 @@ __device__ __forceinline__ uint4 ld_once(const uint4* p) {
 template <typename T, int LPK>
 __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(AttnArgs a, int n_items, int max_units) {
     pdl_entry();
+    pdl_trigger();  // every block of this grid is resident from the start
     constexpr int VEC = 16 / sizeof(T);   // elements of a lane
     constexpr int KPL = 32 / LPK;         // key rows of a load instruction
     constexpr int CHUNK = DS_LOADS * KPL; // keys of a chunk

@@ -60,9 +60,9 @@ static inline int locus_launch_status() { return static_cast<int>(cudaGetLastErr
 
 // Programmatic dependent launch.  A kernel launched with the attribute may be scheduled before the
 // kernel in front of it in the stream has drained; its blocks wait in pdl_entry() until that grid has
-// finished and its writes are visible.  No kernel here signals early (an early signal let waiting
-// blocks take SM slots from the running kernel and measured slower), so what is saved is launch
-// processing between the many short kernels of a decode step.  Launches go through locus_launch();
+// finished and its writes are visible.  Kernels signal late (pdl_trigger() below): a signal at the
+// start of a grid of many waves let waiting blocks take SM slots from the running kernel and measured
+// slower.  What is saved is launch processing between the many short kernels of a decode step.  Launches go through locus_launch();
 // the attribute is only set while the module's switch is on (locus_set_pdl), otherwise the wait is
 // a no-op and the launch an ordinary one.
 static int g_locus_pdl = 0;
@@ -70,6 +70,15 @@ extern "C" void locus_set_pdl(int on) { g_locus_pdl = on; }
 
 __device__ __forceinline__ void pdl_entry() {
     asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// Lets the next kernel of the stream be scheduled once every block of this grid has passed this point
+// (or finished).  The next kernel still waits in its pdl_entry() until this grid is complete, so only
+// its launch and block start-up move under this grid's tail.  Place it where the block has no more
+// blocks of its own grid waiting for a slot behind it: at the start of a grid of one wave, after the
+// main loop of a grid of many.
+__device__ __forceinline__ void pdl_trigger() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
 template <typename... KArgs, typename... Args>

@@ -8,6 +8,7 @@
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const void* __restrict__ table,
                                   int table_dt, float* __restrict__ out, int H) {
     pdl_entry();
+    pdl_trigger();
     const int t = blockIdx.x;
     const size_t row = static_cast<size_t>(tokens[t]) * H;
     float* o = out + static_cast<size_t>(t) * H;
@@ -57,29 +58,50 @@ __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void*
 }
 
 // The common case (float32 in, width a multiple of 4): 16-byte loads, the row kept in registers.
+//
+// With add_src: first x[i] += sum over slots s < add_k (in slot order) of add_src[add_pos[i * add_k + s]]
+// (the outputs of a row's experts, the sum that moe_combine_kernel forms, in the same order), written
+// back to x, then the norm of the new row.  rows must be null then.
 template <typename TW, typename TO>
-__global__ void __launch_bounds__(256) rmsnorm_f32_kernel(const float* __restrict__ x, const TW* __restrict__ w,
+__global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x, const TW* __restrict__ w,
                                                           float eps, TO* __restrict__ out,
-                                                          const int* __restrict__ rows, int H) {
+                                                          const int* __restrict__ rows, int H,
+                                                          const float* __restrict__ add_src,
+                                                          const int* __restrict__ add_pos, int add_k) {
     pdl_entry();
+    pdl_trigger();
     __shared__ float warp_part[8];
     __shared__ float scale_s;
     const int i = blockIdx.x;
-    const float4* src = reinterpret_cast<const float4*>(x + static_cast<size_t>(rows ? rows[i] : i) * H);
+    float4* src = reinterpret_cast<float4*>(x + static_cast<size_t>(rows ? rows[i] : i) * H);
     const int n4 = H >> 2;
+    auto fetch = [&](int j) -> float4 {
+        float4 t = src[j];
+        if (add_src != nullptr) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < add_k; ++s) {
+                const float4 p = reinterpret_cast<const float4*>(
+                    add_src + static_cast<size_t>(add_pos[i * add_k + s]) * H)[j];
+                acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
+            }
+            t.x += acc.x; t.y += acc.y; t.z += acc.z; t.w += acc.w;
+            src[j] = t;
+        }
+        return t;
+    };
     float4 v[4];  // up to 4096 elements per row in registers; wider rows re-read
     float ss = 0.f;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
         const int j = threadIdx.x + u * 256;
         if (j < n4) {
-            v[u] = src[j];
+            v[u] = fetch(j);
             ss = fmaf(v[u].x, v[u].x, ss); ss = fmaf(v[u].y, v[u].y, ss);
             ss = fmaf(v[u].z, v[u].z, ss); ss = fmaf(v[u].w, v[u].w, ss);
         }
     }
     for (int j = threadIdx.x + 1024; j < n4; j += 256) {
-        const float4 t = src[j];
+        const float4 t = fetch(j);
         ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
     }
     ss = warp_sum(ss);
@@ -104,14 +126,21 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(const float* __restric
     }
 }
 
-extern "C" int locus_rmsnorm(const void* x, int x_dt, const void* w, int w_dt, float eps, void* out,
-                             int out_dt, const int* rows, int n_rows, int H, cudaStream_t stream) {
+// add_src / add_pos / add_k: see rmsnorm_f32_kernel; only with float32 x, H a multiple of 4, 16-byte
+// aligned x and add_src, and no row gather.
+extern "C" int locus_rmsnorm(void* x, int x_dt, const void* w, int w_dt, float eps, void* out,
+                             int out_dt, const int* rows, int n_rows, int H, const float* add_src,
+                             const int* add_pos, int add_k, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
-    if (x_dt == LOCUS_DT_F32 && H % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-        const float* xf = static_cast<const float*>(x);
+    const bool fast = x_dt == LOCUS_DT_F32 && H % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    if (add_src != nullptr &&
+        (!fast || rows != nullptr || add_pos == nullptr || add_k <= 0 || (reinterpret_cast<uintptr_t>(add_src) & 15)))
+        return LOCUS_ERR_UNSUPPORTED;
+    if (fast) {
+        float* xf = static_cast<float*>(x);
 #define NORM_LAUNCH(TW, TO)                                                                             \
         locus_launch(rmsnorm_f32_kernel<TW, TO>, n_rows, 256, 0, stream, xf, static_cast<const TW*>(w), eps,      \
-                     static_cast<TO*>(out), rows, H)
+                     static_cast<TO*>(out), rows, H, add_src, add_pos, add_k)
         if (w_dt == LOCUS_DT_BF16 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(bf16, bf16);
         else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_F32) NORM_LAUNCH(float, float);
         else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(float, bf16);
@@ -207,6 +236,7 @@ __global__ void __launch_bounds__(256) rope_kv_write_bf16_kernel(
     bf16* __restrict__ q_out, bf16* __restrict__ pool, const int* __restrict__ slots, int nh, int nkv, int hd,
     int page_tokens, int write_kv) {
     pdl_entry();
+    pdl_trigger();
     __shared__ float cs_c[128], cs_s[128];
     const int t = blockIdx.x;
     const int half = hd / 2;
@@ -289,6 +319,7 @@ extern "C" int locus_rope_kv_write(const void* qkv, int dt, const int* positions
 __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ pair_out,
                                    const int* __restrict__ pair_pos, int k, int H) {
     pdl_entry();
+    pdl_trigger();
     const int t = blockIdx.x;
     for (int j = threadIdx.x; j < H; j += blockDim.x) {
         float acc = 0.f;

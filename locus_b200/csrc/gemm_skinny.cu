@@ -132,6 +132,7 @@ __global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
             }
         }
     }
+    pdl_trigger();  // the weights are read: the next kernel may start up under this block's reduction
     // partial sums of the warps -> shared memory; element (row r, token col) of tile j at [j][col * 16 + r]
     constexpr int SETS = DUAL ? 2 : 1;
     float* mine = red + static_cast<size_t>(warp) * SETS * NT * 128;

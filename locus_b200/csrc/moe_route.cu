@@ -390,6 +390,7 @@ __global__ void __launch_bounds__(256) route_small_kernel(const float* __restric
                                                           int* __restrict__ tile_row0, int* __restrict__ tile_rows,
                                                           int* __restrict__ n_tiles) {
     pdl_entry();
+    pdl_trigger();
     extern __shared__ float rs_smem[];  // probabilities [8][E], then the ints below
     int* s_ids = reinterpret_cast<int*>(rs_smem + 8 * E);  // [T * k]
     int* s_cnt = s_ids + T * k;                             // [E]

@@ -32,11 +32,24 @@ class Runtime:
         self.max_wanted = max_wanted
         self._bufs: Dict[Tuple, torch.Tensor] = {}
         self._objects: Dict[Tuple, object] = {}
+        # An addition to the residual stream that the last feed-forward left to the next norm
+        # (parts.base.PendingAdd).  A feed-forward may leave one only while ``defer_add`` is set:
+        # the model sets it when the next block takes pending additions.
+        self.defer_add = False
+        self._pending = None
         # a second stream for work that does not depend on the main chain (forked and joined
         # with events, also inside a CUDA graph capture)
         self.side_stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
         self._fork_event = torch.cuda.Event() if self.side_stream is not None else None
         self._join_event = torch.cuda.Event() if self.side_stream is not None else None
+
+    def leave_pending(self, add) -> None:
+        assert self.defer_add and self._pending is None
+        self._pending = add
+
+    def take_pending(self):
+        p, self._pending = self._pending, None
+        return p
 
     def side(self):
         """Context in which launches go to the side stream, ordered after everything launched so

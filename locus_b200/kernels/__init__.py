@@ -140,9 +140,17 @@ def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> 
     _check(code, "embed_rows")
 
 
+def rmsnorm_adds(x: torch.Tensor) -> bool:
+    """Whether :func:`rmsnorm` can fold a pending expert sum into rows like ``x``'s."""
+    return x.dtype == torch.float32 and x.shape[-1] % 4 == 0
+
+
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
-            rows: Optional[torch.Tensor] = None) -> None:
-    """out[i] = x[rows[i] if rows else i] * rsqrt(mean(x^2) + eps) * w  (statistics in float32)."""
+            rows: Optional[torch.Tensor] = None, add=None) -> None:
+    """out[i] = x[rows[i] if rows else i] * rsqrt(mean(x^2) + eps) * w  (statistics in float32).
+
+    ``add`` = (pair_out, pair_pos, top_k): first x[i] += the sum that :func:`moe_combine` forms (same
+    order), written back to ``x``; needs :func:`rmsnorm_adds` and no ``rows``."""
     _cuda_c(x, "x")
     _cuda_c(w, "w")
     _cuda_c(out, "out")
@@ -154,9 +162,18 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
         _need(rows.numel() == n, "rmsnorm: rows/out mismatch")
     else:
         _need(x.shape[0] == n, "rmsnorm: x/out mismatch")
+    add_src = add_pos = None
+    add_k = 0
+    if add is not None:
+        add_src, add_pos, add_k = add
+        _need(rows is None and rmsnorm_adds(x), "rmsnorm: cannot fold the expert sum into these rows")
+        _cuda_c(add_src, "pair_out")
+        _i32(add_pos, "pair_pos")
+        _need(add_src.dtype == torch.float32 and add_src.shape[-1] == H and add_pos.numel() >= n * add_k,
+              "rmsnorm: expert sum of another shape")
     code = _lib("elementwise").locus_rmsnorm(
         _p(x), I(dtype_code(x.dtype)), _p(w), I(dtype_code(w.dtype)), F(eps), _p(out),
-        I(dtype_code(out.dtype)), _p(rows), I(n), I(H), _stream()
+        I(dtype_code(out.dtype)), _p(rows), I(n), I(H), _p(add_src), _p(add_pos), I(add_k), _stream()
     )
     _check(code, "rmsnorm")
 

@@ -115,8 +115,15 @@ class Model:
         T = batch.T
         x = rt.rows("model.x", self.plan.hidden_size, torch.float32, T)
         self.embedding.forward(batch.tokens, x)
-        for call, cache in zip(self.plan.order, caches):
+        order = self.plan.order
+        for i, (call, cache) in enumerate(zip(order, caches)):
+            # a block may leave its last addition to the residual stream to the next block's first norm
+            rt.defer_add = i + 1 < len(order) and self.blocks[order[i + 1].layer].takes_pending_add
             self.blocks[call.layer].forward(x, batch, cache, rt)
+        rt.defer_add = False
+        pending = rt.take_pending()
+        if pending is not None:
+            pending.apply(x)
         n = batch.n_want
         logits = rt.buf("model.logits", (rt.max_wanted, self.plan.vocab_size), torch.float32)[:n]
         if n:

@@ -135,9 +135,25 @@ class Part:
         return []
 
 
+class PendingAdd:
+    """An addition to the residual stream that a feed-forward left undone so that the next norm can
+    fold it into its own pass over the rows: x[t] += sum over slots of pair_out[pair_pos[t * k + slot]].
+    Whoever takes it from the runtime must either hand it to a norm that folds it or ``apply`` it."""
+
+    def __init__(self, pair_out: torch.Tensor, pair_pos: torch.Tensor, top_k: int) -> None:
+        self.pair_out, self.pair_pos, self.top_k = pair_out, pair_pos, top_k
+
+    def apply(self, x: torch.Tensor) -> None:
+        from .. import kernels as K
+
+        K.moe_combine(x, self.pair_out, self.pair_pos, self.top_k)
+
+
 class Norm(Part):
-    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-        """out = norm(x) (rows: gather of x rows); statistics in float32."""
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
+                add: Optional[PendingAdd] = None) -> None:
+        """out = norm(x) (rows: gather of x rows); statistics in float32.  ``add``: a pending
+        addition to x that must be done (in x) before the norm: fold it in or call ``add.apply(x)``."""
         raise NotImplementedError
 
 
@@ -179,7 +195,13 @@ class FeedForward(Part):
 
 
 class Arrangement(Part):
-    """How norm, mixer and feed-forward are arranged around the residual stream."""
+    """How norm, mixer and feed-forward are arranged around the residual stream.
+
+    ``takes_pending_add``: the arrangement starts by taking ``rt.take_pending()`` and completing
+    it (usually inside its first norm); only then may the block before it leave its last addition
+    pending."""
+
+    takes_pending_add = False
 
     def forward(self, x: torch.Tensor, batch: "StepBatch", cache: "LayerCache", rt: "Runtime") -> None:
         raise NotImplementedError

@@ -27,13 +27,15 @@ class PreNorm(Arrangement):
         self.norm2 = make_part("norm", norm, f"{prefix}.{norm2_name}")
         self.ff = make_part("feed_forward", feed_forward, f"{prefix}.{ff_prefix}")
 
+    takes_pending_add = True
+
     def sub_parts(self):
         return [self.norm1, self.mixer, self.norm2, self.ff]
 
     def forward(self, x, batch, cache, rt) -> None:
         T = batch.T
         h = rt.rows("block.h", self.hidden, rt.dtype, T)
-        self.norm1.forward(x, h)
+        self.norm1.forward(x, h, add=rt.take_pending())
         self.mixer.forward(h, batch, cache, x, rt)
         self.norm2.forward(x, h)
         self.ff.forward(h, batch, x, rt)

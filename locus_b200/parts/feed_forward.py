@@ -20,7 +20,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels as K
-from .base import FeedForward, TensorSource, register_feed_forward
+from .base import FeedForward, PendingAdd, TensorSource, register_feed_forward
 
 
 class DenseMlp(FeedForward):
@@ -174,9 +174,13 @@ class SparseMoe(FeedForward):
                  scale_rows=lay.sorted_pair)
         if overlap:
             rt.join()
-        K.moe_combine(residual, pair_out, lay.pair_pos, self.k)
         if self.shared is not None and not overlap:
             self.shared.forward(h, batch, residual, rt, row_scale=gamma)
+        if rt.defer_add and K.rmsnorm_adds(residual):
+            # the sum of the experts' outputs is folded into the next block's first norm
+            rt.leave_pending(PendingAdd(pair_out, lay.pair_pos, self.k))
+        else:
+            K.moe_combine(residual, pair_out, lay.pair_pos, self.k)
 
 
 register_feed_forward("dense_mlp", DenseMlp)

@@ -29,8 +29,12 @@ class RMSNorm(Norm):
     def kernel_modules(self, dtype):
         return ["elementwise"]
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-        K.rmsnorm(x, self.params["weight"], self.eps, out, rows)
+    def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None, add=None) -> None:
+        if add is not None and (rows is not None or not K.rmsnorm_adds(x)):
+            add.apply(x)
+            add = None
+        K.rmsnorm(x, self.params["weight"], self.eps, out, rows,
+                  add=None if add is None else (add.pair_out, add.pair_pos, add.top_k))
 
 
 register_norm("rmsnorm", RMSNorm)

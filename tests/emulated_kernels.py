@@ -26,7 +26,14 @@ def embed_rows(tokens, table, out):
     out.copy_(table[tokens.long()].to(out.dtype))
 
 
-def rmsnorm(x, w, eps, out, rows=None):
+def rmsnorm_adds(x):
+    return x.dtype == torch.float32 and x.shape[-1] % 4 == 0
+
+
+def rmsnorm(x, w, eps, out, rows=None, add=None):
+    if add is not None:
+        assert rows is None
+        moe_combine(x[: out.shape[0]], add[0], add[1], add[2])
     xs = _f(x if rows is None else x[rows.long()])[: out.shape[0]]
     ss = (xs * xs).sum(-1, keepdim=True)
     out.copy_((xs * (1.0 / torch.sqrt(ss / xs.shape[-1] + eps)) * _f(w)).to(out.dtype))
@@ -293,7 +300,7 @@ def sample(logits, *, temperature, top_k, top_p, min_p, seeds, counters, out, ke
             kept_count[r] = int(keep.sum())
 
 
-_NAMES = ["embed_rows", "rmsnorm", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
+_NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
           "moe_sort", "route_small", "route_small_takes", "moe_combine", "gather_rows", "apply_penalties", "sample"]
 
 

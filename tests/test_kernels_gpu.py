@@ -62,6 +62,29 @@ def test_rmsnorm(dtype, H):
     close(out2, ref[rows.long()], dtype, "rmsnorm rows")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,k", [(8, 1), (200, 3), (4096 + 1024 + 8, 4)])
+def test_rmsnorm_folds_the_expert_sum(dtype, H, k):
+    """The norm that first adds a row's expert outputs gives, bit for bit, moe_combine followed by
+    the plain norm, and leaves the same sum in x."""
+    T = 6
+    x = rnd(T, H, seed=1, scale=3.0).to(DEV)
+    pair_out = rnd(T * k, H, seed=2, scale=2.0).to(DEV)
+    pair_pos = torch.randperm(T * k, generator=torch.Generator().manual_seed(3)).to(torch.int32).to(DEV)
+    w = (rnd(H, dtype=dtype, seed=4) + 1).to(DEV)
+    assert K.rmsnorm_adds(x)
+    x2, out2 = x.clone(), torch.empty(T, H, dtype=dtype, device=DEV)
+    K.moe_combine(x2, pair_out, pair_pos, k)
+    K.rmsnorm(x2, w, 1e-6, out2)
+    x1, out1 = x.clone(), torch.empty(T, H, dtype=dtype, device=DEV)
+    K.rmsnorm(x1, w, 1e-6, out1, add=(pair_out, pair_pos, k))
+    assert torch.equal(x1, x2) and torch.equal(out1, out2)
+    assert not K.rmsnorm_adds(torch.zeros(2, 6))
+    with pytest.raises(K.KernelError):
+        K.rmsnorm(x1, w, 1e-6, out1[:2], torch.tensor([0, 1], dtype=torch.int32, device=DEV),
+                  add=(pair_out, pair_pos, k))
+
+
 @pytest.mark.parametrize("xdt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
                                      (torch.bfloat16, torch.float32)])
 @pytest.mark.parametrize("M,N,K_", [(1, 1, 8), (5, 331, 120), (70, 130, 72), (129, 64, 2048)])
