@@ -15,6 +15,17 @@
 // bias, SwiGLU of two accumulators, per-row scale, store as bfloat16 / float32 or add into
 // a float32 tensor.  Grouped products (experts) take the tile list that moe_sort built.
 //
+// Pairs (an option, off unless switched on: locus_gemm_tc_set_pair).  Two CTAs on neighbouring SMs (a
+// cluster of two) work as one: tcgen05.mma.cta_group::2 multiplies 256 weight rows (128 from each CTA's shared
+// memory) by the token tile, of which each CTA has loaded only half the rows, so a k-block costs a
+// CTA a third less traffic from L2 for the same MMA work.  Each CTA keeps the accumulators of its own
+// 128 weight rows in its own tensor memory and runs its own epilogue.  The CTA of rank 0 issues the
+// MMAs; the loads of both CTAs count their bytes at rank 0's barrier of the stage, and rank 0's commits
+// release the stage in both.  Measured on the products of a 2,048-token prefill step it is as fast as
+// two independent CTAs per SM, not faster: the thread that issues the MMAs, not the traffic from L2,
+// sets the pace there (an MMA instruction is accepted only when the tensor pipe has room: 4 MMAs of a
+// k-block take about 560 cycles to issue, the whole loop about 700).
+//
 // Every wait on an mbarrier is bounded (about a second of clock cycles); when a wait runs
 // out the kernel records a code in the module's error word, stops waiting and finishes, so
 // a fault in the pipeline shows as an error on the host, never as a hang.  No load uses
@@ -31,7 +42,7 @@
 __device__ int g_tc_error = 0;
 
 struct TcArgs {
-    int M, N, K, TN, dual, stages, tmem_cols;
+    int M, N, K, TN, dual, stages, tmem_cols, pair, kps;
     int accumulate;
     void* out;
     int out_dt;
@@ -70,6 +81,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // Bounded wait: false (and the error word set to `code`) when the limit runs out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -86,6 +102,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+        : "memory");
+}
+
+// The load of the second CTA of a pair: the data goes to its own shared memory, the bytes are counted
+// at the barrier at the same place in the FIRST CTA's shared memory (cta_group::2 allows a barrier of
+// the other CTA of the pair; no multicast).
+__device__ __forceinline__ void tma_load_2d_to_leader(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "{\n\t.reg .b32 rb;\n\t"
+        "mapa.shared::cluster.u32 rb, %4, 0;\n\t"
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [rb];\n\t}"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
         : "memory");
 }
@@ -114,6 +142,24 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
+// The pair's forms: one MMA over both CTAs' operands, and a commit that arrives at the barrier at
+// this place in both CTAs.
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(static_cast<uint16_t>(3))
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -122,11 +168,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
         : "r"(taddr));
 }
 
+// PAIR: the form for clusters of two CTAs.  (A kernel that contains cta_group::2 instructions can only
+// be launched in such clusters, hence two instantiations.)
+template <bool PAIR>
 __global__ void __launch_bounds__(192, 2)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                const __grid_constant__ CUtensorMap map_x, TcArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int rank = PAIR ? (blockIdx.x & 1) : 0;  // place in the pair (the cluster is 2 x 1 x 1)
 
     int x_row0, rows_valid;
     long long w_row0 = static_cast<long long>(blockIdx.x) * TILE_W;
@@ -142,8 +192,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
-    const uint32_t x_bytes = static_cast<uint32_t>(a.TN) * TILE_K * 2;
-    const uint32_t stage_bytes = A_BYTES * (1 + a.dual) + x_bytes;
+    const uint32_t x_bytes = static_cast<uint32_t>(PAIR ? a.TN / 2 : a.TN) * TILE_K * 2;  // a pair: half the rows each
+    // a stage holds a.kps k-blocks ("sub-stages": weights, second weights, tokens, each of one k-block)
+    const uint32_t sub_bytes = A_BYTES * (1 + a.dual) + x_bytes;
+    const uint32_t stage_bytes = a.kps * sub_bytes;
     const uint32_t bars = base + a.stages * stage_bytes;
     // barriers: full[s] at bars + 8 s, empty[s] at bars + 8 (stages + s), accumulator-ready, then the TMEM slot
     const uint32_t bar_full = bars, bar_empty = bars + 8 * a.stages, bar_acc = bars + 16 * a.stages;
@@ -160,51 +212,103 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(a.tmem_cols) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (PAIR) {  // warp 1 of both CTAs, the same slot in both
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(a.tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(a.tmem_cols) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync();  // the other CTA's barriers are initialised before anything arrives at them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *slot_ptr;
     const int nkb = (a.K + TILE_K - 1) / TILE_K;
 
+    // MMA N covers only the valid token rows of this tile, rounded up to 16: a ragged last tile (or an
+    // expert with few rows) costs MMA time for its rows, not for the whole tile.  In a pair the MMA takes
+    // the first n_mma / 2 token rows from each CTA, so rank 1 loads the rows from x_row0 + n_mma / 2 on.
+    const int n_mma = min(a.TN, (rows_valid + 15) & ~15);
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % a.stages;
-                mbar_wait(bar_empty + 8 * s, ((kb / a.stages) & 1) ^ 1, 1);
-                const uint32_t st = base + s * stage_bytes;
-                mbar_expect_tx(bar_full + 8 * s, stage_bytes);
-                tma_load_2d(st, &map_w, kb * TILE_K, static_cast<int>(w_row0), bar_full + 8 * s);
-                if (a.dual) tma_load_2d(st + A_BYTES, &map_w2, kb * TILE_K, static_cast<int>(w_row0), bar_full + 8 * s);
-                tma_load_2d(st + A_BYTES * (1 + a.dual), &map_x, kb * TILE_K, x_row0, bar_full + 8 * s);
+            const int x_first = x_row0 + rank * (n_mma / 2);
+            int s = 0;
+            uint32_t round = 0;  // how often the ring has wrapped (its low bit is the barriers' phase)
+            for (int kb = 0; kb < nkb; kb += a.kps, ++s) {
+                if (s == a.stages) {
+                    s = 0;
+                    ++round;
+                }
+                mbar_wait(bar_empty + 8 * s, (round & 1) ^ 1, 1);
+                const int nsub = min(a.kps, nkb - kb);
+                if (!(PAIR && rank == 1))  // rank 0's barrier counts the bytes of both CTAs of a pair
+                    mbar_expect_tx(bar_full + 8 * s, (PAIR ? 2 : 1) * nsub * sub_bytes);
+                for (int j = 0; j < nsub; ++j) {
+                    const uint32_t st = base + s * stage_bytes + j * sub_bytes;
+                    const int k0 = (kb + j) * TILE_K;
+                    if (PAIR && rank == 1) {
+                        tma_load_2d_to_leader(st, &map_w, k0, static_cast<int>(w_row0), bar_full + 8 * s);
+                        if (a.dual) tma_load_2d_to_leader(st + A_BYTES, &map_w2, k0, static_cast<int>(w_row0), bar_full + 8 * s);
+                        tma_load_2d_to_leader(st + A_BYTES * (1 + a.dual), &map_x, k0, x_first, bar_full + 8 * s);
+                    } else {
+                        tma_load_2d(st, &map_w, k0, static_cast<int>(w_row0), bar_full + 8 * s);
+                        if (a.dual) tma_load_2d(st + A_BYTES, &map_w2, k0, static_cast<int>(w_row0), bar_full + 8 * s);
+                        tma_load_2d(st + A_BYTES * (1 + a.dual), &map_x, k0, x_first, bar_full + 8 * s);
+                    }
+                }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major, N = TN, M = 128
-            // N covers only the valid token rows of this tile, rounded up to 16: a ragged last tile
-            // (or an expert with few rows) costs MMA time for its rows, not for the whole tile
-            const int n_mma = min(a.TN, (rows_valid + 15) & ~15);
+        if (lane == 0 && rank == 0) {  // rank 0 issues the MMAs of a pair
+            // instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major, N = n_mma,
+            // M = 128 (256 over a pair)
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n_mma >> 3) << 17) |
-                                   (static_cast<uint32_t>(TILE_W >> 4) << 24);
-            for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % a.stages;
-                mbar_wait(bar_full + 8 * s, (kb / a.stages) & 1, 2);
+                                   (static_cast<uint32_t>((PAIR ? 2 * TILE_W : TILE_W) >> 4) << 24);
+            // The thread that issues the MMAs is the pace-maker of the tile: an MMA is accepted only when
+            // the tensor pipe has room, so whatever this thread does between the last MMA of one k-block
+            // and the first of the next is time the pipe may stand idle.  Hence: no divisions, descriptors
+            // advanced by addition, and the barrier of the next stage is looked at right after this stage's
+            // MMAs went out (while they run), so that the wait at the top of the loop is usually over.
+            const uint64_t desc0 = make_desc(base);
+            const uint64_t stage_units = stage_bytes >> 4;  // descriptors count in 16-byte units
+            const uint64_t sub_units = sub_bytes >> 4;
+            const uint64_t w2_units = A_BYTES >> 4, x_units = (A_BYTES * (1 + a.dual)) >> 4;
+            int s = 0;
+            uint32_t round = 0;
+            bool ready = mbar_try_wait(bar_full, 0);
+            for (int kb = 0; kb < nkb; kb += a.kps) {
+                if (!ready) mbar_wait(bar_full + 8 * s, round & 1, 2);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t st = base + s * stage_bytes;
-                const uint64_t dw = make_desc(st), dw2 = make_desc(st + A_BYTES);
-                const uint64_t dx = make_desc(st + A_BYTES * (1 + a.dual));
+                const int nsub = min(a.kps, nkb - kb);
+                for (int j = 0; j < nsub; ++j) {
+                    const uint64_t dw = desc0 + s * stage_units + j * sub_units, dw2 = dw + w2_units, dx = dw + x_units;
+                    if (PAIR) {
 #pragma unroll
-                for (int k4 = 0; k4 < TILE_K / 16; ++k4) {
-                    const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
-                    umma_bf16(tmem, dw + 2 * k4, dx + 2 * k4, idesc, acc);  // 16 elements = 32 bytes = 2 units
-                    if (a.dual) umma_bf16(tmem + a.TN, dw2 + 2 * k4, dx + 2 * k4, idesc, acc);
+                        for (int k4 = 0; k4 < TILE_K / 16; ++k4) {
+                            const uint32_t acc = (kb + j > 0 || k4 > 0) ? 1u : 0u;
+                            umma_bf16_pair(tmem, dw + 2 * k4, dx + 2 * k4, idesc, acc);  // 16 elements = 32 bytes = 2 units
+                            if (a.dual) umma_bf16_pair(tmem + a.TN, dw2 + 2 * k4, dx + 2 * k4, idesc, acc);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k4 = 0; k4 < TILE_K / 16; ++k4) {
+                            const uint32_t acc = (kb + j > 0 || k4 > 0) ? 1u : 0u;
+                            umma_bf16(tmem, dw + 2 * k4, dx + 2 * k4, idesc, acc);
+                            if (a.dual) umma_bf16(tmem + a.TN, dw2 + 2 * k4, dx + 2 * k4, idesc, acc);
+                        }
+                    }
                 }
-                umma_commit(bar_empty + 8 * s);  // the stage is free when these MMAs have read it
+                // the stage is free when these MMAs have read it (in both CTAs of a pair)
+                if (PAIR) umma_commit_pair(bar_empty + 8 * s); else umma_commit(bar_empty + 8 * s);
+                if (++s == a.stages) {
+                    s = 0;
+                    ++round;
+                }
+                ready = kb + a.kps < nkb && mbar_try_wait(bar_full + 8 * s, round & 1);
             }
-            umma_commit(bar_acc);
+            if (PAIR) umma_commit_pair(bar_acc); else umma_commit(bar_acc);
         }
     } else {
         const int quarter = warp & 3;  // tensor-memory lanes this warp may read
@@ -312,9 +416,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (PAIR) cluster_sync();  // neither CTA leaves while the other may still reach into it
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
+        if (PAIR) {
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
+        } else {
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
+        }
     }
 }
 
@@ -353,6 +462,12 @@ static bool make_map(CUtensorMap* map, const void* ptr, long long rows, long lon
 
 // Shared-memory budget of the pipeline in KiB; 0 = chosen from the grid size (see below).
 static int g_budget_kb = 0;
+// Pairs of CTAs on (1) or off (0).
+static int g_pair = 0;
+// k-blocks per pipeline stage (1 or 2): with 2 a barrier round covers 8 MMAs instead of 4.
+static int g_kps = 1;
+extern "C" void locus_gemm_tc_set_kps(int k) { g_kps = k == 2 ? 2 : 1; }
+extern "C" void locus_gemm_tc_set_pair(int on) { g_pair = on; }
 extern "C" void locus_gemm_tc_set_budget_kb(int kb) { g_budget_kb = kb; }
 
 static int pow2_at_least(int v) {
@@ -380,10 +495,14 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     CUtensorMap map_w, map_w2, map_x;
     if (!make_map(&map_w, w, w_rows_total, K, K, TILE_W)) return LOCUS_ERR_UNSUPPORTED;
     if (!make_map(&map_w2, dual ? w2 : w, w_rows_total, K, K, TILE_W)) return LOCUS_ERR_UNSUPPORTED;
-    if (!make_map(&map_x, x, x_rows_total, K, ldx, TN)) return LOCUS_ERR_UNSUPPORTED;
+    // pairs of CTAs (see the head of the file) wherever there are two weight tiles to pair
+    const int pair = (g_pair && N > TILE_W) ? 1 : 0;
+    if (!make_map(&map_x, x, x_rows_total, K, ldx, pair ? TN / 2 : TN)) return LOCUS_ERR_UNSUPPORTED;
     TcArgs a;
-    a.M = M; a.N = N; a.K = K; a.TN = TN; a.dual = dual;
-    const int stage_bytes = A_BYTES * (1 + dual) + TN * TILE_K * 2;
+    a.M = M; a.N = N; a.K = K; a.TN = TN; a.dual = dual; a.pair = pair;
+    const int kps = g_kps;
+    a.kps = kps;
+    const int stage_bytes = kps * (A_BYTES * (1 + dual) + (pair ? TN / 2 : TN) * TILE_K * 2);
     const int tiles_y = tile_expert ? max_tiles : ceil_div(M, TN);
     const long long n_blocks = static_cast<long long>(ceil_div(N, TILE_W)) * tiles_y;
     // A grid of more than one block per SM runs two blocks per SM (the epilogue of one overlaps
@@ -393,7 +512,7 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     if (stages > 12) stages = 12;
     if (stages < 2) stages = 2;
     const int nkb = (K + TILE_K - 1) / TILE_K;
-    if (stages > nkb) stages = nkb;
+    if (stages > (nkb + kps - 1) / kps) stages = (nkb + kps - 1) / kps;
     if (stages < 1) return LOCUS_ERR_UNSUPPORTED;
     a.stages = stages;
     a.tmem_cols = pow2_at_least(TN * (1 + dual));
@@ -404,14 +523,32 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 16 * stages + 64 + 4 * TN + 4 * 16 * 36 * 4 + 1024;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+        if (cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(gemm_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
             return static_cast<int>(cudaGetLastError());
         attr_set = true;
     }
     if (tiles_y <= 0) return 0;
     if (tiles_y > 65535) return LOCUS_ERR_UNSUPPORTED;
     dim3 grid(ceil_div(N, TILE_W), tiles_y);
-    gemm_tc_kernel<<<grid, 192, smem, stream>>>(map_w, map_w2, map_x, a);
+    if (pair) grid.x = (grid.x + 1) & ~1u;  // whole pairs: a last CTA without weight rows computes zeros and stores nothing
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(192);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pair ? 1 : 0;
+    if (pair) {
+        cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, map_w, map_w2, map_x, a);
+    } else {
+        cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false>, map_w, map_w2, map_x, a);
+    }
     return locus_launch_status();
 }
 
