@@ -388,6 +388,9 @@ __device__ __forceinline__ uint4 ld_once(const uint4* p) {
     return v;
 }
 
+struct true_tag { static constexpr bool value = true; };
+struct false_tag { static constexpr bool value = false; };
+
 template <typename T, int LPK>
 __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(AttnArgs a, int n_items, int max_units) {
     pdl_entry();
@@ -514,11 +517,14 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
 #pragma unroll
         for (int g = 0; g < DS_LOADS; ++g)
             kreg[g] = live(k_begin, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
-        for (int k0 = k_begin; k0 < k_end; k0 += CHUNK) {
+        // One chunk: FAST when this chunk and the next lie wholly inside the range (the steady state), so
+        // that no load and no score needs a check of its own.
+        auto chunk = [&](int k0, auto fast_tag) {
+            constexpr bool FAST = decltype(fast_tag)::value;
             // V of this chunk
 #pragma unroll
             for (int g = 0; g < DS_LOADS; ++g)
-                vreg[g] = live(k0, g) ? ld_once(pool4 + v_units + base + g * KPL * row_units) : zero4;
+                vreg[g] = (FAST || live(k0, g)) ? ld_once(pool4 + v_units + base + g * KPL * row_units) : zero4;
             // scores of this chunk
             float sc[DS_LOADS];
 #pragma unroll
@@ -530,7 +536,7 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
                 for (int i = 0; i < VEC; ++i) dot = fmaf(q[i], kf[i], dot);
 #pragma unroll
                 for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                sc[g] = live(k0, g) ? dot : -INFINITY;
+                sc[g] = (FAST || live(k0, g)) ? dot : -INFINITY;
             }
             // K of the next chunk, and the block-table entry of the chunk after the next two
             base = chunk_base(k0 + CHUNK, page_next);
@@ -538,12 +544,12 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
             page_next2 = page_of(k0 + 3 * CHUNK);
 #pragma unroll
             for (int g = 0; g < DS_LOADS; ++g)
-                kreg[g] = live(k0 + CHUNK, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+                kreg[g] = (FAST || live(k0 + CHUNK, g)) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
             // running softmax of this lane group, then the weighted sum
             float mx = m;
 #pragma unroll
             for (int g = 0; g < DS_LOADS; ++g) mx = fmaxf(mx, sc[g]);
-            if (mx != -INFINITY) {
+            if (FAST || mx != -INFINITY) {
                 const float corr = exp2f(m - mx);  // 0 on the first live chunk
                 l *= corr;
 #pragma unroll
@@ -558,6 +564,13 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
                     for (int i = 0; i < VEC; ++i) acc[i] = fmaf(pr, vf[i], acc[i]);
                 }
                 m = mx;
+            }
+        };
+        for (int k0 = k_begin; k0 < k_end; k0 += CHUNK) {
+            if (k0 >= t_lo && k0 + 2 * CHUNK <= k_end) {
+                chunk(k0, true_tag());
+            } else {
+                chunk(k0, false_tag());
             }
         }
         // merge the lane groups (ascending group order is kept by always putting the lower group first)
