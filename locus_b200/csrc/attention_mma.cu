@@ -73,7 +73,10 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     bf16* sK = sQ + MQ * LDS;                          // [2][MK][LDS]
     bf16* sV = sK + 2 * MK * LDS;                      // [2][MK][LDS]
 
-    const int seg = a.items[2 * blockIdx.x], qoff = a.items[2 * blockIdx.x + 1];
+    // Items are listed in ascending position; the late tiles of a prompt see the most keys, so the grid
+    // takes them first and the short ones fill the tail.
+    const int item = gridDim.x - 1 - blockIdx.x;
+    const int seg = a.items[2 * item], qoff = a.items[2 * item + 1];
     const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
     const int nq = min(MQ, a.seg_qn[seg] - qoff);
     const int row0 = a.seg_q0[seg] + qoff;
@@ -84,6 +87,7 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     const int t_hi = p0 + nq - 1;
     const int t_lo = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
     const int P = a.page_tokens;
+    const int pshift = (P & (P - 1)) == 0 ? __ffs(P) - 1 : -1;  // pages of 2^k tokens: shifts instead of divisions
     const float scale_log2 = a.scale * 1.4426950408889634f;
 
     // ---- Q tile -> shared (rows past nq are zero)
@@ -102,7 +106,8 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
             const int t = tile0 + r;
             const bool ok = t >= t_lo && t <= t_hi;
             const int tt = ok ? t : t_hi;  // any valid position: the copy size is 0 when !ok
-            const int page = table[tt / P], off = tt % P;
+            const int page = table[pshift >= 0 ? tt >> pshift : tt / P];
+            const int off = pshift >= 0 ? tt & (P - 1) : tt % P;
             const bf16* kb = a.pool + ((static_cast<size_t>(page) * 2) * a.nkv + kvh) * P * HD +
                              static_cast<size_t>(off) * HD + c * 8;
             const bf16* vb = kb + static_cast<size_t>(a.nkv) * P * HD;
