@@ -92,8 +92,7 @@ def test_forced_router_is_that_expert_and_gate_touches_only_the_shared_expert(tm
     p = "model.layers.0.mlp"
     h = torch.randn(4, cfg["hidden_size"], dtype=torch.float64)
     nos = dict(cfg, shared_expert_intermediate_size=0, num_experts_per_tok=1)
-    Wd[f"{p}.gate.weight"] = torch.zeros_like(Wd[f"{p}.gate.weight"])
-    Wd[f"{p}.gate.weight"][5] = 50.0 * h.mean(0).sign() / cfg["hidden_size"] * 0  # all ties -> expert 0
+    Wd[f"{p}.gate.weight"] = torch.zeros_like(Wd[f"{p}.gate.weight"])  # all logits tie: the lowest index, expert 0
     out = plain.moe_block(h, Wd, p, nos)
     e0 = plain.swiglu_mlp(h, *(Wd[f"{p}.experts.0.{n}.weight"] for n in ("gate_proj", "up_proj", "down_proj")))
     assert torch.allclose(out, e0 / cfg["num_experts"], atol=1e-12)  # p = 1/E without renormalisation
