@@ -376,6 +376,7 @@ def test_attn_chunk_tensor_cores(nh, nkv, hd, P, window):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 4, 16, 16, 0), (6, 2, 32, 64, 0), (5, 1, 48, 16, 0),
                                                 (16, 16, 128, 64, 0), (2, 1, 256, 64, 0), (4, 2, 64, 16, 300),
+                                                (4, 2, 128, 64, 300), (8, 8, 64, 32, 50), (6, 3, 32, 32, 0),
                                                 (4, 4, 80, 16, 7)])
 def test_attn_decode(dtype, nh, nkv, hd, P, window):
     segs = [(0, 1), (255, 1), (256, 1), (700, 1), (31, 1)]
@@ -396,6 +397,31 @@ def test_attn_decode(dtype, nh, nkv, hd, P, window):
                       part_ml=part_ml, counters=counters, max_splits=max_splits, **_dev(meta), **kw)
         close(out, ref, dtype, "attn_decode")
         assert int(counters.abs().sum()) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [0, 3000])
+def test_attn_decode_long_contexts(dtype, window):
+    """Thousands of keys per request and very different lengths in one batch: the streaming kernel cuts
+    them into many ranges (and, with few requests, into short ones)."""
+    nh, nkv, hd, P = 4, 2, 128, 64
+    segs = [(9000, 1), (5, 1), (4100, 1)]
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=11, n_pages=260)
+    items = torch.arange(len(segs), dtype=torch.int32)
+    max_splits = 9000 // K.DECODE_SPLIT + 1
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=window, scale=1 / math.sqrt(hd))
+    units = K.decode_units(len(segs), nh, hd, dtype, max_splits, DEV)
+    out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
+    part_o = torch.full((units * hd,), float("nan"), device=DEV)
+    part_ml = torch.full((2 * units,), float("nan"), device=DEV)
+    counters = torch.zeros(len(segs) * nh, dtype=torch.int32, device=DEV)
+    K.attn_decode(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=len(segs), part_o=part_o,
+                  part_ml=part_ml, counters=counters, max_splits=max_splits, **_dev(meta), **kw)
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.attn_decode(q, pool, ref, items=items, n_items=len(segs), part_o=None, part_ml=None, counters=None,
+                   max_splits=max_splits, **meta, **kw)
+    close(out, ref, dtype, "attn_decode, long")
+    assert int(counters.abs().sum()) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
