@@ -392,7 +392,8 @@ struct true_tag { static constexpr bool value = true; };
 struct false_tag { static constexpr bool value = false; };
 
 template <typename T, int LPK>
-__global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(AttnArgs a, int n_items, int max_units) {
+__global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(AttnArgs a, int n_items, int max_units,
+                                                                              int cost_range, int cost_merge) {
     pdl_entry();
     pdl_trigger();  // every block of this grid is resident from the start
     constexpr int VEC = 16 / sizeof(T);   // elements of a lane
@@ -405,15 +406,20 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
     __shared__ int s_first[DS_MAX_ITEMS];   // first key of item i, rounded down to 32
     __shared__ int s_nkeys[DS_MAX_ITEMS];   // keys from there to the query's own position
     __shared__ int s_pref[DS_MAX_ITEMS + 1];  // ranges of the items before i
+    __shared__ int s_seg[DS_MAX_ITEMS], s_pos[DS_MAX_ITEMS], s_row[DS_MAX_ITEMS];  // segment, position, row of q / out
     __shared__ unsigned long long s_best[DS_WARPS];
     __shared__ int s_len;
     int longest = 0;
     for (int i = tid; i < n_items; i += blockDim.x) {
-        const int p = a.seg_ctx[a.items[i]];
+        const int seg = a.items[i];
+        const int p = a.seg_ctx[seg];
         const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
         const int first = t_lo & ~31;
         s_first[i] = first;
         s_nkeys[i] = p - first + 1;
+        s_seg[i] = seg;
+        s_pos[i] = p;
+        s_row[i] = a.seg_q0[seg];
     }
     __syncthreads();
     for (int i = 0; i < n_items; ++i) longest = max(longest, s_nkeys[i]);
@@ -431,8 +437,8 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
             if (units > max_units) continue;  // the scratch does not hold that many partial results
             const long long rounds = (units + n_warps - 1) / n_warps;
             // the merge of a (request, head) runs in one warp and grows with its number of ranges
-            const unsigned long long cost = static_cast<unsigned long long>(rounds) * (len + DS_OVERHEAD) +
-                                            DS_MERGE * static_cast<unsigned long long>((longest + len - 1) / len);
+            const unsigned long long cost = static_cast<unsigned long long>(rounds) * (len + cost_range) +
+                                            cost_merge * static_cast<unsigned long long>((longest + len - 1) / len);
             best = min(best, (cost << 24) | static_cast<unsigned>(c));  // ties: the shorter range
         }
 #pragma unroll
@@ -473,9 +479,7 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
         int item = 0;
         while (s_pref[item + 1] <= r) ++item;  // few items: a linear search
         const int split = r - s_pref[item];
-        const int seg = a.items[item];
-        const int p = a.seg_ctx[seg];
-        const int row = a.seg_q0[seg];
+        const int seg = s_seg[item], p = s_pos[item], row = s_row[item];
         const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
         const int k_begin = s_first[item] + split * len;           // a multiple of 32: chunks do not straddle pages
         const int k_end = min(p + 1, k_begin + len);               // exclusive
@@ -616,25 +620,24 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
         float M = -INFINITY;
         for (int sidx = lane; sidx < n_splits; sidx += 32) M = fmaxf(M, __ldcg(a.part_ml + 2 * (u0 + static_cast<long long>(sidx) * a.nh)));
         M = warp_max(M);
-        float L = 0.f;  // lanes take the ranges in turn, then a fixed tree of shuffles adds the lanes
-        for (int sidx = lane; sidx < n_splits; sidx += 32) {
-            const long long us = u0 + static_cast<long long>(sidx) * a.nh;
-            L += __ldcg(a.part_ml + 2 * us + 1) * exp2f(__ldcg(a.part_ml + 2 * us) - M);
-        }
-        L = warp_sum(L);
-        const float inv = 1.0f / L;
+        // one more pass over the ranges, in ascending order: the denominator (every lane forms the same one)
+        // and this lane's four dimensions of the sum
         for (int d = lane * 4; d < hd; d += 128) {
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            float L = 0.f;
 #pragma unroll 16
             for (int sidx = 0; sidx < n_splits; ++sidx) {
                 const long long us = u0 + static_cast<long long>(sidx) * a.nh;
-                const float w = exp2f(__ldcg(a.part_ml + 2 * us) - M);
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(a.part_ml + 2 * us));
+                const float w = exp2f(ml.x - M);
                 const float4 v = __ldcg(reinterpret_cast<const float4*>(a.part_o + us * hd + d));
+                L = fmaf(ml.y, w, L);
                 o.x = fmaf(v.x, w, o.x);
                 o.y = fmaf(v.y, w, o.y);
                 o.z = fmaf(v.z, w, o.z);
                 o.w = fmaf(v.w, w, o.w);
             }
+            const float inv = 1.0f / L;
             T* dst = static_cast<T*>(a.out) + (static_cast<size_t>(row) * a.nh + h) * hd + d;
             dst[0] = from_f<T>(o.x * inv);
             dst[1] = from_f<T>(o.y * inv);
@@ -642,6 +645,13 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
             dst[3] = from_f<T>(o.w * inv);
         }
     }
+}
+
+// The two constants of the streaming kernel's cost model (in keys); a switch for measurements.
+static int g_ds_cost_range = DS_OVERHEAD, g_ds_cost_merge = DS_MERGE;
+extern "C" void locus_attn_decode_set_cost(int range_overhead, int merge_per_range) {
+    g_ds_cost_range = range_overhead;
+    g_ds_cost_merge = merge_per_range;
 }
 
 static int check_common(int nh, int nkv, int hd, int page_tokens, int window) {
@@ -724,13 +734,13 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
         const dim3 sgrid(n_sm * 4);
         const int units = static_cast<int>(max_units < (1 << 30) ? max_units : (1 << 30));
         if (dt == LOCUS_DT_F32) {
-            if (lpk == 8) locus_launch(attn_decode_stream_kernel<float, 8>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
-            else if (lpk == 16) locus_launch(attn_decode_stream_kernel<float, 16>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
-            else locus_launch(attn_decode_stream_kernel<float, 32>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
+            if (lpk == 8) locus_launch(attn_decode_stream_kernel<float, 8>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
+            else if (lpk == 16) locus_launch(attn_decode_stream_kernel<float, 16>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
+            else locus_launch(attn_decode_stream_kernel<float, 32>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
         } else {
-            if (lpk == 8) locus_launch(attn_decode_stream_kernel<bf16, 8>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
-            else if (lpk == 16) locus_launch(attn_decode_stream_kernel<bf16, 16>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
-            else locus_launch(attn_decode_stream_kernel<bf16, 32>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units);
+            if (lpk == 8) locus_launch(attn_decode_stream_kernel<bf16, 8>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
+            else if (lpk == 16) locus_launch(attn_decode_stream_kernel<bf16, 16>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
+            else locus_launch(attn_decode_stream_kernel<bf16, 32>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
         }
         return locus_launch_status();
     }

@@ -8,23 +8,24 @@
 //
 //   D[n, t] (tensor memory, lane n, column t) = sum_k W[n0 + n, k] * x[t0 + t, k]
 //
-// One CTA computes one 128 x TN output tile over the whole K (no split of K: the order of
-// the sum for an element depends on K only).  Warp 0 issues TMA loads (one elected thread),
-// warp 1 allocates tensor memory and issues the MMAs (one elected thread), warps 2-5 read
-// the accumulators back (tcgen05.ld, each warp its own 32 lanes) and run the epilogue:
-// bias, SwiGLU of two accumulators, per-row scale, store as bfloat16 / float32 or add into
-// a float32 tensor.  Grouped products (experts) take the tile list that moe_sort built.
+// A 128 x TN output tile is computed over the whole K by one CTA (no split of K: the order of
+// the sum for an element depends on K only).  The kernel is persistent: one CTA per SM walks
+// over the tiles in a fixed stride.  Warp 0 issues TMA loads (one elected thread) and runs
+// ahead across tile boundaries, so the pipeline never drains between tiles; warp 1 allocates
+// tensor memory and issues the MMAs (one elected thread) into one of TWO accumulator buffers;
+// warps 2-5 read the other buffer back (tcgen05.ld, each warp its own 32 lanes) and run the
+// epilogue while the next tile's MMAs run: bias, SwiGLU of two accumulators, per-row scale,
+// store as bfloat16 / float32 or add into a float32 tensor, through a small transpose in shared
+// memory so that stores are 16 or 32 bytes wide.  Grouped products (experts) take the tile list
+// that moe_sort built.
 //
-// Pairs (an option, off unless switched on: locus_gemm_tc_set_pair).  Two CTAs on neighbouring SMs (a
-// cluster of two) work as one: tcgen05.mma.cta_group::2 multiplies 256 weight rows (128 from each CTA's shared
-// memory) by the token tile, of which each CTA has loaded only half the rows, so a k-block costs a
-// CTA a third less traffic from L2 for the same MMA work.  Each CTA keeps the accumulators of its own
-// 128 weight rows in its own tensor memory and runs its own epilogue.  The CTA of rank 0 issues the
-// MMAs; the loads of both CTAs count their bytes at rank 0's barrier of the stage, and rank 0's commits
-// release the stage in both.  Measured on the products of a 2,048-token prefill step it is as fast as
-// two independent CTAs per SM, not faster: the thread that issues the MMAs, not the traffic from L2,
-// sets the pace there (an MMA instruction is accepted only when the tensor pipe has room: 4 MMAs of a
-// k-block take about 560 cycles to issue, the whole loop about 700).
+// What sets the pace (measured with clock stamps in the kernel, taken out again): the thread
+// that issues the MMAs -- an MMA is accepted only when the tensor pipe has room, 4 MMAs of a
+// k-block take about 560 cycles to issue and the whole loop about 700 -- and the epilogue, which
+// must stay well below the main loop of a tile to hide behind it.  Hence the lean issue loop,
+// and the SwiGLU switch as a template parameter: as a run-time flag the compiler evaluated the
+// SwiGLU arithmetic for every product and selected afterwards, which made the epilogue as long
+// as the main loop.
 //
 // Every wait on an mbarrier is bounded (about a second of clock cycles); when a wait runs
 // out the kernel records a code in the module's error word, stops waiting and finishes, so
@@ -41,8 +42,12 @@
 
 __device__ int g_tc_error = 0;
 
+struct TileGeom {
+    int x_row0, rows_valid, tx, w_row0;  // first token row, live token rows, weight tile, first weight row
+};
+
 struct TcArgs {
-    int M, N, K, TN, dual, stages, tmem_cols, pair, kps;
+    int M, N, K, TN, dual, stages, tmem_cols, tiles_x, tiles_y, acc_bufs;
     int accumulate;
     void* out;
     int out_dt;
@@ -81,11 +86,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
 // Bounded wait: false (and the error word set to `code`) when the limit runs out.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int code) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -102,18 +102,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int cod
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
     asm volatile(
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
-        : "memory");
-}
-
-// The load of the second CTA of a pair: the data goes to its own shared memory, the bytes are counted
-// at the barrier at the same place in the FIRST CTA's shared memory (cta_group::2 allows a barrier of
-// the other CTA of the pair; no multicast).
-__device__ __forceinline__ void tma_load_2d_to_leader(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-    asm volatile(
-        "{\n\t.reg .b32 rb;\n\t"
-        "mapa.shared::cluster.u32 rb, %4, 0;\n\t"
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [rb];\n\t}"
         ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
         : "memory");
 }
@@ -142,24 +130,6 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
-// The pair's forms: one MMA over both CTAs' operands, and a commit that arrives at the barrier at
-// this place in both CTAs.
-__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
-    asm volatile(
-        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
-        ::"r"(bar), "h"(static_cast<uint16_t>(3))
-        : "memory");
-}
-
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -168,262 +138,344 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
         : "r"(taddr));
 }
 
-// PAIR: the form for clusters of two CTAs.  (A kernel that contains cta_group::2 instructions can only
-// be launched in such clusters, hence two instantiations.)
-template <bool PAIR>
-__global__ void __launch_bounds__(192, 2)
+// Persistent kernel: a block walks over output tiles (tile index t = blockIdx.x, + gridDim.x, ...;
+// the token tile varies fastest so that blocks running at the same time share weight tiles in L2).
+// The loader runs ahead across tile boundaries, so the pipeline never drains between tiles, and
+// two accumulator buffers in tensor memory let the MMAs of the next tile run while the epilogue
+// warps drain this one.
+template <bool DUAL>
+__global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
                const __grid_constant__ CUtensorMap map_x, TcArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int rank = PAIR ? (blockIdx.x & 1) : 0;  // place in the pair (the cluster is 2 x 1 x 1)
 
-    int x_row0, rows_valid;
-    long long w_row0 = static_cast<long long>(blockIdx.x) * TILE_W;
-    if (a.tile_expert != nullptr) {
-        const int tile = blockIdx.y;
-        if (tile >= *a.n_tiles) return;  // uniform for the whole block
-        x_row0 = a.tile_row0[tile];
-        rows_valid = a.tile_rows[tile];
-        w_row0 += static_cast<long long>(a.tile_expert[tile]) * a.N;
-    } else {
-        x_row0 = blockIdx.y * a.TN;
-        rows_valid = min(a.TN, a.M - x_row0);
-    }
+    const int tiles_y = a.tiles_y;
+    const int n_y = a.tile_expert != nullptr ? min(tiles_y, *a.n_tiles) : tiles_y;  // live token tiles
+    // only live tiles are numbered, so that every block gets the same number of them (within one)
+    const long long n_total = static_cast<long long>(a.tiles_x) * n_y;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
-    const uint32_t x_bytes = static_cast<uint32_t>(PAIR ? a.TN / 2 : a.TN) * TILE_K * 2;  // a pair: half the rows each
-    // a stage holds a.kps k-blocks ("sub-stages": weights, second weights, tokens, each of one k-block)
-    const uint32_t sub_bytes = A_BYTES * (1 + a.dual) + x_bytes;
-    const uint32_t stage_bytes = a.kps * sub_bytes;
+    const uint32_t x_bytes = static_cast<uint32_t>(a.TN) * TILE_K * 2;
+    const uint32_t stage_bytes = A_BYTES * (1 + DUAL) + x_bytes;
     const uint32_t bars = base + a.stages * stage_bytes;
-    // barriers: full[s] at bars + 8 s, empty[s] at bars + 8 (stages + s), accumulator-ready, then the TMEM slot
-    const uint32_t bar_full = bars, bar_empty = bars + 8 * a.stages, bar_acc = bars + 16 * a.stages;
-    const uint32_t slot = bar_acc + 8;
+    // barriers: full[s], empty[s], accumulator full[2], accumulator empty[2], then the TMEM slot
+    const uint32_t bar_full = bars, bar_empty = bars + 8 * a.stages;
+    const uint32_t bar_acc_full = bars + 16 * a.stages, bar_acc_empty = bar_acc_full + 16;
+    const uint32_t slot = bar_acc_empty + 16;
     volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (slot - smem_u32(smem_raw)));
+    const int acc_cols = a.TN * (1 + DUAL);  // columns of one accumulator buffer
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < a.stages; ++s) {
             mbar_init(bar_full + 8 * s, 1);
             mbar_init(bar_empty + 8 * s, 1);
         }
-        mbar_init(bar_acc, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + 8 * b, 1);
+            mbar_init(bar_acc_empty + 8 * b, 4);  // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {
-        if (PAIR) {  // warp 1 of both CTAs, the same slot in both
-            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(a.tmem_cols) : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-        } else {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(a.tmem_cols) : "memory");
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-        }
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot), "r"(a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (PAIR) cluster_sync();  // the other CTA's barriers are initialised before anything arrives at them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *slot_ptr;
     const int nkb = (a.K + TILE_K - 1) / TILE_K;
 
-    // MMA N covers only the valid token rows of this tile, rounded up to 16: a ragged last tile (or an
-    // expert with few rows) costs MMA time for its rows, not for the whole tile.  In a pair the MMA takes
-    // the first n_mma / 2 token rows from each CTA, so rank 1 loads the rows from x_row0 + n_mma / 2 on.
-    const int n_mma = min(a.TN, (rows_valid + 15) & ~15);
+    // Per-tile geometry, the same for every role.  For grouped products it comes from the tile list in
+    // global memory; every role fetches it a tile or more ahead so that the latency of those loads
+    // falls into the work on the tile before.
+    auto tile_geom = [&](long long t) -> TileGeom {
+        TileGeom g;
+        g.x_row0 = 0;
+        g.rows_valid = 0;
+        g.tx = 0;
+        g.w_row0 = 0;
+        if (t >= n_total) return g;  // past the end: an empty tile, never worked on
+        const int ti = static_cast<int>(t);  // the host refuses products of 2^31 tiles or more
+        const int ty = ti / a.tiles_x;  // blocks that run together share a token tile
+        g.tx = ti - ty * a.tiles_x;
+        g.w_row0 = g.tx * TILE_W;
+        if (a.tile_expert != nullptr) {
+            g.x_row0 = a.tile_row0[ty];
+            g.rows_valid = a.tile_rows[ty];
+            g.w_row0 += a.tile_expert[ty] * a.N;  // the host refuses weights of 2^31 rows or more
+        } else {
+            g.x_row0 = ty * a.TN;
+            g.rows_valid = min(a.TN, a.M - g.x_row0);
+        }
+        return g;
+    };
+    const long long t_step = gridDim.x;
+
     if (warp == 0) {
         if (lane == 0) {
-            const int x_first = x_row0 + rank * (n_mma / 2);
-            int s = 0;
+            int s = 0;          // stage of the ring, running over all tiles
             uint32_t round = 0;  // how often the ring has wrapped (its low bit is the barriers' phase)
-            for (int kb = 0; kb < nkb; kb += a.kps, ++s) {
-                if (s == a.stages) {
-                    s = 0;
-                    ++round;
-                }
-                mbar_wait(bar_empty + 8 * s, (round & 1) ^ 1, 1);
-                const int nsub = min(a.kps, nkb - kb);
-                if (!(PAIR && rank == 1))  // rank 0's barrier counts the bytes of both CTAs of a pair
-                    mbar_expect_tx(bar_full + 8 * s, (PAIR ? 2 : 1) * nsub * sub_bytes);
-                for (int j = 0; j < nsub; ++j) {
-                    const uint32_t st = base + s * stage_bytes + j * sub_bytes;
-                    const int k0 = (kb + j) * TILE_K;
-                    if (PAIR && rank == 1) {
-                        tma_load_2d_to_leader(st, &map_w, k0, static_cast<int>(w_row0), bar_full + 8 * s);
-                        if (a.dual) tma_load_2d_to_leader(st + A_BYTES, &map_w2, k0, static_cast<int>(w_row0), bar_full + 8 * s);
-                        tma_load_2d_to_leader(st + A_BYTES * (1 + a.dual), &map_x, k0, x_first, bar_full + 8 * s);
-                    } else {
-                        tma_load_2d(st, &map_w, k0, static_cast<int>(w_row0), bar_full + 8 * s);
-                        if (a.dual) tma_load_2d(st + A_BYTES, &map_w2, k0, static_cast<int>(w_row0), bar_full + 8 * s);
-                        tma_load_2d(st + A_BYTES * (1 + a.dual), &map_x, k0, x_first, bar_full + 8 * s);
+            bool ok = true;      // false once a bounded wait ran out: the role stops
+            TileGeom g = tile_geom(blockIdx.x);
+            for (long long t = blockIdx.x; t < n_total && ok; t += t_step) {
+                const TileGeom g_next = tile_geom(t + t_step);
+                const int x_row0 = g.x_row0, w_row0 = g.w_row0;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(bar_empty + 8 * s, (round & 1) ^ 1, 1)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t st = base + s * stage_bytes;
+                    mbar_expect_tx(bar_full + 8 * s, stage_bytes);
+                    tma_load_2d(st, &map_w, kb * TILE_K, w_row0, bar_full + 8 * s);
+                    if (DUAL) tma_load_2d(st + A_BYTES, &map_w2, kb * TILE_K, w_row0, bar_full + 8 * s);
+                    tma_load_2d(st + A_BYTES * (1 + DUAL), &map_x, kb * TILE_K, x_row0, bar_full + 8 * s);
+                    if (++s == a.stages) {
+                        s = 0;
+                        ++round;
                     }
                 }
+                g = g_next;
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && rank == 0) {  // rank 0 issues the MMAs of a pair
-            // instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major, N = n_mma,
-            // M = 128 (256 over a pair)
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n_mma >> 3) << 17) |
-                                   (static_cast<uint32_t>((PAIR ? 2 * TILE_W : TILE_W) >> 4) << 24);
-            // The thread that issues the MMAs is the pace-maker of the tile: an MMA is accepted only when
-            // the tensor pipe has room, so whatever this thread does between the last MMA of one k-block
-            // and the first of the next is time the pipe may stand idle.  Hence: no divisions, descriptors
-            // advanced by addition, and the barrier of the next stage is looked at right after this stage's
-            // MMAs went out (while they run), so that the wait at the top of the loop is usually over.
+        if (lane == 0) {
+            // This thread sets the pace of the block: an MMA is accepted only when the tensor pipe has room,
+            // so what the thread does between the last MMA of one k-block and the first of the next is time
+            // the pipe may stand idle.  Hence no divisions, descriptors advanced by addition, and a look at
+            // the next stage's barrier right after this stage's MMAs went out.
+            unsigned n_done = 0;
+            int s = 0, buf = 0;
+            uint32_t round = 0, acc_round = 0;
+            bool ok = true;
             const uint64_t desc0 = make_desc(base);
             const uint64_t stage_units = stage_bytes >> 4;  // descriptors count in 16-byte units
-            const uint64_t sub_units = sub_bytes >> 4;
-            const uint64_t w2_units = A_BYTES >> 4, x_units = (A_BYTES * (1 + a.dual)) >> 4;
-            int s = 0;
-            uint32_t round = 0;
-            bool ready = mbar_try_wait(bar_full, 0);
-            for (int kb = 0; kb < nkb; kb += a.kps) {
-                if (!ready) mbar_wait(bar_full + 8 * s, round & 1, 2);
+            const uint64_t w2_units = A_BYTES >> 4, x_units = (A_BYTES * (1 + DUAL)) >> 4;
+            bool ready = false;
+            TileGeom g = tile_geom(blockIdx.x);
+            for (long long t = blockIdx.x; t < n_total && ok; t += t_step) {
+                const TileGeom g_next = tile_geom(t + t_step);
+                const int rows_valid = g.rows_valid;
+                g = g_next;
+                // the epilogue must have drained this buffer (acc_bufs tiles ago)
+                if (!mbar_wait(bar_acc_empty + 8 * buf, (acc_round & 1) ^ 1, 4)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int nsub = min(a.kps, nkb - kb);
-                for (int j = 0; j < nsub; ++j) {
-                    const uint64_t dw = desc0 + s * stage_units + j * sub_units, dw2 = dw + w2_units, dx = dw + x_units;
-                    if (PAIR) {
-#pragma unroll
-                        for (int k4 = 0; k4 < TILE_K / 16; ++k4) {
-                            const uint32_t acc = (kb + j > 0 || k4 > 0) ? 1u : 0u;
-                            umma_bf16_pair(tmem, dw + 2 * k4, dx + 2 * k4, idesc, acc);  // 16 elements = 32 bytes = 2 units
-                            if (a.dual) umma_bf16_pair(tmem + a.TN, dw2 + 2 * k4, dx + 2 * k4, idesc, acc);
-                        }
-                    } else {
-#pragma unroll
-                        for (int k4 = 0; k4 < TILE_K / 16; ++k4) {
-                            const uint32_t acc = (kb + j > 0 || k4 > 0) ? 1u : 0u;
-                            umma_bf16(tmem, dw + 2 * k4, dx + 2 * k4, idesc, acc);
-                            if (a.dual) umma_bf16(tmem + a.TN, dw2 + 2 * k4, dx + 2 * k4, idesc, acc);
-                        }
+                // instruction descriptor: f32 accumulate, bf16 x bf16, both operands K-major, M = 128; N covers
+                // only the valid token rows of this tile, rounded up to 16: a ragged tile (or an expert with
+                // few rows) costs MMA time for its rows, not for the whole tile
+                const int n_mma = min(a.TN, (rows_valid + 15) & ~15);
+                const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n_mma >> 3) << 17) |
+                                       (static_cast<uint32_t>(TILE_W >> 4) << 24);
+                const uint32_t d0 = tmem + buf * acc_cols;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!ready && !mbar_wait(bar_full + 8 * s, round & 1, 2)) {
+                        ok = false;
+                        break;
                     }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t dw = desc0 + s * stage_units, dw2 = dw + w2_units, dx = dw + x_units;
+#pragma unroll
+                    for (int k4 = 0; k4 < TILE_K / 16; ++k4) {
+                        const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+                        umma_bf16(d0, dw + 2 * k4, dx + 2 * k4, idesc, acc);  // 16 elements = 32 bytes = 2 units
+                        if (DUAL) umma_bf16(d0 + a.TN, dw2 + 2 * k4, dx + 2 * k4, idesc, acc);
+                    }
+                    umma_commit(bar_empty + 8 * s);  // the stage is free when these MMAs have read it
+                    if (++s == a.stages) {
+                        s = 0;
+                        ++round;
+                    }
+                    ready = mbar_try_wait(bar_full + 8 * s, round & 1);  // (past the last stage: simply not ready)
                 }
-                // the stage is free when these MMAs have read it (in both CTAs of a pair)
-                if (PAIR) umma_commit_pair(bar_empty + 8 * s); else umma_commit(bar_empty + 8 * s);
-                if (++s == a.stages) {
-                    s = 0;
-                    ++round;
+                if (!ok) break;
+                umma_commit(bar_acc_full + 8 * buf);
+                ++n_done;
+                if (++buf == a.acc_bufs) {
+                    buf = 0;
+                    ++acc_round;
                 }
-                ready = kb + a.kps < nkb && mbar_try_wait(bar_full + 8 * s, round & 1);
             }
-            if (PAIR) umma_commit_pair(bar_acc); else umma_commit(bar_acc);
         }
     } else {
         const int quarter = warp & 3;  // tensor-memory lanes this warp may read
         const int row = quarter * 32 + lane;
-        const long long n = static_cast<long long>(blockIdx.x) * TILE_W + row;  // output column
-        const bool n_ok = n < a.N;
-        // while the MMAs run: the scale of every token row of the tile -> shared memory
-        float* scales = reinterpret_cast<float*>(smem_raw + (slot + 16 - smem_u32(smem_raw)));
-        if (a.row_scale) {
-            for (int c = threadIdx.x - 64; c < a.TN; c += 128) {
-                const int r = x_row0 + c;
-                scales[c] = c < rows_valid ? a.row_scale[a.scale_rows ? a.scale_rows[r] : r] : 0.f;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps only
-        }
-        const float bias = (a.bias && n_ok) ? ld_dyn(a.bias, a.bias_dt, n) : 0.f;
-        // Wide stores: the warp's 32 output columns x 16 token rows go through a small transpose in
-        // shared memory so that a lane writes 8 consecutive columns of one token (16 or 32 bytes).
-        // Needs rows of out that start on 16-byte boundaries and a full 32-column stripe.
-        float* stage = reinterpret_cast<float*>(smem_raw + ((slot + 16 + 4 * a.TN + 15) & ~15u) - smem_u32(smem_raw)) +
+        // each epilogue warp keeps its own copy of the tile's row scales: no barrier between the warps
+        float* scales = reinterpret_cast<float*>(smem_raw + (slot + 16 - smem_u32(smem_raw))) + (warp - 2) * a.TN;
+        float* stage = reinterpret_cast<float*>(smem_raw + ((slot + 16 + 16 * a.TN + 15) & ~15u) - smem_u32(smem_raw)) +
                        (warp - 2) * (16 * 36);
-        const long long n_warp = static_cast<long long>(blockIdx.x) * TILE_W + quarter * 32;
         const int esize = a.out_dt == LOCUS_DT_F32 ? 4 : 2;
-        const bool wide = n_warp + 32 <= a.N && (a.ldo * esize) % 16 == 0 &&
-                          (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
-        mbar_wait(bar_acc, 0, 3);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t lane_addr = tmem + (static_cast<uint32_t>(quarter * 32) << 16);
+        const bool rows_aligned = (a.ldo * esize) % 16 == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
         float* outf = static_cast<float*>(a.out);
-        for (int c0 = 0; c0 < a.TN; c0 += 16) {
-            if (c0 >= rows_valid) break;  // uniform
-            uint32_t v[16], u[16];
-            tmem_ld16(lane_addr + c0, v);
-            if (a.dual) tmem_ld16(lane_addr + a.TN + c0, u);
-            // narrow add-into epilogue: fetch the 16 old values while the accumulators arrive
-            float old[16];
-            if (a.accumulate && !wide) {
+        unsigned n_done = 0;
+        int buf = 0;
+        uint32_t acc_round = 0;
+        // Row scales come through two dependent loads (row index, then scale) behind the tile list: the
+        // lane holds the scales of this tile, the row indices of the next and the geometry of the two
+        // after it, each fetched one tile before it is needed.
+        constexpr int NS = 256 / 32;  // token rows of a tile per lane
+        TileGeom g = tile_geom(blockIdx.x), g1 = tile_geom(blockIdx.x + t_step), g2 = tile_geom(blockIdx.x + 2 * t_step);
+        auto scale_index = [&](const TileGeom& q, int k) -> int {
+            const int c = lane + 32 * k;
+            if (c >= q.rows_valid) return -1;
+            return a.scale_rows ? a.scale_rows[q.x_row0 + c] : q.x_row0 + c;
+        };
+        float sc[NS];
+        int idx1[NS];
+        if (a.row_scale) {
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const bool ok = n_ok && c0 + j < rows_valid;
-                    old[j] = ok ? outf[static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n] : 0.f;
-                }
+            for (int k = 0; k < NS; ++k) {
+                const int i0 = scale_index(g, k);
+                sc[k] = i0 >= 0 ? a.row_scale[i0] : 0.f;
+                idx1[k] = scale_index(g1, k);
             }
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-            float val[16];
+        }
+        for (long long t = blockIdx.x; t < n_total; t += t_step) {
+            const TileGeom g3 = tile_geom(t + 3 * t_step);
+            const int x_row0 = g.x_row0, rows_valid = g.rows_valid, tx = g.tx;
+            const long long n = static_cast<long long>(tx) * TILE_W + row;  // output column of this lane
+            const bool n_ok = n < a.N;
+            if (a.row_scale) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                float x = __uint_as_float(v[j]);
-                if (a.dual) {
-                    const float g = x;
-                    x = g / (1.0f + expf(-g)) * __uint_as_float(u[j]);
+                for (int k = 0; k < NS; ++k) {
+                    if (lane + 32 * k < a.TN) scales[lane + 32 * k] = sc[k];
                 }
-                x += bias;
-                if (a.row_scale) x *= scales[c0 + j];
-                val[j] = x;
-            }
-            if (wide) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) stage[j * 36 + lane] = val[j];
                 __syncwarp();
 #pragma unroll
+                for (int k = 0; k < NS; ++k) {
+                    sc[k] = idx1[k] >= 0 ? a.row_scale[idx1[k]] : 0.f;  // the next tile's
+                    idx1[k] = scale_index(g2, k);                        // the one after
+                }
+            }
+            g = g1;
+            g1 = g2;
+            g2 = g3;
+            const float bias = (a.bias && n_ok) ? ld_dyn(a.bias, a.bias_dt, n) : 0.f;
+            // Wide stores: the warp's 32 output columns x 16 token rows go through a small transpose in
+            // shared memory so that a lane writes 8 consecutive columns of one token (16 or 32 bytes).
+            const long long n_warp = static_cast<long long>(tx) * TILE_W + quarter * 32;
+            const bool wide = rows_aligned && n_warp + 32 <= a.N;
+            // Add-into with wide stores reads the old values of out: those loads do not depend on the
+            // accumulators, so they are issued one 16-row step ahead (the first before the accumulators
+            // are waited for) and their latency falls into the step before.
+            const bool rmw = wide && a.accumulate;
+            const int c_end = min(a.TN, rows_valid);
+            const int wj = lane >> 2, wc = (lane & 3) * 8;  // token row (of 8) and first column of a wide store
+            auto load_old = [&](int c0, float4 (&o)[4]) {
+#pragma unroll
                 for (int half = 0; half < 2; ++half) {
-                    const int j = (lane >> 2) + 8 * half;
+                    const int j = wj + 8 * half;
                     if (c0 + j < rows_valid) {
-                        const int c = (lane & 3) * 8;
-                        const float4 lo = *reinterpret_cast<const float4*>(stage + j * 36 + c);
-                        const float4 hi = *reinterpret_cast<const float4*>(stage + j * 36 + c + 4);
-                        const size_t o = static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n_warp + c;
-                        if (a.out_dt == LOCUS_DT_F32) {
-                            float4* dst = reinterpret_cast<float4*>(outf + o);
-                            if (a.accumulate) {
-                                const float4 p0 = dst[0], p1 = dst[1];
-                                dst[0] = make_float4(p0.x + lo.x, p0.y + lo.y, p0.z + lo.z, p0.w + lo.w);
-                                dst[1] = make_float4(p1.x + hi.x, p1.y + hi.y, p1.z + hi.z, p1.w + hi.w);
-                            } else {
+                        const float4* src = reinterpret_cast<const float4*>(
+                            outf + static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n_warp + wc);
+                        o[2 * half] = src[0];
+                        o[2 * half + 1] = src[1];
+                    }
+                }
+            };
+            float4 old_a[4], old_b[4];
+            if (rmw) load_old(0, old_a);
+            if (!mbar_wait(bar_acc_full + 8 * buf, acc_round & 1, 3)) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t lane_addr = tmem + buf * acc_cols + (static_cast<uint32_t>(quarter * 32) << 16);
+            auto do_cols = [&](int c0, const float4 (&oldw)[4]) {
+                uint32_t v[16], u[16];
+                tmem_ld16(lane_addr + c0, v);
+                if (DUAL) tmem_ld16(lane_addr + a.TN + c0, u);
+                // narrow add-into epilogue: fetch the 16 old values while the accumulators arrive
+                float old[16];
+                if (a.accumulate && !wide) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const bool ok = n_ok && c0 + j < rows_valid;
+                        old[j] = ok ? outf[static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n] : 0.f;
+                    }
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                float val[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float x = __uint_as_float(v[j]);
+                    if (DUAL) {
+                        const float g = x;
+                        x = __fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(u[j]);
+                    }
+                    x += bias;
+                    if (a.row_scale) x *= scales[c0 + j];
+                    val[j] = x;
+                }
+                if (wide) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) stage[j * 36 + lane] = val[j];
+                    __syncwarp();
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const int j = wj + 8 * half;
+                        if (c0 + j < rows_valid) {
+                            float4 lo = *reinterpret_cast<const float4*>(stage + j * 36 + wc);
+                            float4 hi = *reinterpret_cast<const float4*>(stage + j * 36 + wc + 4);
+                            const size_t o = static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n_warp + wc;
+                            if (a.out_dt == LOCUS_DT_F32) {
+                                float4* dst = reinterpret_cast<float4*>(outf + o);
+                                if (a.accumulate) {
+                                    const float4 p0 = oldw[2 * half], p1 = oldw[2 * half + 1];
+                                    lo = make_float4(p0.x + lo.x, p0.y + lo.y, p0.z + lo.z, p0.w + lo.w);
+                                    hi = make_float4(p1.x + hi.x, p1.y + hi.y, p1.z + hi.z, p1.w + hi.w);
+                                }
                                 dst[0] = lo;
                                 dst[1] = hi;
+                            } else {
+                                __nv_bfloat162 b0 = __floats2bfloat162_rn(lo.x, lo.y), b1 = __floats2bfloat162_rn(lo.z, lo.w);
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(hi.x, hi.y), b3 = __floats2bfloat162_rn(hi.z, hi.w);
+                                uint4 pk;
+                                pk.x = *reinterpret_cast<uint32_t*>(&b0);
+                                pk.y = *reinterpret_cast<uint32_t*>(&b1);
+                                pk.z = *reinterpret_cast<uint32_t*>(&b2);
+                                pk.w = *reinterpret_cast<uint32_t*>(&b3);
+                                *reinterpret_cast<uint4*>(static_cast<bf16*>(a.out) + o) = pk;
                             }
+                        }
+                    }
+                    __syncwarp();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j >= rows_valid || !n_ok) continue;
+                        const size_t o = static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n;
+                        if (a.accumulate) {
+                            outf[o] = old[j] + val[j];
                         } else {
-                            __nv_bfloat162 b0 = __floats2bfloat162_rn(lo.x, lo.y), b1 = __floats2bfloat162_rn(lo.z, lo.w);
-                            __nv_bfloat162 b2 = __floats2bfloat162_rn(hi.x, hi.y), b3 = __floats2bfloat162_rn(hi.z, hi.w);
-                            uint4 pk;
-                            pk.x = *reinterpret_cast<uint32_t*>(&b0);
-                            pk.y = *reinterpret_cast<uint32_t*>(&b1);
-                            pk.z = *reinterpret_cast<uint32_t*>(&b2);
-                            pk.w = *reinterpret_cast<uint32_t*>(&b3);
-                            *reinterpret_cast<uint4*>(static_cast<bf16*>(a.out) + o) = pk;
+                            st_dyn(a.out, a.out_dt, o, val[j]);
                         }
                     }
                 }
-                __syncwarp();
-            } else {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    if (c0 + j >= rows_valid || !n_ok) continue;
-                    const size_t o = static_cast<size_t>(x_row0 + c0 + j) * a.ldo + n;
-                    if (a.accumulate) {
-                        outf[o] = old[j] + val[j];
-                    } else {
-                        st_dyn(a.out, a.out_dt, o, val[j]);
-                    }
+            };
+            for (int c0 = 0; c0 < c_end; c0 += 32) {  // uniform bounds
+                if (rmw && c0 + 16 < c_end) load_old(c0 + 16, old_b);
+                do_cols(c0, old_a);
+                if (c0 + 16 < c_end) {
+                    if (rmw && c0 + 32 < c_end) load_old(c0 + 32, old_a);
+                    do_cols(c0 + 16, old_b);
                 }
+            }
+            // this warp has read everything it needs from the buffer: hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_acc_empty + 8 * buf) : "memory");
+            ++n_done;
+            if (++buf == a.acc_bufs) {
+                buf = 0;
+                ++acc_round;
             }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (PAIR) cluster_sync();  // neither CTA leaves while the other may still reach into it
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (PAIR) {
-            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
-        } else {
-            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
-        }
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(a.tmem_cols) : "memory");
     }
 }
 
@@ -462,12 +514,6 @@ static bool make_map(CUtensorMap* map, const void* ptr, long long rows, long lon
 
 // Shared-memory budget of the pipeline in KiB; 0 = chosen from the grid size (see below).
 static int g_budget_kb = 0;
-// Pairs of CTAs on (1) or off (0).
-static int g_pair = 0;
-// k-blocks per pipeline stage (1 or 2): with 2 a barrier round covers 8 MMAs instead of 4.
-static int g_kps = 1;
-extern "C" void locus_gemm_tc_set_kps(int k) { g_kps = k == 2 ? 2 : 1; }
-extern "C" void locus_gemm_tc_set_pair(int on) { g_pair = on; }
 extern "C" void locus_gemm_tc_set_budget_kb(int kb) { g_budget_kb = kb; }
 
 static int pow2_at_least(int v) {
@@ -495,32 +541,31 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     CUtensorMap map_w, map_w2, map_x;
     if (!make_map(&map_w, w, w_rows_total, K, K, TILE_W)) return LOCUS_ERR_UNSUPPORTED;
     if (!make_map(&map_w2, dual ? w2 : w, w_rows_total, K, K, TILE_W)) return LOCUS_ERR_UNSUPPORTED;
-    // pairs of CTAs (see the head of the file) wherever there are two weight tiles to pair
-    const int pair = (g_pair && N > TILE_W) ? 1 : 0;
-    if (!make_map(&map_x, x, x_rows_total, K, ldx, pair ? TN / 2 : TN)) return LOCUS_ERR_UNSUPPORTED;
+    if (!make_map(&map_x, x, x_rows_total, K, ldx, TN)) return LOCUS_ERR_UNSUPPORTED;
     TcArgs a;
-    a.M = M; a.N = N; a.K = K; a.TN = TN; a.dual = dual; a.pair = pair;
-    const int kps = g_kps;
-    a.kps = kps;
-    const int stage_bytes = kps * (A_BYTES * (1 + dual) + (pair ? TN / 2 : TN) * TILE_K * 2);
+    a.M = M; a.N = N; a.K = K; a.TN = TN; a.dual = dual;
+    const int stage_bytes = A_BYTES * (1 + dual) + TN * TILE_K * 2;
     const int tiles_y = tile_expert ? max_tiles : ceil_div(M, TN);
-    const long long n_blocks = static_cast<long long>(ceil_div(N, TILE_W)) * tiles_y;
-    // A grid of more than one block per SM runs two blocks per SM (the epilogue of one overlaps
-    // the MMAs of the other): half the shared memory each.  A small grid gets deep pipelines.
-    const int budget = g_budget_kb > 0 ? g_budget_kb * 1024 : (n_blocks > 160 ? 100 * 1024 : 200 * 1024);
+    const int tiles_x = ceil_div(N, TILE_W);
+    const long long n_tiles_all = static_cast<long long>(tiles_x) * tiles_y;
+    // one block per SM with the whole shared memory as its pipeline
+    const int budget = (g_budget_kb > 0 ? g_budget_kb : 200) * 1024;
     int stages = budget / stage_bytes;
     if (stages > 12) stages = 12;
     if (stages < 2) stages = 2;
     const int nkb = (K + TILE_K - 1) / TILE_K;
-    if (stages > (nkb + kps - 1) / kps) stages = (nkb + kps - 1) / kps;
+    if (stages > nkb) stages = nkb;
     if (stages < 1) return LOCUS_ERR_UNSUPPORTED;
     a.stages = stages;
-    a.tmem_cols = pow2_at_least(TN * (1 + dual));
+    // two accumulator buffers where the 512 columns of tensor memory hold them
+    a.acc_bufs = 2 * TN * (1 + dual) <= 512 ? 2 : 1;
+    a.tmem_cols = pow2_at_least(a.acc_bufs * TN * (1 + dual));
     if (a.tmem_cols > 512) return LOCUS_ERR_UNSUPPORTED;
+    a.tiles_x = tiles_x; a.tiles_y = tiles_y;
     a.accumulate = accumulate; a.out = out; a.out_dt = out_dt; a.ldo = ldo; a.bias = bias; a.bias_dt = bias_dt;
     a.row_scale = row_scale; a.scale_rows = scale_rows; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles;
-    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 16 * stages + 64 + 4 * TN + 4 * 16 * 36 * 4 + 1024;
+    const size_t smem = static_cast<size_t>(stages) * stage_bytes + 16 * stages + 96 + 16 * TN + 4 * 16 * 36 * 4 + 1024;
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(gemm_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess ||
@@ -529,26 +574,16 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
         attr_set = true;
     }
     if (tiles_y <= 0) return 0;
-    if (tiles_y > 65535) return LOCUS_ERR_UNSUPPORTED;
-    dim3 grid(ceil_div(N, TILE_W), tiles_y);
-    if (pair) grid.x = (grid.x + 1) & ~1u;  // whole pairs: a last CTA without weight rows computes zeros and stores nothing
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(192);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = pair ? 1 : 0;
-    if (pair) {
-        cudaLaunchKernelEx(&cfg, gemm_tc_kernel<true>, map_w, map_w2, map_x, a);
-    } else {
-        cudaLaunchKernelEx(&cfg, gemm_tc_kernel<false>, map_w, map_w2, map_x, a);
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
+            return static_cast<int>(cudaGetLastError());
     }
+    const unsigned grid = static_cast<unsigned>(n_tiles_all < n_sm ? n_tiles_all : n_sm);
+    if (dual) gemm_tc_kernel<true><<<grid, 192, smem, stream>>>(map_w, map_w2, map_x, a);
+    else gemm_tc_kernel<false><<<grid, 192, smem, stream>>>(map_w, map_w2, map_x, a);
     return locus_launch_status();
 }
 

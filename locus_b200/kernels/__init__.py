@@ -264,18 +264,6 @@ def expert_tile(n_pairs: int, n_experts: int) -> int:
     return 16
 
 
-def tc_options(*, pairs: Optional[bool] = None, k_blocks_per_stage: Optional[int] = None) -> None:
-    """Options of the tensor-core product kernel: ``pairs`` runs it as clusters of two CTAs that
-    share one MMA (cta_group::2; off by default, it measured no faster than two CTAs per SM),
-    ``k_blocks_per_stage`` (1 or 2) is how much of K one pipeline stage holds."""
-    lib = _lib("gemm_tc")
-    if pairs is not None:
-        lib.locus_gemm_tc_set_pair(I(1 if pairs else 0))
-    if k_blocks_per_stage is not None:
-        _need(k_blocks_per_stage in (1, 2), "tc_options: 1 or 2 k-blocks per stage")
-        lib.locus_gemm_tc_set_kps(I(k_blocks_per_stage))
-
-
 def tc_error() -> int:
     """Error word of the tensor-core module (0 = fine); reading it synchronises the device.
     Non-zero: a bounded wait inside a kernel ran out (1 producer, 2 MMA, 3 epilogue)."""

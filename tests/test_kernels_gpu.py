@@ -62,31 +62,6 @@ def test_rmsnorm(dtype, H):
     close(out2, ref[rows.long()], dtype, "rmsnorm rows")
 
 
-@pytest.mark.parametrize("pairs,kps", [(True, 1), (True, 2), (False, 2)])
-@pytest.mark.parametrize("M,N,K_,dual", [(300, 1408, 2048, True), (129, 256, 2048 + 64, False), (70, 130, 72, False),
-                                          (2048, 640, 192, False)])
-def test_tensor_core_options_give_the_same_product(pairs, kps, M, N, K_, dual):
-    """Clusters of two CTAs sharing an MMA, and two k-blocks per stage: the same sums in the same
-    order as the default form, so the same bits."""
-    x, w = rnd(M, K_, dtype=torch.bfloat16, seed=3).to(DEV), rnd(N, K_, dtype=torch.bfloat16, seed=4, scale=0.1).to(DEV)
-    w2 = rnd(N, K_, dtype=torch.bfloat16, seed=5, scale=0.1).to(DEV) if dual else None
-    bias = rnd(N, dtype=torch.bfloat16, seed=6).to(DEV)
-    outs = []
-    try:
-        for on in (False, True):
-            K.tc_options(pairs=pairs and on, k_blocks_per_stage=kps if on else 1)
-            out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=DEV)
-            K.linear(x, w, out, w2=w2, bias=None if dual else bias)
-            outs.append(out)
-    finally:
-        K.tc_options(pairs=False, k_blocks_per_stage=1)
-    assert K.tc_error() == 0
-    assert torch.equal(outs[0], outs[1])
-    ref = x.double() @ w.double().T
-    ref = torch.nn.functional.silu(ref) * (x.double() @ w2.double().T) if dual else ref + bias.double()
-    close(outs[1], ref, torch.bfloat16, "tensor-core product")
-
-
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,k", [(8, 1), (200, 3), (4096 + 1024 + 8, 4)])
 def test_rmsnorm_folds_the_expert_sum(dtype, H, k):
