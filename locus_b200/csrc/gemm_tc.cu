@@ -34,6 +34,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include <string.h>
 
 #define TILE_W 128      // weight rows per tile (MMA M)
 #define TILE_K 64       // k elements per stage: 128 bytes of bfloat16, one swizzle row
@@ -41,6 +42,16 @@
 #define WAIT_LIMIT 2000000000LL
 
 __device__ int g_tc_error = 0;
+
+// Tensor maps of the activations with boxes of 16, 32, 64, 96, ... 256 rows: a tile fetches the
+// smallest box that covers its live rows (the tile of an expert with a handful of rows would
+// otherwise pull a whole token tile through L2 for every k-block).
+#define X_BOXES 9
+struct XMaps {
+    CUtensorMap m[X_BOXES];
+};
+__host__ __device__ __forceinline__ int x_box_index(int rows) { return rows <= 16 ? 0 : (rows + 31) / 32; }
+__host__ __device__ __forceinline__ int x_box_rows(int index) { return index == 0 ? 16 : 32 * index; }
 
 struct TileGeom {
     int x_row0, rows_valid, tx, w_row0;  // first token row, live token rows, weight tile, first weight row
@@ -146,7 +157,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* v) {
 template <bool DUAL>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_w2,
-               const __grid_constant__ CUtensorMap map_x, TcArgs a) {
+               const __grid_constant__ XMaps maps_x, TcArgs a) {
     extern __shared__ uint8_t smem_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -223,16 +234,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (long long t = blockIdx.x; t < n_total && ok; t += t_step) {
                 const TileGeom g_next = tile_geom(t + t_step);
                 const int x_row0 = g.x_row0, w_row0 = g.w_row0;
+                const int box = x_box_index(g.rows_valid);
+                const CUtensorMap* map_x = &maps_x.m[box];
+                const uint32_t bytes = A_BYTES * (1 + DUAL) + static_cast<uint32_t>(min(x_box_rows(box), a.TN)) * (TILE_K * 2);
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(bar_empty + 8 * s, (round & 1) ^ 1, 1)) {
                         ok = false;
                         break;
                     }
                     const uint32_t st = base + s * stage_bytes;
-                    mbar_expect_tx(bar_full + 8 * s, stage_bytes);
+                    mbar_expect_tx(bar_full + 8 * s, bytes);
                     tma_load_2d(st, &map_w, kb * TILE_K, w_row0, bar_full + 8 * s);
                     if (DUAL) tma_load_2d(st + A_BYTES, &map_w2, kb * TILE_K, w_row0, bar_full + 8 * s);
-                    tma_load_2d(st + A_BYTES * (1 + DUAL), &map_x, kb * TILE_K, x_row0, bar_full + 8 * s);
+                    tma_load_2d(st + A_BYTES * (1 + DUAL), map_x, kb * TILE_K, x_row0, bar_full + 8 * s);
                     if (++s == a.stages) {
                         s = 0;
                         ++round;
@@ -538,10 +552,21 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
         return LOCUS_ERR_UNSUPPORTED;
     if (accumulate && out_dt != LOCUS_DT_F32) return LOCUS_ERR_UNSUPPORTED;
     if (w_rows_total >= (1LL << 31) || x_rows_total >= (1LL << 31)) return LOCUS_ERR_UNSUPPORTED;
-    CUtensorMap map_w, map_w2, map_x;
+    CUtensorMap map_w, map_w2;
+    XMaps maps_x;
+    memset(&maps_x, 0, sizeof(maps_x));
     if (!make_map(&map_w, w, w_rows_total, K, K, TILE_W)) return LOCUS_ERR_UNSUPPORTED;
     if (!make_map(&map_w2, dual ? w2 : w, w_rows_total, K, K, TILE_W)) return LOCUS_ERR_UNSUPPORTED;
-    if (!make_map(&map_x, x, x_rows_total, K, ldx, TN)) return LOCUS_ERR_UNSUPPORTED;
+    {
+        // boxes that tiles of this call can ask for: every size up to TN for a grouped product (the rows of
+        // a tile are known on the device only), the full tile and the last, ragged one for a plain product
+        const int full = x_box_index(TN), last = x_box_index(M % TN == 0 ? TN : M % TN);
+        for (int i = 0; i <= full; ++i) {
+            if (tile_expert == nullptr && i != full && i != last) continue;
+            const int rows = x_box_rows(i) < TN ? x_box_rows(i) : TN;
+            if (!make_map(&maps_x.m[i], x, x_rows_total, K, ldx, rows)) return LOCUS_ERR_UNSUPPORTED;
+        }
+    }
     TcArgs a;
     a.M = M; a.N = N; a.K = K; a.TN = TN; a.dual = dual;
     const int stage_bytes = A_BYTES * (1 + dual) + TN * TILE_K * 2;
@@ -582,8 +607,8 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
             return static_cast<int>(cudaGetLastError());
     }
     const unsigned grid = static_cast<unsigned>(n_tiles_all < n_sm ? n_tiles_all : n_sm);
-    if (dual) gemm_tc_kernel<true><<<grid, 192, smem, stream>>>(map_w, map_w2, map_x, a);
-    else gemm_tc_kernel<false><<<grid, 192, smem, stream>>>(map_w, map_w2, map_x, a);
+    if (dual) gemm_tc_kernel<true><<<grid, 192, smem, stream>>>(map_w, map_w2, maps_x, a);
+    else gemm_tc_kernel<false><<<grid, 192, smem, stream>>>(map_w, map_w2, maps_x, a);
     return locus_launch_status();
 }
 
