@@ -463,6 +463,43 @@ def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, se
     _check(code, "attn_chunk_mma", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
 
+TC_ATTN_HEAD_DIM = 128   # the tcgen05 attention kernel: this head size, pages of a multiple of 64 tokens
+TC_ATTN_MIN_TOKENS = 256  # portions of fewer new tokens in a step stay with the mma.sync kernel
+
+
+def attn_chunk_tc_takes(q: torch.Tensor, head_dim: int, page_tokens: int, n_tokens: int) -> bool:
+    """Whether the tcgen05 kernel of prompt portions takes this step: bfloat16, head size 128, pages of
+    a multiple of 64 tokens, and enough new tokens to fill blocks of 128 queries."""
+    return (USE_TENSOR_CORES and q.dtype == torch.bfloat16 and head_dim == TC_ATTN_HEAD_DIM
+            and page_tokens % 64 == 0 and n_tokens >= TC_ATTN_MIN_TOKENS)
+
+
+def attn_chunk_tc(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
+                  seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
+                  items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                  page_tokens: int, window: int, scale: float) -> None:
+    """Attention of portions of prompts with tcgen05 tensor cores (scores and sums in tensor memory):
+    ``items`` as for :func:`attn_chunk_mma` (tiles of 64 queries, a segment's tiles in ascending order;
+    a block takes two)."""
+    _cuda_c(q, "q")
+    _cuda_c(out, "out")
+    _cuda_c(pool, "pool")
+    _i32(block_table, "block_table")
+    _i32(items, "items")
+    _need(q.dtype == pool.dtype == out.dtype == torch.bfloat16, "attn_chunk_tc: bfloat16 only")
+    code = _lib("attention_tc").locus_attn_chunk_tc(
+        _p(q), LL(q.shape[0]), _p(pool), LL(pool.shape[0]), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
+        _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads), I(head_dim),
+        I(page_tokens), I(window), F(scale), _stream()
+    )
+    _check(code, "attn_chunk_tc", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim}, pages of {page_tokens})")
+
+
+def attn_tc_error() -> int:
+    """Error word of the tcgen05 attention module (0 = fine); reading it synchronises the device."""
+    return int(_lib("attention_tc").locus_attn_tc_error())
+
+
 DECODE_SPLIT = 128
 
 

@@ -65,7 +65,7 @@ class Attention(Mixer):
         return out
 
     def kernel_modules(self, dtype):
-        return ["elementwise", "gemm_simt", "gemv", "attention"] + (["gemm_skinny", "gemm_tc", "attention_mma"] if dtype == torch.bfloat16 else [])
+        return ["elementwise", "gemm_simt", "gemv", "attention"] + (["gemm_skinny", "gemm_tc", "attention_mma", "attention_tc"] if dtype == torch.bfloat16 else [])
 
     def cache_needs(self):
         return PagedKvSpec(self.n_kv_heads, self.head_dim, self.window), None
@@ -94,7 +94,9 @@ class Attention(Mixer):
                       head_dim=self.head_dim, page_tokens=gb.page_tokens, window=self.window,
                       scale=self.scale)
         if batch.n_chunk_items:
-            if K.attn_chunk_mma_takes(q, self.head_dim):
+            if K.attn_chunk_tc_takes(q, self.head_dim, gb.page_tokens, T):
+                K.attn_chunk_tc(q, cache.pool, o, items=batch.chunk_items64, n_items=batch.n_chunk_items64, **common)
+            elif K.attn_chunk_mma_takes(q, self.head_dim):
                 K.attn_chunk_mma(q, cache.pool, o, items=batch.chunk_items64, n_items=batch.n_chunk_items64, **common)
             else:
                 K.attn_chunk(q, cache.pool, o, items=batch.chunk_items, n_items=batch.n_chunk_items, **common)

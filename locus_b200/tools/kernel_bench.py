@@ -115,13 +115,16 @@ def bench_attn_chunk(args) -> None:
     tile = K.MMA_QUERY_TILE if mma else 16
     items = torch.tensor([(0, o) for o in range(0, T, tile)], dtype=torch.int32, device="cuda:0")
 
+    tc = mma and not args.mma_sync and K.attn_chunk_tc_takes(q, args.head_dim, args.page_tokens, T)
+
     def fn():
-        (K.attn_chunk_mma if mma else K.attn_chunk)(q, pool, out, items=items, n_items=items.shape[0], **meta, **kw)
+        call = K.attn_chunk_tc if tc else (K.attn_chunk_mma if mma else K.attn_chunk)
+        call(q, pool, out, items=items, n_items=items.shape[0], **meta, **kw)
 
     us = _time(fn, args.iters, args.graph)
     flops = 4.0 * args.heads * args.head_dim * (T * ctx + T * (T + 1) / 2)
     print(f"attn_chunk tokens={T} ctx={ctx} heads={args.heads}/{args.kv_heads} head_dim={args.head_dim} "
-          f"{'tensor cores' if mma else 'cuda cores'}: {us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
+          f"{'tcgen05' if tc else ('mma.sync' if mma else 'cuda cores')}: {us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
 
 
 def main(argv=None) -> int:
@@ -144,6 +147,7 @@ def main(argv=None) -> int:
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--window", type=int, default=0)
     ap.add_argument("--cuda-cores", action="store_true", help="attn_chunk: the CUDA-core kernel")
+    ap.add_argument("--mma-sync", action="store_true", help="attn_chunk: the mma.sync kernel where tcgen05 would run")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("kernel_bench: no CUDA device", file=sys.stderr)

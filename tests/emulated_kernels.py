@@ -26,6 +26,10 @@ def embed_rows(tokens, table, out):
     out.copy_(table[tokens.long()].to(out.dtype))
 
 
+def attn_chunk_tc_takes(q, head_dim, page_tokens, n_tokens):
+    return False
+
+
 def rmsnorm_adds(x):
     return x.dtype == torch.float32 and x.shape[-1] % 4 == 0
 
@@ -300,7 +304,7 @@ def sample(logits, *, temperature, top_k, top_p, min_p, seeds, counters, out, ke
             kept_count[r] = int(keep.sum())
 
 
-_NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
+_NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "attn_chunk_tc_takes", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
           "moe_sort", "route_small", "route_small_takes", "moe_combine", "gather_rows", "apply_penalties", "sample"]
 
 

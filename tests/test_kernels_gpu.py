@@ -348,6 +348,32 @@ def test_attn_chunk_tensor_cores(nh, nkv, hd, P, window):
     close(out, ref, dtype, "attn_chunk_mma")
 
 
+@pytest.mark.parametrize("nh,nkv,P,window", [(2, 2, 64, 0), (4, 1, 128, 0), (3, 3, 64, 100), (2, 1, 64, 1), (4, 2, 192, 333)])
+def test_attn_chunk_tcgen05(nh, nkv, P, window):
+    """Portions of 2 to 700 tokens at contexts that straddle the 128-key tiles and the pages; whatever lies
+    in a request's pages behind its last token is NaN and must not reach the result."""
+    dtype, hd = torch.bfloat16, 128
+    segs = [(0, 5), (33, 17), (100, 2), (15, 140), (64, 64), (190, 200), (63, 1 + 128), (0, 700), (1000, 300)]
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=window + 7, n_pages=80)
+    for s, (c, n) in enumerate(segs):
+        end = c + n
+        if end % P:
+            pool[int(meta["block_table"][s, end // P]), :, :, end % P :, :] = float("nan")
+    items = []
+    for s, (c, n) in enumerate(segs):
+        items += [(s, o) for o in range(0, n, K.MMA_QUERY_TILE)]
+    items_t = torch.tensor(items, dtype=torch.int32)
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=window, scale=1 / math.sqrt(hd))
+    assert K.attn_chunk_tc_takes(q.to(DEV), hd, P, T)
+    assert not K.attn_chunk_tc_takes(q.to(DEV), hd, 48, T) and not K.attn_chunk_tc_takes(q.to(DEV), 64, P, T)
+    out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+    K.attn_chunk_tc(q.to(DEV), pool.to(DEV), out, items=items_t.to(DEV), n_items=len(items), **_dev(meta), **kw)
+    assert K.attn_tc_error() == 0
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.attn_chunk(q, torch.nan_to_num(pool, nan=1e4), ref, items=items_t, n_items=len(items), **meta, **kw)
+    close(out, ref, dtype, "attn_chunk_tc")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 4, 16, 16, 0), (6, 2, 32, 64, 0), (5, 1, 48, 16, 0),
                                                 (16, 16, 128, 64, 0), (2, 1, 256, 64, 0), (4, 2, 64, 16, 300),
