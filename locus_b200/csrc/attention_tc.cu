@@ -16,7 +16,7 @@
 //
 // S and PV are double-buffered in tensor memory (4 x 128 columns), so the tensor pipe computes the
 // scores of the next tile while the softmax warps work on this one, and the sum of a tile is added
-// one tile late, while the next P is in the making.  Warp 0: TMA; warp 1: MMA issue (one thread);
+// one tile late, while the tensor pipe multiplies the next P (two buffers) by its V.  Warp 0: TMA; warp 1: MMA issue (one thread);
 // warps 2-9: softmax and output, two threads per query row (64 keys and 64 output dimensions each).  Head size 128 only (other sizes and pages that are not a multiple
 // of 64 tokens go to the mma.sync kernel).
 //
@@ -131,6 +131,19 @@ __device__ __forceinline__ void at_ld32(uint32_t taddr, uint32_t* v) {
           "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
         : "r"(taddr));
 }
+// 2^x for x <= 0 by the special-function unit alone (exp2f adds range handling that the softmax does
+// not need: a result that underflows may be zero).
+__device__ __forceinline__ float at_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// Two probabilities (finite, in [0, 1]) as bfloat16, rounded to nearest (ties upward) with integer
+// arithmetic: the conversion instruction runs on the same narrow pipe as ex2 and would add half as
+// much again to what already takes as long as the tile's MMAs.
+__device__ __forceinline__ uint32_t at_pack_prob(float lo, float hi) {
+    return __byte_perm(__float_as_uint(lo) + 0x8000u, __float_as_uint(hi) + 0x8000u, 0x7632);
+}
 __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -138,7 +151,7 @@ __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
 
 __global__ void __launch_bounds__(320, 1)
 attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, TcAttnArgs a) {
-    extern __shared__ uint8_t at_raw[];
+    extern __shared__ __align__(1024) uint8_t at_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the late tiles of a prompt see the most keys: the grid takes them first
     const int item = gridDim.x - 1 - blockIdx.x;
@@ -155,10 +168,16 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int n_tiles = (t_hi - first_tile) / AT_MK + 1;
     const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
 
-    // shared memory: Q, K[2], V[2], P (each a tile of two swizzled halves), then the barriers
-    const uint32_t base = (at_smem(at_raw) + 1023u) & ~1023u;
+    // shared memory: Q, K[2], V[2], P[2] (each a tile of two swizzled halves), then the barriers.  That is
+    // all the shared memory a block can have, so the tiles start at the very base, which must be
+    // 1024-byte aligned for the swizzle (checked: a block that finds it otherwise reports and leaves).
+    const uint32_t base = at_smem(at_raw);
+    if (base & 1023u) {
+        if (threadIdx.x == 0) atomicCAS(&g_at_error, 0, 12);
+        return;
+    }
     const uint32_t sQ = base, sK = sQ + AT_TILE_BYTES, sV = sK + 2 * AT_TILE_BYTES, sP = sV + 2 * AT_TILE_BYTES;
-    const uint32_t bars = sP + AT_TILE_BYTES;
+    const uint32_t bars = sP + 2 * AT_TILE_BYTES;
     const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, k_free = bars + 40, v_free = bars + 56;
     const uint32_t s_full = bars + 72, s_free = bars + 88, pv_full = bars + 104, pv_free = bars + 120, p_ready = bars + 136;
     const uint32_t slot = bars + 144;
@@ -256,7 +275,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int ks = 0; ks < AT_MK / 16; ++ks) {
-                    const uint64_t dp = at_desc_k(sP + (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32);
+                    const uint64_t dp = at_desc_k(sP + b * AT_TILE_BYTES + (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32);
                     const uint64_t dv = at_desc_mn(sV + b * AT_TILE_BYTES + ks * (16 * 128), AT_HALF_BYTES);
                     at_mma(tPV + b * AT_HD, dp, dv, idesc2, ks > 0);
                 }
@@ -277,7 +296,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         for (int d = 0; d < 64; ++d) o[d] = 0.f;
         float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
         uint8_t* at_generic = at_raw + (base - at_smem(at_raw));
-        uint8_t* gP = at_generic + (sP - base) + half * AT_HALF_BYTES + r * 128;
+        uint8_t* gP0 = at_generic + (sP - base) + half * AT_HALF_BYTES + r * 128;
         float* xch = reinterpret_cast<float*>(at_generic + (slot + 16 - base));  // [2 tile parities][2 halves][128 rows]
         bool ok = true;
         const int lo = a.window > 0 ? max(0, pq - a.window + 1) : 0;  // first key this row sees
@@ -337,10 +356,10 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             mx = fmaxf(mx, with_partner(b, mx)) * scale_log2;  // the scale is positive: the maximum can be scaled last
             mx = fmaxf(mx, m_run);
             const float m_ref = mx == -INFINITY ? 0.f : mx;       // exp2(-inf - 0) = 0 for a row without keys so far
-            const float alpha = mx == -INFINITY ? 1.f : exp2f(m_run - mx);
-            // the sum of the tile before this one (its P used the maximum of then)
-            if (j > 0 && !add_sum(j - 1, alpha_prev)) ok = false;
-            // P = exp2(s * scale - m) as bfloat16 into shared memory (K-major operand, 128-byte swizzle)
+            const float alpha = mx == -INFINITY ? 1.f : at_exp2(m_run - mx);
+            // P = exp2(s * scale - m) as bfloat16 into shared memory (K-major operand, 128-byte swizzle); the
+            // buffer of tile j - 2 is free: its MMA finished before the sum of tile j - 2 was added (below)
+            uint8_t* gP = gP0 + b * AT_TILE_BYTES;
             float sum = 0.f;
 #pragma unroll
             for (int q8 = 0; q8 < 8; ++q8) {  // 16-byte pieces of 8 probabilities
@@ -348,19 +367,19 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const uint32_t raw = q8 < 4 ? s0[8 * q8 + i] : s1[8 * (q8 - 4) + i];
-                    pr[i] = exp2f(fmaf(__uint_as_float(raw), scale_log2, -m_ref));
+                    const float x = fmaf(__uint_as_float(raw), scale_log2, -m_ref);
+                    pr[i] = at_exp2(x);
                     sum += pr[i];
                 }
                 uint4 pk;
-                pk.x = at_pack(pr[0], pr[1]);
-                pk.y = at_pack(pr[2], pr[3]);
-                pk.z = at_pack(pr[4], pr[5]);
-                pk.w = at_pack(pr[6], pr[7]);
+                pk.x = at_pack_prob(pr[0], pr[1]);
+                pk.y = at_pack_prob(pr[2], pr[3]);
+                pk.z = at_pack_prob(pr[4], pr[5]);
+                pk.w = at_pack_prob(pr[6], pr[7]);
                 *reinterpret_cast<uint4*>(gP + ((q8 ^ (r & 7)) << 4)) = pk;
             }
             l_run = l_run * alpha + sum;
             m_run = mx;
-            alpha_prev = alpha;  // the factor that takes O from the maximum of tile j - 1 to that of tile j
             // the last tile may hold rows of V behind the sequence's end (never written, any bit pattern): zero them
             if (tile_first + AT_MK - 1 > t_hi) {
                 if (!at_wait(v_full + 8 * b, (j >> 1) & 1, 11)) ok = false;
@@ -378,6 +397,10 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 at_arrive(s_free + 8 * b);
                 at_arrive(p_ready);
             }
+            // the sum of the tile before this one (its P used the maximum of then), while the tensor pipe
+            // multiplies this tile's P by V
+            if (j > 0 && !add_sum(j - 1, alpha_prev)) ok = false;
+            alpha_prev = alpha;  // the factor that takes O from the maximum of tile j - 1 to that of tile j
         }
         if (!add_sum(n_tiles - 1, alpha_prev)) ok = false;
         {
@@ -459,7 +482,7 @@ extern "C" int locus_attn_chunk_tc(const void* q, long long T, const void* pool,
     a.out = static_cast<bf16*>(out); a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx;
     a.block_table = block_table; a.table_stride = table_stride; a.items = items; a.nh = nh; a.nkv = nkv;
     a.page_tokens = page_tokens; a.window = window; a.scale = scale;
-    const size_t smem = 6 * AT_TILE_BYTES + 256 + 2 * 2 * 128 * 4 + 1024;
+    const size_t smem = 7 * AT_TILE_BYTES + 160 + 2 * 2 * 128 * 4;
     static bool set = false;
     if (!set) {
         if (cudaFuncSetAttribute(attn_chunk_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
