@@ -206,6 +206,11 @@ class ModelRunner:
             if code:
                 raise RuntimeError(f"tensor-core kernel fault: a pipeline wait ran out (code {code}: "
                                    "1 = loader, 2 = MMA issuer, 3 = epilogue); results since the last check are invalid")
+        if self.device.type == "cuda" and "attention_tc" in K._LIBS:
+            code = K.attn_tc_error()
+            if code:
+                raise RuntimeError(f"tensor-core attention fault: a pipeline wait ran out or shared memory was "
+                                   f"misaligned (code {code}); results since the last check are invalid")
 
     # ------------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
