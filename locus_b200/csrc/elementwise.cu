@@ -348,10 +348,27 @@ __global__ void gather_rows_kernel(const TA* __restrict__ src, const int* __rest
     for (int j = threadIdx.x; j < W; j += blockDim.x) o[j] = s[j];
 }
 
+// The same in 16-byte pieces (rows that start on 16-byte boundaries and are a multiple of 16 bytes long).
+__global__ void gather_rows16_kernel(const uint4* __restrict__ src, const int* __restrict__ idx, int div,
+                                     uint4* __restrict__ out, int W16) {
+    const int i = blockIdx.x;
+    const uint4* s = src + static_cast<size_t>(idx[i] / div) * W16;
+    uint4* o = out + static_cast<size_t>(i) * W16;
+    for (int j = threadIdx.x; j < W16; j += blockDim.x) o[j] = s[j];
+}
+
 extern "C" int locus_gather_rows(const void* src, int dt, const int* idx, int div, void* out,
                                  int n, int W, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (div <= 0) return LOCUS_ERR_UNSUPPORTED;
+    const size_t row_bytes = static_cast<size_t>(W) * (dt == LOCUS_DT_F32 ? 4 : 2);
+    if ((dt == LOCUS_DT_F32 || dt == LOCUS_DT_BF16) && row_bytes % 16 == 0 &&
+        ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out)) & 15) == 0) {
+        const int W16 = static_cast<int>(row_bytes / 16);
+        gather_rows16_kernel<<<n, W16 < 256 ? 128 : 256, 0, stream>>>(static_cast<const uint4*>(src), idx, div,
+                                                                  static_cast<uint4*>(out), W16);
+        return locus_launch_status();
+    }
     if (dt == LOCUS_DT_F32) {
         gather_rows_kernel<float><<<n, 256, 0, stream>>>(static_cast<const float*>(src), idx, div,
                                                          static_cast<float*>(out), W);

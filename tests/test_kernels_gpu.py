@@ -213,6 +213,17 @@ def test_router_on_tensor_cores(T, H, E, k, renorm):
         assert torch.equal(one[0], logits[t]), f"token {t} alone differs from token {t} in the batch"
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("W", [8, 20, 200, 2048, 6])
+def test_gather_rows(dtype, W):
+    """out[i] = src[idx[i] // div], in 16-byte pieces where the rows allow it and element by element else."""
+    src = rnd(37, W, dtype=dtype, seed=W).to(DEV)
+    idx = torch.randint(0, 37 * 3, (90,), generator=torch.Generator().manual_seed(W)).to(torch.int32).to(DEV)
+    out = torch.zeros(90, W, dtype=dtype, device=DEV)
+    K.gather_rows(src, idx, 3, out, 90)
+    assert torch.equal(out, src[(idx.long() // 3)])
+
+
 @pytest.mark.parametrize("T,E,k,tile,gate,renorm", [(1, 4, 2, 8, True, True), (8, 60, 4, 8, True, False),
                                                      (13, 7, 3, 16, False, True), (16, 33, 16, 32, True, True),
                                                      (5, 512, 6, 8, False, False)])
