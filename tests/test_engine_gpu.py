@@ -34,6 +34,7 @@ REQUESTS = {  # name -> (length, seed); lengths straddle page edges (16 and 64) 
     "A": [(5, 1), (17, 2), (33, 3), (64, 4), (200, 5)],
     "B": [(1, 1), (7, 2), (64, 3), (100, 4), (129, 5), (300, 6)],
     "C": [(2, 1), (25, 2), (49, 3), (130, 4), (290, 5)],
+    "D": [(700, 1), (333, 2), (40, 3)],
 }
 
 
@@ -180,6 +181,30 @@ def test_whole_requests_alone(case, dtype):
     got = run_trace(runner, cache, case, [[(rid, len(t))] for rid, t in case.tokens.items()])
     check(case, got, dtype, "whole")
     assert cache.free_pages() == cache.total_pages()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_portions_with_head_size_128(dtype, tmp_path_factory):
+    """Head size 128, pages of 64 tokens, steps of 256 and more new tokens: in bfloat16 these portions run
+    on the tcgen05 attention kernel (blocks of 128 queries, two of the step's 64-query tiles each), shorter
+    steps and single tokens on the other kernels, all against the same cache."""
+    import locus_b200.kernels as K
+
+    case = Case("D", tmp_path_factory.mktemp("models_d"))
+    used = []
+    orig = K.attn_chunk_tc
+    K.attn_chunk_tc = lambda *a, **k: (used.append(1), orig(*a, **k))[1]
+    try:
+        for steps in ([[("r0", 700)], [("r1", 333)], [("r2", 40)]],
+                      [[("r0", 300), ("r2", 40)], [("r0", 256), ("r1", 77)], [("r0", 143), ("r1", 255)], [("r0", 1), ("r1", 1)]]):
+            runner, cache = make_runner(case, dtype, page_tokens=64, n_pages=24, max_tokens=768, max_seq=1024)
+            got = run_trace(runner, cache, case, steps)
+            check(case, got, dtype, "long portions, head size 128")
+            assert cache.free_pages() == cache.total_pages()
+    finally:
+        K.attn_chunk_tc = orig
+    assert (len(used) > 0) == (dtype == torch.bfloat16)
+    assert K.attn_tc_error() == 0 if dtype == torch.bfloat16 else True
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -39,8 +39,20 @@ TINY_C = {
     "eos_token_id": -1,
 }
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
-SEEDS = {"A": 0, "B": 1, "C": 5}
+# Head size 128 (the size of the tcgen05 attention kernel), otherwise small; used by the tests that run
+# long portions through the engine with pages of 64 tokens.
+TINY_D = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "num_hidden_layers": 2, "hidden_size": 96, "num_attention_heads": 3, "num_key_value_heads": 1,
+    "head_dim": 128, "vocab_size": 211, "rope_theta": 10000.0, "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 1024, "decoder_sparse_step": 1, "num_experts": 6, "num_experts_per_tok": 2,
+    "norm_topk_prob": False, "moe_intermediate_size": 24, "shared_expert_intermediate_size": 48,
+    "intermediate_size": 64, "qkv_bias": True, "tie_word_embeddings": True, "use_sliding_window": False,
+    "mlp_only_layers": [], "hidden_act": "silu", "eos_token_id": -1,
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+SEEDS = {"A": 0, "B": 1, "C": 5, "D": 9}
 
 
 def config(name: str) -> dict:
