@@ -61,7 +61,8 @@ __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void*
 //
 // With add_src: first x[i] += sum over slots s < add_k (in slot order) of add_src[add_pos[i * add_k + s]]
 // (the outputs of a row's experts, the sum that moe_combine_kernel forms, in the same order), written
-// back to x, then the norm of the new row.  rows must be null then.
+// back to x, then the norm of the new row.  With rows the sum goes into the norm only and x stays as
+// it was (a row may be named twice, and nobody reads the other rows' sums).
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x, const TW* __restrict__ w,
                                                           float eps, TO* __restrict__ out,
@@ -73,7 +74,9 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x,
     __shared__ float warp_part[8];
     __shared__ float scale_s;
     const int i = blockIdx.x;
-    float4* src = reinterpret_cast<float4*>(x + static_cast<size_t>(rows ? rows[i] : i) * H);
+    const int r = rows ? rows[i] : i;
+    float4* src = reinterpret_cast<float4*>(x + static_cast<size_t>(r) * H);
+    const bool write_back = rows == nullptr;
     const int n4 = H >> 2;
     auto fetch = [&](int j) -> float4 {
         float4 t = src[j];
@@ -81,14 +84,16 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x,
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int s = 0; s < add_k; ++s) {
                 const float4 p = reinterpret_cast<const float4*>(
-                    add_src + static_cast<size_t>(add_pos[i * add_k + s]) * H)[j];
+                    add_src + static_cast<size_t>(add_pos[r * add_k + s]) * H)[j];
                 acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
             }
             t.x += acc.x; t.y += acc.y; t.z += acc.z; t.w += acc.w;
-            src[j] = t;
+            if (write_back) src[j] = t;
         }
         return t;
     };
+    // second reading of a row too wide for the registers: x holds the sum already unless it was left alone
+    auto fetch_again = [&](int j) -> float4 { return write_back ? src[j] : fetch(j); };
     float4 v[4];  // up to 4096 elements per row in registers; wider rows re-read
     float ss = 0.f;
 #pragma unroll
@@ -117,7 +122,7 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x,
     TO* dst = out + static_cast<size_t>(i) * H;
     for (int j = threadIdx.x; j < n4; j += 256) {
         const int u = j >> 8;
-        const float4 t = u < 4 ? v[u] : src[j];
+        const float4 t = u < 4 ? v[u] : fetch_again(j);
         const int c = j << 2;
         dst[c] = from_f<TO>(t.x * scale * to_f(w[c]));
         dst[c + 1] = from_f<TO>(t.y * scale * to_f(w[c + 1]));
@@ -127,14 +132,14 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x,
 }
 
 // add_src / add_pos / add_k: see rmsnorm_f32_kernel; only with float32 x, H a multiple of 4, 16-byte
-// aligned x and add_src, and no row gather.
+// aligned x and add_src.
 extern "C" int locus_rmsnorm(void* x, int x_dt, const void* w, int w_dt, float eps, void* out,
                              int out_dt, const int* rows, int n_rows, int H, const float* add_src,
                              const int* add_pos, int add_k, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const bool fast = x_dt == LOCUS_DT_F32 && H % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     if (add_src != nullptr &&
-        (!fast || rows != nullptr || add_pos == nullptr || add_k <= 0 || (reinterpret_cast<uintptr_t>(add_src) & 15)))
+        (!fast || add_pos == nullptr || add_k <= 0 || (reinterpret_cast<uintptr_t>(add_src) & 15)))
         return LOCUS_ERR_UNSUPPORTED;
     if (fast) {
         float* xf = static_cast<float*>(x);

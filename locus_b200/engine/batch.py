@@ -34,7 +34,7 @@ class Runtime:
         self._objects: Dict[Tuple, object] = {}
         # An addition to the residual stream that the last feed-forward left to the next norm
         # (parts.base.PendingAdd).  A feed-forward may leave one only while ``defer_add`` is set:
-        # the model sets it when the next block takes pending additions.
+        # the model sets it when the next block, or the final norm, takes pending additions.
         self.defer_add = False
         self._pending = None
         # a second stream for work that does not depend on the main chain (forked and joined

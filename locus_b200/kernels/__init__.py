@@ -150,7 +150,8 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
     """out[i] = x[rows[i] if rows else i] * rsqrt(mean(x^2) + eps) * w  (statistics in float32).
 
     ``add`` = (pair_out, pair_pos, top_k): first x[i] += the sum that :func:`moe_combine` forms (same
-    order), written back to ``x``; needs :func:`rmsnorm_adds` and no ``rows``."""
+    order), written back to ``x``; needs :func:`rmsnorm_adds`.  With ``rows`` the sum enters the norm
+    of the gathered rows only and ``x`` stays as it was."""
     _cuda_c(x, "x")
     _cuda_c(w, "w")
     _cuda_c(out, "out")
@@ -166,10 +167,11 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
     add_k = 0
     if add is not None:
         add_src, add_pos, add_k = add
-        _need(rows is None and rmsnorm_adds(x), "rmsnorm: cannot fold the expert sum into these rows")
+        _need(rmsnorm_adds(x), "rmsnorm: cannot fold the expert sum into these rows")
         _cuda_c(add_src, "pair_out")
         _i32(add_pos, "pair_pos")
-        _need(add_src.dtype == torch.float32 and add_src.shape[-1] == H and add_pos.numel() >= n * add_k,
+        _need(add_src.dtype == torch.float32 and add_src.shape[-1] == H
+              and add_pos.numel() >= (n if rows is None else x.shape[0]) * add_k,
               "rmsnorm: expert sum of another shape")
     code = _lib("elementwise").locus_rmsnorm(
         _p(x), I(dtype_code(x.dtype)), _p(w), I(dtype_code(w.dtype)), F(eps), _p(out),

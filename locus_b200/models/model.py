@@ -117,18 +117,18 @@ class Model:
         self.embedding.forward(batch.tokens, x)
         order = self.plan.order
         for i, (call, cache) in enumerate(zip(order, caches)):
-            # a block may leave its last addition to the residual stream to the next block's first norm
-            rt.defer_add = i + 1 < len(order) and self.blocks[order[i + 1].layer].takes_pending_add
+            # a block may leave its last addition to the residual stream to the next block's first norm,
+            # the last block to the final norm
+            rt.defer_add = i + 1 == len(order) or self.blocks[order[i + 1].layer].takes_pending_add
             self.blocks[call.layer].forward(x, batch, cache, rt)
         rt.defer_add = False
+        # what the last block left undone only matters in the rows whose logits are wanted
         pending = rt.take_pending()
-        if pending is not None:
-            pending.apply(x)
         n = batch.n_want
         logits = rt.buf("model.logits", (rt.max_wanted, self.plan.vocab_size), torch.float32)[:n]
         if n:
             hw = rt.buf("model.h_want", (rt.max_wanted, self.plan.hidden_size), rt.dtype)[:n]
-            self.final_norm.forward(x, hw, rows=batch.want_rows)
+            self.final_norm.forward(x, hw, rows=batch.want_rows, add=pending)
             self.head.forward(hw, logits)
         return logits
 

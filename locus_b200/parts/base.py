@@ -153,7 +153,9 @@ class Norm(Part):
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None,
                 add: Optional[PendingAdd] = None) -> None:
         """out = norm(x) (rows: gather of x rows); statistics in float32.  ``add``: a pending
-        addition to x that must be done (in x) before the norm: fold it in or call ``add.apply(x)``."""
+        addition to x that must be done (in x) before the norm: fold it in or call ``add.apply(x)``.
+        A caller that gives ``rows`` as well reads x no more afterwards, so the addition then only
+        has to show in ``out``."""
         raise NotImplementedError
 
 

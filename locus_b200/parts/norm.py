@@ -30,7 +30,7 @@ class RMSNorm(Norm):
         return ["elementwise"]
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, rows: Optional[torch.Tensor] = None, add=None) -> None:
-        if add is not None and (rows is not None or not K.rmsnorm_adds(x)):
+        if add is not None and not K.rmsnorm_adds(x):
             add.apply(x)
             add = None
         K.rmsnorm(x, self.params["weight"], self.eps, out, rows,

@@ -35,9 +35,11 @@ def rmsnorm_adds(x):
 
 
 def rmsnorm(x, w, eps, out, rows=None, add=None):
-    if add is not None:
-        assert rows is None
+    if add is not None and rows is None:
         moe_combine(x[: out.shape[0]], add[0], add[1], add[2])
+    elif add is not None:
+        x = x.clone()
+        moe_combine(x, add[0], add[1], add[2])
     xs = _f(x if rows is None else x[rows.long()])[: out.shape[0]]
     ss = (xs * xs).sum(-1, keepdim=True)
     out.copy_((xs * (1.0 / torch.sqrt(ss / xs.shape[-1] + eps)) * _f(w)).to(out.dtype))

@@ -80,9 +80,13 @@ def test_rmsnorm_folds_the_expert_sum(dtype, H, k):
     K.rmsnorm(x1, w, 1e-6, out1, add=(pair_out, pair_pos, k))
     assert torch.equal(x1, x2) and torch.equal(out1, out2)
     assert not K.rmsnorm_adds(torch.zeros(2, 6))
+    # with a gather of rows (one of them named twice) the sum shows in the output alone
+    rows = torch.tensor([4, 1, 4], dtype=torch.int32, device=DEV)
+    x3, out3 = x.clone(), torch.empty(3, H, dtype=dtype, device=DEV)
+    K.rmsnorm(x3, w, 1e-6, out3, rows, add=(pair_out, pair_pos, k))
+    assert torch.equal(x3, x) and torch.equal(out3, out2[rows.long()])
     with pytest.raises(K.KernelError):
-        K.rmsnorm(x1, w, 1e-6, out1[:2], torch.tensor([0, 1], dtype=torch.int32, device=DEV),
-                  add=(pair_out, pair_pos, k))
+        K.rmsnorm(x1, w, 1e-6, out1, add=(pair_out, pair_pos[: T * k - 1], k))
 
 
 @pytest.mark.parametrize("xdt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
