@@ -102,9 +102,9 @@ def moe_block(h: torch.Tensor, W: Dict[str, torch.Tensor], prefix: str, cfg: dic
     come from this function's own probabilities) -- tests use it to follow an engine whose
     router, fed rounded activations, chose the other side of a near-tie.  ``aux`` collects the
     selection and the probabilities per token."""
-    out = torch.zeros_like(h)
     r = h @ W[f"{prefix}.gate.weight"].T
     k, norm = cfg["num_experts_per_tok"], cfg.get("norm_topk_prob", False)
+    picks = []
     for t in range(h.shape[0]):
         ids, wts = moe_select(r[t], k, norm)
         if aux is not None:
@@ -114,18 +114,25 @@ def moe_block(h: torch.Tensor, W: Dict[str, torch.Tensor], prefix: str, cfg: dic
             ids = list(forced[t])
             wsum = sum(p[e] for e in ids) if norm else 1.0
             wts = [p[e] / wsum for e in ids]
-        acc = torch.zeros_like(h[t])
-        for e, w in zip(ids, wts):
-            acc = acc + w * swiglu_mlp(h[t], W[f"{prefix}.experts.{e}.gate_proj.weight"],
-                                       W[f"{prefix}.experts.{e}.up_proj.weight"],
-                                       W[f"{prefix}.experts.{e}.down_proj.weight"])
-        if cfg.get("shared_expert_intermediate_size", 0) > 0:
-            z = W[f"{prefix}.shared_expert_gate.weight"][0] @ h[t]
-            gamma = 1.0 / (1.0 + torch.exp(-z))
-            acc = acc + gamma * swiglu_mlp(h[t], W[f"{prefix}.shared_expert.gate_proj.weight"],
-                                           W[f"{prefix}.shared_expert.up_proj.weight"],
-                                           W[f"{prefix}.shared_expert.down_proj.weight"])
-        out[t] = acc
+        picks.append((ids, wts))
+    # every expert once, over the tokens that picked it (its weights are read once, not per token)
+    picked_out = [[None] * k for _ in picks]
+    for e in sorted({e for ids, _ in picks for e in ids}):
+        who = [(t, s) for t, (ids, _) in enumerate(picks) for s, x in enumerate(ids) if x == e]
+        y = swiglu_mlp(h[torch.tensor([t for t, _ in who])], W[f"{prefix}.experts.{e}.gate_proj.weight"],
+                       W[f"{prefix}.experts.{e}.up_proj.weight"], W[f"{prefix}.experts.{e}.down_proj.weight"])
+        for i, (t, s) in enumerate(who):
+            picked_out[t][s] = y[i]
+    out = torch.zeros_like(h)
+    for t, (ids, wts) in enumerate(picks):
+        for s in range(len(ids)):
+            out[t] = out[t] + wts[s] * picked_out[t][s]
+    if cfg.get("shared_expert_intermediate_size", 0) > 0:
+        z = h @ W[f"{prefix}.shared_expert_gate.weight"][0]
+        gamma = 1.0 / (1.0 + torch.exp(-z))
+        out = out + gamma[:, None] * swiglu_mlp(h, W[f"{prefix}.shared_expert.gate_proj.weight"],
+                                                W[f"{prefix}.shared_expert.up_proj.weight"],
+                                                W[f"{prefix}.shared_expert.down_proj.weight"])
     return out
 
 
@@ -160,13 +167,29 @@ def attention_block(h: torch.Tensor, W: Dict[str, torch.Tensor], prefix: str, cf
     return o @ W[f"{prefix}.o_proj.weight"].T
 
 
+class _CastOnRead(dict):
+    """The checkpoint's tensors, converted to the working type when read (a large model converted
+    as a whole would not fit in memory)."""
+
+    def __init__(self, weights, dtype):
+        super().__init__(weights)
+        self.dtype = dtype
+
+    def __getitem__(self, name):
+        return super().__getitem__(name).to(self.dtype)
+
+    def get(self, name, default=None):
+        return self[name] if name in self else default
+
+
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
             dtype: torch.dtype = torch.float32, forced_routing: Optional[dict] = None,
-            aux: Optional[dict] = None) -> torch.Tensor:
+            aux: Optional[dict] = None, positions: Optional[Sequence[int]] = None) -> torch.Tensor:
     """src/locus/model/llama.cpp:426-515: embed; per layer x += attn(norm(x)), x += ffn(norm(x));
-    final norm; head (the embedding when tied).  Returns logits [T, vocab] for every position.
+    final norm; head (the embedding when tied).  Returns logits [T, vocab] for every position, or for
+    ``positions`` only.
     ``forced_routing``: {"model.layers.N.mlp": [experts of token 0, of token 1, ...]}."""
-    W = {k: v.to(dtype) for k, v in weights.items()}
+    W = _CastOnRead(weights, dtype)
     eps = cfg["rms_norm_eps"]
     x = W["model.embed_tokens.weight"][torch.tensor(list(tokens), dtype=torch.long)]
     for l in range(cfg["num_hidden_layers"]):
@@ -180,6 +203,8 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
             x = x + swiglu_mlp(h, W[f"{p}.mlp.gate_proj.weight"], W[f"{p}.mlp.up_proj.weight"],
                                W[f"{p}.mlp.down_proj.weight"])
     h = rmsnorm(x, W["model.norm.weight"], eps)
+    if positions is not None:
+        h = h[torch.tensor(list(positions), dtype=torch.long)]
     head = W["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) else W["lm_head.weight"]
     return h @ head.T
 

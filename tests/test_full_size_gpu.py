@@ -1,0 +1,169 @@
+"""The engine at the layer sizes of Qwen1.5-MoE-A2.7B (hidden 2048, 16 heads of 128, 60 experts of
+1408 with 4 picked, a shared expert of 5632, the vocabulary of 151,936; two layers of them) against
+the plain implementation in float64, in float32 and in bfloat16.
+
+The tiny configurations cannot reach what these sizes reach: the tensor-core products with their
+real tile shapes and token boxes, the tcgen05 attention kernel under sixteen heads, sixty experts
+with four picks, the head's product over the real vocabulary.  The requests are fed whole, then in
+portions beside one another and token by token, from pages that are used again.
+"""
+import pytest
+import torch
+
+import plain_qwen2moe as plain
+from test_engine_gpu import TOL
+from tiny_configs import random_tokens
+
+pytestmark = pytest.mark.gpu
+
+FULL = {
+    "architectures": ["Qwen2MoeForCausalLM"], "model_type": "qwen2_moe",
+    "num_hidden_layers": 2, "hidden_size": 2048, "num_attention_heads": 16, "num_key_value_heads": 16,
+    "head_dim": 128, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
+    "max_position_embeddings": 8192, "decoder_sparse_step": 1, "num_experts": 60, "num_experts_per_tok": 4,
+    "norm_topk_prob": False, "moe_intermediate_size": 1408, "shared_expert_intermediate_size": 5632,
+    "intermediate_size": 5632, "qkv_bias": True, "tie_word_embeddings": False, "use_sliding_window": False,
+    "mlp_only_layers": [], "hidden_act": "silu", "eos_token_id": -1,
+}
+# Two experts whose probabilities in the oracle are this close (relative) may be swapped by the engine.
+# In bfloat16 the router reads activations rounded to 8 bits of mantissa.  Measured against the oracle at
+# this width, the engine's probabilities of the picked experts are off by 0.3% on average in the first
+# layer (1.5% at most among 2,400) and by 0.45% in the second: a logit error of sigma = 0.004 to 0.005, so
+# that the difference of two logits has sigma = 0.007 and a swap at a gap of 2% is a 3-sigma event, seen
+# about once among the 2,000 choices of this test.  3% is a little over 4 sigma.
+NEAR_TIE = {torch.float32: 1e-5, torch.bfloat16: 3e-2}
+LENGTHS = {"r0": 600, "r1": 331, "r2": 70}
+# the same requests cut two ways; (request, new tokens) per step
+WHOLE = [[("r0", 600)], [("r1", 331)], [("r2", 70)]]
+MIXED = [[("r0", 300), ("r2", 40)], [("r0", 256), ("r1", 77)], [("r0", 40), ("r1", 250), ("r2", 28)],
+         [("r0", 2), ("r1", 2), ("r2", 1)], [("r0", 1), ("r1", 1), ("r2", 1)], [("r0", 1), ("r1", 1)]]
+
+
+def wanted(n):
+    """Places of a portion whose logits are compared: its ends and a few between."""
+    return sorted({0, n - 1, n // 2, n // 3, (7 * n) // 8})
+
+
+class FullCase:
+    def __init__(self, tmp):
+        from locus_b200.weights.loader import write_random_model
+        import locus_b200.models  # noqa: F401
+
+        self.dir = write_random_model(FULL, 3, str(tmp / "full"), torch.bfloat16)
+        self.cfg, self.weights = plain.load_folder(self.dir)
+        self.tokens = {rid: random_tokens(n, FULL["vocab_size"], 40 + n) for rid, n in LENGTHS.items()}
+        self.positions = {}
+        for steps in (WHOLE, MIXED):
+            fed = {}
+            for step in steps:
+                for rid, n in step:
+                    a = fed.get(rid, 0)
+                    self.positions.setdefault(rid, set()).update(a + w for w in wanted(n))
+                    fed[rid] = a + n
+            assert fed == LENGTHS
+        self.positions = {rid: sorted(p) for rid, p in self.positions.items()}
+        self._own = {}
+        self._followed = {}
+
+    def own(self, rid):
+        if rid not in self._own:
+            aux = {}
+            lg = plain.forward(self.cfg, self.weights, self.tokens[rid], torch.float64, aux=aux,
+                               positions=self.positions[rid])
+            self._own[rid] = (lg, aux)
+        return self._own[rid]
+
+    def following(self, rid, routed, near_tie):
+        """Oracle logits at the compared places with the engine's expert choices.  Layer by layer:
+        the engine's choice in a layer may differ from the oracle's only where the oracle's
+        probabilities, computed with the engine's choices in the layers before, are within
+        ``near_tie`` of each other; the oracle then takes the engine's choice and goes on."""
+        lg, aux = self.own(rid)
+        forced = {}
+        for prefix, per_pos in routed.items():   # in layer order
+            rows, n_diff = [], 0
+            for pos, (ids, probs) in enumerate(aux[prefix]):
+                eng = per_pos[pos]
+                if sorted(eng) != sorted(ids):
+                    n_diff += 1
+                    kth = min(float(probs[e]) for e in ids)
+                    for e in eng:
+                        assert float(probs[e]) >= kth * (1 - near_tie), (
+                            f"{rid} {prefix} position {pos}: the engine picked expert {e} "
+                            f"(p={float(probs[e]):.6f}) although the k-th best has p={kth:.6f}")
+                rows.append(eng)
+            forced[prefix] = rows
+            if n_diff:
+                key = (rid, repr(sorted(forced.items())))   # both ways of cutting mostly choose alike
+                if key not in self._followed:
+                    aux = {}
+                    lg = plain.forward(self.cfg, self.weights, self.tokens[rid], torch.float64, aux=aux,
+                                       forced_routing=dict(forced), positions=self.positions[rid])
+                    self._followed[key] = (lg, aux)
+                lg, aux = self._followed[key]
+        return lg
+
+
+@pytest.fixture(scope="module")
+def full(tmp_path_factory):
+    return FullCase(tmp_path_factory.mktemp("full_size"))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_full_layer_sizes(full, dtype):
+    import locus_b200.kernels as K
+    from locus_b200.cache import CacheManager
+    from locus_b200.engine.step import ModelRunner, StepEntry
+    from locus_b200.models import load_model
+
+    model = load_model(full.dir, dtype, "cuda:0")
+    # 18 pages of 64 tokens, what the three requests hold together (10 + 6 + 2); the second way of
+    # cutting runs on the pages that the first gave back (poisoned in between)
+    cache = CacheManager(model.cache_needs(), page_tokens=64, n_pages=18, n_state_slots=4, max_seq_tokens=1024,
+                         dtype=dtype, device="cuda:0", poison=True)
+    runner = ModelRunner(model, cache, max_tokens=640, max_segments=4)
+    for steps in (WHOLE, MIXED):
+        seen = []
+        for part in model.all_parts():
+            if hasattr(part, "observer"):
+                part.observer = lambda prefix, ids, wts: seen.append((prefix, ids.cpu().tolist()))
+        fed, got, routed = {}, {}, {}
+        for step in steps:
+            seen.clear()
+            entries = []
+            for rid, n in step:
+                a = fed.get(rid, 0)
+                seq = cache.get(rid) or cache.open(rid)
+                assert cache.ensure_capacity(seq, n), f"out of pages for {rid}"
+                entries.append(StepEntry(seq, full.tokens[rid][a : a + n], wanted(n)))
+            logits = runner.step(entries).float().cpu()
+            row = lrow = 0
+            for rid, n in step:
+                a = fed.get(rid, 0)
+                for w in wanted(n):
+                    got.setdefault(rid, {})[a + w] = logits[lrow].clone()
+                    lrow += 1
+                for prefix, ids in seen:
+                    routed.setdefault(rid, {}).setdefault(prefix, {}).update({a + i: ids[row + i] for i in range(n)})
+                row += n
+                fed[rid] = a + n
+            for rid, n in step:
+                if fed[rid] == LENGTHS[rid]:
+                    cache.release(cache.get(rid))
+            cache.check_invariants()
+        assert cache.free_pages() == cache.total_pages()
+        tol_max, tol_mean = TOL[dtype]
+        for rid in LENGTHS:
+            ref = full.following(rid, routed[rid], NEAR_TIE[dtype])
+            places = full.positions[rid]
+            mine = torch.stack([got[rid][p] for p in places if p in got[rid]]).double()
+            ref = ref[[i for i, p in enumerate(places) if p in got[rid]]]
+            assert torch.isfinite(mine).all()
+            scale = float(ref.abs().max())
+            err = (mine - ref).abs()
+            assert float(err.max()) <= tol_max * scale, (
+                f"{rid}: max error {float(err.max()):.3e} > {tol_max * scale:.3e} at place "
+                f"{places[int(err.max(dim=1).values.argmax())]}")
+            assert float(err.mean()) <= tol_mean * scale, f"{rid}: mean error {float(err.mean()):.3e}"
+    if dtype == torch.bfloat16:
+        assert K.attn_tc_error() == 0
