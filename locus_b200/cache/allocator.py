@@ -4,12 +4,15 @@ Same contract as the reference's ``BlockAllocator``
 (src/locus/kv/block_allocator.hpp:25-73, block_allocator.cpp:7-54): a free list that hands
 out the most recently freed id first (ids 0, 1, 2, ... from a fresh pool), a count per id,
 ``retain`` to share, ``release`` to drop one reference (the id is free again at zero), and
-errors on misuse (double free, retain of a free id, id out of range).  Not thread-safe; the
-scheduler serialises access.
+errors on misuse (double free, retain of a free id, id out of range).  The pool itself is
+the ``Pool`` of ``csrc/host_core.cpp``, the type the cache's own pools are made of; this
+class words its return codes.  Not thread-safe; the scheduler serialises access.
 """
 from __future__ import annotations
 
 from typing import List
+
+from . import native
 
 
 class AllocatorError(RuntimeError):
@@ -20,9 +23,14 @@ class PageAllocator:
     def __init__(self, n: int) -> None:
         if n < 0:
             raise ValueError("pool size must not be negative")
+        self._lib = native.lib()
+        self._pool = self._lib.locus_pool_new(n)
         self._n = n
-        self._free: List[int] = list(range(n - 1, -1, -1))  # pop() hands out 0 first
-        self._refs: List[int] = [0] * n
+
+    def __del__(self) -> None:
+        pool, self._pool = getattr(self, "_pool", None), None
+        if pool:
+            self._lib.locus_pool_delete(pool)
 
     @property
     def total(self) -> int:
@@ -30,42 +38,41 @@ class PageAllocator:
 
     @property
     def free(self) -> int:
-        return len(self._free)
+        return self._lib.locus_pool_free(self._pool)
 
     def ref_count(self, i: int) -> int:
-        self._check(i)
-        return self._refs[i]
+        r = self._lib.locus_pool_refs(self._pool, int(i))
+        if r < 0:
+            self._out_of_range(i)
+        return r
 
     def allocate(self) -> int:
-        if not self._free:
+        i = self._lib.locus_pool_allocate(self._pool)
+        if i < 0:
             raise AllocatorError("pool exhausted")
-        i = self._free.pop()
-        self._refs[i] = 1
         return i
 
     def allocate_many(self, n: int) -> List[int]:
         """``n`` ids, all or nothing."""
-        if n > len(self._free):
-            raise AllocatorError(f"pool exhausted: {n} wanted, {len(self._free)} free")
+        if n > self.free:
+            raise AllocatorError(f"pool exhausted: {n} wanted, {self.free} free")
         return [self.allocate() for _ in range(n)]
 
     def retain(self, i: int) -> None:
-        self._check(i)
-        if self._refs[i] == 0:
+        r = self._lib.locus_pool_retain(self._pool, int(i))
+        if r == -1:
+            self._out_of_range(i)
+        if r == -2:
             raise AllocatorError(f"retain of free id {i}")
-        self._refs[i] += 1
 
     def release(self, i: int) -> bool:
         """Drop one reference; True when the id went back to the free list."""
-        self._check(i)
-        if self._refs[i] == 0:
+        r = self._lib.locus_pool_release(self._pool, int(i))
+        if r == -1:
+            self._out_of_range(i)
+        if r == -2:
             raise AllocatorError(f"release of free id {i} (freed twice)")
-        self._refs[i] -= 1
-        if self._refs[i] == 0:
-            self._free.append(i)
-            return True
-        return False
+        return r == 1
 
-    def _check(self, i: int) -> None:
-        if not (0 <= i < self._n):
-            raise AllocatorError(f"id {i} out of range 0..{self._n - 1}")
+    def _out_of_range(self, i: int) -> None:
+        raise AllocatorError(f"id {i} out of range 0..{self._n - 1}")

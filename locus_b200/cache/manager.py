@@ -11,46 +11,83 @@ as every position they hold has fallen out of the window.  A request also takes 
 slot when it is opened; layers with per-request state keep a tensor
 [n_state_slots, *shape] that the slot indexes.
 
+The bookkeeping (pools, tables, what a window has passed) is host code in C++
+(``csrc/host_core.cpp``); this module owns the device tensors, words the errors, and hands
+the step function the native object that assembles a step's descriptors from the tables.
+
 Device layout of a group: ``pool[call, page, 0=K|1=V, kv_head, slot_in_page, head_dim]``;
 a layer call sees ``pool[call]``.  A page id means the same page in every call of the group.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from ..engine.batch import LayerCache
 from ..parts.base import PagedKvSpec, StateSpec
-from .allocator import AllocatorError, PageAllocator
+from . import native
+from .allocator import AllocatorError  # noqa: F401  (part of this package's interface)
 
 
 class CacheError(RuntimeError):
     pass
 
 
-@dataclass
 class SeqCache:
-    """What one request holds: tokens cached, one page table per group, a state slot."""
+    """What one request holds: tokens cached, one page table per group, a state slot.  A view of
+    the native record; after ``release`` it reads as closed and empty."""
 
-    seq_id: object
-    n_tokens: int = 0
-    tables: Dict[int, List[int]] = field(default_factory=dict)  # -1 = page given back (window)
-    state_slot: int = -1
-    open: bool = True
+    __slots__ = ("seq_id", "_cache", "_handle")
+
+    def __init__(self, cache: "CacheManager", seq_id, handle: int) -> None:
+        self.seq_id = seq_id
+        self._cache = cache
+        self._handle = handle
+
+    @property
+    def open(self) -> bool:
+        return bool(self._cache._lib.locus_cache_is_open(self._cache._core, self._handle))
+
+    @property
+    def n_tokens(self) -> int:
+        return max(0, self._cache._lib.locus_cache_n_tokens(self._cache._core, self._handle))
+
+    @property
+    def state_slot(self) -> int:
+        return self._cache._lib.locus_cache_state_slot(self._cache._core, self._handle)
+
+    @property
+    def tables(self) -> Dict[int, List[int]]:
+        """A copy of the page table of every group; -1 = page given back (window)."""
+        return {g.gid: self._cache.table_row(self, g.gid) for g in self._cache.groups}
 
     def pages_held(self, gid: int) -> int:
-        return sum(1 for p in self.tables.get(gid, ()) if p >= 0)
+        return sum(1 for p in self._cache.table_row(self, gid) if p >= 0)
 
 
 class _Group:
-    def __init__(self, gid: int, spec: PagedKvSpec, n_pages: int) -> None:
+    def __init__(self, gid: int, spec: PagedKvSpec) -> None:
         self.gid = gid
         self.spec = spec
         self.calls: List[int] = []
-        self.allocator = PageAllocator(n_pages)
         self.pool: Optional[torch.Tensor] = None
+
+
+class _StateSlots:
+    """Counts of the per-request state slots."""
+
+    def __init__(self, cache: "CacheManager") -> None:
+        self._cache = cache
+
+    @property
+    def free(self) -> int:
+        return self._cache._lib.locus_cache_slots_free(self._cache._core)
+
+    @property
+    def total(self) -> int:
+        return self._cache._lib.locus_cache_slots_total(self._cache._core)
 
 
 class CacheManager:
@@ -89,12 +126,22 @@ class CacheManager:
             if gid is None:
                 gid = len(self.groups)
                 by_spec[paged] = gid
-                self.groups.append(_Group(gid, paged, n_pages))
+                self.groups.append(_Group(gid, paged))
             g = self.groups[gid]
             self._call_group.append(gid)
             self._call_index.append(len(g.calls))
             g.calls.append(i)
-        self.state_slots = PageAllocator(n_state_slots)
+        self._lib = native.lib()
+        windows = (ctypes.c_int * max(1, len(self.groups)))(*[g.spec.window for g in self.groups])
+        self._core = self._lib.locus_cache_new(len(self.groups), windows, page_tokens, n_pages, n_state_slots,
+                                               max_seq_tokens)
+        if not self._core:
+            raise ValueError("the native cache could not be created from these sizes")
+        assert self._lib.locus_cache_table_width(self._core) == self.table_width
+        self.state_slots = _StateSlots(self)
+        # (group, page) pairs that a commit or a release made free
+        self._freed = (ctypes.c_int * (2 * max(1, len(self.groups)) * max(1, self.table_width)))()
+        self._row = (ctypes.c_int * max(1, self.table_width))()
         self._state: List[Optional[torch.Tensor]] = []
         for i, (paged, state, cache_of) in enumerate(needs):
             if cache_of is not None:
@@ -123,8 +170,8 @@ class CacheManager:
     def free_pages(self, gid: Optional[int] = None) -> int:
         """Free pages of one group, or the smallest count over all groups."""
         if gid is not None:
-            return self.groups[gid].allocator.free
-        return min((g.allocator.free for g in self.groups), default=self.n_pages)
+            return self._lib.locus_cache_free_pages(self._core, gid)
+        return min((self._lib.locus_cache_free_pages(self._core, g.gid) for g in self.groups), default=self.n_pages)
 
     def total_pages(self) -> int:
         return self.n_pages
@@ -144,14 +191,14 @@ class CacheManager:
         """Start a request: takes a state slot (zeroed); raises CacheError when none is free."""
         if seq_id in self._live:
             raise CacheError(f"request {seq_id!r} is already open")
-        try:
-            slot = self.state_slots.allocate()
-        except AllocatorError:
-            raise CacheError("no free state slot") from None
+        handle = self._lib.locus_cache_open(self._core)
+        if handle < 0:
+            raise CacheError("no free state slot")
+        seq = SeqCache(self, seq_id, handle)
+        slot = seq.state_slot
         for st in self._state:
             if st is not None:
                 st[slot].zero_()
-        seq = SeqCache(seq_id=seq_id, state_slot=slot, tables={g.gid: [] for g in self.groups})
         self._live[seq_id] = seq
         return seq
 
@@ -163,47 +210,35 @@ class CacheManager:
 
     def capacity(self, seq: SeqCache) -> int:
         """Tokens the request's tables can hold without taking another page."""
-        if not self.groups:
-            return self.max_seq_tokens
-        return min(len(seq.tables[g.gid]) for g in self.groups) * self.page_tokens
+        return max(0, self._lib.locus_cache_capacity(self._core, seq._handle))
 
     def pages_missing(self, seq: SeqCache, n_more: int) -> Dict[int, int]:
         want = self.pages_for(seq.n_tokens + n_more)
-        return {g.gid: max(0, want - len(seq.tables[g.gid])) for g in self.groups}
+        return {g.gid: max(0, want - len(self.table_row(seq, g.gid))) for g in self.groups}
 
     def ensure_capacity(self, seq: SeqCache, n_more: int) -> bool:
         """Make room for ``n_more`` tokens after the cached ones, in every group, all or
         nothing: False (and nothing taken) when any group is short of pages."""
         self._check_open(seq)
-        if seq.n_tokens + n_more > self.max_seq_tokens:
+        r = self._lib.locus_cache_ensure(self._core, seq._handle, int(n_more))
+        if r == -2:
             raise CacheError(f"request {seq.seq_id!r}: {seq.n_tokens + n_more} tokens exceed the "
                              f"limit of {self.max_seq_tokens}")
-        missing = self.pages_missing(seq, n_more)
-        for g in self.groups:
-            if missing[g.gid] > g.allocator.free:
-                return False
-        for g in self.groups:
-            seq.tables[g.gid].extend(g.allocator.allocate_many(missing[g.gid]))
-        return True
+        if r < 0:
+            self._not_open(seq)
+        return r == 1
 
     def commit(self, seq: SeqCache, n: int) -> None:
         """``n`` tokens were written after the cached ones.  Gives back window pages that no
         later query can see: a query at position p sees keys t > p - window, the next query
         is at position n_tokens, so pages wholly below n_tokens - window + 1 are dead."""
         self._check_open(seq)
-        if seq.n_tokens + n > self.capacity(seq):
+        r = self._lib.locus_cache_commit(self._core, seq._handle, int(n), self._freed, len(self._freed))
+        if r == -3:
             raise CacheError(f"request {seq.seq_id!r}: commit of {n} tokens beyond its capacity")
-        seq.n_tokens += n
-        for g in self.groups:
-            w = g.spec.window
-            if w <= 0:
-                continue
-            dead = (seq.n_tokens - w + 1) // self.page_tokens
-            table = seq.tables[g.gid]
-            for i in range(min(max(dead, 0), len(table))):
-                if table[i] >= 0:
-                    self._give_back(g, table[i])
-                    table[i] = -1
+        if r < 0:
+            self._not_open(seq)
+        self._poison_freed(r)
 
     def adopt(self, seq: SeqCache, n: int) -> bool:
         """Declare ``n`` more tokens as cached without writing them: takes the pages and
@@ -217,32 +252,38 @@ class CacheManager:
     def release(self, seq: SeqCache) -> None:
         """The request ends (or is preempted): everything it holds goes back."""
         self._check_open(seq)
-        for g in self.groups:
-            for p in seq.tables[g.gid]:
-                if p >= 0:
-                    self._give_back(g, p)
-            seq.tables[g.gid] = []
-        self.state_slots.release(seq.state_slot)
-        seq.state_slot = -1
-        seq.n_tokens = 0
-        seq.open = False
+        r = self._lib.locus_cache_release(self._core, seq._handle, self._freed, len(self._freed))
+        if r < 0:
+            self._not_open(seq)
         del self._live[seq.seq_id]
+        self._poison_freed(r)
 
-    def _give_back(self, g: _Group, page: int) -> None:
-        freed = g.allocator.release(page)
-        if freed and self.poison and g.pool is not None:
-            g.pool[:, page].fill_(float("nan"))
+    def _poison_freed(self, n_pairs: int) -> None:
+        if not self.poison:
+            return
+        assert 2 * n_pairs <= len(self._freed)
+        for i in range(n_pairs):
+            g = self.groups[self._freed[2 * i]]
+            if g.pool is not None:
+                g.pool[:, self._freed[2 * i + 1]].fill_(float("nan"))
+
+    def _not_open(self, seq: SeqCache) -> None:
+        raise CacheError(f"request {seq.seq_id!r} is not open in this cache")
 
     def _check_open(self, seq: SeqCache) -> None:
-        if not seq.open or self._live.get(seq.seq_id) is not seq:
-            raise CacheError(f"request {seq.seq_id!r} is not open in this cache")
+        if seq._cache is not self or self._live.get(seq.seq_id) is not seq or not seq.open:
+            self._not_open(seq)
 
     # -- step descriptors -----------------------------------------------------
     def table_row(self, seq: SeqCache, gid: int) -> List[int]:
-        return seq.tables[gid]
+        """A copy of the request's page table of one group (empty once the request is closed)."""
+        if seq._cache is not self:
+            self._not_open(seq)
+        n = self._lib.locus_cache_table(self._core, seq._handle, gid, self._row, len(self._row))
+        return list(self._row[: max(0, n)])
 
     def slot_of(self, seq: SeqCache, gid: int, pos: int) -> int:
-        page = seq.tables[gid][pos // self.page_tokens]
+        page = self.table_row(seq, gid)[pos // self.page_tokens]
         if page < 0:
             raise CacheError(f"request {seq.seq_id!r}: position {pos} lies in a page already given back")
         return page * self.page_tokens + pos % self.page_tokens
@@ -250,21 +291,22 @@ class CacheManager:
     # -- invariants -----------------------------------------------------------
     def check_invariants(self) -> None:
         """No page lost, held twice or free while held; state slots likewise.  Raises."""
-        for g in self.groups:
-            held: Dict[int, int] = {}
-            for seq in self._live.values():
-                for p in seq.tables[g.gid]:
-                    if p >= 0:
-                        held[p] = held.get(p, 0) + 1
-            for p, c in held.items():
-                if c != 1:
-                    raise CacheError(f"group {g.gid}: page {p} is held {c} times")
-                if g.allocator.ref_count(p) != 1:
-                    raise CacheError(f"group {g.gid}: page {p} is held but its count is {g.allocator.ref_count(p)}")
-            if len(held) + g.allocator.free != g.allocator.total:
-                raise CacheError(f"group {g.gid}: {g.allocator.total - g.allocator.free - len(held)} pages lost")
-        slots = [s.state_slot for s in self._live.values()]
-        if len(set(slots)) != len(slots):
+        d = (ctypes.c_int * 3)()
+        code = self._lib.locus_cache_check(self._core, d)
+        if code == 1:
+            raise CacheError(f"group {d[0]}: page {d[1]} is held {d[2]} times")
+        if code == 2:
+            raise CacheError(f"group {d[0]}: page {d[1]} is held but its count is {d[2]}")
+        if code == 3:
+            raise CacheError(f"group {d[0]}: {d[1]} pages lost")
+        if code == 4:
             raise CacheError("a state slot is held twice")
-        if len(slots) + self.state_slots.free != self.state_slots.total:
+        if code == 5:
             raise CacheError("state slots lost")
+        if len(self._live) + self.state_slots.free != self.state_slots.total:
+            raise CacheError("the requests known here and the native records differ")
+
+    def __del__(self) -> None:
+        core, self._core = getattr(self, "_core", None), None
+        if core:
+            self._lib.locus_cache_delete(core)

@@ -1,8 +1,10 @@
-"""Builds the CUDA kernel modules for sm_100a with nvcc and loads them with ctypes.
+"""Builds the native modules and loads them with ctypes: the CUDA kernel modules for sm_100a
+with nvcc, the host modules with the C++ compiler.
 
-Each ``<name>.cu`` in this folder is one module with ``extern "C"`` entry points; it is
-compiled to ``_build/lib<name>-<hash>.so`` where the hash covers the source, the shared
-headers and the compiler flags, so a stale library is never loaded.  Modules are built on
+Each ``<name>.cu`` (kernels) or ``<name>.cpp`` (host code without CUDA) in this folder is one
+module with ``extern "C"`` entry points; it is compiled to ``_build/lib<name>-<hash>.so``
+where the hash covers the source, the shared headers and the compiler flags, so a stale
+library is never loaded.  Modules are built on
 demand: a model asks for the modules its parts need, and only those are compiled, in
 parallel, with a progress line every few seconds.  There is no fallback: if nvcc is
 missing or a module fails to build, loading raises :class:`KernelBuildError`.
@@ -32,6 +34,8 @@ NVCC_FLAGS = [
     "-Xcompiler",
     "-fPIC",
 ]
+
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
 
 HEADERS = ["common.cuh"]
 
@@ -75,16 +79,32 @@ def _build_dir() -> str:
         return d
 
 
+def _find_cxx() -> Optional[str]:
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(cand) if cand else None
+        if path:
+            return path
+    return None
+
+
 def module_names() -> List[str]:
-    return sorted(f[:-3] for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
+    return sorted(os.path.splitext(f)[0] for f in os.listdir(CSRC_DIR) if f.endswith((".cu", ".cpp")))
+
+
+def _is_host_module(name: str) -> bool:
+    return os.path.isfile(os.path.join(CSRC_DIR, name + ".cpp"))
 
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for f in [name + ".cu"] + HEADERS + MODULE_HEADERS.get(name, []):
+    if _is_host_module(name):
+        files, flags = [name + ".cpp"], HOST_FLAGS
+    else:
+        files, flags = [name + ".cu"] + HEADERS + MODULE_HEADERS.get(name, []), NVCC_FLAGS + MODULE_FLAGS.get(name, [])
+    for f in files:
         with open(os.path.join(CSRC_DIR, f), "rb") as fh:
             h.update(fh.read())
-    h.update(" ".join(NVCC_FLAGS + MODULE_FLAGS.get(name, [])).encode())
+    h.update(" ".join(flags).encode())
     return h.hexdigest()[:16]
 
 
@@ -93,6 +113,13 @@ def library_path(name: str) -> str:
 
 
 def _compile_cmd(name: str, out: str) -> List[str]:
+    if _is_host_module(name):
+        src = os.path.join(CSRC_DIR, name + ".cpp")
+        cxx = _find_cxx()
+        if cxx is not None:
+            return [cxx] + HOST_FLAGS + ["-o", out, src]
+        # no C++ compiler of its own on the path: nvcc hands the file to the one it was set up with
+        return [_find_nvcc(), "-O2", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "-o", out, src]
     return (
         [_find_nvcc()]
         + NVCC_FLAGS
@@ -109,7 +136,7 @@ def build(names: Optional[Iterable[str]] = None, verbose: bool = True) -> Dict[s
     if not todo:
         return paths
     log = (lambda s: print(s, file=sys.stderr, flush=True)) if verbose else (lambda s: None)
-    log(f"[locus_b200] compiling {len(todo)} CUDA module(s) for sm_100a: {', '.join(todo)}")
+    log(f"[locus_b200] compiling {len(todo)} module(s) (CUDA for sm_100a, host code): {', '.join(todo)}")
     procs = {}
     t0 = time.time()
     for n in todo:
@@ -128,7 +155,7 @@ def build(names: Optional[Iterable[str]] = None, verbose: bool = True) -> Dict[s
                 out = p.stdout.read().decode(errors="replace")
                 pending.discard(n)
                 if p.returncode != 0:
-                    errors.append(f"{n}.cu:\n{out}")
+                    errors.append(f"{n}:\n{out}")
                     if os.path.exists(tmp):
                         os.remove(tmp)
                 else:
@@ -148,7 +175,7 @@ def build(names: Optional[Iterable[str]] = None, verbose: bool = True) -> Dict[s
                 last = time.time()
                 log(f"[locus_b200]   still compiling: {', '.join(sorted(pending))} ({last - t0:.0f}s)")
     if errors:
-        raise KernelBuildError("nvcc failed:\n" + "\n".join(errors))
+        raise KernelBuildError("compilation failed:\n" + "\n".join(errors))
     return paths
 
 

@@ -24,6 +24,7 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
+from ..cache import native
 from ..cache.manager import CacheError, CacheManager, SeqCache
 from .. import kernels as K
 from ..kernels import DECODE_SPLIT
@@ -43,7 +44,24 @@ class StepEntry:
     want: Sequence[int] = ()
 
 
+class _BuildArgs:
+    """The arrays that carry a step's entries to the native assembly and its layout back, made once."""
+
+    def __init__(self, max_tokens: int, max_segments: int, max_wanted: int, n_groups: int) -> None:
+        self.counts = np.zeros(max_segments, dtype=np.int32)
+        self.want_counts = np.zeros(max_segments, dtype=np.int32)
+        self.handles = np.zeros(max_segments, dtype=np.int64)
+        self.tokens = np.zeros(max(1, max_tokens), dtype=np.int64)
+        self.wants = np.zeros(max(1, max_wanted), dtype=np.int64)
+        self.layout = np.zeros(2 * (ModelRunner._N_FIELDS + 2 * n_groups), dtype=np.int32)
+        self.info = np.zeros(8, dtype=np.int32)
+        for name in ("counts", "want_counts", "handles", "tokens", "wants", "layout", "info"):
+            setattr(self, "p_" + name, getattr(self, name).ctypes.data)
+
+
 class ModelRunner:
+    _N_FIELDS = 10  # fields of a step before the per-group ones (csrc/host_core.cpp: locus_step_build)
+
     def __init__(self, model, cache: CacheManager, *, max_tokens: int, max_segments: int,
                  max_wanted: Optional[int] = None, use_graphs: bool = False) -> None:
         self.model = model
@@ -67,7 +85,11 @@ class ModelRunner:
         self._host_events = [torch.cuda.Event() if on_gpu else None for _ in range(2)]
         self._host_used = [False, False]
         self._host_turn = 0
+        self._host_ptrs = [h.data_ptr() for h in self._hosts]
+        self._host_np = [h.numpy() for h in self._hosts]
         self._dev = torch.empty(size, dtype=torch.int32, device=self.device)
+        self._args = _BuildArgs(max_tokens, max_segments, self.max_wanted, G)
+        self._views: Dict[bytes, list] = {}
         self._graphs: Dict[int, torch.cuda.CUDAGraph] = {}
         self._graph_logits: Dict[int, torch.Tensor] = {}
         self._graph_launches: Dict[int, int] = {}
@@ -75,128 +97,115 @@ class ModelRunner:
         self.stats = {"steps": 0, "tokens": 0, "graph_replays": 0, "h2d_bytes": 0}
 
     # ------------------------------------------------------------------
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
-        plan = self.model.plan
-        if not entries:
-            raise StepError("a step needs at least one entry")
-        if len(entries) > self.max_segments:
-            raise StepError(f"{len(entries)} requests in a step, the runner was built for {self.max_segments}")
-        seen = set()
-        T = 0
-        n_want = 0
-        for e in entries:
-            if id(e.seq) in seen:
-                raise StepError(f"request {e.seq.seq_id!r} appears twice in a step")
-            seen.add(id(e.seq))
-            n = len(e.tokens)
-            if n == 0:
-                raise StepError(f"request {e.seq.seq_id!r}: no tokens in its entry")
-            for t in e.tokens:
-                if not (0 <= int(t) < plan.vocab_size):
-                    raise StepError(f"request {e.seq.seq_id!r}: token {t} outside the vocabulary "
-                                    f"0..{plan.vocab_size - 1}")
-            if e.seq.n_tokens + n > plan.max_positions:
-                raise StepError(f"request {e.seq.seq_id!r}: context overflow, {e.seq.n_tokens + n} tokens "
-                                f"exceed max_position_embeddings {plan.max_positions}")
-            if not e.seq.open or self.cache.get(e.seq.seq_id) is not e.seq:
-                raise CacheError(f"request {e.seq.seq_id!r} is not open in the runner's cache")
-            if e.seq.n_tokens + n > self.cache.capacity(e.seq):
-                raise CacheError(f"request {e.seq.seq_id!r}: capacity for {n} more tokens was not ensured")
-            for w in e.want:
-                if not (0 <= int(w) < n):
-                    raise StepError(f"request {e.seq.seq_id!r}: wanted place {w} is not among its {n} tokens")
-            T += n
-            n_want += len(e.want)
-        if T > self.max_tokens:
-            raise StepError(f"{T} tokens in a step, the runner was built for {self.max_tokens}")
-        if n_want > self.max_wanted:
-            raise StepError(f"{n_want} logits rows wanted, the runner was built for {self.max_wanted}")
-
     def _build(self, entries: Sequence[StepEntry], fixed_splits: bool) -> StepBatch:
-        cache = self.cache
-        P = cache.page_tokens
-        W = cache.table_width
-        tokens: List[int] = []
-        positions: List[int] = []
-        seg_q0, seg_qn, seg_ctx, slots_state, want_rows = [], [], [], [], []
-        chunk_items: List[int] = []
-        chunk_items64: List[int] = []
-        decode_items: List[int] = []
-        longest = 0
-        for s, e in enumerate(entries):
-            n, ctx = len(e.tokens), e.seq.n_tokens
-            seg_q0.append(len(tokens))
-            seg_qn.append(n)
-            seg_ctx.append(ctx)
-            slots_state.append(e.seq.state_slot)
-            for w in e.want:
-                want_rows.append(len(tokens) + int(w))
-            tokens.extend(int(t) for t in e.tokens)
-            positions.extend(range(ctx, ctx + n))
-            longest = max(longest, ctx + n)
-            if n == 1:
-                decode_items.append(s)
-            else:
-                for q in range(0, n, CHUNK_TILE):
-                    chunk_items.extend((s, q))
-                for q in range(0, n, K.MMA_QUERY_TILE):
-                    chunk_items64.extend((s, q))
-        T, n_seg = len(tokens), len(entries)
-        fields = [tokens, positions, seg_q0, seg_qn, seg_ctx, slots_state, want_rows, chunk_items, decode_items,
-                  chunk_items64]
-        group_fields = []
-        for g in cache.groups:
-            slots: List[int] = []
-            table: List[int] = []
-            for e in entries:
-                row = e.seq.tables[g.gid]
-                ctx = e.seq.n_tokens
-                for pos in range(ctx, ctx + len(e.tokens)):
-                    page = row[pos // P]
-                    if page < 0:
-                        raise CacheError(f"request {e.seq.seq_id!r}: position {pos} lies in a page given back")
-                    slots.append(page * P + pos % P)
-                table.extend(row)
-                table.extend([-1] * (W - len(row)))
-            group_fields.append((slots, table))
-            fields.extend((slots, table))
-        off = 0
-        views = []
+        """Check the entries and write the step's descriptors: one native call that reads the
+        requests' page tables where they live and fills the pinned staging buffer, then one
+        copy to the device."""
+        cache, plan = self.cache, self.model.plan
+        n_seg = len(entries)
+        if n_seg == 0:
+            raise StepError("a step needs at least one entry")
+        if n_seg > self.max_segments:
+            raise StepError(f"{n_seg} requests in a step, the runner was built for {self.max_segments}")
+        live = cache._live
+        for e in entries:
+            if live.get(e.seq.seq_id) is not e.seq:
+                raise CacheError(f"request {e.seq.seq_id!r} is not open in the runner's cache")
+        a = self._args
+        counts = [len(e.tokens) for e in entries]
+        want_counts = [len(e.want) for e in entries]
+        T_all, W_all = sum(counts), sum(want_counts)
+        if T_all > self.max_tokens:
+            raise StepError(f"{T_all} tokens in a step, the runner was built for {self.max_tokens}")
+        if W_all > self.max_wanted:
+            raise StepError(f"{W_all} logits rows wanted, the runner was built for {self.max_wanted}")
+        a.counts[:n_seg] = counts
+        a.want_counts[:n_seg] = want_counts
+        a.handles[:n_seg] = [e.seq._handle for e in entries]
+        try:
+            a.tokens[:T_all] = [t for e in entries for t in e.tokens]
+            a.wants[:W_all] = [w for e in entries for w in e.want]
+        except OverflowError:
+            raise StepError("a token id or wanted place does not fit 64 bits: outside the vocabulary") from None
+
         turn = self._host_turn
-        self._host_turn ^= 1
         if self._host_used[turn] and self._host_events[turn] is not None:
             self._host_events[turn].synchronize()
         host = self._hosts[turn]
-        hn = host.numpy()
-        for f in fields:
-            n = len(f)
-            if n:
-                hn[off : off + n] = f
-            views.append((off, n))
-            off += n
+        code = cache._lib.locus_step_build(
+            cache._core, n_seg, a.p_handles, a.p_counts, a.p_tokens, a.p_want_counts, a.p_wants, plan.vocab_size,
+            plan.max_positions, self.max_tokens, self.max_segments, self.max_wanted, CHUNK_TILE, K.MMA_QUERY_TILE,
+            self._host_ptrs[turn], host.numel(), a.p_layout, a.p_info)
+        info = a.info
+        if code:
+            self._raise_build_error(code, entries, int(info[6]), int(info[7]))
+        self._host_turn ^= 1
+        layout = a.layout
+        off = int(layout[-2]) + int(layout[-1])
         self._dev[:off].copy_(host[:off], non_blocking=True)
         if self._host_events[turn] is not None:
             self._host_events[turn].record()
             self._host_used[turn] = True
         self.stats["h2d_bytes"] += off * 4
 
-        def dv(i):
-            o, n = views[i]
-            return self._dev[o : o + n]
+        # the device views of a layout are made once: steps of the same shape (every decode step of
+        # a batch size) have the same layout
+        key = layout.tobytes()
+        views = self._views.get(key)
+        if views is None:
+            if len(self._views) > 256:
+                self._views.clear()
+            views = [self._dev[int(layout[2 * i]) : int(layout[2 * i]) + int(layout[2 * i + 1])]
+                     for i in range(len(layout) // 2)]
+            views[7], views[9] = views[7].view(-1, 2), views[9].view(-1, 2)
+            W = cache.table_width
+            for gi in range(len(cache.groups)):
+                views[self._N_FIELDS + 2 * gi + 1] = views[self._N_FIELDS + 2 * gi + 1].view(n_seg, W)
+            self._views[key] = views
+        hn = self._host_np[turn]
 
+        def hv(i):
+            return hn[layout[2 * i] : layout[2 * i] + layout[2 * i + 1]].tolist()
+
+        longest = int(info[2])
         max_splits = (cache.max_seq_tokens - 1) // DECODE_SPLIT + 1 if fixed_splits else (longest - 1) // DECODE_SPLIT + 1
         batch = StepBatch(
-            T=T, n_seg=n_seg, tokens=dv(0), positions=dv(1), seg_q0=dv(2), seg_qn=dv(3), seg_ctx=dv(4),
-            state_slots=dv(5), want_rows=dv(6), n_want=len(want_rows),
-            chunk_items=dv(7).view(-1, 2), n_chunk_items=len(chunk_items) // 2,
-            chunk_items64=dv(9).view(-1, 2), n_chunk_items64=len(chunk_items64) // 2,
-            decode_items=dv(8), n_decode_items=len(decode_items), max_splits=max_splits,
-            host_seg_q0=seg_q0, host_seg_qn=seg_qn, host_seg_ctx=seg_ctx, host_state_slots=slots_state,
+            T=int(info[0]), n_seg=n_seg, tokens=views[0], positions=views[1], seg_q0=views[2], seg_qn=views[3],
+            seg_ctx=views[4], state_slots=views[5], want_rows=views[6], n_want=int(info[1]),
+            chunk_items=views[7], n_chunk_items=int(info[3]), chunk_items64=views[9], n_chunk_items64=int(info[5]),
+            decode_items=views[8], n_decode_items=int(info[4]), max_splits=max_splits,
+            host_seg_q0=hv(2), host_seg_qn=hv(3), host_seg_ctx=hv(4), host_state_slots=hv(5),
         )
         for gi, g in enumerate(cache.groups):
-            batch.groups[g.gid] = GroupBatch(block_table=dv(10 + 2 * gi + 1).view(n_seg, W), slots=dv(10 + 2 * gi),
-                                             page_tokens=P)
+            batch.groups[g.gid] = GroupBatch(block_table=views[self._N_FIELDS + 2 * gi + 1],
+                                             slots=views[self._N_FIELDS + 2 * gi], page_tokens=cache.page_tokens)
         return batch
+
+    def _raise_build_error(self, code: int, entries, at: int, value: int) -> None:
+        """Words the native step assembly's refusal (its codes are listed in csrc/host_core.cpp)."""
+        plan = self.model.plan
+        e = entries[at] if 0 <= at < len(entries) else None
+        who = repr(e.seq.seq_id) if e is not None else "?"
+        n = len(e.tokens) if e is not None else 0
+        if code == 3:
+            raise StepError(f"request {who} appears twice in a step")
+        if code == 4:
+            raise StepError(f"request {who}: no tokens in its entry")
+        if code == 5:
+            raise StepError(f"request {who}: token {int(e.tokens[value])} outside the vocabulary "
+                            f"0..{plan.vocab_size - 1}")
+        if code == 6:
+            raise StepError(f"request {who}: context overflow, {value} tokens exceed max_position_embeddings "
+                            f"{plan.max_positions}")
+        if code == 7:
+            raise CacheError(f"request {who} is not open in the runner's cache")
+        if code == 8:
+            raise CacheError(f"request {who}: capacity for {n} more tokens was not ensured")
+        if code == 9:
+            raise StepError(f"request {who}: wanted place {int(e.want[value])} is not among its {n} tokens")
+        if code == 12:
+            raise CacheError(f"request {who}: position {value} lies in a page given back")
+        raise StepError(f"the step could not be assembled (code {code})")
 
     def check_device_errors(self) -> None:
         """Raise if a kernel recorded a fault since the last check (a bounded wait of the
@@ -217,7 +226,6 @@ class ModelRunner:
         """Run the entries' tokens; returns logits [n_wanted, vocab] (float32, on the device,
         rows in the order of the entries and of their ``want``; valid until the next step).
         The requests' token counts are advanced."""
-        self._validate(entries)
         decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         graphed = self.use_graphs and decode_only and self.device.type == "cuda"
         batch = self._build(entries, fixed_splits=graphed)

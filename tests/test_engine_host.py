@@ -118,3 +118,71 @@ def test_generation_through_the_engine_matches_plain_greedy(name, tmp_path):
     from locus_b200.sampling.sampler import SamplingParams
     c = eng.generate(prompts[:1], max_new_tokens=5, sampling=SamplingParams(repeat_penalty=1.5, presence_penalty=0.5))
     assert len(c[0]) == 5
+
+
+def plain_descriptors(cache, entries, chunk_tile, mma_tile):
+    """The descriptors of a step, written down from their definitions with lists."""
+    P, W = cache.page_tokens, cache.table_width
+    out = {k: [] for k in ("tokens", "positions", "seg_q0", "seg_qn", "seg_ctx", "state_slots", "want_rows",
+                           "chunk_items", "decode_items", "chunk_items64")}
+    groups = {g.gid: {"slots": [], "table": []} for g in cache.groups}
+    for s, e in enumerate(entries):
+        n, ctx = len(e.tokens), e.seq.n_tokens
+        out["seg_q0"].append(len(out["tokens"]))
+        out["seg_qn"].append(n)
+        out["seg_ctx"].append(ctx)
+        out["state_slots"].append(e.seq.state_slot)
+        out["want_rows"] += [len(out["tokens"]) + w for w in e.want]
+        out["tokens"] += list(e.tokens)
+        out["positions"] += list(range(ctx, ctx + n))
+        if n == 1:
+            out["decode_items"].append(s)
+        else:
+            out["chunk_items"] += [[s, q] for q in range(0, n, chunk_tile)]
+            out["chunk_items64"] += [[s, q] for q in range(0, n, mma_tile)]
+        for gid, row in e.seq.tables.items():
+            groups[gid]["slots"] += [row[p // P] * P + p % P for p in range(ctx, ctx + n)]
+            groups[gid]["table"].append(row + [-1] * (W - len(row)))
+    return out, groups
+
+
+def test_step_descriptors_match_a_plain_assembly(tmp_path):
+    """The native step assembly against the same descriptors built with Python lists: random mixed steps
+    over a cache with a window group (tables with holes) beside a full one, requests that end and come back."""
+    import random
+
+    import locus_b200.kernels as K
+    from locus_b200.engine.step import CHUNK_TILE
+
+    cfg, W, model, cache, runner = setup("C", tmp_path, n_pages=40, page=16, max_tokens=96)
+    assert any(g.spec.window > 0 for g in cache.groups) and any(g.spec.window == 0 for g in cache.groups)
+    rng = random.Random(4)
+    names = ["a", "b", "c", "d"]
+    for it in range(60):
+        entries = []
+        for r in rng.sample(names, rng.randint(1, 4)):
+            seq = cache.get(r) or cache.open(r)
+            n = rng.choice([1, 1, 2, 3, 16, 17, 23])
+            if seq.n_tokens + n > 150 or not cache.ensure_capacity(seq, n):
+                cache.release(seq)
+                continue
+            toks = [rng.randrange(cfg["vocab_size"]) for _ in range(n)]
+            entries.append(StepEntry(seq, toks, sorted(rng.sample(range(n), rng.randint(0, min(n, 3))))))
+        if not entries:
+            continue
+        want, want_groups = plain_descriptors(cache, entries, CHUNK_TILE, K.MMA_QUERY_TILE)
+        batch = runner._build(entries, fixed_splits=False)
+        for k, v in want.items():
+            got = getattr(batch, k)
+            assert got.tolist() == v, (it, k)
+        assert (batch.T, batch.n_seg, batch.n_want) == (len(want["tokens"]), len(entries), len(want["want_rows"]))
+        assert (batch.n_chunk_items, batch.n_chunk_items64, batch.n_decode_items) == (
+            len(want["chunk_items"]), len(want["chunk_items64"]), len(want["decode_items"]))
+        assert batch.host_seg_q0 == want["seg_q0"] and batch.host_seg_ctx == want["seg_ctx"]
+        assert batch.host_seg_qn == want["seg_qn"] and batch.host_state_slots == want["state_slots"]
+        for gid, g in want_groups.items():
+            assert batch.groups[gid].slots.tolist() == g["slots"], (it, gid)
+            assert batch.groups[gid].block_table.tolist() == g["table"], (it, gid)
+        for e in entries:
+            cache.commit(e.seq, len(e.tokens))
+        cache.check_invariants()
