@@ -255,15 +255,12 @@ def token_tile(m: int, dual: bool = False) -> int:
 
 
 def expert_tile(n_pairs: int, n_experts: int) -> int:
-    """Row tile of a grouped product from the mean number of rows per expert."""
-    mean = n_pairs / max(1, n_experts)
-    if mean >= 96:
-        return 128
-    if mean >= 40:
-        return 64
-    if mean >= 12:
-        return 32
-    return 16
+    """Row tile of a grouped product on the tensor cores.  Always the full 128 rows: a tile reads its
+    tokens through a box that fits the rows it really has (16 to 256), so a tile with few rows costs little,
+    and every expert's weights stream once.  Measured on the routed experts of 60 x (2048 -> 1408 -> 2048),
+    4 picks: 75 us for 8 tokens, 148 us for 32, 173 us for 64, 181 us for 512, 238 us for 2,048 (the
+    weight-streaming kernel with tiles of 8 to 32 rows: 79, 167, 219, 626 us)."""
+    return 128
 
 
 def tc_error() -> int:

@@ -3,6 +3,7 @@
     python -m locus_b200.tools.kernel_bench linear --m 2048 --n 6144 --k 2048 [--dual] [--accumulate] [--iters 20]
     python -m locus_b200.tools.kernel_bench attn_decode --batch 8 --ctx 4000 [--heads 16 --kv-heads 16 --head-dim 128]
     python -m locus_b200.tools.kernel_bench attn_chunk --tokens 2048 --ctx 0
+    python -m locus_b200.tools.kernel_bench experts --tokens 2048 [--experts 60 --top-k 4 --k 2048 --n 1408] [--part up|down]
 
 Times with CUDA events after warm-up.  Weights rotate through enough copies that the L2
 cannot hold them (``linear``); attention reads a cache larger than the L2 at the default
@@ -75,6 +76,58 @@ def bench_linear(args) -> None:
           f"(tensor-core error word {K.tc_error() if dt == torch.bfloat16 else 0})")
 
 
+def bench_experts(args) -> None:
+    """The two grouped products of the routed experts as the sparse-MoE block runs them: SwiGLU of
+    gate and up ([E, n, k] each) over the tokens laid out by expert, then down ([E, k, n]) with the
+    routing weight of each row, into float32 rows.  Every token picks ``top_k`` distinct experts at
+    random; the layers' weights rotate through copies so that the L2 cannot hold them."""
+    dev = "cuda:0"
+    dt = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    T, E, k, H, I = args.tokens, args.experts, args.top_k, args.k, args.n
+    n_pairs = T * k
+    g = torch.Generator(device="cpu").manual_seed(1)
+    ids = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).reshape(-1).to(dev)
+    wts = torch.rand(n_pairs, device=dev)
+    el = 2 if dt == torch.bfloat16 else 4
+    layer_bytes = 3 * E * I * H * el
+    copies = max(1, min(8, int(3e9 // layer_bytes)))
+    gate = [(torch.randn(E, I, H, device=dev) * 0.02).to(dt) for _ in range(copies)]
+    up = [(torch.randn(E, I, H, device=dev) * 0.02).to(dt) for _ in range(copies)]
+    down = [(torch.randn(E, H, I, device=dev) * 0.02).to(dt) for _ in range(copies)]
+    h = torch.randn(T, H, device=dev).to(dt)
+    tile = args.tile or (K.FEW_ROWS if T <= K.FEW_ROWS else K.expert_tile(n_pairs, E))
+    streamed = tile <= (K.SKINNY_ROWS if dt == torch.bfloat16 else K.FEW_ROWS)
+    if not streamed and dt != torch.bfloat16:
+        tile = 64
+    lay = K.ExpertLayout(n_pairs, E, 64, dev)
+    K.moe_sort(ids, n_pairs, lay, tile)
+    xs = torch.empty(n_pairs, H, device=dev, dtype=dt)
+    K.gather_rows(h, lay.sorted_pair, k, xs, n_pairs)
+    act = torch.empty(n_pairs, I, device=dev, dtype=dt)
+    pair_out = torch.empty(n_pairs, H, device=dev, dtype=torch.float32)
+    state = {"i": 0}
+
+    def fn():
+        i = state["i"] % copies
+        state["i"] += 1
+        if args.part in ("both", "up"):
+            if streamed:
+                K.linear(h, gate[i], act, w2=up[i], x_rows=lay.sorted_pair, x_row_div=k, layout=lay, n_rows=n_pairs)
+            else:
+                K.linear(xs, gate[i], act, w2=up[i], layout=lay, n_rows=n_pairs)
+        if args.part in ("both", "down"):
+            K.linear(act, down[i], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts, scale_rows=lay.sorted_pair)
+
+    us = _time(fn, args.iters, args.graph)
+    share = {"both": 3, "up": 2, "down": 1}[args.part]
+    used = int((torch.bincount(ids.long(), minlength=E) > 0).sum())
+    flops = 2.0 * n_pairs * H * I * share
+    wbytes = used * I * H * el * share
+    print(f"experts T={T} E={E} top_k={k} hidden={H} inner={I} part={args.part} tile={tile} {args.dtype}: "
+          f"{us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s  weights of the {used} experts used {wbytes / us / 1e3:.1f} GB/s  "
+          f"(tensor-core error word {K.tc_error() if dt == torch.bfloat16 else 0})")
+
+
 def _paged(args, B: int, ctx: int, new: int):
     dev = "cuda:0"
     dt = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
@@ -129,7 +182,7 @@ def bench_attn_chunk(args) -> None:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="kernel_bench")
-    ap.add_argument("kernel", choices=["linear", "attn_decode", "attn_chunk"])
+    ap.add_argument("kernel", choices=["linear", "attn_decode", "attn_chunk", "experts"])
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--graph", action="store_true", help="time a CUDA graph of the calls")
@@ -146,13 +199,18 @@ def main(argv=None) -> int:
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--page-tokens", type=int, default=64)
     ap.add_argument("--window", type=int, default=0)
+    ap.add_argument("--experts", type=int, default=60)
+    ap.add_argument("--top-k", type=int, default=4)
+    ap.add_argument("--tile", type=int, default=0, help="experts: rows of a tile instead of the engine's choice")
+    ap.add_argument("--part", default="both", choices=["both", "up", "down"], help="experts: which product")
     ap.add_argument("--cuda-cores", action="store_true", help="attn_chunk: the CUDA-core kernel")
     ap.add_argument("--mma-sync", action="store_true", help="attn_chunk: the mma.sync kernel where tcgen05 would run")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("kernel_bench: no CUDA device", file=sys.stderr)
         return 1
-    {"linear": bench_linear, "attn_decode": bench_attn_decode, "attn_chunk": bench_attn_chunk}[args.kernel](args)
+    {"linear": bench_linear, "attn_decode": bench_attn_decode, "attn_chunk": bench_attn_chunk,
+     "experts": bench_experts}[args.kernel](args)
     return 0
 
 
