@@ -55,6 +55,8 @@ __host__ __device__ __forceinline__ int x_box_rows(int index) { return index == 
 
 struct TileGeom {
     int x_row0, rows_valid, tx, w_row0;  // first token row, live token rows, weight tile, first weight row
+    int kb0, kb1;   // k-blocks of this unit of work (all of them unless the product is split along K)
+    int out_row0;   // first row of the tile in out (x_row0, or the split's rows in the scratch)
 };
 
 struct TcArgs {
@@ -71,6 +73,10 @@ struct TcArgs {
     const int* tile_row0;
     const int* tile_rows;
     const int* n_tiles;
+    // A product with few tiles is split along K so that every SM has work: split s of a tile sums k-blocks
+    // [s * kb_per_split, ...) and stores its float32 sums to rows [s * M, (s + 1) * M) of the scratch that
+    // out then points to; splitk_reduce_kernel adds the splits up in order and does the epilogue.
+    int splits, kb_per_split;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -164,7 +170,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int tiles_y = a.tiles_y;
     const int n_y = a.tile_expert != nullptr ? min(tiles_y, *a.n_tiles) : tiles_y;  // live token tiles
     // only live tiles are numbered, so that every block gets the same number of them (within one)
-    const long long n_total = static_cast<long long>(a.tiles_x) * n_y;
+    const long long n_total = static_cast<long long>(a.tiles_x) * n_y * a.splits;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;  // swizzled tiles need 1024-byte alignment
     const uint32_t x_bytes = static_cast<uint32_t>(a.TN) * TILE_K * 2;
@@ -208,8 +214,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         g.rows_valid = 0;
         g.tx = 0;
         g.w_row0 = 0;
+        g.kb0 = g.kb1 = 0;
+        g.out_row0 = 0;
         if (t >= n_total) return g;  // past the end: an empty tile, never worked on
-        const int ti = static_cast<int>(t);  // the host refuses products of 2^31 tiles or more
+        int ti = static_cast<int>(t);  // the host refuses products of 2^31 tiles or more
+        int split = 0;
+        if (a.splits > 1) {  // the splits of a tile run side by side
+            split = ti % a.splits;
+            ti /= a.splits;
+        }
+        g.kb0 = split * a.kb_per_split;
+        g.kb1 = min(nkb, g.kb0 + a.kb_per_split);
         const int ty = ti / a.tiles_x;  // blocks that run together share a token tile
         g.tx = ti - ty * a.tiles_x;
         g.w_row0 = g.tx * TILE_W;
@@ -221,6 +236,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             g.x_row0 = ty * a.TN;
             g.rows_valid = min(a.TN, a.M - g.x_row0);
         }
+        g.out_row0 = g.x_row0 + split * a.M;
         return g;
     };
     const long long t_step = gridDim.x;
@@ -237,7 +253,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const int box = x_box_index(g.rows_valid);
                 const CUtensorMap* map_x = &maps_x.m[box];
                 const uint32_t bytes = A_BYTES * (1 + DUAL) + static_cast<uint32_t>(min(x_box_rows(box), a.TN)) * (TILE_K * 2);
-                for (int kb = 0; kb < nkb; ++kb) {
+                const int kb_end = g.kb1;
+                for (int kb = g.kb0; kb < kb_end; ++kb) {
                     if (!mbar_wait(bar_empty + 8 * s, (round & 1) ^ 1, 1)) {
                         ok = false;
                         break;
@@ -272,7 +289,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             TileGeom g = tile_geom(blockIdx.x);
             for (long long t = blockIdx.x; t < n_total && ok; t += t_step) {
                 const TileGeom g_next = tile_geom(t + t_step);
-                const int rows_valid = g.rows_valid;
+                const int rows_valid = g.rows_valid, kb_first = g.kb0, kb_end = g.kb1;
                 g = g_next;
                 // the epilogue must have drained this buffer (acc_bufs tiles ago)
                 if (!mbar_wait(bar_acc_empty + 8 * buf, (acc_round & 1) ^ 1, 4)) break;
@@ -284,7 +301,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n_mma >> 3) << 17) |
                                        (static_cast<uint32_t>(TILE_W >> 4) << 24);
                 const uint32_t d0 = tmem + buf * acc_cols;
-                for (int kb = 0; kb < nkb; ++kb) {
+                for (int kb = kb_first; kb < kb_end; ++kb) {
                     if (!ready && !mbar_wait(bar_full + 8 * s, round & 1, 2)) {
                         ok = false;
                         break;
@@ -293,7 +310,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     const uint64_t dw = desc0 + s * stage_units, dw2 = dw + w2_units, dx = dw + x_units;
 #pragma unroll
                     for (int k4 = 0; k4 < TILE_K / 16; ++k4) {
-                        const uint32_t acc = (kb > 0 || k4 > 0) ? 1u : 0u;
+                        const uint32_t acc = (kb > kb_first || k4 > 0) ? 1u : 0u;
                         umma_bf16(d0, dw + 2 * k4, dx + 2 * k4, idesc, acc);  // 16 elements = 32 bytes = 2 units
                         if (DUAL) umma_bf16(d0 + a.TN, dw2 + 2 * k4, dx + 2 * k4, idesc, acc);
                     }
@@ -348,7 +365,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         for (long long t = blockIdx.x; t < n_total; t += t_step) {
             const TileGeom g3 = tile_geom(t + 3 * t_step);
-            const int x_row0 = g.x_row0, rows_valid = g.rows_valid, tx = g.tx;
+            const int rows_valid = g.rows_valid, tx = g.tx;
+            const int x_row0 = g.out_row0;  // rows of out; the row scales go by the token rows (scale_index)
             const long long n = static_cast<long long>(tx) * TILE_W + row;  // output column of this lane
             const bool n_ok = n < a.N;
             if (a.row_scale) {
@@ -493,6 +511,39 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
 }
 
+// Sums the splits of a product that was split along K, in the order of the splits, and does the
+// epilogue of the unsplit kernel: + bias, x row scale, then store or add into out.  part: [splits, M, N]
+// float32; one thread per 4 columns (N is a multiple of 4).
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, int splits, int M, int N,
+                                                            const void* __restrict__ bias, int bias_dt,
+                                                            const float* __restrict__ row_scale,
+                                                            const int* __restrict__ scale_rows, void* out, int out_dt,
+                                                            long long ldo, int accumulate) {
+    pdl_entry();
+    pdl_trigger();
+    const int n4 = N >> 2;
+    const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= static_cast<long long>(M) * n4) return;
+    const int row = static_cast<int>(i / n4), c = static_cast<int>(i - static_cast<long long>(row) * n4) << 2;
+    const size_t plane = static_cast<size_t>(M) * N;
+    const float* p = part + static_cast<size_t>(row) * N + c;
+    float4 acc = *reinterpret_cast<const float4*>(p);
+    for (int s = 1; s < splits; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(p + s * plane);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    float v[4] = {acc.x, acc.y, acc.z, acc.w};
+    const float scale = row_scale ? row_scale[scale_rows ? scale_rows[row] : row] : 1.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        if (bias) v[j] += ld_dyn(bias, bias_dt, c + j);
+        if (row_scale) v[j] *= scale;
+        const size_t o = static_cast<size_t>(row) * ldo + c + j;
+        if (accumulate) static_cast<float*>(out)[o] += v[j];
+        else st_dyn(out, out_dt, o, v[j]);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -540,11 +591,15 @@ static int pow2_at_least(int v) {
 // Plain product: M rows of x, N = w_rows_total.  Grouped: w holds E experts of N rows each,
 // x rows are the expert-sorted pairs, the tile list has tiles of TN rows.
 // TN: token tile, a multiple of 16 in 16..256 (dual: at most 128... 256 columns of tensor memory each).
+// splits > 1 (plain products of one weight matrix, N a multiple of 4): the K range is cut into that many
+// parts that run as tiles of their own and leave float32 sums in split_scratch [splits, M, N]; a second
+// kernel adds them in order and does the epilogue.  The splits are renumbered so that none is empty.
 extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ldx, const void* w, const void* w2,
                              long long w_rows_total, const void* bias, int bias_dt, void* out, int out_dt,
                              int accumulate, const float* row_scale, const int* scale_rows, int M, int N, int K,
                              long long ldo, int TN, const int* tile_expert, const int* tile_row0,
-                             const int* tile_rows, const int* n_tiles, int max_tiles, cudaStream_t stream) {
+                             const int* tile_rows, const int* n_tiles, int max_tiles, float* split_scratch,
+                             int splits, cudaStream_t stream) {
     const int dual = w2 != nullptr ? 1 : 0;
     if (N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
     if (TN < 16 || TN > 256 || TN % 16 != 0 || (dual && TN > 256)) return LOCUS_ERR_UNSUPPORTED;
@@ -587,8 +642,25 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
     a.tmem_cols = pow2_at_least(a.acc_bufs * TN * (1 + dual));
     if (a.tmem_cols > 512) return LOCUS_ERR_UNSUPPORTED;
     a.tiles_x = tiles_x; a.tiles_y = tiles_y;
-    a.accumulate = accumulate; a.out = out; a.out_dt = out_dt; a.ldo = ldo; a.bias = bias; a.bias_dt = bias_dt;
-    a.row_scale = row_scale; a.scale_rows = scale_rows; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
+    a.splits = 1;
+    a.kb_per_split = nkb;
+    if (splits > 1) {
+        if (dual || tile_expert != nullptr || split_scratch == nullptr || N % 4 != 0 ||
+            (reinterpret_cast<uintptr_t>(split_scratch) & 15))
+            return LOCUS_ERR_UNSUPPORTED;
+        a.kb_per_split = ceil_div(nkb, splits < nkb ? splits : nkb);
+        a.splits = ceil_div(nkb, a.kb_per_split);
+        if (n_tiles_all * a.splits >= (1LL << 31)) return LOCUS_ERR_UNSUPPORTED;
+    }
+    const bool split = a.splits > 1;
+    a.accumulate = split ? 0 : accumulate;
+    a.out = split ? split_scratch : out;
+    a.out_dt = split ? LOCUS_DT_F32 : out_dt;
+    a.ldo = split ? N : ldo;
+    a.bias = split ? nullptr : bias;
+    a.bias_dt = bias_dt;
+    a.row_scale = split ? nullptr : row_scale;
+    a.scale_rows = split ? nullptr : scale_rows; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles;
     const size_t smem = static_cast<size_t>(stages) * stage_bytes + 16 * stages + 96 + 16 * TN + 4 * 16 * 36 * 4 + 1024;
     static bool attr_set = false;
@@ -606,9 +678,16 @@ extern "C" int locus_gemm_tc(const void* x, long long x_rows_total, long long ld
         if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sm <= 0)
             return static_cast<int>(cudaGetLastError());
     }
-    const unsigned grid = static_cast<unsigned>(n_tiles_all < n_sm ? n_tiles_all : n_sm);
+    const long long n_units = n_tiles_all * a.splits;
+    const unsigned grid = static_cast<unsigned>(n_units < n_sm ? n_units : n_sm);
     if (dual) gemm_tc_kernel<true><<<grid, 192, smem, stream>>>(map_w, map_w2, maps_x, a);
     else gemm_tc_kernel<false><<<grid, 192, smem, stream>>>(map_w, map_w2, maps_x, a);
+    if (split) {
+        const long long n_threads = static_cast<long long>(M) * (N / 4);
+        locus_launch(splitk_reduce_kernel, static_cast<unsigned>((n_threads + 255) / 256), 256, 0, stream,
+                     static_cast<const float*>(split_scratch), a.splits, M, N, bias, bias_dt, row_scale, scale_rows,
+                     out, out_dt, ldo, accumulate);
+    }
     return locus_launch_status();
 }
 

@@ -11,7 +11,7 @@ plain torch functions of the same signature to exercise the engine's host logic.
 from __future__ import annotations
 
 import ctypes
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -93,6 +93,11 @@ class stream_scope:
 # kernels launched through this module since import (several entry points launch two)
 launches = 0
 _LAUNCHES_OF = {"moe_sort": 2}
+
+
+def _count_launches(n: int) -> None:
+    global launches
+    launches += n
 
 
 def _check(code: int, what: str, detail: str = "") -> None:
@@ -246,12 +251,77 @@ def skinny_takes(x: torch.Tensor, w: torch.Tensor, m: int, layout: Optional["Exp
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def token_tile(m: int, dual: bool = False) -> int:
-    """Token tile (the N side of the MMA) for ``m`` rows."""
-    for t in (16, 32, 64, 128):
+_N_SM = 0
+
+
+def _sm_count() -> int:
+    global _N_SM
+    if _N_SM == 0:
+        _N_SM = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _N_SM
+
+
+SPLIT_SCRATCH_BYTES = 64 << 20   # float32 partial sums of a product split along K
+_PLANS: dict = {}
+_SPLIT_SCRATCH: dict = {}
+
+
+def token_tile(m: int, dual: bool = False, n_weight_tiles: int = 0, k: int = 0) -> int:
+    """Token tile of a plain product on the tensor cores (see :func:`tc_plan`)."""
+    return tc_plan(m, n_weight_tiles * 128, k, dual)[0]
+
+
+def tc_plan(m: int, n: int, k: int, dual: bool) -> Tuple[int, int]:
+    """(token tile, splits along K) of a plain product of ``m`` rows with an [n, k] weight on the
+    tcgen05 kernel.  While a tile waits for its weights its time hardly depends on its tokens (measured at
+    k = 2048, one tile per SM: 12.7 us with 32 tokens, 13.5 with 64, 15 with 128, 18.3 with 256: 0.38 us
+    + 0.75 ns per token for every 64 of k), so what counts is how many rounds the tiles make over the SMs,
+    and a product with few tiles (a 2048-row weight has 16) leaves most SMs idle unless it is also cut
+    along k; the partial sums then cost a second kernel.  The plan with the least estimated time wins."""
+    key = (m, n, k, dual)
+    plan = _PLANS.get(key)
+    if plan is not None:
+        return plan
+    top = 128 if dual else 256
+    cands = [t for t in (16, 32, 64, 128, 256) if t <= top]
+    n_w = max(1, -(-n // 128))
+    if k <= 0:  # sizes unknown: the smallest tile that holds the rows
+        plan = (next((t for t in cands if m <= t), top), 1)
+        _PLANS[key] = plan
+        return plan
+    n_sm = _sm_count()
+    nkb = -(-k // 64)
+    best, best_cost = (top, 1), None
+    for t in cands:
+        if t < 32 and m > t:
+            continue
+        tiles = -(-m // t) * n_w
+        per_kb = (0.38 + 0.00075 * t) * (1.15 if dual else 1.0)
+        options = [1]
+        if not dual and n % 4 == 0 and tiles * 2 <= n_sm and nkb >= 8:
+            s_max = min(n_sm // tiles, nkb // 2, 16, SPLIT_SCRATCH_BYTES // (4 * m * n))
+            options += [s for s in range(2, s_max + 1)]
+        for sp in options:
+            kb = -(-nkb // sp)
+            sp = -(-nkb // kb)
+            rounds = -(-(tiles * sp) // n_sm)
+            cost = rounds * (1.0 + kb * per_kb)
+            if sp > 1:
+                cost += 3.0 + sp * m * n * 4 / 4e6   # the second kernel and its reading of the partial sums
+            if best_cost is None or cost < best_cost - 1e-9 or (abs(cost - best_cost) <= 1e-9 and t > best[0]):
+                best, best_cost = (t, sp), cost
         if m <= t:
-            return t
-    return 128 if dual else 256
+            break
+    _PLANS[key] = best
+    return best
+
+
+def _split_scratch(device) -> torch.Tensor:
+    t = _SPLIT_SCRATCH.get(device)
+    if t is None:
+        t = torch.empty(SPLIT_SCRATCH_BYTES // 4, dtype=torch.float32, device=device)
+        _SPLIT_SCRATCH[device] = t
+    return t
 
 
 def expert_tile(n_pairs: int, n_experts: int) -> int:
@@ -347,21 +417,25 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
     if tensor_cores_take(x, w, x_rows):
         # bfloat16 x bfloat16: tcgen05 kernel (csrc/gemm_tc.cu)
         if layout is not None:
-            TN = layout.tile_m
+            TN, splits, scratch = layout.tile_m, 1, None
             te, t0, tr, nt = layout.tile_expert, layout.tile_row0, layout.tile_rows, layout.n_tiles
             max_tiles = layout.tiles_for(M)
         else:
             _need(w.dim() == 2, "linear: w must be [N, K]")
-            TN = token_tile(M, w2 is not None)
+            TN, splits = tc_plan(M, N, K, w2 is not None)
+            if splits > 1:
+                scratch = _split_scratch(x.device)
             te = t0 = tr = nt = None
             max_tiles = 0
         code = _lib("gemm_tc").locus_gemm_tc(
             _p(x), LL(M), LL(x.stride(0)), _p(w), _p(w2), LL(w.numel() // K), _p(bias),
             I(dtype_code(bias.dtype) if bias is not None else 0), _p(out), I(dtype_code(out.dtype)),
             I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), I(M), I(N), I(K), LL(out.stride(0)), I(TN),
-            _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), _stream()
+            _p(te), _p(t0), _p(tr), _p(nt), I(max_tiles), _p(scratch if splits > 1 else None), I(splits), _stream()
         )
-        _check(code, "linear", f"(tensor cores; M={M}, N={N}, K={K}, token tile {TN})")
+        if splits > 1 and code == 0:
+            _count_launches(1)   # the kernel that adds the splits up
+        _check(code, "linear", f"(tensor cores; M={M}, N={N}, K={K}, token tile {TN}, {splits} splits)")
         return
     if layout is not None:
         _need(layout.tile_m == 64, "linear: the CUDA-core product uses 64-row tiles")

@@ -203,9 +203,20 @@ def main(argv=None) -> int:
     ap.add_argument("--top-k", type=int, default=4)
     ap.add_argument("--tile", type=int, default=0, help="experts: rows of a tile instead of the engine's choice")
     ap.add_argument("--part", default="both", choices=["both", "up", "down"], help="experts: which product")
+    ap.add_argument("--skinny-rows", type=int, default=-1,
+                    help="linear: most rows that go to the weight-streaming kernel instead of the engine's limit")
+    ap.add_argument("--token-tile", type=int, default=0,
+                    help="linear: token tile of the tcgen05 kernel instead of the engine's choice")
+    ap.add_argument("--splits", type=int, default=0,
+                    help="linear: with --token-tile, parts along K (0 = not split)")
     ap.add_argument("--cuda-cores", action="store_true", help="attn_chunk: the CUDA-core kernel")
     ap.add_argument("--mma-sync", action="store_true", help="attn_chunk: the mma.sync kernel where tcgen05 would run")
     args = ap.parse_args(argv)
+    if args.skinny_rows >= 0:
+        K.SKINNY_ROWS = args.skinny_rows
+        K.FEW_ROWS = min(K.FEW_ROWS, args.skinny_rows)
+    if args.token_tile:
+        K.tc_plan = lambda m, n, k, dual: (args.token_tile, max(1, args.splits))
     if not torch.cuda.is_available():
         print("kernel_bench: no CUDA device", file=sys.stderr)
         return 1

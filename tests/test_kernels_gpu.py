@@ -599,6 +599,43 @@ def test_linear_tensor_cores_large_tiles(M, N, K_):
     assert K.tc_error() == 0
 
 
+@pytest.mark.parametrize("M,N,K_,tile,splits", [(64, 2048, 2048, 64, 8), (70, 132, 5632, 32, 16), (257, 64, 200, 128, 3),
+                                                (512, 2048, 1408, 256, 4), (40, 260, 72, 64, 2)])
+def test_linear_tensor_cores_split_along_k(M, N, K_, tile, splits, monkeypatch):
+    """A product with few tiles is cut along K: the partial sums of the parts are added up in order by a
+    second kernel that also does the epilogue.  Forced plans (the last k-block ragged, more parts asked
+    for than there are k-blocks) and the plan the wrapper itself makes."""
+    dt = torch.bfloat16
+    x, w = rnd(M, K_, dtype=dt, seed=3), rnd(N, K_, dtype=dt, seed=4, scale=0.05)
+    bias, rs = rnd(N, dtype=dt, seed=5), rnd(2 * M, seed=6)
+    rows = torch.randperm(2 * M, generator=torch.Generator().manual_seed(7))[:M].to(torch.int32)
+    own = K.tc_plan(M, N, K_, False)
+    for plan in ((tile, splits), own):
+        monkeypatch.setattr(K, "tc_plan", lambda m, n, k, dual, plan=plan: plan if not dual else (min(plan[0], 128), 1))
+        before = K.launches
+        out = torch.empty(M, N, dtype=dt, device=DEV)
+        K.linear(x.to(DEV), w.to(DEV), out, bias=bias.to(DEV))
+        if plan[1] > 1:
+            assert K.launches - before == 2
+        ref = torch.empty(M, N, dtype=torch.float64)
+        EK.linear(x, w, ref, bias=bias)
+        close(out, ref, dt, f"split linear + bias {plan}")
+        res0 = rnd(M, N, seed=8)
+        res = res0.clone().to(DEV)
+        K.linear(x.to(DEV), w.to(DEV), res, row_scale=rs.to(DEV), scale_rows=rows.to(DEV), accumulate=True)
+        ref2 = res0.clone().double()
+        EK.linear(x, w, ref2, row_scale=rs, scale_rows=rows, accumulate=True)
+        close(res, ref2, dt, f"split linear, scaled rows added into float32 {plan}")
+        # the same rows give the same bits wherever they stand in a larger product of the same plan
+        if M >= 48:
+            part = torch.empty(M, N, dtype=torch.float32, device=DEV)
+            K.linear(x.to(DEV), w.to(DEV), part)
+            again = torch.empty(M, N, dtype=torch.float32, device=DEV)
+            K.linear(x.to(DEV), w.to(DEV), again)
+            assert torch.equal(part, again)
+    assert K.tc_error() == 0
+
+
 @pytest.mark.parametrize("tile", [8, 16, 32, 64, 128])  # 8: the row-streaming kernel
 def test_linear_grouped_tensor_cores_every_tile(tile):
     T, E, k, H, I = 210, 7, 3, 136, 72
