@@ -235,13 +235,18 @@ def few_rows_take(x: torch.Tensor, w: torch.Tensor, m: int, layout: Optional["Ex
     return (rows_ok and K % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 32 == 0 and w.data_ptr() % 32 == 0)
 
 
-SKINNY_ROWS = 32      # most rows of x per tile of the weight-streaming tensor-core kernel
+# Most rows of a plain product that go to the weight-streaming tensor-core kernel (it takes up to 32, and
+# expert tiles of 8, 16 or 32 rows).  The four dense products of a layer at the A2.7B sizes take 46 us with
+# either kernel at 16 rows; at 24 rows 59 us there and 47 us on the tcgen05 kernel (cut along K where it has
+# few tiles), at 32 rows 61 and 47.
+SKINNY_ROWS = 16
+SKINNY_TILE_ROWS = 32  # largest expert tile of that kernel's grouped form
 SKINNY_MIN_ROWS = 1
 
 
 def skinny_takes(x: torch.Tensor, w: torch.Tensor, m: int, layout: Optional["ExpertLayout"] = None) -> bool:
     """Whether :func:`linear` runs this product with the weight-streaming tensor-core kernel:
-    bfloat16 x bfloat16, at most 32 rows (per expert tile of 8, 16 or 32 rows when grouped)."""
+    bfloat16 x bfloat16, at most ``SKINNY_ROWS`` rows (per expert tile of 8, 16 or 32 rows when grouped)."""
     K = x.shape[-1]
     if layout is not None:
         rows_ok = layout.tile_m in (8, 16, 32)

@@ -129,7 +129,7 @@ class SparseMoe(FeedForward):
         widths_ok = self.I % 8 == 0 and self.hidden % 8 == 0
         all_bf16 = (K.tensor_cores_take(h, self.params["gate_exps"]) and widths_ok
                     and self.params["down_exps"].dtype == torch.bfloat16)
-        streamed = (all_bf16 and tile <= K.SKINNY_ROWS) or (widths_ok and tile <= K.FEW_ROWS)
+        streamed = (all_bf16 and tile <= K.SKINNY_TILE_ROWS) or (widths_ok and tile <= K.FEW_ROWS)
         if not streamed and not all_bf16:
             tile = 64
         sorted_already = False

@@ -96,7 +96,7 @@ def bench_experts(args) -> None:
     down = [(torch.randn(E, H, I, device=dev) * 0.02).to(dt) for _ in range(copies)]
     h = torch.randn(T, H, device=dev).to(dt)
     tile = args.tile or (K.FEW_ROWS if T <= K.FEW_ROWS else K.expert_tile(n_pairs, E))
-    streamed = tile <= (K.SKINNY_ROWS if dt == torch.bfloat16 else K.FEW_ROWS)
+    streamed = tile <= (K.SKINNY_TILE_ROWS if dt == torch.bfloat16 else K.FEW_ROWS)
     if not streamed and dt != torch.bfloat16:
         tile = 64
     lay = K.ExpertLayout(n_pairs, E, 64, dev)

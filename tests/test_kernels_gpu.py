@@ -668,8 +668,10 @@ def test_linear_grouped_tensor_cores_every_tile(tile):
 
 
 @pytest.mark.parametrize("M,N,K_", [(2, 61, 2048), (8, 2048, 1408), (9, 100, 72), (17, 331, 120), (32, 6144, 2048)])
-def test_linear_skinny_rows(M, N, K_):
-    """2..32 rows of bfloat16: the weight-streaming tensor-core kernel, every epilogue."""
+def test_linear_skinny_rows(M, N, K_, monkeypatch):
+    """2..32 rows of bfloat16: the weight-streaming tensor-core kernel, every epilogue (the wrapper sends
+    it at most ``SKINNY_ROWS`` rows; the kernel takes 32)."""
+    monkeypatch.setattr(K, "SKINNY_ROWS", 32)
     dt = torch.bfloat16
     x, w = rnd(M, K_, dtype=dt, seed=3), rnd(N, K_, dtype=dt, seed=4, scale=0.05)
     assert K.skinny_takes(x.to(DEV), w.to(DEV), M)
