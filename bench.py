@@ -147,6 +147,8 @@ def main() -> int:
     dev = "cuda:0"
     torch.cuda.set_device(0)
     raw = dict(A27B, num_hidden_layers=args.layers)
+    if args.context > raw["max_position_embeddings"]:
+        raw["max_position_embeddings"] = args.context  # a longer synthetic context than the model was trained for
     entry = find_arch("Qwen2MoeForCausalLM")
     cfg = entry.parse_config(raw)
     t0 = time.time()
@@ -159,8 +161,9 @@ def main() -> int:
     P = 64
     ctx = args.context
     max_b = args.batch if args.no_points else max(64, args.batch)
-    n_pages = max_b * (-(-ctx // P))
-    cache = CacheManager(model.cache_needs(), page_tokens=P, n_pages=n_pages, n_state_slots=max_b, max_seq_tokens=ctx,
+    n_pages = max(max_b * (-(-ctx // P)), -(-PREFILL_TOKENS // P))
+    cache = CacheManager(model.cache_needs(), page_tokens=P, n_pages=n_pages, n_state_slots=max_b,
+                         max_seq_tokens=max(ctx, PREFILL_TOKENS),
                          dtype=torch.bfloat16, device=dev)
     for g in cache.groups:  # synthetic cache contents for the steps that start from an adopted context
         flat = g.pool.view(-1)
