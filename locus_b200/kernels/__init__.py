@@ -324,10 +324,14 @@ def tc_plan(m: int, n: int, k: int, dual: bool) -> Tuple[int, int]:
 
 
 def _split_scratch(device) -> torch.Tensor:
-    t = _SPLIT_SCRATCH.get(device)
+    """The partial sums' buffer of the stream that launches: products on different streams (the shared expert
+    beside the routed ones) must not share one.  Made at a stream's first split product, which is never inside
+    a graph capture: a step is run once in the open before it is captured."""
+    key = (device, _stream().value)
+    t = _SPLIT_SCRATCH.get(key)
     if t is None:
         t = torch.empty(SPLIT_SCRATCH_BYTES // 4, dtype=torch.float32, device=device)
-        _SPLIT_SCRATCH[device] = t
+        _SPLIT_SCRATCH[key] = t
     return t
 
 
