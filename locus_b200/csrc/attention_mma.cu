@@ -11,6 +11,11 @@
 // (attention.cu): [n_pages][2][nkv][page_tokens][hd]; items are (segment, first query of
 // a 64-query tile).
 //
+// A step with few such blocks (a short portion behind a long context) leaves most SMs idle and each
+// block streaming thousands of keys alone; the key tiles of an item are then cut into n_splits ranges
+// that run as blocks of their own (blockIdx.z) and leave unnormalised sums, running maxima and
+// denominators in a scratch; attn_chunk_merge_kernel adds the ranges up in ascending order.
+//
 // Head sizes: multiples of 16 up to 128 (template instances 16, 32, 48, 64, 96, 128); other
 // sizes are refused and the caller uses the CUDA-core kernel.  Rows in shared memory are
 // padded by 16 bytes so that ldmatrix reads no bank twice.
@@ -31,7 +36,18 @@ struct MmaAttnArgs {
     const int* items;
     int nh, nkv, page_tokens, window;
     float scale;
+    int n_splits;     // ranges of key tiles per item (1: the block writes out itself)
+    float* part_o;    // [item][head][split][MQ][hd] unnormalised sums
+    float* part_ml;   // [item][head][split][MQ][2] running maximum (base 2, scaled) and denominator
 };
+
+// Key tiles of an item: the first tile's first position and their number (the same in both kernels).
+__device__ __forceinline__ void item_tiles(int p0, int nq, int window, int& first_tile, int& n_tiles) {
+    const int t_hi = p0 + nq - 1;
+    const int t_lo = window > 0 ? max(0, p0 - window + 1) : 0;
+    first_tile = (t_lo / MK) * MK;
+    n_tiles = (t_hi - first_tile) / MK + 1;
+}
 
 __device__ __forceinline__ uint32_t sm_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -90,6 +106,15 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     const int pshift = (P & (P - 1)) == 0 ? __ffs(P) - 1 : -1;  // pages of 2^k tokens: shifts instead of divisions
     const float scale_log2 = a.scale * 1.4426950408889634f;
 
+    // this block's range of the item's key tiles
+    int first_tile, n_tiles_all;
+    item_tiles(p0, nq, a.window, first_tile, n_tiles_all);
+    const int split = blockIdx.z;
+    const int per_split = (n_tiles_all + a.n_splits - 1) / a.n_splits;
+    first_tile += split * per_split * MK;
+    const int n_tiles = max(0, min(per_split, n_tiles_all - split * per_split));
+    if (n_tiles == 0) return;  // the merge counts the live ranges the same way
+
     // ---- Q tile -> shared (rows past nq are zero)
     for (int i = tid; i < MQ * CH; i += 128) {
         const int r = i / CH, c = i % CH;
@@ -117,8 +142,6 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
         cp_commit();
     };
 
-    const int first_tile = (t_lo / MK) * MK;
-    const int n_tiles = (t_hi - first_tile) / MK + 1;
     load_kv(first_tile, 0);
 
     // ---- Q fragments of this warp's 16 rows, kept in registers
@@ -262,6 +285,20 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
         l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 1);
         l_run[rr] += __shfl_xor_sync(0xffffffffu, l_run[rr], 2);
     }
+    if (a.n_splits > 1) {
+        const size_t unit = (static_cast<size_t>(item) * a.nh + h) * a.n_splits + split;
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            const int r = warp * 16 + g + rr * 8;
+            if (r >= nq) continue;
+            float* po = a.part_o + (unit * MQ + r) * HD;
+#pragma unroll
+            for (int d = 0; d < DT; ++d)
+                *reinterpret_cast<float2*>(po + d * 8 + qd * 2) = make_float2(o[d][rr * 2], o[d][rr * 2 + 1]);
+            if (qd == 0) *reinterpret_cast<float2*>(a.part_ml + (unit * MQ + r) * 2) = make_float2(m_run[rr], l_run[rr]);
+        }
+        return;
+    }
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
         const int r = warp * 16 + g + rr * 8;
@@ -275,6 +312,50 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     }
 }
 
+#define MERGE_MAX_SPLITS 16
+
+// out[row][head] = sum over the live ranges s (ascending) of o_s 2^(m_s - M) / sum of l_s 2^(m_s - M), M = max m_s.
+// One thread per (query row, two adjacent dimensions) of an (item, head); the loads of all ranges are
+// issued together (the loops are unrolled over the most ranges there can be).
+__global__ void __launch_bounds__(128) attn_chunk_merge_kernel(MmaAttnArgs a, int hd) {
+    const int item = blockIdx.y, h = blockIdx.z;
+    const int seg = a.items[2 * item], qoff = a.items[2 * item + 1];
+    const int nq = min(MQ, a.seg_qn[seg] - qoff);
+    const int half = hd >> 1;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nq * half) return;
+    const int r = i / half, d = (i - r * half) * 2;
+    const int row0 = a.seg_q0[seg] + qoff;
+    int first_tile, n_tiles;
+    item_tiles(a.seg_ctx[seg] + qoff, nq, a.window, first_tile, n_tiles);
+    const int per_split = (n_tiles + a.n_splits - 1) / a.n_splits;
+    const int live = (n_tiles + per_split - 1) / per_split;
+    const size_t unit0 = (static_cast<size_t>(item) * a.nh + h) * a.n_splits;
+    float2 ml[MERGE_MAX_SPLITS], v[MERGE_MAX_SPLITS];
+#pragma unroll
+    for (int s = 0; s < MERGE_MAX_SPLITS; ++s) {
+        ml[s] = make_float2(-INFINITY, 0.f);
+        v[s] = make_float2(0.f, 0.f);
+        if (s < live) {
+            ml[s] = *reinterpret_cast<const float2*>(a.part_ml + ((unit0 + s) * MQ + r) * 2);
+            v[s] = *reinterpret_cast<const float2*>(a.part_o + ((unit0 + s) * MQ + r) * hd + d);
+        }
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < MERGE_MAX_SPLITS; ++s) M = fmaxf(M, ml[s].x);
+    float L = 0.f, x = 0.f, y = 0.f;
+#pragma unroll
+    for (int s = 0; s < MERGE_MAX_SPLITS; ++s) {
+        const float w = ml[s].x == -INFINITY ? 0.f : exp2f(ml[s].x - M);
+        L += ml[s].y * w;
+        x += v[s].x * w;
+        y += v[s].y * w;
+    }
+    const float inv = 1.0f / L;
+    *reinterpret_cast<uint32_t*>(a.out + (static_cast<size_t>(row0 + r) * a.nh + h) * hd + d) = pack_bf16(x * inv, y * inv);
+}
+
 template <int HD>
 static int launch(const MmaAttnArgs& a, int n_items, cudaStream_t stream) {
     constexpr size_t smem = sizeof(bf16) * (HD + 8) * (MQ + 4 * MK);
@@ -284,23 +365,30 @@ static int launch(const MmaAttnArgs& a, int n_items, cudaStream_t stream) {
             return static_cast<int>(cudaGetLastError());
         set = true;
     }
-    dim3 grid(n_items, a.nh);
+    dim3 grid(n_items, a.nh, a.n_splits);
     attn_chunk_mma_kernel<HD><<<grid, 128, smem, stream>>>(a);
+    if (a.n_splits > 1)
+        attn_chunk_merge_kernel<<<dim3((MQ * (HD / 2) + 127) / 128, n_items, a.nh), 128, 0, stream>>>(a, HD);
     return locus_launch_status();
 }
 
 // items: [n_items, 2] = (segment, first query of a 64-query tile).  bfloat16 only.
+// n_splits > 1: part_o holds n_items * nh * n_splits * 64 * hd floats, part_ml n_items * nh * n_splits * 128.
 extern "C" int locus_attn_chunk_mma(const void* q, const void* pool, void* out, const int* seg_q0, const int* seg_qn,
                                     const int* seg_ctx, const int* block_table, int table_stride, const int* items,
                                     int n_items, int nh, int nkv, int hd, int page_tokens, int window, float scale,
-                                    cudaStream_t stream) {
+                                    int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535 || page_tokens <= 0 || window < 0) return LOCUS_ERR_UNSUPPORTED;
+    if (n_splits < 1 || n_splits > MERGE_MAX_SPLITS || (n_splits > 1 && n_items > 65535) || (n_splits > 1 && (part_o == nullptr || part_ml == nullptr)) ||
+        ((reinterpret_cast<uintptr_t>(part_o) | reinterpret_cast<uintptr_t>(part_ml)) & 7))
+        return LOCUS_ERR_UNSUPPORTED;
     MmaAttnArgs a;
     a.q = static_cast<const bf16*>(q); a.pool = static_cast<const bf16*>(pool); a.out = static_cast<bf16*>(out);
     a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx; a.block_table = block_table;
     a.table_stride = table_stride; a.items = items; a.nh = nh; a.nkv = nkv; a.page_tokens = page_tokens;
     a.window = window; a.scale = scale;
+    a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
     switch (hd) {
         case 16: return launch<16>(a, n_items, stream);
         case 32: return launch<32>(a, n_items, stream);

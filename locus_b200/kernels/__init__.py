@@ -528,23 +528,57 @@ def attn_chunk_mma_takes(q: torch.Tensor, head_dim: int) -> bool:
     return USE_TENSOR_CORES and q.dtype == torch.bfloat16 and head_dim in MMA_HEAD_DIMS
 
 
+MMA_ATTN_MAX_SPLITS = 16
+
+
+def attn_chunk_mma_scratch(head_dim: int) -> Tuple[int, int]:
+    """Floats of the two scratch buffers (sums; maxima and denominators) that :func:`attn_chunk_mma` needs
+    to cut the keys of a step with few 64-query tiles into ranges (at most two blocks per SM are made)."""
+    units = 2 * _sm_count() + MMA_ATTN_MAX_SPLITS
+    return units * MMA_QUERY_TILE * head_dim, units * MMA_QUERY_TILE * 2
+
+
+def attn_chunk_mma_splits(n_items: int, n_heads: int, max_ctx: int) -> int:
+    """Ranges the keys of every item are cut into: enough for two blocks per SM when the step has fewer
+    blocks than SMs (a short portion behind a long context), down to one tile of 64 keys per range.  A block
+    takes about 1.9 us per key tile and the merge 2.5 us, so from four tiles on the cut pays: 64 tokens behind
+    1,024 take 35 us in one range and 11 us in 16; 52 behind 30,000, 880 us and 91 us."""
+    blocks = n_items * n_heads
+    n_sm = _sm_count()
+    tiles = -(-max_ctx // MMA_QUERY_TILE)
+    if blocks >= n_sm or tiles < 4:
+        return 1
+    return max(1, min(MMA_ATTN_MAX_SPLITS, (2 * n_sm) // blocks, tiles))
+
+
 def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
                    seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
                    items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                   page_tokens: int, window: int, scale: float) -> None:
+                   page_tokens: int, window: int, scale: float, n_splits: int = 1,
+                   part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
     """Attention of portions of prompts on the tensor cores: ``items`` [n_items, 2] =
-    (segment, first query of a 64-query tile); otherwise as :func:`attn_chunk`."""
+    (segment, first query of a 64-query tile); otherwise as :func:`attn_chunk`.  ``n_splits`` > 1
+    (:func:`attn_chunk_mma_splits`) with scratch of :func:`attn_chunk_mma_scratch` floats: the keys of
+    every item are cut into that many ranges, merged in ascending order by a second kernel."""
     _cuda_c(q, "q")
     _cuda_c(out, "out")
     _cuda_c(pool, "pool")
     _i32(block_table, "block_table")
     _i32(items, "items")
     _need(q.dtype == pool.dtype == out.dtype == torch.bfloat16, "attn_chunk_mma: bfloat16 only")
+    if n_splits > 1:
+        units = n_items * n_heads * n_splits
+        _need(part_o is not None and part_ml is not None and part_o.dtype == part_ml.dtype == torch.float32
+              and part_o.numel() >= units * MMA_QUERY_TILE * head_dim and part_ml.numel() >= units * MMA_QUERY_TILE * 2,
+              "attn_chunk_mma: scratch too small for these ranges")
     code = _lib("attention_mma").locus_attn_chunk_mma(
         _p(q), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx), _p(block_table), I(block_table.shape[1]),
-        _p(items), I(n_items), I(n_heads), I(n_kv_heads), I(head_dim), I(page_tokens), I(window), F(scale), _stream()
+        _p(items), I(n_items), I(n_heads), I(n_kv_heads), I(head_dim), I(page_tokens), I(window), F(scale),
+        I(n_splits), _p(part_o if n_splits > 1 else None), _p(part_ml if n_splits > 1 else None), _stream()
     )
-    _check(code, "attn_chunk_mma", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
+    if n_splits > 1 and code == 0:
+        _count_launches(1)
+    _check(code, "attn_chunk_mma", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim}, {n_splits} key ranges)")
 
 
 TC_ATTN_HEAD_DIM = 128   # the tcgen05 attention kernel: this head size, pages of a multiple of 64 tokens

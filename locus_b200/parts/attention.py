@@ -97,7 +97,18 @@ class Attention(Mixer):
             if K.attn_chunk_tc_takes(q, self.head_dim, gb.page_tokens, T):
                 K.attn_chunk_tc(q, cache.pool, o, items=batch.chunk_items64, n_items=batch.n_chunk_items64, **common)
             elif K.attn_chunk_mma_takes(q, self.head_dim):
-                K.attn_chunk_mma(q, cache.pool, o, items=batch.chunk_items64, n_items=batch.n_chunk_items64, **common)
+                # few 64-query tiles behind a long context: the keys of every tile are cut into ranges
+                keys = batch.max_splits * K.DECODE_SPLIT
+                if self.window > 0:
+                    keys = min(keys, self.window + K.MMA_QUERY_TILE)
+                n_splits = K.attn_chunk_mma_splits(batch.n_chunk_items64, self.n_heads, keys)
+                part_o = part_ml = None
+                if n_splits > 1:
+                    n_o, n_ml = K.attn_chunk_mma_scratch(self.head_dim)
+                    part_o = rt.buf("attention.chunk_part_o", (n_o,), torch.float32)
+                    part_ml = rt.buf("attention.chunk_part_ml", (n_ml,), torch.float32)
+                K.attn_chunk_mma(q, cache.pool, o, items=batch.chunk_items64, n_items=batch.n_chunk_items64,
+                                 n_splits=n_splits, part_o=part_o, part_ml=part_ml, **common)
             else:
                 K.attn_chunk(q, cache.pool, o, items=batch.chunk_items, n_items=batch.n_chunk_items, **common)
         if batch.n_decode_items:

@@ -142,8 +142,12 @@ def attn_chunk(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_i
           scale=scale)
 
 
+def attn_chunk_mma_splits(n_items, n_heads, max_ctx):
+    return 1
+
+
 def attn_chunk_mma(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_items, n_heads, n_kv_heads,
-                   head_dim, page_tokens, window, scale):
+                   head_dim, page_tokens, window, scale, n_splits=1, part_o=None, part_ml=None):
     attn_chunk(q, pool, out, seg_q0=seg_q0, seg_qn=seg_qn, seg_ctx=seg_ctx, block_table=block_table, items=items,
                n_items=n_items, n_heads=n_heads, n_kv_heads=n_kv_heads, head_dim=head_dim, page_tokens=page_tokens,
                window=window, scale=scale)

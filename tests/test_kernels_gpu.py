@@ -361,6 +361,22 @@ def test_attn_chunk_tensor_cores(nh, nkv, hd, P, window):
     ref = torch.zeros(T, nh * hd, dtype=torch.float64)
     EK.attn_chunk(q, pool, ref, items=items_t, n_items=len(items), **meta, **kw)
     close(out, ref, dtype, "attn_chunk_mma")
+    # the keys of every tile cut into ranges (more ranges than some items have tiles) and merged: the same result
+    for n_splits in (2, 3, 7):
+        units = len(items) * nh * n_splits * K.MMA_QUERY_TILE
+        part_o = torch.full((units * hd,), float("nan"), device=DEV)
+        part_ml = torch.full((units * 2,), float("nan"), device=DEV)
+        out_s = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        before = K.launches
+        K.attn_chunk_mma(q.to(DEV), pool.to(DEV), out_s, items=items_t.to(DEV), n_items=len(items), n_splits=n_splits,
+                         part_o=part_o, part_ml=part_ml, **_dev(meta), **kw)
+        assert K.launches - before == 2
+        close(out_s, ref, dtype, f"attn_chunk_mma in {n_splits} key ranges")
+    with pytest.raises(K.KernelError):
+        K.attn_chunk_mma(q.to(DEV), pool.to(DEV), out, items=items_t.to(DEV), n_items=len(items), n_splits=2,
+                         part_o=part_o[:8], part_ml=part_ml, **_dev(meta), **kw)
+    assert K.attn_chunk_mma_splits(200, 16, 100000) == 1 and K.attn_chunk_mma_splits(1, 16, 130) == 1
+    assert 1 < K.attn_chunk_mma_splits(1, 16, 30000) <= K.MMA_ATTN_MAX_SPLITS
 
 
 @pytest.mark.parametrize("nh,nkv,P,window", [(2, 2, 64, 0), (4, 1, 128, 0), (3, 3, 64, 100), (2, 1, 64, 1), (4, 2, 192, 333)])
