@@ -123,7 +123,7 @@ def main() -> int:
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
-                          "pip cannot install /root/reference (a C++/CMake project: neither setup.py nor pyproject.toml); "
+                          "pip cannot install the reference (a C++/CMake project: neither setup.py nor pyproject.toml); "
                           "its CUDA backend is an sm_50 per-call matvec offload that needs a GGUF file with a tokenizer"}))
         return 0
     if args.gpus != 1:

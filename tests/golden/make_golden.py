@@ -107,7 +107,9 @@ def wstr(f, s):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of the reference> [build folder]")
+    ref = sys.argv[1]
     build = sys.argv[2] if len(sys.argv) > 2 else tempfile.mkdtemp(prefix="locus_ref_build_")
     subprocess.check_call(["cmake", "-S", ref, "-B", build, "-DCMAKE_BUILD_TYPE=Release",
                            "-DCMAKE_DISABLE_FIND_PACKAGE_CUDAToolkit=ON", "-DCMAKE_DISABLE_FIND_PACKAGE_Vulkan=ON"],

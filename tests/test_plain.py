@@ -137,7 +137,7 @@ def test_sampling_helpers():
 
 def test_golden_logits_of_the_reference():
     """tests/golden/ holds logits computed by the reference's own C++ model code (compiled
-    on the CPU by tests/golden/make_golden.sh) for seeded tiny models; see its README."""
+    on the CPU by tests/golden/make_golden.py) for seeded tiny models; see its README."""
     path = os.path.join(HERE, "golden", "golden.json")
     if not os.path.isfile(path):
         pytest.skip("no golden file committed")
