@@ -70,6 +70,8 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--tokenizers", action="store_true", help="list tokenizer families and exit")
     ap.add_argument("--capabilities", action="store_true", help="list archs+backends+quants+tokenizers, exit")
     ap.add_argument("--ctx", type=int, default=0, help="cap the KV pool at N tokens (default min(model context, 4096))")
+    ap.add_argument("--kv-fraction", type=float, default=0.0,
+                    help="instead of --ctx: size the KV pool to this share of the free device memory")
     ap.add_argument("--concurrent", type=int, default=1, help="submit the prompt N times and report aggregate tok/s")
     ap.add_argument("--batch-decode", action="store_true", help="decode all running requests in one batch (always on here)")
     ap.add_argument("--no-batch-prefill", action="store_true", help="force per-token prompt ingestion")
@@ -137,7 +139,7 @@ def main(argv=None) -> int:
         conc = max(1, args.concurrent)
         eng = Engine.from_model_dir(args.model, dtype=args.dtype, ctx=args.ctx, page_tokens=args.page_tokens,
                                     max_batch_tokens=max(args.max_batch_tokens, conc), chunk=chunk,
-                                    max_running=max(conc, 1))
+                                    max_running=max(conc, 1), kv_fraction=args.kv_fraction)
         plan = eng.model.plan
         cfg = plan.config
         print(f"{torch.cuda.get_device_name(0)} | backend=cuda-sm100a | dtype={args.dtype} | layers={len(plan.layers)} "

@@ -36,21 +36,35 @@ class Engine:
     def from_model_dir(cls, model_dir: str, *, dtype: str = "bfloat16", ctx: int = 0, page_tokens: int = 64,
                        max_batch_tokens: int = 2048, chunk: int = 2048, max_running: int = 64,
                        decode_headroom: int = 16, device: str = "cuda:0", use_graphs: bool = True,
-                       max_seq_tokens: int = 0) -> "Engine":
+                       max_seq_tokens: int = 0, kv_fraction: float = 0.0) -> "Engine":
         """``ctx``: tokens the cache pool holds in all (default: min(model context, 4096), the
-        reference's default, src/locus/model/llama.cpp:389-398)."""
+        reference's default, src/locus/model/llama.cpp:389-398).  ``kv_fraction`` > 0 instead sizes
+        the pool to that fraction of the device memory that is free once the weights are loaded (the
+        way to use a 180 GB device for many long requests); a request may then grow to the model's
+        context."""
         from ..models.model import load_model
 
         model = load_model(model_dir, parse_dtype(dtype), device)
         return cls.from_model(model, ctx=ctx, page_tokens=page_tokens, max_batch_tokens=max_batch_tokens,
                               chunk=chunk, max_running=max_running, decode_headroom=decode_headroom,
-                              use_graphs=use_graphs, max_seq_tokens=max_seq_tokens)
+                              use_graphs=use_graphs, max_seq_tokens=max_seq_tokens, kv_fraction=kv_fraction)
 
     @classmethod
     def from_model(cls, model, *, ctx: int = 0, page_tokens: int = 64, max_batch_tokens: int = 2048,
                    chunk: int = 2048, max_running: int = 64, decode_headroom: int = 16,
-                   use_graphs: bool = True, max_seq_tokens: int = 0) -> "Engine":
+                   use_graphs: bool = True, max_seq_tokens: int = 0, kv_fraction: float = 0.0) -> "Engine":
         plan = model.plan
+        if kv_fraction > 0:
+            if not (kv_fraction <= 1.0) or model.device.type != "cuda":
+                raise ValueError("kv_fraction is a share (0, 1] of the free memory of a CUDA device")
+            per_token = CacheManager(model.cache_needs(), page_tokens=page_tokens, n_pages=0, n_state_slots=1,
+                                     max_seq_tokens=1, dtype=model.dtype, allocate_device=False).bytes_per_token()
+            free, _ = torch.cuda.mem_get_info(model.device)
+            ctx = int(free * kv_fraction) // max(1, per_token * page_tokens) * page_tokens
+            if ctx < page_tokens:
+                raise ValueError(f"kv_fraction {kv_fraction} of {free} free bytes holds no page of {page_tokens} tokens")
+            if max_seq_tokens <= 0:
+                max_seq_tokens = min(plan.max_positions, ctx)
         if ctx <= 0:
             ctx = min(plan.max_positions, 4096)
         if max_seq_tokens <= 0:

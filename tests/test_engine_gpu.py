@@ -355,6 +355,23 @@ def test_generate_greedy_and_sampled(case, dtype):
     assert eng.cache.free_pages() == eng.cache.total_pages()
 
 
+def test_pool_sized_by_a_share_of_free_memory(tmp_path_factory):
+    """``kv_fraction`` sizes the pool from the device memory that is free after the weights are loaded."""
+    from locus_b200.engine.engine import Engine
+
+    c = Case("A", tmp_path_factory.mktemp("models_kvf"))
+    free, _ = torch.cuda.mem_get_info()
+    share = (64 << 20) / free   # about 64 MiB of cache
+    eng = Engine.from_model_dir(c.dir, dtype="bfloat16", page_tokens=64, max_running=4, kv_fraction=share)
+    held = eng.cache.total_pages() * 64 * eng.cache.bytes_per_token()
+    assert 0.5 * (64 << 20) <= held <= (64 << 20) + 64 * eng.cache.bytes_per_token()
+    assert eng.cache.max_seq_tokens == min(c.cfg["max_position_embeddings"], eng.cache.total_pages() * 64)
+    out = eng.generate([c.tokens["r1"][:9]], max_new_tokens=4)
+    assert len(out[0]) == 4 and eng.cache.free_pages() == eng.cache.total_pages()
+    with pytest.raises(ValueError, match="kv_fraction"):
+        Engine.from_model_dir(c.dir, dtype="bfloat16", kv_fraction=1.5)
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_trace_run_program(case, dtype, tmp_path):
     """bin/trace_run as a program: a mixed trace with a pool of 4 x 64-token pages short of
