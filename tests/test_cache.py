@@ -166,3 +166,25 @@ def test_random_workload_loses_nothing(seed):
         c.release(s)
     c.check_invariants()
     assert all(c.free_pages(g.gid) == 12 for g in c.groups) and c.state_slots.free == 3
+
+
+def test_a_closed_request_stays_closed_when_its_record_is_used_again():
+    """The native record of a released request is reused by the next one; the old view must not see it."""
+    c = mk(n_pages=4)
+    a = c.open("a")
+    assert c.ensure_capacity(a, 20) and a.pages_held(0) == 2
+    c.commit(a, 20)
+    c.release(a)
+    b = c.open("b")   # takes a's record and state slot
+    assert c.ensure_capacity(b, 5)
+    assert not a.open and a.n_tokens == 0 and a.state_slot == -1 and a.tables == {0: []}
+    assert b.open and b.tables[0] != [] and c.capacity(a) == 0
+    for call in (lambda: c.ensure_capacity(a, 1), lambda: c.commit(a, 1), lambda: c.release(a)):
+        with pytest.raises(CacheError, match="not open"):
+            call()
+    other = mk(n_pages=4)
+    with pytest.raises(CacheError, match="not open"):
+        other.ensure_capacity(b, 1)   # a request of another cache
+    c.release(b)
+    c.check_invariants()
+    assert c.free_pages() == 4 and c.state_slots.free == 3
