@@ -218,6 +218,11 @@ __device__ __forceinline__ void select_token(const float* __restrict__ lg, float
     for (int x = lane; x < E; x += 32) p[x] = p[x] / sum;
     __syncwarp();
     float wsum = 0.f;
+    // After the butterfly every lane knows the pick; lane r keeps the probability of pick r, so that the
+    // weights go out with one store per lane at the end (up to 32 picks; beyond that they take the way
+    // through global memory).
+    const bool in_lanes = k <= 32;
+    float my_w = 0.f;
     for (int r = 0; r < k; ++r) {
         float best = -1.f;
         int best_e = 0x7fffffff;
@@ -237,17 +242,20 @@ __device__ __forceinline__ void select_token(const float* __restrict__ lg, float
                 best_e = oe;
             }
         }
+        if (lane == r) my_w = best;
         if (lane == 0) {
             ids[t * k + r] = best_e;
             if (s_ids != nullptr) s_ids[t * k + r] = best_e;
-            wts[t * k + r] = best;
+            if (!in_lanes) wts[t * k + r] = best;
             p[best_e] = -2.f;
         }
         wsum += best;
         __syncwarp();
     }
-    if (lane == 0) {
-        const float div = renorm ? wsum : 1.0f;
+    const float div = renorm ? wsum : 1.0f;
+    if (in_lanes) {
+        if (lane < k) wts[t * k + lane] = my_w / div * scale;
+    } else if (lane == 0) {
         for (int r = 0; r < k; ++r) wts[t * k + r] = wts[t * k + r] / div * scale;
     }
 }
@@ -381,7 +389,8 @@ extern "C" int locus_moe_sort(const int* ids, int n_pairs, int E, int tile_m, in
 #define RS_MAX_PAIRS 1024
 #define RS_MAX_E 512
 
-__global__ void __launch_bounds__(256) route_small_kernel(const float* __restrict__ logits, int ld,
+#define RS_WARPS 16   // a warp per token for up to 16 tokens
+__global__ void __launch_bounds__(32 * RS_WARPS) route_small_kernel(const float* __restrict__ logits, int ld,
                                                           int* __restrict__ ids, float* __restrict__ wts,
                                                           float* __restrict__ gamma, int T, int E, int k, int has_gate,
                                                           int renorm, float scale, int tile_m, int* __restrict__ counts,
@@ -391,14 +400,14 @@ __global__ void __launch_bounds__(256) route_small_kernel(const float* __restric
                                                           int* __restrict__ n_tiles) {
     pdl_entry();
     pdl_trigger();
-    extern __shared__ float rs_smem[];  // probabilities [8][E], then the ints below
-    int* s_ids = reinterpret_cast<int*>(rs_smem + 8 * E);  // [T * k]
+    extern __shared__ float rs_smem[];  // probabilities [RS_WARPS][E], then the ints below
+    int* s_ids = reinterpret_cast<int*>(rs_smem + RS_WARPS * E);  // [T * k]
     int* s_cnt = s_ids + T * k;                             // [E]
     int* s_off = s_cnt + E;                                 // [E + 1]
     int* s_tile = s_off + E + 1;                            // [E + 1]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int n_pairs = T * k;
-    for (int t = wid; t < T; t += 8)
+    for (int t = wid; t < T; t += RS_WARPS)
         select_token(logits + static_cast<size_t>(t) * ld, rs_smem + wid * E, t, lane, ids, wts, gamma, s_ids, E, k,
                      has_gate, renorm, scale);
     __syncthreads();
@@ -473,8 +482,8 @@ extern "C" int locus_route_small(const float* logits, int ld, int* ids, float* w
     if (T <= 0) return 0;
     if (E <= 0 || k <= 0 || k > E || ld < E + (has_gate ? 1 : 0) || tile_m <= 0) return LOCUS_ERR_UNSUPPORTED;
     if (E > RS_MAX_E || static_cast<long long>(T) * k > RS_MAX_PAIRS) return LOCUS_ERR_UNSUPPORTED;
-    const size_t smem = sizeof(float) * 8 * E + sizeof(int) * (static_cast<size_t>(T) * k + 3 * E + 2);
-    locus_launch(route_small_kernel, 1, 256, smem, stream, logits, ld, ids, wts, gamma, T, E, k, has_gate, renorm,
+    const size_t smem = sizeof(float) * RS_WARPS * E + sizeof(int) * (static_cast<size_t>(T) * k + 3 * E + 2);
+    locus_launch(route_small_kernel, 1, 32 * RS_WARPS, smem, stream, logits, ld, ids, wts, gamma, T, E, k, has_gate, renorm,
                  scale, tile_m, counts, offsets, sorted_pair, pair_pos, tile_expert, tile_row0, tile_rows, n_tiles);
     return locus_launch_status();
 }
