@@ -355,6 +355,36 @@ def test_generate_greedy_and_sampled(case, dtype):
     assert eng.cache.free_pages() == eng.cache.total_pages()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_generation_survives_running_out_of_pages(case, dtype):
+    """A pool too small for all requests at once: the newest request is preempted and recomputed later,
+    and every request still gets the tokens it gets from a large pool."""
+    from locus_b200.engine.engine import Engine
+
+    names = list(case.tokens)[-3:]
+    prompts = [case.tokens[r][:n] for r, n in zip(names, (30, 41, 25))]
+    big = Engine.from_model_dir(case.dir, dtype=dtype, ctx=1024, page_tokens=16, max_batch_tokens=32, chunk=16,
+                                max_running=4, decode_headroom=0)
+    want = big.generate(prompts, max_new_tokens=24)
+    # 7 pages of 16 tokens: any single request fits (at most 65 tokens), two of them do not
+    small = Engine.from_model_dir(case.dir, dtype=dtype, ctx=7 * 16, page_tokens=16, max_batch_tokens=32, chunk=16,
+                                  max_running=4, decode_headroom=0)
+    got = small.generate(prompts, max_new_tokens=24)
+    assert small.sched.counters["preemptions"] > 0 and small.sched.counters["failed"] == 0
+    assert small.cache.free_pages() == small.cache.total_pages()
+    small.cache.check_invariants()
+    if dtype == "float32":
+        assert got == want
+    else:
+        # bfloat16: a recomputed request runs in other batches; a token may differ only where the oracle's
+        # two best logits are within the rounding of the element type
+        for p, o in zip(prompts, got):
+            ref = plain.forward(case.cfg, case.weights, p + o, torch.float64)
+            for i, tok in enumerate(o):
+                row = ref[len(p) + i - 1]
+                assert float(row.max() - row[tok]) <= TOL[torch.bfloat16][0] * float(ref.abs().max()) * 2
+
+
 def test_pool_sized_by_a_share_of_free_memory(tmp_path_factory):
     """``kv_fraction`` sizes the pool from the device memory that is free after the weights are loaded."""
     from locus_b200.engine.engine import Engine
