@@ -202,6 +202,34 @@ class CacheManager:
         self._live[seq_id] = seq
         return seq
 
+    def adopt_native(self, seq_id, handle: int) -> SeqCache:
+        """The view of a request that native code (the scheduler) opened in this cache: zeroes its state slot
+        and makes it known here, as ``open`` does."""
+        if seq_id in self._live:
+            raise CacheError(f"request {seq_id!r} is already open")
+        seq = SeqCache(self, seq_id, handle)
+        if not seq.open:
+            raise CacheError(f"request {seq_id!r}: the handle is not open in this cache")
+        slot = seq.state_slot
+        for st in self._state:
+            if st is not None:
+                st[slot].zero_()
+        self._live[seq_id] = seq
+        return seq
+
+    def forget_native(self, seq: SeqCache, freed_pairs: Sequence[int] = ()) -> None:
+        """Native code released the request: drop its view; ``freed_pairs``: the (group, page) it freed."""
+        if self._live.get(seq.seq_id) is seq:
+            del self._live[seq.seq_id]
+        self.poison_pairs(freed_pairs)
+
+    def poison_pairs(self, pairs: Sequence[int]) -> None:
+        if self.poison:
+            for i in range(0, len(pairs) - 1, 2):
+                g = self.groups[pairs[i]]
+                if g.pool is not None:
+                    g.pool[:, pairs[i + 1]].fill_(float("nan"))
+
     def get(self, seq_id) -> Optional[SeqCache]:
         return self._live.get(seq_id)
 

@@ -1,4 +1,4 @@
-"""The host library (``csrc/host_core.cpp``: pools, page tables, step assembly) loaded with
+"""The host library (``csrc/host_core.cpp``: pools, page tables, step assembly, scheduler) loaded with
 ctypes, its entry points declared.  Compiled on first use like the kernel modules; there is
 no Python stand-in: without a C++ compiler the import of the cache fails with the build error."""
 from __future__ import annotations
@@ -48,6 +48,20 @@ def lib() -> ctypes.CDLL:
                                          c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p,
                                          c_void_p]),
         }
+        sig.update({
+            "locus_sched_new": (c_void_p, [c_void_p, c_int, c_int, c_int, c_int, c_int]),
+            "locus_sched_delete": (None, [c_void_p]),
+            "locus_sched_add": (c_int, [c_void_p, c_int64, c_int]),
+            "locus_sched_forget": (None, [c_void_p, c_int64]),
+            "locus_sched_admit": (c_int, [c_void_p]),
+            "locus_sched_plan": (c_int, [c_void_p, P_I64, c_int]),
+            "locus_sched_fed": (None, [c_void_p, c_int64, c_int]),
+            "locus_sched_token": (None, [c_void_p, c_int64, c_int]),
+            "locus_sched_events": (c_int, [c_void_p, P_I64, c_int]),
+            "locus_sched_freed": (c_int, [c_void_p, P_INT, c_int]),
+            "locus_sched_queue": (c_int, [c_void_p, c_int, P_I64, c_int]),
+            "locus_sched_count": (c_int, [c_void_p, c_int]),
+        })
         for name, (res, args) in sig.items():
             f = getattr(L, name)
             f.restype, f.argtypes = res, args

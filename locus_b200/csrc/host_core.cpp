@@ -1,6 +1,7 @@
-// Host side of the cache and of the step: pools of ids with reference counts, the page tables of
-// the live requests (one table per request and cache group), and the assembly of a step's
-// descriptors into one buffer that travels to the device in a single copy.
+// Host side of the cache, of the step and of the request loop: pools of ids with reference counts,
+// the page tables of the live requests (one table per request and cache group), the assembly of a
+// step's descriptors into one buffer that travels to the device in a single copy, and the scheduler's
+// decisions (admission, portions under a token budget, preemption when pages run out).
 //
 // Plain C entry points over opaque pointers; no CUDA in here.  Every function reports misuse by a
 // negative return code (the caller words the message); nothing throws across the boundary.
@@ -8,8 +9,11 @@
 // The reference keeps the same bookkeeping in C++ (src/locus/kv/block_allocator.cpp:7-54,
 // src/locus/kv/paged_cache.cpp:62-85) with one geometry for all layers; here a request holds one
 // table per group of layers, and a group with a window gives pages back while the request lives.
+#include <algorithm>
 #include <cstdint>
 #include <cstring>
+#include <deque>
+#include <unordered_map>
 #include <vector>
 
 namespace {
@@ -433,6 +437,249 @@ int locus_step_build(void* cv, int n_entries, const int64_t* handles, const int*
     info[4] = static_cast<int>(n_decode);
     info[5] = static_cast<int>(n_chunk_mma);
     return 0;
+}
+
+}  // extern "C"
+
+// ---- scheduler -----------------------------------------------------------------------------
+//
+// The decisions of the request loop over the cache above: which waiting request is admitted, which
+// tokens of which running request go into the next step, who gives way when pages run out.  The
+// policy is the reference engine's (src/locus/engine/engine.cpp:503-634): admission first come first
+// served while the pool has free pages for prompt + generated + headroom tokens (nothing is reserved,
+// nobody overtakes the front of the queue); when a request cannot get its pages the newest admitted
+// request is preempted (its pages go back, it returns to the FRONT of the queue and is recomputed
+// later); a request that is itself the newest sits the step out, or fails if it runs alone; a request
+// whose next token has no position left fails with a context overflow.  Unlike the reference, portions
+// of prompts and decode tokens share one step and one token budget: decode tokens first, the rest to
+// portions in admission order, each at most `chunk` tokens.
+//
+// The caller keeps the tokens and the records; this side keeps lengths and states, and reports what it
+// decided as events (kind, request, argument) that the caller applies to its records.
+namespace {
+
+enum : int { ST_WAITING = 0, ST_RUNNING = 1, ST_DONE = 2, ST_FAILED = 3 };
+enum : int { EV_ADMITTED = 1, EV_PREEMPTED = 2, EV_FAILED = 3, EV_DONE = 4 };
+enum : int { WHY_OVERFLOW = 1, WHY_POOL_TOO_SMALL = 2 };
+
+struct SReq {
+    int stream_len = 0;  // prompt + generated tokens
+    int n_fed = 0;       // of them, through the model
+    int status = ST_WAITING;
+    int64_t handle = -1;
+    int preemptions = 0;
+};
+
+struct Sched {
+    Cache* cache;
+    int max_batch_tokens, chunk, headroom, max_running, max_positions;
+    std::deque<int64_t> waiting;
+    std::vector<int64_t> running;  // in admission order
+    std::unordered_map<int64_t, SReq> reqs;
+    std::vector<int64_t> events;   // triples (kind, request, argument)
+    std::vector<int> freed;        // (group, page) pairs that became free since the caller last asked
+    int n_preemptions = 0, n_admitted = 0;
+
+    void event(int kind, int64_t rid, int64_t arg) {
+        events.push_back(kind);
+        events.push_back(rid);
+        events.push_back(arg);
+    }
+    int free_pages() const {
+        int least = cache->n_pages;
+        for (const Pool& p : cache->pools) least = std::min(least, p.n_free());
+        return least;
+    }
+    void give_back(SReq& r) {
+        if (r.handle < 0) return;
+        const size_t before = freed.size();
+        freed.resize(before + 2 * static_cast<size_t>(cache->n_groups()) * static_cast<size_t>(cache->table_width));
+        const int n = locus_cache_release(cache, r.handle, freed.data() + before,
+                                          static_cast<int>(freed.size() - before));
+        freed.resize(before + 2 * static_cast<size_t>(n > 0 ? n : 0));
+        r.handle = -1;
+    }
+    void finish(int64_t rid, SReq& r, int status, int why) {
+        give_back(r);
+        running.erase(std::remove(running.begin(), running.end(), rid), running.end());
+        r.status = status;
+        event(status == ST_DONE ? EV_DONE : EV_FAILED, rid, why);
+    }
+    void preempt(int64_t rid, SReq& r) {
+        give_back(r);
+        r.n_fed = 0;
+        r.status = ST_WAITING;
+        r.preemptions += 1;
+        running.erase(std::remove(running.begin(), running.end(), rid), running.end());
+        waiting.push_front(rid);  // victims go to the front
+        n_preemptions += 1;
+        event(EV_PREEMPTED, rid, 0);
+    }
+};
+
+Sched* as_sched(void* p) { return static_cast<Sched*>(p); }
+
+}  // namespace
+
+extern "C" {
+
+void* locus_sched_new(void* cache, int max_batch_tokens, int chunk, int headroom, int max_running,
+                      int max_positions) {
+    if (cache == nullptr || max_batch_tokens <= 0 || chunk <= 0 || headroom < 0 || max_running <= 0) return nullptr;
+    Sched* s = new Sched();
+    s->cache = as_cache(cache);
+    s->max_batch_tokens = max_batch_tokens;
+    s->chunk = chunk;
+    s->headroom = headroom;
+    s->max_running = max_running;
+    s->max_positions = max_positions;
+    return s;
+}
+void locus_sched_delete(void* s) { delete as_sched(s); }
+
+// A new request of prompt_len tokens joins the end of the queue.  0 ok; -1 the id is in use.
+int locus_sched_add(void* sv, int64_t rid, int prompt_len) {
+    Sched* s = as_sched(sv);
+    if (s->reqs.count(rid)) return -1;
+    SReq r;
+    r.stream_len = prompt_len;
+    s->reqs[rid] = r;
+    s->waiting.push_back(rid);
+    return 0;
+}
+// The record of a finished request is dropped.
+void locus_sched_forget(void* sv, int64_t rid) {
+    Sched* s = as_sched(sv);
+    auto it = s->reqs.find(rid);
+    if (it != s->reqs.end() && (it->second.status == ST_DONE || it->second.status == ST_FAILED)) s->reqs.erase(it);
+}
+
+// Admits from the front of the queue while there is room; returns how many were admitted.
+int locus_sched_admit(void* sv) {
+    Sched* s = as_sched(sv);
+    int n = 0;
+    while (!s->waiting.empty() && static_cast<int>(s->running.size()) < s->max_running) {
+        const int64_t rid = s->waiting.front();
+        SReq& r = s->reqs[rid];
+        const int want = pages_of(r.stream_len + s->headroom, s->cache->page_tokens);
+        if (want > s->free_pages() || s->cache->slots.n_free() == 0) break;  // nobody overtakes the front
+        s->waiting.pop_front();
+        r.handle = locus_cache_open(s->cache);
+        r.status = ST_RUNNING;
+        r.n_fed = 0;
+        s->running.push_back(rid);
+        s->n_admitted += 1;
+        s->event(EV_ADMITTED, rid, r.handle);
+        ++n;
+    }
+    return n;
+}
+
+// Chooses the next step's tokens and takes their pages.  Writes (request, first stream index, tokens,
+// wants logits) per planned request to out (cap entries of 4), in admission order; returns their number.
+int locus_sched_plan(void* sv, int64_t* out, int cap) {
+    Sched* s = as_sched(sv);
+    Cache* c = s->cache;
+    // context overflow: the next token to feed has no position left
+    {
+        const std::vector<int64_t> snapshot = s->running;
+        for (int64_t rid : snapshot) {
+            SReq& r = s->reqs[rid];
+            if (r.n_fed + 1 > s->max_positions || r.n_fed + 1 > c->max_seq_tokens) s->finish(rid, r, ST_FAILED, WHY_OVERFLOW);
+        }
+    }
+    std::vector<int64_t> order;
+    for (int64_t rid : s->running)
+        if (s->reqs[rid].stream_len - s->reqs[rid].n_fed == 1) order.push_back(rid);
+    for (int64_t rid : s->running)
+        if (s->reqs[rid].stream_len - s->reqs[rid].n_fed > 1) order.push_back(rid);
+    std::unordered_map<int64_t, std::pair<int, int>> planned;  // request -> (start, n)
+    int budget = s->max_batch_tokens;
+    for (int64_t rid : order) {
+        auto it = s->reqs.find(rid);
+        if (it == s->reqs.end() || it->second.status != ST_RUNNING || budget <= 0) continue;
+        SReq& r = it->second;
+        const int left = r.stream_len - r.n_fed;
+        int n = std::min(std::min(left, budget), s->chunk);
+        n = std::min(n, std::min(s->max_positions - r.n_fed, c->max_seq_tokens - r.n_fed));
+        if (n <= 0) continue;
+        bool ok = true;
+        while (locus_cache_ensure(c, r.handle, n) != 1) {
+            const int64_t victim = s->running.back();
+            if (victim == rid) {
+                if (s->running.size() == 1) s->finish(rid, r, ST_FAILED, WHY_POOL_TOO_SMALL);
+                ok = false;  // the newest but not alone: it sits this step out
+                break;
+            }
+            planned.erase(victim);
+            s->preempt(victim, s->reqs[victim]);
+        }
+        if (!ok) continue;
+        planned[rid] = std::make_pair(r.n_fed, n);
+        budget -= n;
+    }
+    int n_out = 0;
+    for (int64_t rid : s->running) {
+        auto it = planned.find(rid);
+        if (it == planned.end()) continue;
+        if (n_out < cap) {
+            const SReq& r = s->reqs[rid];
+            out[4 * n_out] = rid;
+            out[4 * n_out + 1] = it->second.first;
+            out[4 * n_out + 2] = it->second.second;
+            out[4 * n_out + 3] = (it->second.first + it->second.second == r.stream_len) ? 1 : 0;
+        }
+        ++n_out;
+    }
+    return n_out;
+}
+
+// n tokens of the request went through the model.
+void locus_sched_fed(void* sv, int64_t rid, int n) {
+    auto it = as_sched(sv)->reqs.find(rid);
+    if (it != as_sched(sv)->reqs.end()) it->second.n_fed += n;
+}
+// A token was generated for the request; finished != 0: it ends here (everything it holds goes back).
+void locus_sched_token(void* sv, int64_t rid, int finished) {
+    Sched* s = as_sched(sv);
+    auto it = s->reqs.find(rid);
+    if (it == s->reqs.end()) return;
+    it->second.stream_len += 1;
+    if (finished) s->finish(rid, it->second, ST_DONE, 0);
+}
+
+// The events since the last call, as triples (kind, request, argument), at most cap triples; returns the
+// number written and forgets them.  Kinds: 1 admitted (argument = cache handle), 2 preempted, 3 failed
+// (argument: 1 context overflow, 2 pool too small for the request), 4 done.
+int locus_sched_events(void* sv, int64_t* out, int cap) {
+    Sched* s = as_sched(sv);
+    const int n = std::min(cap, static_cast<int>(s->events.size() / 3));
+    std::copy(s->events.begin(), s->events.begin() + 3 * n, out);
+    s->events.erase(s->events.begin(), s->events.begin() + 3 * n);
+    return n;
+}
+// The (group, page) pairs that became free through this scheduler since the last call (at most cap ints).
+int locus_sched_freed(void* sv, int* out, int cap) {
+    Sched* s = as_sched(sv);
+    const int n = std::min(cap, static_cast<int>(s->freed.size()));
+    std::copy(s->freed.begin(), s->freed.begin() + n, out);
+    s->freed.erase(s->freed.begin(), s->freed.begin() + n);
+    return n / 2;
+}
+// Queue contents: which = 0 waiting (front first), 1 running (admission order); returns the length.
+int locus_sched_queue(void* sv, int which, int64_t* out, int cap) {
+    Sched* s = as_sched(sv);
+    int n = 0;
+    if (which == 0) {
+        for (int64_t rid : s->waiting) { if (n < cap) out[n] = rid; ++n; }
+    } else {
+        for (int64_t rid : s->running) { if (n < cap) out[n] = rid; ++n; }
+    }
+    return n;
+}
+int locus_sched_count(void* sv, int which) {
+    Sched* s = as_sched(sv);
+    return which == 0 ? static_cast<int>(s->waiting.size()) : static_cast<int>(s->running.size());
 }
 
 }  // extern "C"

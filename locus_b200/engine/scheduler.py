@@ -24,6 +24,11 @@ Where this differs: prompt portions and decode tokens share one batch and one bu
 (``max_batch_tokens``: decode tokens first, the rest to portions in admission order, each
 at most ``chunk`` tokens), and a preempted request re-feeds prompt + generated tokens as
 one stream in portions.
+
+The decisions are made by host code in C++ (``csrc/host_core.cpp``: ``locus_sched_*``), next
+to the cache whose pages it takes and gives back; it keeps lengths and states and reports
+what it decided as events.  This class keeps the records with their tokens, applies the
+events to them and mirrors the queues.
 """
 from __future__ import annotations
 
@@ -32,6 +37,9 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
 
+import ctypes
+
+from ..cache import native
 from ..cache.manager import CacheError, CacheManager, SeqCache
 from ..sampling.sampler import GREEDY, SamplingParams
 
@@ -90,18 +98,80 @@ class Planned:
 
 
 class Scheduler:
+    _EV_ADMITTED, _EV_PREEMPTED, _EV_FAILED, _EV_DONE = 1, 2, 3, 4
+    _WHY = {1: "context overflow", 2: "kv pool too small for request"}
+
     def __init__(self, cache: CacheManager, config: SchedulerConfig, max_positions: int,
                  eos_token_id: int = -1) -> None:
         self.cache = cache
         self.cfg = config
         self.max_positions = max_positions
         self.eos = eos_token_id
-        self.waiting: Deque[int] = deque()
+        self.waiting: Deque[int] = deque()   # mirrors of the native queues
         self.running: List[int] = []
         self.requests: Dict[int, Request] = {}
         self._terminal: Deque[int] = deque()
         self._next_id = 1
         self.counters = {"preemptions": 0, "failed": 0, "done": 0, "admitted": 0}
+        self._lib = native.lib()
+        self._core = self._lib.locus_sched_new(cache._core, config.max_batch_tokens, config.chunk,
+                                               config.decode_headroom, config.max_running, max_positions)
+        if not self._core:
+            raise ValueError("scheduler: token budget, portion size and max_running must be positive")
+        self._ids = (ctypes.c_int64 * 4096)()
+        self._plan = (ctypes.c_int64 * (4 * max(1, config.max_running)))()
+        self._pairs = (ctypes.c_int * 4096)()
+
+    def __del__(self) -> None:
+        core, self._core = getattr(self, "_core", None), None
+        if core:
+            self._lib.locus_sched_delete(core)
+
+    # -- what the native side decided -----------------------------------------
+    def _sync(self) -> None:
+        """Apply the native side's events to the records, poison the pages it freed (tests), mirror the queues."""
+        lib, core = self._lib, self._core
+        changed = False
+        while True:
+            n = lib.locus_sched_events(core, self._ids, len(self._ids) // 3)
+            changed = changed or n > 0
+            for i in range(n):
+                kind, rid, arg = self._ids[3 * i], self._ids[3 * i + 1], self._ids[3 * i + 2]
+                r = self.requests[rid]
+                if kind == self._EV_ADMITTED:
+                    r.seq = self.cache.adopt_native(r.id, arg)
+                    r.status = Status.RUNNING
+                    r.n_fed = 0
+                    self.counters["admitted"] += 1
+                elif kind == self._EV_PREEMPTED:
+                    self.cache.forget_native(r.seq)
+                    r.seq = None
+                    r.n_fed = 0
+                    r.status = Status.WAITING
+                    r.preemptions += 1
+                    self.counters["preemptions"] += 1
+                elif kind == self._EV_FAILED:
+                    r.error = self._WHY.get(arg, "failed")
+                    self._record_end(r, Status.FAILED)
+                else:
+                    self._record_end(r, Status.DONE)
+            if n < len(self._ids) // 3:
+                break
+        while True:
+            n = lib.locus_sched_freed(core, self._pairs, len(self._pairs))
+            self.cache.poison_pairs(self._pairs[: 2 * n])
+            if 2 * n < len(self._pairs):
+                break
+        if changed:   # the queues only change with an event
+            self.waiting = deque(self._queue(0))
+            self.running = self._queue(1)
+
+    def _queue(self, which: int) -> List[int]:
+        n = self._lib.locus_sched_count(self._core, which)
+        if n > len(self._ids):
+            self._ids = (ctypes.c_int64 * (2 * n))()
+        n = self._lib.locus_sched_queue(self._core, which, self._ids, len(self._ids))
+        return list(self._ids[:n])
 
     # -- submission ---------------------------------------------------------
     def admit_error(self, n_prompt: int) -> str:
@@ -127,10 +197,12 @@ class Scheduler:
         self.requests[rid] = r
         err = self.admit_error(len(r.prompt))
         if err:
-            self._fail(r, err)
+            r.error = err
+            self._record_end(r, Status.FAILED)   # never reaches the native queue
         elif r.max_new_tokens <= 0:
-            self._finish(r, Status.DONE)
+            self._record_end(r, Status.DONE)
         else:
+            self._lib.locus_sched_add(self._core, rid, len(r.prompt))
             self.waiting.append(rid)
         return rid
 
@@ -140,11 +212,15 @@ class Scheduler:
     def release_record(self, rid: int) -> None:
         r = self.requests.get(rid)
         if r is not None and r.status in (Status.DONE, Status.FAILED):
-            del self.requests[rid]
+            self._drop(rid)
             try:
                 self._terminal.remove(rid)
             except ValueError:
                 pass
+
+    def _drop(self, rid: int) -> None:
+        self.requests.pop(rid, None)
+        self._lib.locus_sched_forget(self._core, rid)
 
     def has_runnable_work(self) -> bool:
         """False when nothing runs and the front of the queue cannot be admitted even with
@@ -161,95 +237,43 @@ class Scheduler:
 
     # -- one iteration --------------------------------------------------------
     def admit(self) -> None:
-        while self.waiting and len(self.running) < self.cfg.max_running:
-            r = self.requests[self.waiting[0]]
-            want = self.cache.pages_for(r.stream_len() + self.cfg.decode_headroom)
-            if want > self.cache.free_pages() or self.cache.state_slots.free == 0:
-                break  # first come first served: nobody overtakes the front
-            self.waiting.popleft()
-            r.seq = self.cache.open(r.id)
-            r.status = Status.RUNNING
-            r.n_fed = 0
-            self.running.append(r.id)
-            self.counters["admitted"] += 1
+        """First come first served while requests fit (see the module's text); native."""
+        if self._lib.locus_sched_admit(self._core):
+            self._sync()
 
     def plan(self) -> List[Planned]:
         """Choose this step's tokens and take their pages.  Decode tokens (one left to feed)
-        first, then portions in admission order under the budget."""
-        planned: Dict[int, Planned] = {}
-        budget = self.cfg.max_batch_tokens
-        # context overflow: the next token to feed has no position left
-        for rid in list(self.running):
-            r = self.requests[rid]
-            if r.n_fed + 1 > self.max_positions or r.n_fed + 1 > self.cache.max_seq_tokens:
-                self._fail(r, "context overflow")
-        order = [rid for rid in self.running if self.requests[rid].stream_len() - self.requests[rid].n_fed == 1]
-        order += [rid for rid in self.running if self.requests[rid].stream_len() - self.requests[rid].n_fed > 1]
-        for rid in order:
-            r = self.requests.get(rid)
-            if r is None or r.status != Status.RUNNING or budget <= 0:
-                continue
-            left = r.stream_len() - r.n_fed
-            n = min(left, budget, self.cfg.chunk,
-                    self.max_positions - r.n_fed, self.cache.max_seq_tokens - r.n_fed)
-            if n <= 0:
-                continue
-            ok = self._make_room(r, n, planned)
-            if not ok:
-                continue
-            planned[rid] = Planned(r, r.n_fed, n, wants_logits=(r.n_fed + n == r.stream_len()))
-            budget -= n
-        # keep admission order in the batch: rows of a request do not depend on it, but a
-        # stable order makes steps reproducible
-        return [planned[rid] for rid in self.running if rid in planned]
-
-    def _make_room(self, r: Request, n: int, planned: Dict[int, Planned]) -> bool:
-        while not self.cache.ensure_capacity(r.seq, n):
-            victim = self.requests[self.running[-1]]
-            if victim is r:
-                if len(self.running) == 1:
-                    self._fail(r, "kv pool too small for request")
-                return False  # newest but not alone: sit this step out
-            planned.pop(victim.id, None)
-            self._preempt(victim)
-        return True
-
-    def _preempt(self, victim: Request) -> None:
-        self.cache.release(victim.seq)
-        victim.seq = None
-        victim.n_fed = 0
-        victim.status = Status.WAITING
-        victim.preemptions += 1
-        self.running.remove(victim.id)
-        self.waiting.appendleft(victim.id)  # victims go to the front
-        self.counters["preemptions"] += 1
+        first, then portions in admission order under the budget; native."""
+        n = self._lib.locus_sched_plan(self._core, self._plan, len(self._plan) // 4)
+        self._sync()
+        out = []
+        for i in range(n):
+            rid, start, cnt, wants = (self._plan[4 * i + j] for j in range(4))
+            out.append(Planned(self.requests[rid], int(start), int(cnt), bool(wants)))
+        return out
 
     def fed(self, p: Planned) -> None:
         p.request.n_fed += p.n
+        self._lib.locus_sched_fed(self._core, p.request.id, p.n)
 
     def accept_token(self, r: Request, token: int) -> bool:
         """Append a sampled token; True when the request is finished by it (end-of-sequence
         token, which is kept in ``generated`` as in the reference, or the length limit)."""
         r.generated.append(int(token))
-        if int(token) == self.eos or len(r.generated) >= r.max_new_tokens:
-            self._finish(r, Status.DONE)
-            return True
-        return False
+        finished = int(token) == self.eos or len(r.generated) >= r.max_new_tokens
+        self._lib.locus_sched_token(self._core, r.id, 1 if finished else 0)
+        if finished:
+            self._sync()
+        return finished
 
     # -- endings --------------------------------------------------------------
-    def _finish(self, r: Request, status: Status) -> None:
+    def _record_end(self, r: Request, status: Status) -> None:
+        """The record of a request that ended (the native side has given back what it held)."""
         if r.seq is not None:
-            self.cache.release(r.seq)
+            self.cache.forget_native(r.seq)
             r.seq = None
-        if r.id in self.running:
-            self.running.remove(r.id)
         r.status = status
         self.counters["done" if status == Status.DONE else "failed"] += 1
         self._terminal.append(r.id)
         while len(self._terminal) > self.cfg.max_retained_terminal:
-            old = self._terminal.popleft()
-            self.requests.pop(old, None)
-
-    def _fail(self, r: Request, why: str) -> None:
-        r.error = why
-        self._finish(r, Status.FAILED)
+            self._drop(self._terminal.popleft())

@@ -204,3 +204,66 @@ def test_sampling_params_are_checked():
     with pytest.raises(ValueError, match="top_k"):
         eng.submit([1], 1, SamplingParams(top_k=-1))
     assert eng.submit([1, 2], 0) and eng.get(1) is None or True
+
+
+def test_native_scheduler_decides_like_the_plain_one():
+    """Random workloads (arrivals between steps, pools that run out, window groups, long prompts, end-of-
+    sequence tokens): the native scheduler and the plain Python policy, each over a cache of its own, must
+    plan the same batches step by step and end every request alike."""
+    import random
+
+    from plain_scheduler import PlainScheduler
+
+    from locus_b200.cache import CacheManager
+    from locus_b200.engine.scheduler import Scheduler, SchedulerConfig
+    from locus_b200.parts.base import PagedKvSpec
+
+    def token_after(rid, n):  # the "model": next token from the request and its length
+        return (rid * 7919 + n * 31) % 97
+
+    for seed in range(12):
+        rng = random.Random(seed)
+        needs = [(PagedKvSpec(2, 16, 0), None, None)] + ([(PagedKvSpec(2, 16, 24), None, None)] if seed % 3 == 0 else [])
+        n_pages = rng.choice([4, 6, 9, 30])
+        max_pos = rng.choice([64, 200])
+        cfg = SchedulerConfig(max_batch_tokens=rng.choice([8, 24, 64]), chunk=rng.choice([4, 16, 64]),
+                              decode_headroom=rng.choice([0, 4, 16]), max_running=rng.choice([2, 3, 8]),
+                              max_retained_terminal=1000)
+        eos = 5
+        pair = []
+        for cls in (Scheduler, PlainScheduler):
+            cache = CacheManager(needs, page_tokens=16, n_pages=n_pages, n_state_slots=cfg.max_running,
+                                 max_seq_tokens=max_pos, device="cpu", allocate_device=False)
+            pair.append((cls(cache, cfg, max_pos, eos), cache))
+        arrivals = [(rng.randint(0, 30), rng.randint(1, 70), rng.randint(0, 40)) for _ in range(rng.randint(3, 14))]
+        for step in range(400):
+            plans = []
+            for sched, cache in pair:
+                for at, n_prompt, n_new in arrivals:
+                    if at == step:
+                        sched.submit(list(range(1, n_prompt + 1)), n_new)
+                sched.admit()
+                planned = sched.plan()
+                plans.append([(p.request.id, p.start, p.n, p.wants_logits) for p in planned])
+                for p in planned:
+                    assert p.request.seq.n_tokens == p.start
+                    cache.commit(p.request.seq, p.n)
+                    sched.fed(p)
+                for p in planned:
+                    if p.wants_logits:
+                        sched.accept_token(p.request, token_after(p.request.id, p.request.stream_len()))
+                cache.check_invariants()
+            assert plans[0] == plans[1], (seed, step, plans)
+            a, b = pair[0][0], pair[1][0]
+            assert list(a.waiting) == list(b.waiting) and a.running == b.running, (seed, step)
+            if step > 30 and not a.has_runnable_work():
+                break
+        a, b = pair[0][0], pair[1][0]
+        assert a.counters == b.counters, seed
+        assert a.has_runnable_work() == b.has_runnable_work()
+        for rid, r in a.requests.items():
+            q = b.requests[rid]
+            assert (r.status, r.error, r.generated, r.preemptions, r.n_fed) == (q.status, q.error, q.generated, q.preemptions, q.n_fed), (seed, rid)
+        for sched, cache in pair:
+            if sched.idle():
+                assert cache.free_pages() == cache.total_pages() and cache.state_slots.free == cache.state_slots.total
