@@ -29,8 +29,8 @@
 //
 // Every wait on an mbarrier is bounded (about a second of clock cycles); when a wait runs
 // out the kernel records a code in the module's error word, stops waiting and finishes, so
-// a fault in the pipeline shows as an error on the host, never as a hang.  No load uses
-// cluster multicast.
+// a fault in the pipeline shows as an error on the host, never as a hang.  Every TMA load goes
+// to the shared memory of the block that issued it; nothing is sent to other blocks.
 #include <cuda.h>
 
 #include "common.cuh"
