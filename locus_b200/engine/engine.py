@@ -13,7 +13,7 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..sampling.sampler import GREEDY, Sampler, SamplingParams
-from .scheduler import Planned, Request, Scheduler, SchedulerConfig, Status
+from .scheduler import Request, Scheduler, SchedulerConfig, Status
 from .step import ModelRunner, StepEntry
 
 

@@ -35,12 +35,12 @@ from __future__ import annotations
 import enum
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
+from typing import Deque, Dict, List, Optional, Sequence
 
 import ctypes
 
 from ..cache import native
-from ..cache.manager import CacheError, CacheManager, SeqCache
+from ..cache.manager import CacheManager, SeqCache
 from ..sampling.sampler import GREEDY, SamplingParams
 
 

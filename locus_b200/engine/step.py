@@ -19,12 +19,11 @@ by the number of requests; every other shape is launched kernel by kernel.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, Optional, Sequence
 
 import numpy as np
 import torch
 
-from ..cache import native
 from ..cache.manager import CacheError, CacheManager, SeqCache
 from .. import kernels as K
 from ..kernels import DECODE_SPLIT

@@ -6,13 +6,13 @@ architecture: the architecture is the plan.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Tuple
+from typing import List, Optional, Tuple
 
 import torch
 
-from ..config.base import find_arch, load_config
+from ..config.base import load_config
 from ..engine.batch import LayerCache, Runtime, StepBatch
-from ..parts.base import (LayerCall, ModelPlan, PagedKvSpec, Part, PartSpec, StateSpec, TensorSource,
+from ..parts.base import (ModelPlan, PagedKvSpec, Part, PartSpec, StateSpec, TensorSource,
                           iter_parts, make_part)
 
 

@@ -38,7 +38,6 @@ def main(argv=None) -> int:
                     help="most tokens in one step (default: --max-tokens)")
     args = ap.parse_args(argv)
 
-    import numpy as np
     import torch
 
     if not torch.cuda.is_available():

@@ -20,12 +20,12 @@ from __future__ import annotations
 import hashlib
 import json
 import os
-from typing import Dict, List, Optional, Tuple
+from typing import Dict, List, Tuple
 
 import torch
 
 from ..config.base import find_arch
-from .safetensors_io import ModelFiles, write_safetensors
+from .safetensors_io import write_safetensors
 
 
 class WeightError(ValueError):

@@ -8,12 +8,10 @@ order under one token budget.
 """
 from __future__ import annotations
 
-import enum
 from collections import deque
-from dataclasses import dataclass, field
-from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
+from typing import Deque, Dict, List, Optional, Sequence
 
-from locus_b200.cache.manager import CacheError, CacheManager, SeqCache
+from locus_b200.cache.manager import CacheManager
 from locus_b200.engine.scheduler import Planned, Request, SchedulerConfig, Status
 from locus_b200.sampling.sampler import GREEDY, SamplingParams
 
