@@ -82,6 +82,7 @@ def main(argv=None) -> int:
                 arr.astype("<f4", copy=False).tofile(os.path.join(args.out, f"{step}.f32"))
             else:
                 torch.cuda.synchronize()
+            runner.check_device_errors()  # a bounded wait of a tensor-core pipeline that ran out: fail here
         for rid in rec.get("end", []):
             seq = cache.get(rid)
             if seq is not None:
