@@ -8,8 +8,6 @@ loops; they are not a product path and nothing in ``locus_b200`` imports them.
 """
 from __future__ import annotations
 
-import math
-from typing import Optional
 
 import torch
 

@@ -1,6 +1,5 @@
 """Configuration, registry, safetensors and weight-loading errors (no GPU)."""
 import json
-import os
 
 import pytest
 import torch
@@ -8,7 +7,7 @@ import torch
 import locus_b200.models  # noqa: F401
 from locus_b200.config import ConfigError, Qwen2MoeConfig, archs, find_arch, load_config
 from locus_b200.models.model import Model
-from locus_b200.weights.loader import RandomSource, WeightError, load_weights, random_tensor, write_random_model
+from locus_b200.weights.loader import RandomSource, WeightError, load_weights, random_tensor
 from locus_b200.weights.safetensors_io import ModelFiles, SafetensorsError, write_safetensors
 from tiny_configs import config, make_model_dir
 

@@ -8,7 +8,6 @@ program.  Pages are poisoned with NaN when created and when given back, so a rea
 stale or unwritten slot shows in the logits.
 """
 import json
-import math
 import os
 import subprocess
 import sys
@@ -17,7 +16,7 @@ import pytest
 import torch
 
 import plain_qwen2moe as plain
-from tiny_configs import config, make_model_dir, random_tokens
+from tiny_configs import make_model_dir, random_tokens
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))

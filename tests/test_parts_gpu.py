@@ -11,7 +11,7 @@ import torch
 import plain_qwen2moe as plain
 from locus_b200 import kernels as K
 from locus_b200.cache import CacheManager
-from locus_b200.engine.batch import GroupBatch, LayerCache, Runtime, StepBatch
+from locus_b200.engine.batch import GroupBatch, Runtime, StepBatch
 from locus_b200.parts import PartSpec, make_part
 from locus_b200.weights.loader import random_tensor
 

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_qwen2moe as plain
-from tiny_configs import config, make_model_dir, random_tokens
+from tiny_configs import make_model_dir, random_tokens
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 

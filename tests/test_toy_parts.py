@@ -5,7 +5,6 @@ as a model folder, loaded, stepped in portions and mixed batches, and compared w
 whole-sequence computation.  Runs on the GPU (marked gpu) and, with the kernels replaced
 by their torch twins, on the CPU.
 """
-import json
 import os
 
 import pytest
