@@ -186,3 +186,34 @@ def test_step_descriptors_match_a_plain_assembly(tmp_path):
         for e in entries:
             cache.commit(e.seq, len(e.tokens))
         cache.check_invariants()
+
+
+def test_step_refuses_numbers_that_fit_no_field(tmp_path):
+    """Token ids and wanted places far outside 32 (or 64) bits, negative ones, more wanted rows or requests
+    than the runner was built for, a released request: refused with an error, nothing runs, the next good
+    step is unharmed."""
+    cfg, W, model, cache, runner = setup("A", tmp_path)
+    s = cache.open("a")
+    assert cache.ensure_capacity(s, 4)
+    for bad in ([1, 2 ** 40, 3], [-1, 2, 3], [2 ** 31, 1], [1, 2 ** 70]):
+        with pytest.raises(StepError, match="outside the vocabulary"):
+            runner.step([StepEntry(s, bad, [])])
+    for bad in ([-1], [2 ** 40], [2 ** 70]):
+        with pytest.raises(StepError, match="wanted place|outside"):
+            runner.step([StepEntry(s, [1, 2, 3], bad)])
+    with pytest.raises(StepError, match="rows wanted"):
+        small = ModelRunner(model, cache, max_tokens=64, max_segments=4, max_wanted=2)
+        small.step([StepEntry(s, [1, 2, 3], [0, 1, 2])])
+    others = [cache.open(f"o{i}") for i in range(3)]
+    extra = CacheManager(model.cache_needs(), page_tokens=16, n_pages=2, n_state_slots=8, max_seq_tokens=32, device="cpu")
+    with pytest.raises(StepError, match="requests in a step"):
+        many = [StepEntry(o, [1], []) for o in others] + [StepEntry(s, [1], [])] + [StepEntry(extra.open("e"), [1], [])]
+        runner.step(many)
+    gone = others[0]
+    cache.release(gone)
+    with pytest.raises(CacheError, match="not open"):
+        runner.step([StepEntry(gone, [1], [])])
+    assert s.n_tokens == 0
+    lg = runner.step([StepEntry(s, [1, 2, 3], [2])])   # and a good step still runs
+    ref = plain.forward(cfg, W, [1, 2, 3], torch.float64)
+    assert float((lg[0].double() - ref[2]).abs().max()) <= 2e-5 * float(ref.abs().max())
