@@ -121,7 +121,7 @@ class Engine:
                 tokens = self.sampler.sample(
                     logits, [r.sampling for r in reqs], [r.seed for r in reqs],
                     [len(r.generated) for r in reqs],
-                    [r.prompt + r.generated for r in reqs] if any(r.sampling.has_penalties() for r in reqs) else None,
+                    [_history_tail(r) for r in reqs] if any(r.sampling.has_penalties() for r in reqs) else None,
                 )
                 for r, tok in zip(reqs, tokens):
                     s.accept_token(r, tok)
@@ -143,7 +143,17 @@ class Engine:
             n += 1
             if max_steps and n >= max_steps:
                 break
+        self.check_device_errors()
         return n
+
+    def check_device_errors(self) -> None:
+        """Raise if a kernel recorded a fault since the last check (the runner's error words; reading
+        them synchronises the device).  The reference fails a request with a reason rather than
+        returning garbage (src/locus/engine/engine.cpp:198-211); a kernel whose bounded wait ran out
+        ends with invalid output, so tokens must not be handed out before this was read."""
+        check = getattr(self.runner, "check_device_errors", None)
+        if check is not None:
+            check()
 
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 64, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, min_p: float = 0.0, seed: int = 0,
@@ -172,6 +182,18 @@ class Engine:
         d["waiting"] = len(self.sched.waiting)
         d["running"] = len(self.sched.running)
         return d
+
+
+def _history_tail(r: Request) -> List[int]:
+    """The last ``repeat_last_n`` tokens of a request (prompt, then generated): what the penalties see."""
+    n = r.sampling.repeat_last_n if r.sampling.has_penalties() else 0
+    if n <= 0:
+        return []
+    g = r.generated
+    if len(g) >= n:
+        return g[len(g) - n :]
+    p = r.prompt
+    return list(p[max(0, len(p) - (n - len(g))) :]) + list(g)
 
 
 def parse_dtype(name) -> torch.dtype:

@@ -44,6 +44,8 @@ class SamplingParams:
             raise ValueError("min_p must be within [0, 1]")
         if self.repeat_penalty <= 0.0:
             raise ValueError("repeat_penalty must be positive")
+        if self.repeat_last_n < 0:
+            raise ValueError("repeat_last_n must not be negative")
 
 
 GREEDY = SamplingParams()
@@ -54,29 +56,45 @@ class Sampler:
     pinned buffer; the result comes back as int32."""
 
     def __init__(self, device, max_rows: int, max_history: int = 64) -> None:
+        """``max_history``: tokens of history per row that the penalty buffers hold at first; they
+        grow to the largest ``repeat_last_n`` that a request brings."""
         self.device = torch.device(device)
         self.max_rows = max_rows
-        self.max_history = max_history
-        pin = self.device.type == "cuda"
+        self._pin = self.device.type == "cuda"
         R = max_rows
-        # float block: temperature, top_p, min_p, repeat, freq, presence ; int block: top_k
-        self._hf = torch.zeros(6 * R, dtype=torch.float32, pin_memory=pin)
+        # float block: temperature, top_p, min_p, repeat, freq, presence; int block: top_k; long block: seed, counter
+        self._hf = torch.zeros(6 * R, dtype=torch.float32, pin_memory=self._pin)
         self._df = torch.zeros(6 * R, dtype=torch.float32, device=self.device)
-        self._hi = torch.zeros(R * (1 + max_history), dtype=torch.int32, pin_memory=pin)
-        self._di = torch.zeros(R * (1 + max_history), dtype=torch.int32, device=self.device)
-        self._hl = torch.zeros(2 * R, dtype=torch.int64, pin_memory=pin)
+        self._hi = torch.zeros(R, dtype=torch.int32, pin_memory=self._pin)
+        self._di = torch.zeros(R, dtype=torch.int32, device=self.device)
+        self._hl = torch.zeros(2 * R, dtype=torch.int64, pin_memory=self._pin)
         self._dl = torch.zeros(2 * R, dtype=torch.int64, device=self.device)
         self._out = torch.zeros(R, dtype=torch.int32, device=self.device)
-        self._out_host = torch.zeros(R, dtype=torch.int32, pin_memory=pin)
-        self._all_greedy_loaded = False
+        self._out_host = torch.zeros(R, dtype=torch.int32, pin_memory=self._pin)
+        self.max_history = 0
+        self._grow_history(max(1, max_history))
+        # rows 0 .. _greedy_rows - 1 of the device blocks hold plain greedy parameters (0: not known to)
+        self._greedy_rows = 0
         self.d2h_bytes = 0
         self.h2d_bytes = 0
+
+    def _grow_history(self, n: int) -> None:
+        """Room for ``n`` tokens of history per row (the only allocation after construction: a request
+        with a longer ``repeat_last_n`` than any before it)."""
+        if n <= self.max_history:
+            return
+        cap = max(64, self.max_history)
+        while cap < n:
+            cap *= 2
+        self.max_history = cap
+        self._hh = torch.full((self.max_rows, cap), -1, dtype=torch.int32, pin_memory=self._pin)
+        self._dh = torch.full((self.max_rows, cap), -1, dtype=torch.int32, device=self.device)
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], seeds: Sequence[int],
                counters: Sequence[int], histories: Optional[Sequence[Sequence[int]]] = None) -> List[int]:
         """One token for each row of ``logits`` [R, V].  ``counters[i]``: index of the token
         being generated for request i (the draw's counter).  ``histories``: recent tokens of
-        each request, needed only when a row has penalties."""
+        each request (at least its last ``repeat_last_n``), needed only when a row has penalties."""
         tokens = self.sample_device(logits, params, seeds, counters, histories)
         R = logits.shape[0]
         self._out_host[:R].copy_(tokens[:R], non_blocking=False)
@@ -87,39 +105,44 @@ class Sampler:
         R = logits.shape[0]
         if R > self.max_rows:
             raise ValueError(f"{R} rows, the sampler was built for {self.max_rows}")
+        if len(params) != R:
+            raise ValueError(f"{len(params)} sampling parameters for {R} rows of logits")
         all_greedy = all(p.temperature <= 0.0 and not p.has_penalties() for p in params)
         Rm = self.max_rows
-        if not (all_greedy and self._all_greedy_loaded):
-            hf = self._hf
-            for i, p in enumerate(params):
-                hf[i] = p.temperature
-                hf[Rm + i] = p.top_p
-                hf[2 * Rm + i] = p.min_p
-                hf[3 * Rm + i] = p.repeat_penalty
-                hf[4 * Rm + i] = p.frequency_penalty
-                hf[5 * Rm + i] = p.presence_penalty
-                self._hi[i] = p.top_k
-                self._hl[i] = int(seeds[i]) & 0x7FFFFFFFFFFFFFFF
-                self._hl[Rm + i] = int(counters[i])
-            self._df.copy_(self._hf, non_blocking=True)
-            self._di[:Rm].copy_(self._hi[:Rm], non_blocking=True)
-            self._dl.copy_(self._hl, non_blocking=True)
-            self.h2d_bytes += 6 * 4 * Rm + 4 * Rm + 16 * Rm
-            self._all_greedy_loaded = all_greedy
+        # a batch of plain greedy rows needs no upload while the device rows it uses are known to be greedy
+        if not (all_greedy and R <= self._greedy_rows):
+            hf = self._hf.view(6, Rm)
+            hf[0, :R] = torch.tensor([p.temperature for p in params], dtype=torch.float32)
+            hf[1, :R] = torch.tensor([p.top_p for p in params], dtype=torch.float32)
+            hf[2, :R] = torch.tensor([p.min_p for p in params], dtype=torch.float32)
+            hf[3, :R] = torch.tensor([p.repeat_penalty for p in params], dtype=torch.float32)
+            hf[4, :R] = torch.tensor([p.frequency_penalty for p in params], dtype=torch.float32)
+            hf[5, :R] = torch.tensor([p.presence_penalty for p in params], dtype=torch.float32)
+            self._hi[:R] = torch.tensor([p.top_k for p in params], dtype=torch.int32)
+            self._hl[:R] = torch.tensor([int(s) & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=torch.int64)
+            self._hl[Rm : Rm + R] = torch.tensor([int(c) for c in counters], dtype=torch.int64)
+            self._df.view(6, Rm)[:, :R].copy_(hf[:, :R], non_blocking=True)
+            self._di[:R].copy_(self._hi[:R], non_blocking=True)
+            self._dl.view(2, Rm)[:, :R].copy_(self._hl.view(2, Rm)[:, :R], non_blocking=True)
+            self.h2d_bytes += (6 * 4 + 4 + 16) * R
+            # rows beyond R keep what an earlier batch left: greedy only if they were and this batch is
+            self._greedy_rows = max(R, self._greedy_rows) if all_greedy else 0
         if any(p.has_penalties() for p in params):
             if histories is None:
                 raise ValueError("penalties need the requests' token histories")
-            H = self.max_history
-            hist = self._hi[Rm : Rm + R * H].view(R, H)
+            need = max(min(p.repeat_last_n, len(h)) for p, h in zip(params, histories))
+            self._grow_history(need)
+            n_hist = max(1, need)
+            hist = self._hh.view(-1)[: R * n_hist].view(R, n_hist)
             hist.fill_(-1)
             for i, (p, h) in enumerate(zip(params, histories)):
-                n = min(p.repeat_last_n, H, len(h))
+                n = min(p.repeat_last_n, len(h)) if p.has_penalties() else 0
                 if n:
                     hist[i, :n] = torch.tensor(list(h[len(h) - n :]), dtype=torch.int32)
-            dh = self._di[Rm : Rm + R * H]
-            dh.copy_(self._hi[Rm : Rm + R * H], non_blocking=True)
-            self.h2d_bytes += 4 * R * H
-            K.apply_penalties(logits, dh.view(R, H), self._df[3 * Rm :], self._df[4 * Rm :], self._df[5 * Rm :])
+            dh = self._dh.view(-1)[: R * n_hist].view(R, n_hist)
+            dh.copy_(hist, non_blocking=True)
+            self.h2d_bytes += 4 * R * n_hist
+            K.apply_penalties(logits, dh, self._df[3 * Rm :], self._df[4 * Rm :], self._df[5 * Rm :])
         K.sample(logits, temperature=self._df[:Rm], top_k=self._di[:Rm], top_p=self._df[Rm : 2 * Rm],
                  min_p=self._df[2 * Rm : 3 * Rm], seeds=self._dl[:Rm], counters=self._dl[Rm:], out=self._out)
         return self._out
