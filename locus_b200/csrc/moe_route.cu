@@ -27,6 +27,146 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float* o) {
     }
 }
 
+// How a token's experts are chosen from its router logits, as the reference's moe_select does it
+// (src/locus/model/llama.cpp:900-980): scores = softmax over all experts, or a sigmoid of each logit;
+// selection scores = scores (+ sel_bias, which never enters the weights); with n_group > 1 only the
+// n_group_used groups with the largest sum of their two best selection scores stay eligible (the others are
+// masked to -1e30); k rounds of arg-max with strict '>' (ties to the lowest index); weight = score / wsum *
+// scale, wsum = sum of the picked scores when renorm, else 1.
+#define SCORE_SOFTMAX 0
+#define SCORE_SIGMOID 1
+struct RouteOpts {
+    int k, renorm, score_fn, n_group, n_group_used;
+    float scale;
+    const float* sel_bias;  // [E] float32 or null
+};
+
+__host__ inline bool route_opts_ok(const RouteOpts& o, int E) {
+    if (E <= 0 || o.k <= 0 || o.k > E) return false;
+    if (o.score_fn != SCORE_SOFTMAX && o.score_fn != SCORE_SIGMOID) return false;
+    if (o.n_group < 1 || o.n_group > 32 || E % o.n_group != 0) return false;
+    if (o.n_group > 1 && (o.n_group_used < 1 || o.n_group_used > o.n_group)) return false;
+    return true;
+}
+
+// Scores, selection and weights of one token by one warp.  lg: the token's logits (column E, when
+// has_gate, is the logit of the shared-expert gate); p: 2 * E floats of shared memory of this warp;
+// s_ids (or null): where the picks are also kept for the block.  The selection is total: a score that is
+// not a number counts as the lowest, so every pick is an expert index below E whatever the logits hold.
+__device__ __forceinline__ void select_token(const float* __restrict__ lg, float* p, int t, int lane,
+                                             int* __restrict__ ids, float* __restrict__ wts,
+                                             float* __restrict__ gamma, int* s_ids, int E, int has_gate,
+                                             const RouteOpts o) {
+    float* sel = p + E;
+    const int k = o.k;
+    if (o.score_fn == SCORE_SOFTMAX) {
+        float mx = -INFINITY;
+        for (int x = lane; x < E; x += 32) {
+            const float v = __ldcg(lg + x);
+            p[x] = v;
+            mx = fmaxf(mx, v);
+        }
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int x = lane; x < E; x += 32) {
+            const float v = expf(p[x] - mx);
+            p[x] = v;
+            sum += v;
+        }
+        sum = warp_sum(sum);
+        for (int x = lane; x < E; x += 32) p[x] = p[x] / sum;
+    } else {
+        for (int x = lane; x < E; x += 32) p[x] = 1.0f / (1.0f + expf(-__ldcg(lg + x)));
+    }
+    if (has_gate && lane == 0) gamma[t] = 1.0f / (1.0f + expf(-__ldcg(lg + E)));
+    for (int x = lane; x < E; x += 32) {
+        const float v = p[x] + (o.sel_bias != nullptr ? o.sel_bias[x] : 0.f);
+        sel[x] = (v == v) ? v : -3.0e38f;
+    }
+    __syncwarp();
+    if (o.n_group > 1) {
+        const int per = E / o.n_group;
+        const bool has_group = lane < o.n_group;
+        float gs = -INFINITY;
+        if (has_group) {
+            float top1 = -1e30f, top2 = -1e30f;
+            for (int e = lane * per; e < (lane + 1) * per; ++e) {
+                const float v = sel[e];
+                if (v > top1) {
+                    top2 = top1;
+                    top1 = v;
+                } else if (v > top2) {
+                    top2 = v;
+                }
+            }
+            gs = top1 + (per > 1 ? top2 : 0.0f);
+        }
+        unsigned keep = 0;
+        for (int r = 0; r < o.n_group_used; ++r) {
+            const bool open = has_group && !((keep >> lane) & 1u);
+            float best = open ? gs : -INFINITY;
+            int bi = open ? lane : 0x7fffffff;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, d);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, d);
+                if (ov > best || (ov == best && oi < bi)) {
+                    best = ov;
+                    bi = oi;
+                }
+            }
+            if (bi < 32) keep |= 1u << bi;
+        }
+        __syncwarp();
+        for (int x = lane; x < E; x += 32)
+            if (!((keep >> (x / per)) & 1u)) sel[x] = -1e30f;
+        __syncwarp();
+    }
+    float wsum = 0.f;
+    // After the butterfly every lane knows the pick; lane r keeps the score of pick r, so that the
+    // weights go out with one store per lane at the end (up to 32 picks; beyond that they take the way
+    // through global memory).
+    const bool in_lanes = k <= 32;
+    float my_w = 0.f;
+    for (int r = 0; r < k; ++r) {
+        float best = -INFINITY;  // taken experts hold -inf, everything else is above it
+        int best_e = 0x7fffffff;
+        for (int x = lane; x < E; x += 32) {
+            const float v = sel[x];
+            if (v > best) {  // ascending x keeps the lowest index on ties
+                best = v;
+                best_e = x;
+            }
+        }
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, d);
+            const int oe = __shfl_xor_sync(0xffffffffu, best_e, d);
+            if (ov > best || (ov == best && oe < best_e)) {
+                best = ov;
+                best_e = oe;
+            }
+        }
+        if (best_e >= E) best_e = 0;  // cannot happen while k <= E; keeps every index in range regardless
+        const float w = p[best_e];
+        if (lane == r) my_w = w;
+        if (lane == 0) {
+            ids[t * k + r] = best_e;
+            if (s_ids != nullptr) s_ids[t * k + r] = best_e;
+            if (!in_lanes) wts[t * k + r] = w;
+            sel[best_e] = -INFINITY;
+        }
+        wsum += w;
+        __syncwarp();
+    }
+    const float div = o.renorm ? wsum : 1.0f;
+    if (in_lanes) {
+        if (lane < k) wts[t * k + lane] = my_w / div * o.scale;
+    } else if (lane == 0) {
+        for (int r = 0; r < k; ++r) wts[t * k + r] = wts[t * k + r] / div * o.scale;
+    }
+}
+
 // Grid (token tiles of RT_TOK, expert groups of RT_WARPS).  A block stages its tokens'
 // activations in shared memory; each warp computes the router logit of one expert (the shared
 // gate counts as expert E) for all tokens of the tile, every weight read once per tile, and
@@ -36,19 +176,17 @@ __device__ __forceinline__ void load8<bf16>(const bf16* p, float* o) {
 //   wr       [E, H]   router weight; wg [H] weight of the shared-expert gate (or null)
 //   ids      [T, k]   picked experts in pick order; wts [T, k] their weights
 //   gamma    [T]      sigmoid(wg . h) (written only when wg != null)
-// Selection: k rounds of arg-max over softmax probabilities with strict '>' (ties go to the
-// lowest index).  weight = p / wsum * scale with wsum = sum of picked p when renorm, else 1.
+// Selection and weights: select_token above.
 // The order in which a logit is summed depends on H only (8-element chunks per lane when H
 // is a multiple of 8, single elements else), not on the tile or its other tokens.
 template <typename TX, typename TW>
 __global__ void __launch_bounds__(256) router_topk_kernel(
     const TX* __restrict__ h, const TW* __restrict__ wr, const void* __restrict__ wg, int wg_dt,
     float* __restrict__ logits, int* __restrict__ counters, int* __restrict__ ids,
-    float* __restrict__ wts, float* __restrict__ gamma, int T, int H, int E, int k, int renorm,
-    float scale) {
+    float* __restrict__ wts, float* __restrict__ gamma, int T, int H, int E, const RouteOpts o) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     TX* hs = reinterpret_cast<TX*>(smem_raw);                                        // [RT_TOK][H]
-    float* probs = reinterpret_cast<float*>(smem_raw + sizeof(TX) * RT_TOK * H);     // [RT_TOK][E1]
+    float* probs = reinterpret_cast<float*>(smem_raw + sizeof(TX) * RT_TOK * H);     // [RT_TOK][2 E]
     __shared__ int is_last;
     const int E1 = E + (wg != nullptr ? 1 : 0);
     const int tile = blockIdx.x, grp = blockIdx.y;
@@ -105,57 +243,8 @@ __global__ void __launch_bounds__(256) router_topk_kernel(
     if (threadIdx.x == 0) counters[tile] = 0;
     if (wid >= nt) return;
     const int t = t0 + wid;
-    const float* lg = logits + static_cast<size_t>(t) * E1;
-    float* p = probs + wid * E1;
-    float mx = -INFINITY;
-    for (int x = lane; x < E; x += 32) {
-        const float v = __ldcg(lg + x);
-        p[x] = v;
-        mx = fmaxf(mx, v);
-    }
-    if (wg != nullptr && lane == 0) gamma[t] = 1.0f / (1.0f + expf(-__ldcg(lg + E)));
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int x = lane; x < E; x += 32) {
-        const float v = expf(p[x] - mx);
-        p[x] = v;
-        sum += v;
-    }
-    sum = warp_sum(sum);
-    for (int x = lane; x < E; x += 32) p[x] = p[x] / sum;
-    __syncwarp();
-    float wsum = 0.f;
-    for (int r = 0; r < k; ++r) {
-        float best = -1.f;
-        int best_e = 0x7fffffff;
-        for (int x = lane; x < E; x += 32) {
-            const float v = p[x];
-            if (v > best) {  // taken experts hold -2; ascending x keeps the lowest index on ties
-                best = v;
-                best_e = x;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (ov > best || (ov == best && oe < best_e)) {
-                best = ov;
-                best_e = oe;
-            }
-        }
-        if (lane == 0) {
-            ids[t * k + r] = best_e;
-            wts[t * k + r] = best;
-            p[best_e] = -2.f;
-        }
-        wsum += best;
-        __syncwarp();
-    }
-    if (lane == 0) {
-        const float div = renorm ? wsum : 1.0f;
-        for (int r = 0; r < k; ++r) wts[t * k + r] = wts[t * k + r] / div * scale;
-    }
+    select_token(logits + static_cast<size_t>(t) * E1, probs + wid * 2 * E, t, lane, ids, wts, gamma, nullptr, E,
+                 wg != nullptr ? 1 : 0, o);
 }
 
 // logits: scratch [T, E (+1 with a gate)] floats; counters: ceil(T / 8) ints, zero before the
@@ -163,12 +252,14 @@ __global__ void __launch_bounds__(256) router_topk_kernel(
 extern "C" int locus_router_topk(const void* h, int x_dt, const void* wr, int w_dt, const void* wg,
                                  int wg_dt, float* logits, int* counters, int* ids, float* wts,
                                  float* gamma, int T, int H, int E, int k, int renorm, float scale,
+                                 int score_fn, const float* sel_bias, int n_group, int n_group_used,
                                  cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (E <= 0 || k <= 0 || k > E) return LOCUS_ERR_UNSUPPORTED;
+    const RouteOpts o{k, renorm, score_fn, n_group, n_group_used, scale, sel_bias};
+    if (!route_opts_ok(o, E)) return LOCUS_ERR_UNSUPPORTED;
     const int E1 = E + (wg != nullptr ? 1 : 0);
     const size_t xsize = x_dt == LOCUS_DT_F32 ? 4 : 2;
-    const size_t smem = xsize * RT_TOK * H + sizeof(float) * RT_TOK * E1;
+    const size_t smem = xsize * RT_TOK * H + sizeof(float) * RT_TOK * 2 * E;
     if (smem > 200 * 1024) return LOCUS_ERR_UNSUPPORTED;
     dim3 grid(ceil_div(T, RT_TOK), ceil_div(E1, RT_WARPS));
     if (grid.y > 65535) return LOCUS_ERR_UNSUPPORTED;
@@ -179,7 +270,7 @@ extern "C" int locus_router_topk(const void* h, int x_dt, const void* wr, int w_
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
         router_topk_kernel<TX, TW><<<grid, 256, smem, stream>>>(                                 \
             static_cast<const TX*>(h), static_cast<const TW*>(wr), wg, wg_dt, logits, counters,  \
-            ids, wts, gamma, T, H, E, k, renorm, scale);                                         \
+            ids, wts, gamma, T, H, E, o);                                                        \
     } while (0)
     if (x_dt == LOCUS_DT_F32 && w_dt == LOCUS_DT_F32) ROUTER_LAUNCH(float, float);
     else if (x_dt == LOCUS_DT_BF16 && w_dt == LOCUS_DT_BF16) ROUTER_LAUNCH(bf16, bf16);
@@ -193,94 +284,31 @@ extern "C" int locus_router_topk(const void* h, int x_dt, const void* wr, int w_
 // ---------------------------------------------------------------------------
 // Selection alone, from router logits that another kernel produced (the bfloat16 path computes
 // them on the tensor cores): one warp per token.  logits [T, E (+1)] float32; column E, when
-// has_gate, is the logit of the shared-expert gate.  Same softmax, selection and weights as above.
-// Softmax, selection and weights of one token by one warp.  lg: the token's logits; p: E floats of
-// shared memory of this warp; s_ids (or null): where the picks are also kept for the block.
-__device__ __forceinline__ void select_token(const float* __restrict__ lg, float* p, int t, int lane,
-                                             int* __restrict__ ids, float* __restrict__ wts,
-                                             float* __restrict__ gamma, int* s_ids, int E, int k, int has_gate,
-                                             int renorm, float scale) {
-    float mx = -INFINITY;
-    for (int x = lane; x < E; x += 32) {
-        const float v = lg[x];
-        p[x] = v;
-        mx = fmaxf(mx, v);
-    }
-    if (has_gate && lane == 0) gamma[t] = 1.0f / (1.0f + expf(-lg[E]));
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int x = lane; x < E; x += 32) {
-        const float v = expf(p[x] - mx);
-        p[x] = v;
-        sum += v;
-    }
-    sum = warp_sum(sum);
-    for (int x = lane; x < E; x += 32) p[x] = p[x] / sum;
-    __syncwarp();
-    float wsum = 0.f;
-    // After the butterfly every lane knows the pick; lane r keeps the probability of pick r, so that the
-    // weights go out with one store per lane at the end (up to 32 picks; beyond that they take the way
-    // through global memory).
-    const bool in_lanes = k <= 32;
-    float my_w = 0.f;
-    for (int r = 0; r < k; ++r) {
-        float best = -1.f;
-        int best_e = 0x7fffffff;
-        for (int x = lane; x < E; x += 32) {
-            const float v = p[x];
-            if (v > best) {
-                best = v;
-                best_e = x;
-            }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
-            if (ov > best || (ov == best && oe < best_e)) {
-                best = ov;
-                best_e = oe;
-            }
-        }
-        if (lane == r) my_w = best;
-        if (lane == 0) {
-            ids[t * k + r] = best_e;
-            if (s_ids != nullptr) s_ids[t * k + r] = best_e;
-            if (!in_lanes) wts[t * k + r] = best;
-            p[best_e] = -2.f;
-        }
-        wsum += best;
-        __syncwarp();
-    }
-    const float div = renorm ? wsum : 1.0f;
-    if (in_lanes) {
-        if (lane < k) wts[t * k + lane] = my_w / div * scale;
-    } else if (lane == 0) {
-        for (int r = 0; r < k; ++r) wts[t * k + r] = wts[t * k + r] / div * scale;
-    }
-}
-
+// has_gate, is the logit of the shared-expert gate.  Same scores, selection and weights as above.
 __global__ void __launch_bounds__(256) router_select_kernel(const float* __restrict__ logits, int ld,
                                                             int* __restrict__ ids, float* __restrict__ wts,
-                                                            float* __restrict__ gamma, int T, int E, int k,
-                                                            int has_gate, int renorm, float scale) {
+                                                            float* __restrict__ gamma, int T, int E,
+                                                            int has_gate, const RouteOpts o) {
     pdl_entry();
-    extern __shared__ float probs_all[];  // [warps][E]
+    extern __shared__ float probs_all[];  // [warps][2 E]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int t = blockIdx.x * (blockDim.x >> 5) + wid;
     if (t >= T) return;
-    select_token(logits + static_cast<size_t>(t) * ld, probs_all + wid * E, t, lane, ids, wts, gamma, nullptr, E, k,
-                 has_gate, renorm, scale);
+    select_token(logits + static_cast<size_t>(t) * ld, probs_all + wid * 2 * E, t, lane, ids, wts, gamma, nullptr, E,
+                 has_gate, o);
 }
 
 extern "C" int locus_router_select(const float* logits, int ld, int* ids, float* wts, float* gamma, int T, int E,
-                                   int k, int has_gate, int renorm, float scale, cudaStream_t stream) {
+                                   int k, int has_gate, int renorm, float scale, int score_fn,
+                                   const float* sel_bias, int n_group, int n_group_used, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (E <= 0 || k <= 0 || k > E || ld < E + (has_gate ? 1 : 0)) return LOCUS_ERR_UNSUPPORTED;
-    const size_t smem = sizeof(float) * 8 * E;
-    if (smem > 48 * 1024) return LOCUS_ERR_UNSUPPORTED;
-    locus_launch(router_select_kernel, ceil_div(T, 8), 256, smem, stream, logits, ld, ids, wts, gamma, T, E, k, has_gate,
-                 renorm, scale);
+    const RouteOpts o{k, renorm, score_fn, n_group, n_group_used, scale, sel_bias};
+    if (!route_opts_ok(o, E) || ld < E + (has_gate ? 1 : 0)) return LOCUS_ERR_UNSUPPORTED;
+    const size_t smem = sizeof(float) * 8 * 2 * E;
+    if (smem > 200 * 1024) return LOCUS_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    locus_launch(router_select_kernel, ceil_div(T, 8), 256, smem, stream, logits, ld, ids, wts, gamma, T, E, has_gate, o);
     return locus_launch_status();
 }
 
@@ -392,24 +420,25 @@ extern "C" int locus_moe_sort(const int* ids, int n_pairs, int E, int tile_m, in
 #define RS_WARPS 16   // a warp per token for up to 16 tokens
 __global__ void __launch_bounds__(32 * RS_WARPS) route_small_kernel(const float* __restrict__ logits, int ld,
                                                           int* __restrict__ ids, float* __restrict__ wts,
-                                                          float* __restrict__ gamma, int T, int E, int k, int has_gate,
-                                                          int renorm, float scale, int tile_m, int* __restrict__ counts,
+                                                          float* __restrict__ gamma, int T, int E, int has_gate,
+                                                          const RouteOpts o, int tile_m, int* __restrict__ counts,
                                                           int* __restrict__ offsets, int* __restrict__ sorted_pair,
                                                           int* __restrict__ pair_pos, int* __restrict__ tile_expert,
                                                           int* __restrict__ tile_row0, int* __restrict__ tile_rows,
                                                           int* __restrict__ n_tiles) {
     pdl_entry();
     pdl_trigger();
-    extern __shared__ float rs_smem[];  // probabilities [RS_WARPS][E], then the ints below
-    int* s_ids = reinterpret_cast<int*>(rs_smem + RS_WARPS * E);  // [T * k]
+    extern __shared__ float rs_smem[];  // scores [RS_WARPS][2 E], then the ints below
+    const int k = o.k;
+    int* s_ids = reinterpret_cast<int*>(rs_smem + RS_WARPS * 2 * E);  // [T * k]
     int* s_cnt = s_ids + T * k;                             // [E]
     int* s_off = s_cnt + E;                                 // [E + 1]
     int* s_tile = s_off + E + 1;                            // [E + 1]
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int n_pairs = T * k;
     for (int t = wid; t < T; t += RS_WARPS)
-        select_token(logits + static_cast<size_t>(t) * ld, rs_smem + wid * E, t, lane, ids, wts, gamma, s_ids, E, k,
-                     has_gate, renorm, scale);
+        select_token(logits + static_cast<size_t>(t) * ld, rs_smem + wid * 2 * E, t, lane, ids, wts, gamma, s_ids, E,
+                     has_gate, o);
     __syncthreads();
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int c = 0;
@@ -476,14 +505,18 @@ __global__ void __launch_bounds__(32 * RS_WARPS) route_small_kernel(const float*
 }
 
 extern "C" int locus_route_small(const float* logits, int ld, int* ids, float* wts, float* gamma, int T, int E,
-                                 int k, int has_gate, int renorm, float scale, int tile_m, int* counts,
+                                 int k, int has_gate, int renorm, float scale, int score_fn, const float* sel_bias,
+                                 int n_group, int n_group_used, int tile_m, int* counts,
                                  int* offsets, int* sorted_pair, int* pair_pos, int* tile_expert, int* tile_row0,
                                  int* tile_rows, int* n_tiles, cudaStream_t stream) {
     if (T <= 0) return 0;
-    if (E <= 0 || k <= 0 || k > E || ld < E + (has_gate ? 1 : 0) || tile_m <= 0) return LOCUS_ERR_UNSUPPORTED;
+    const RouteOpts o{k, renorm, score_fn, n_group, n_group_used, scale, sel_bias};
+    if (!route_opts_ok(o, E) || ld < E + (has_gate ? 1 : 0) || tile_m <= 0) return LOCUS_ERR_UNSUPPORTED;
     if (E > RS_MAX_E || static_cast<long long>(T) * k > RS_MAX_PAIRS) return LOCUS_ERR_UNSUPPORTED;
-    const size_t smem = sizeof(float) * RS_WARPS * E + sizeof(int) * (static_cast<size_t>(T) * k + 3 * E + 2);
-    locus_launch(route_small_kernel, 1, 32 * RS_WARPS, smem, stream, logits, ld, ids, wts, gamma, T, E, k, has_gate, renorm,
-                 scale, tile_m, counts, offsets, sorted_pair, pair_pos, tile_expert, tile_row0, tile_rows, n_tiles);
+    const size_t smem = sizeof(float) * RS_WARPS * 2 * E + sizeof(int) * (static_cast<size_t>(T) * k + 3 * E + 2);
+    if (smem > 48 * 1024)
+        cudaFuncSetAttribute(route_small_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    locus_launch(route_small_kernel, 1, 32 * RS_WARPS, smem, stream, logits, ld, ids, wts, gamma, T, E, has_gate, o,
+                 tile_m, counts, offsets, sorted_pair, pair_pos, tile_expert, tile_row0, tile_rows, n_tiles);
     return locus_launch_status();
 }

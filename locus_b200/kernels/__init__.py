@@ -669,6 +669,22 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
     _check(code, "attn_decode", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
 
+SCORE_FUNCTIONS = {"softmax": 0, "sigmoid": 1}
+
+
+def _route_rule(score_fn: str, sel_bias: Optional[torch.Tensor], n_group: int, n_group_used: int, n_experts: int,
+                what: str):
+    """The arguments that say how experts are chosen, checked: (score code, bias pointer, groups, groups used)."""
+    _need(score_fn in SCORE_FUNCTIONS, f"{what}: score function {score_fn!r} (known: {', '.join(SCORE_FUNCTIONS)})")
+    if sel_bias is not None:
+        _need(sel_bias.is_cuda and sel_bias.dtype == torch.float32 and sel_bias.is_contiguous()
+              and sel_bias.numel() == n_experts, f"{what}: the selection bias must be float32 [n_experts]")
+    _need(1 <= n_group <= 32 and n_experts % n_group == 0,
+          f"{what}: {n_group} groups must divide {n_experts} experts (at most 32 groups)")
+    _need(n_group == 1 or 1 <= n_group_used <= n_group, f"{what}: groups used must be within 1..{n_group}")
+    return I(SCORE_FUNCTIONS[score_fn]), _p(sel_bias), I(n_group), I(n_group_used)
+
+
 class RouterScratch:
     """Scratch of :func:`router_topk`: the router logits of a step and one counter per tile of
     8 tokens (zero between launches)."""
@@ -681,9 +697,12 @@ class RouterScratch:
 
 def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.Tensor],
                 ids: torch.Tensor, wts: torch.Tensor, gamma: Optional[torch.Tensor], *, top_k: int,
-                renorm: bool, scale: float = 1.0, scratch: Optional[RouterScratch] = None) -> None:
-    """Router: softmax over all experts, top-k by repeated arg-max, weights; and
-    gamma = sigmoid(w_gate . h) when the shared expert is gated.  All in float32.
+                renorm: bool, scale: float = 1.0, scratch: Optional[RouterScratch] = None, score_fn: str = "softmax",
+                sel_bias: Optional[torch.Tensor] = None, n_group: int = 1, n_group_used: int = 1) -> None:
+    """Router: scores of all experts (``score_fn``: softmax over them, or a sigmoid of each logit), top-k by
+    repeated arg-max, weights; and gamma = sigmoid(w_gate . h) when the shared expert is gated.  All in float32.
+    ``sel_bias`` [E] is added to the scores for the selection only; with ``n_group`` > 1 only the
+    ``n_group_used`` groups of experts with the best two-score sums are eligible.
     ``scratch`` must hold T tokens of E (+1 with a gate) logits (made on the fly when None)."""
     _cuda_c(h, "h")
     _cuda_c(w_router, "w_router")
@@ -703,7 +722,8 @@ def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.
     code = _lib("moe_route").locus_router_topk(
         _p(h), I(dtype_code(h.dtype)), _p(w_router), I(dtype_code(w_router.dtype)), _p(w_gate),
         I(dtype_code(w_gate.dtype) if w_gate is not None else 0), _p(scratch.logits), _p(scratch.counters),
-        _p(ids), _p(wts), _p(gamma), I(T), I(H), I(E), I(top_k), I(1 if renorm else 0), F(scale), _stream()
+        _p(ids), _p(wts), _p(gamma), I(T), I(H), I(E), I(top_k), I(1 if renorm else 0), F(scale),
+        *_route_rule(score_fn, sel_bias, n_group, n_group_used, E, "router_topk"), _stream()
     )
     _check(code, "router_topk", f"(H={H}, E={E}, k={top_k})")
 
@@ -728,9 +748,11 @@ def router_logits(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor) ->
 
 
 def router_select(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch.Tensor, wts: torch.Tensor,
-                  gamma: Optional[torch.Tensor], *, n_tokens: int, top_k: int, renorm: bool, scale: float = 1.0) -> None:
-    """Softmax over the first ``n_experts`` columns of ``logits``, top-k by repeated arg-max,
-    weights; gamma = sigmoid(column n_experts) when ``has_gate``."""
+                  gamma: Optional[torch.Tensor], *, n_tokens: int, top_k: int, renorm: bool, scale: float = 1.0,
+                  score_fn: str = "softmax", sel_bias: Optional[torch.Tensor] = None, n_group: int = 1,
+                  n_group_used: int = 1) -> None:
+    """Scores from the first ``n_experts`` columns of ``logits``, top-k by repeated arg-max,
+    weights (the rule of :func:`router_topk`); gamma = sigmoid(column n_experts) when ``has_gate``."""
     _need(logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1, "router_select: float32 logits")
     _i32(ids, "ids")
     _need(wts.dtype == torch.float32 and wts.numel() >= n_tokens * top_k and ids.numel() >= n_tokens * top_k,
@@ -739,7 +761,8 @@ def router_select(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: tor
         _need(gamma is not None and gamma.dtype == torch.float32 and gamma.numel() >= n_tokens, "router_select: gamma")
     code = _lib("moe_route").locus_router_select(
         _p(logits), I(logits.stride(0)), _p(ids), _p(wts), _p(gamma), I(n_tokens), I(n_experts), I(top_k),
-        I(1 if has_gate else 0), I(1 if renorm else 0), F(scale), _stream()
+        I(1 if has_gate else 0), I(1 if renorm else 0), F(scale),
+        *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "router_select"), _stream()
     )
     _check(code, "router_select", f"(E={n_experts}, k={top_k})")
 
@@ -772,7 +795,8 @@ def route_small_takes(n_tokens: int, top_k: int, n_experts: int) -> bool:
 
 def route_small(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch.Tensor, wts: torch.Tensor,
                 gamma: Optional[torch.Tensor], layout: ExpertLayout, *, n_tokens: int, top_k: int, renorm: bool,
-                scale: float = 1.0, tile_m: Optional[int] = None) -> None:
+                scale: float = 1.0, tile_m: Optional[int] = None, score_fn: str = "softmax",
+                sel_bias: Optional[torch.Tensor] = None, n_group: int = 1, n_group_used: int = 1) -> None:
     """``router_select`` followed by ``moe_sort`` in one launch, for batches that
     ``route_small_takes``: same picks, weights and layout."""
     _need(route_small_takes(n_tokens, top_k, n_experts), "route_small: batch too large")
@@ -789,7 +813,8 @@ def route_small(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch
         layout.tile_m = tile_m
     code = _lib("moe_route").locus_route_small(
         _p(logits), I(logits.stride(0)), _p(ids), _p(wts), _p(gamma), I(n_tokens), I(n_experts), I(top_k),
-        I(1 if has_gate else 0), I(1 if renorm else 0), F(scale), I(layout.tile_m), _p(layout.counts),
+        I(1 if has_gate else 0), I(1 if renorm else 0), F(scale),
+        *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "route_small"), I(layout.tile_m), _p(layout.counts),
         _p(layout.offsets), _p(layout.sorted_pair), _p(layout.pair_pos), _p(layout.tile_expert),
         _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _stream()
     )

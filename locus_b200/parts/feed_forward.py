@@ -55,10 +55,21 @@ class SparseMoe(FeedForward):
 
     def __init__(self, prefix: str, *, hidden: int, n_experts: int, top_k: int, norm_topk: bool,
                  expert_intermediate: int, shared_intermediate: int = 0, shared_gate: bool = True,
-                 weight_scale: float = 1.0) -> None:
+                 weight_scale: float = 1.0, score_fn: str = "softmax", selection_bias: bool = False,
+                 n_group: int = 1, n_group_used: int = 1) -> None:
+        """``score_fn``: "softmax" over all experts or "sigmoid" of each router logit; ``selection_bias``:
+        a float32 tensor ``<prefix>.gate.selection_bias`` [n_experts] is added to the scores for the
+        selection only; ``n_group`` > 1: group-limited routing with ``n_group_used`` groups (the
+        parameters of the reference's ``moe_select``, src/locus/model/llama.cpp:900-980)."""
         super().__init__(prefix)
         if not (1 <= top_k <= n_experts):
             raise ValueError(f"sparse_moe: top_k {top_k} must be within 1..{n_experts}")
+        if score_fn not in K.SCORE_FUNCTIONS:
+            raise ValueError(f"sparse_moe: score function {score_fn!r} (known: {', '.join(K.SCORE_FUNCTIONS)})")
+        if not (1 <= n_group <= 32) or n_experts % n_group or not (1 <= n_group_used <= n_group):
+            raise ValueError(f"sparse_moe: {n_group} groups ({n_group_used} used) do not fit {n_experts} experts")
+        self.score_fn, self.has_sel_bias = score_fn, bool(selection_bias)
+        self.n_group, self.n_group_used = int(n_group), int(n_group_used)
         self.hidden, self.E, self.k = int(hidden), int(n_experts), int(top_k)
         self.norm_topk, self.I, self.Is = bool(norm_topk), int(expert_intermediate), int(shared_intermediate)
         self.shared_gate = bool(shared_gate) and self.Is > 0
@@ -84,6 +95,8 @@ class SparseMoe(FeedForward):
         }
         if self.shared_gate:
             s["shared_gate"] = (1, self.hidden)
+        if self.has_sel_bias:
+            s["sel_bias"] = (self.E,)
         return s
 
     def sources(self):
@@ -96,6 +109,8 @@ class SparseMoe(FeedForward):
                                     e * self.hidden))
         if self.shared_gate:
             out.append(TensorSource(f"{p}.shared_expert_gate.weight", (1, self.hidden), "shared_gate"))
+        if self.has_sel_bias:
+            out.append(TensorSource(f"{p}.gate.selection_bias", (self.E,), "sel_bias", 0, "bias"))
         return out
 
     def kernel_modules(self, dtype):
@@ -111,6 +126,10 @@ class SparseMoe(FeedForward):
             lambda: K.RouterScratch(rt.max_tokens, self.E + 1, rt.device),
         )
         self._router_all = None
+        bias = self.params.get("sel_bias")
+        self._rule = dict(top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale, score_fn=self.score_fn,
+                          sel_bias=bias.float().contiguous() if bias is not None else None, n_group=self.n_group,
+                          n_group_used=self.n_group_used)
         r, g = self.params["router"], self.params.get("shared_gate")
         if (rt.dtype == torch.bfloat16 and r.dtype == torch.bfloat16 and self.hidden % 8 == 0
                 and (g is None or g.dtype == torch.bfloat16)):
@@ -139,15 +158,14 @@ class SparseMoe(FeedForward):
             K.router_logits(h, self._router_all, logits)
             if K.route_small_takes(T, self.k, self.E):
                 # a decode-sized batch: selection and the expert layout in one launch
-                K.route_small(logits, self.E, self.shared_gate, ids, wts, gamma, lay, n_tokens=T, top_k=self.k,
-                              renorm=self.norm_topk, scale=self.weight_scale, tile_m=tile)
+                K.route_small(logits, self.E, self.shared_gate, ids, wts, gamma, lay, n_tokens=T, tile_m=tile,
+                              **self._rule)
                 sorted_already = True
             else:
-                K.router_select(logits, self.E, self.shared_gate, ids, wts, gamma, n_tokens=T, top_k=self.k,
-                                renorm=self.norm_topk, scale=self.weight_scale)
+                K.router_select(logits, self.E, self.shared_gate, ids, wts, gamma, n_tokens=T, **self._rule)
         else:
             K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,
-                          top_k=self.k, renorm=self.norm_topk, scale=self.weight_scale, scratch=self._scratch)
+                          scratch=self._scratch, **self._rule)
         if self.observer is not None:
             self.observer(self.prefix, ids[:n_pairs].view(T, self.k), wts[:n_pairs].view(T, self.k))
         # The shared expert needs only h and gamma: for a few tokens, where no kernel fills the

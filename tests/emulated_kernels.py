@@ -161,25 +161,46 @@ def attn_decode(q, pool, out, *, seg_q0, seg_qn, seg_ctx, block_table, items, n_
           scale=scale)
 
 
-def router_topk(h, w_router, w_gate, ids, wts, gamma, *, top_k, renorm, scale=1.0, scratch=None):
+def _select(logits_row, top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used):
+    """The selection rule of csrc/moe_route.cu (select_token) for one token."""
+    E = logits_row.shape[0]
+    r = logits_row
+    if score_fn == "softmax":
+        e = torch.exp(r - r.max())
+        p = e / e.sum()
+    else:
+        p = 1.0 / (1.0 + torch.exp(-r))
+    sel = p.clone() if sel_bias is None else p + sel_bias.to(p.dtype).cpu()
+    sel = torch.where(torch.isnan(sel), torch.full_like(sel, -3.0e38), sel)
+    if n_group > 1:
+        per = E // n_group
+        gs = []
+        for g in range(n_group):
+            top2 = torch.sort(torch.cat([sel[g * per : (g + 1) * per], torch.full((2,), -1e30, dtype=sel.dtype)]), descending=True).values
+            gs.append(float(top2[0]) + (float(top2[1]) if per > 1 else 0.0))
+        keep = []
+        for _ in range(n_group_used):
+            keep.append(max((g for g in range(n_group) if g not in keep), key=lambda g: (gs[g], -g)))
+        for x in range(E):
+            if x // per not in keep:
+                sel[x] = -1e30
+    picked = []
+    for _ in range(top_k):
+        best = max((x for x in range(E) if x not in picked), key=lambda x: (float(sel[x]), -x))
+        picked.append(best)
+    wsum = sum(p[x] for x in picked) if renorm else 1.0
+    return picked, [float(p[x] / wsum * scale) for x in picked]
+
+
+def router_topk(h, w_router, w_gate, ids, wts, gamma, *, top_k, renorm, scale=1.0, scratch=None, score_fn="softmax",
+                sel_bias=None, n_group=1, n_group_used=1):
     T = h.shape[0]
     r = _f(h) @ _f(w_router).T
-    p = torch.softmax(r, dim=-1)
     for t in range(T):
-        sel = p[t].clone()
-        picked = []
-        for _ in range(top_k):
-            best = -1
-            for e in range(sel.shape[0]):
-                if e in picked:
-                    continue
-                if best < 0 or sel[e] > sel[best]:
-                    best = e
-            picked.append(best)
-        wsum = sum(p[t, e] for e in picked) if renorm else 1.0
+        picked, w = _select(r[t], top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used)
         for j, e in enumerate(picked):
             ids[t * top_k + j] = e
-            wts[t * top_k + j] = float(p[t, e] / wsum * scale)
+            wts[t * top_k + j] = w[j]
     if w_gate is not None:
         z = _f(h) @ _f(w_gate).reshape(-1)
         gamma[:T] = (1.0 / (1.0 + torch.exp(-z))).to(gamma.dtype)
@@ -190,22 +211,14 @@ def router_logits(h, w_all, logits):
     logits[:T, :n] = (_f(h) @ _f(w_all).T).to(logits.dtype)
 
 
-def router_select(logits, n_experts, has_gate, ids, wts, gamma, *, n_tokens, top_k, renorm, scale=1.0):
-    p = torch.softmax(_f(logits[:n_tokens, :n_experts]), dim=-1)
+def router_select(logits, n_experts, has_gate, ids, wts, gamma, *, n_tokens, top_k, renorm, scale=1.0,
+                  score_fn="softmax", sel_bias=None, n_group=1, n_group_used=1):
+    lg = _f(logits[:n_tokens, :n_experts])
     for t in range(n_tokens):
-        picked = []
-        for _ in range(top_k):
-            best = -1
-            for e in range(n_experts):
-                if e in picked:
-                    continue
-                if best < 0 or p[t, e] > p[t, best]:
-                    best = e
-            picked.append(best)
-        wsum = sum(p[t, e] for e in picked) if renorm else 1.0
+        picked, w = _select(lg[t], top_k, renorm, scale, score_fn, sel_bias, n_group, n_group_used)
         for j, e in enumerate(picked):
             ids[t * top_k + j] = e
-            wts[t * top_k + j] = float(p[t, e] / wsum * scale)
+            wts[t * top_k + j] = w[j]
     if has_gate:
         z = _f(logits[:n_tokens, n_experts])
         gamma[:n_tokens] = (1.0 / (1.0 + torch.exp(-z))).to(gamma.dtype)
@@ -216,9 +229,9 @@ def route_small_takes(n_tokens, top_k, n_experts):
 
 
 def route_small(logits, n_experts, has_gate, ids, wts, gamma, layout, *, n_tokens, top_k, renorm, scale=1.0,
-                tile_m=None):
+                tile_m=None, **rule):
     router_select(logits, n_experts, has_gate, ids, wts, gamma, n_tokens=n_tokens, top_k=top_k, renorm=renorm,
-                  scale=scale)
+                  scale=scale, **rule)
     moe_sort(ids, n_tokens * top_k, layout, tile_m)
 
 

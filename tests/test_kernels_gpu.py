@@ -9,6 +9,7 @@ import torch
 
 import emulated_kernels as EK
 import locus_b200.kernels as K
+import plain_qwen2moe as plain
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -270,6 +271,91 @@ def test_router_ties_go_to_lowest_index():
     wts = torch.zeros(6, device=DEV)
     K.router_topk(h.to(DEV), wr.to(DEV), None, ids, wts, None, top_k=3, renorm=False)
     assert ids.cpu().tolist() == [4, 0, 1, 4, 0, 1]
+
+
+@pytest.mark.parametrize("T,E,k,score_fn,bias,groups,used,renorm",
+                         [(5, 12, 3, "sigmoid", False, 1, 1, True), (9, 60, 4, "softmax", True, 1, 1, False),
+                          (16, 64, 8, "sigmoid", True, 8, 3, True), (40, 24, 5, "softmax", False, 4, 2, False),
+                          (3, 9, 9, "sigmoid", True, 3, 1, False)])
+def test_router_rule_score_function_bias_and_groups(T, E, k, score_fn, bias, groups, used, renorm):
+    """Every selection kernel with the other rules of the reference's moe_select: sigmoid scores, a bias that
+    enters the selection but not the weights, group-limited routing; against the twin and the plain function."""
+    g = torch.Generator().manual_seed(T * 100 + E)
+    logits = torch.randn(T, E + 1, generator=g) * 2
+    sel_bias = torch.randn(E, generator=g) * 0.5 if bias else None
+    rule = dict(top_k=k, renorm=renorm, scale=1.5, score_fn=score_fn, n_group=groups, n_group_used=used)
+    ref_ids, ref_w = torch.zeros(T * k, dtype=torch.int32), torch.zeros(T * k)
+    EK.router_select(logits, E, False, ref_ids, ref_w, None, n_tokens=T, sel_bias=sel_bias, **rule)
+    for t in range(T):
+        ids_p, w_p = plain.moe_select(logits[t, :E].double(), k, renorm, 1.5, score_fn,
+                                      sel_bias.double() if bias else None, groups, used)
+        assert ids_p == ref_ids[t * k : (t + 1) * k].tolist()
+        assert torch.allclose(torch.tensor([float(x) for x in w_p]), ref_w[t * k : (t + 1) * k], rtol=1e-5, atol=1e-7)
+    dev_bias = sel_bias.to(DEV) if bias else None
+    # selection alone
+    ids, wts = torch.full((T * k,), -1, dtype=torch.int32, device=DEV), torch.zeros(T * k, device=DEV)
+    K.router_select(logits.to(DEV), E, False, ids, wts, None, n_tokens=T, sel_bias=dev_bias, **rule)
+    assert torch.equal(ids.cpu(), ref_ids)
+    assert torch.allclose(wts.cpu(), ref_w, rtol=1e-5, atol=1e-7)
+    # selection + layout in one launch
+    if K.route_small_takes(T, k, E):
+        ids1, wts1 = torch.full((T * k,), -1, dtype=torch.int32, device=DEV), torch.zeros(T * k, device=DEV)
+        K.route_small(logits.to(DEV), E, False, ids1, wts1, None, K.ExpertLayout(T * k, E, 64, DEV), n_tokens=T,
+                      tile_m=8, sel_bias=dev_bias, **rule)
+        assert torch.equal(ids1, ids) and torch.equal(wts1, wts)
+    # the fused float32 router: logits = h . w^T with an identity-like weight reproduces the same logits
+    h = torch.zeros(T, E + 7)
+    h[:, :E] = logits[:, :E]
+    wr = torch.zeros(E, E + 7)
+    wr[:, :E] = torch.eye(E)
+    ids2, wts2 = torch.full((T * k,), -1, dtype=torch.int32, device=DEV), torch.zeros(T * k, device=DEV)
+    K.router_topk(h.to(DEV), wr.to(DEV), None, ids2, wts2, None, sel_bias=dev_bias, **rule)
+    assert torch.equal(ids2.cpu(), ref_ids)
+    assert torch.allclose(wts2.cpu(), ref_w, rtol=1e-5, atol=1e-7)
+    with pytest.raises(K.KernelError, match="groups"):
+        K.router_select(logits.to(DEV), E, False, ids, wts, None, n_tokens=T, top_k=k, renorm=renorm, n_group=E + 1)
+    with pytest.raises(K.KernelError, match="score function"):
+        K.router_select(logits.to(DEV), E, False, ids, wts, None, n_tokens=T, top_k=k, renorm=renorm, score_fn="relu")
+
+
+@pytest.mark.parametrize("score_fn", ["softmax", "sigmoid"])
+def test_router_selection_is_total_for_logits_that_are_no_numbers(score_fn):
+    """NaN and infinite router logits (a broken checkpoint, an overflow upstream) must still give k distinct
+    expert indices below E for every token: the indices address weights and shared memory downstream."""
+    T, E, k = 6, 20, 4
+    logits = torch.randn(T, E + 1, generator=torch.Generator().manual_seed(3))
+    logits[0, :E] = float("nan")
+    logits[1, 5] = float("inf")
+    logits[2, 7] = float("nan")
+    logits[3, :E] = float("-inf")
+    logits[4, 2], logits[4, 9] = float("inf"), float("-inf")
+    for kind in ("select", "small", "fused"):
+        ids, wts = torch.full((T * k,), -1, dtype=torch.int32, device=DEV), torch.zeros(T * k, device=DEV)
+        lay = K.ExpertLayout(T * k, E, 64, DEV)
+        if kind == "select":
+            K.router_select(logits.to(DEV), E, False, ids, wts, None, n_tokens=T, top_k=k, renorm=True, score_fn=score_fn)
+            K.moe_sort(ids, T * k, lay, 8)
+        elif kind == "small":
+            K.route_small(logits.to(DEV), E, False, ids, wts, None, lay, n_tokens=T, top_k=k, renorm=True, tile_m=8,
+                          score_fn=score_fn)
+        else:
+            h = torch.zeros(T, E + 4)
+            h[:, :E] = logits[:, :E]
+            wr = torch.zeros(E, E + 4)
+            wr[:, :E] = torch.eye(E)
+            K.router_topk(h.to(DEV), wr.to(DEV), None, ids, wts, None, top_k=k, renorm=True, score_fn=score_fn)
+            K.moe_sort(ids, T * k, lay, 8)
+        torch.cuda.synchronize()
+        got = ids.cpu().view(T, k)
+        assert int(got.min()) >= 0 and int(got.max()) < E, (kind, got)
+        for t in range(T):
+            assert len(set(got[t].tolist())) == k, (kind, t, got[t])
+        assert sorted(lay.sorted_pair.cpu().tolist()) == list(range(T * k)), kind
+        # the rows without bad numbers are untouched by their neighbours
+        ref_ids, ref_w = torch.zeros(k, dtype=torch.int32), torch.zeros(k)
+        EK.router_select(logits[5:6], E, False, ref_ids, ref_w, None, n_tokens=1, top_k=k, renorm=True, score_fn=score_fn)
+        assert got[5].tolist() == ref_ids.tolist()
+        assert torch.allclose(wts.cpu()[5 * k :], ref_w, rtol=1e-5, atol=1e-7)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
