@@ -132,7 +132,8 @@ def main(argv=None) -> int:
 
             with open(args.config, "r", encoding="utf-8") as f:
                 raw = json.load(f)
-            write_random_model(raw, args.random_weights, args.model, parse_dtype(args.dtype))
+            write_random_model(raw, args.random_weights, args.model, parse_dtype(args.dtype),
+                               device="cuda:0" if torch.cuda.is_available() else "cpu")
         chunk = 1 if args.no_batch_prefill else args.chunk
         conc = max(1, args.concurrent)
         eng = Engine.from_model_dir(args.model, dtype=args.dtype, ctx=args.ctx, page_tokens=args.page_tokens,

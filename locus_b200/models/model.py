@@ -67,10 +67,6 @@ class Model:
                 out.append((p, s))
         return out
 
-    def ignorable_tensor_names(self) -> List[str]:
-        """Tensors a checkpoint may hold that the model does not read."""
-        return ["lm_head.weight"] if getattr(self.head, "tied", False) else []
-
     def kernel_modules(self) -> List[str]:
         mods = {"sampling"}
         for p in self.all_parts():
@@ -103,8 +99,6 @@ class Model:
         from ..csrc import build
         build.ensure(self.kernel_modules())
         self.rt = rt
-        if getattr(self.head, "tied", False):
-            self.head.params["weight"] = self.embedding.params["table"]
         for p in self.all_parts():
             p.bind(rt)
 

@@ -57,9 +57,11 @@ def build_plan(cfg: Qwen2MoeConfig) -> ModelPlan:
         layers=layers,
         order=[LayerCall(l) for l in range(cfg.num_hidden_layers)],
         final_norm=PartSpec("rmsnorm", {"width": cfg.hidden_size, "eps": cfg.rms_norm_eps, "prefix": "model.norm"}),
-        head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size,
-                                 "tied": cfg.tie_word_embeddings, "prefix": "lm_head"}),
+        head=PartSpec("linear", {"vocab": cfg.vocab_size, "hidden": cfg.hidden_size, "prefix": "lm_head",
+                                 "tied_to": "model.embed_tokens.weight" if cfg.tie_word_embeddings else ""}),
         config=cfg,
+        # checkpoints of this family may carry the rotary tables, and a copy of the head even when it is tied
+        ignorable_tensors=("*.rotary_emb.inv_freq",) + (("lm_head.weight",) if cfg.tie_word_embeddings else ()),
     )
 
 

@@ -62,6 +62,9 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     config: Any = None
+    # checkpoint tensors (shell-style patterns) that files of this architecture may hold and the model
+    # does not read: left-overs of the format such as tables that are recomputed
+    ignorable_tensors: Tuple[str, ...] = ()
 
     def describe(self) -> Dict[str, Any]:
         return {

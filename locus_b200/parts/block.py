@@ -5,7 +5,8 @@ of the reference's forward (src/locus/model/llama.cpp:485-509).  The residual st
 float32 in every mode; the normed activations have the model's element type.
 
 ``Embedding``: x = table[token] (llama.cpp:450).  ``LmHead``: logits = W . h in float32,
-W being the embedding table when the head is tied (llama.cpp:292-297, 512-513).
+W being the embedding table when the head is tied (llama.cpp:292-297, 512-513): the head then
+names the embedding's tensor as the source of its weight.
 """
 from __future__ import annotations
 
@@ -60,19 +61,18 @@ class Embedding(Part):
 
 
 class LmHead(Part):
-    """``tied``: no tensor of its own; the model hands it the embedding table."""
+    """``tied_to``: the checkpoint tensor that is the head's weight when the head has none of its own
+    (the embedding table of a tied model); two parts that name the same tensor share one device copy."""
 
-    def __init__(self, prefix: str, *, vocab: int, hidden: int, tied: bool) -> None:
+    def __init__(self, prefix: str, *, vocab: int, hidden: int, tied_to: str = "") -> None:
         super().__init__(prefix)
-        self.vocab, self.hidden, self.tied = int(vocab), int(hidden), bool(tied)
+        self.vocab, self.hidden, self.tied_to = int(vocab), int(hidden), str(tied_to or "")
 
     def param_shapes(self):
-        return {} if self.tied else {"weight": (self.vocab, self.hidden)}
+        return {"weight": (self.vocab, self.hidden)}
 
     def sources(self):
-        if self.tied:
-            return []
-        return [TensorSource(self.prefix + ".weight", (self.vocab, self.hidden), "weight")]
+        return [TensorSource(self.tied_to or self.prefix + ".weight", (self.vocab, self.hidden), "weight")]
 
     def kernel_modules(self, dtype):
         return ["gemm_simt", "gemv"] + (["gemm_skinny", "gemm_tc"] if dtype == torch.bfloat16 else [])

@@ -12,12 +12,12 @@ tensors become int32.  In a float32 model every floating tensor is float32.
 
 The random-weights mode writes a model folder (config.json + model.safetensors) from a
 configuration and a seed: linear and embedding weights N(0, 0.02), biases N(0, 0.02), norm
-weights 1 + N(0, 0.01); each tensor has its own generator seeded by (seed, tensor name), so
-values do not depend on the order of generation.
+weights 1 + N(0, 0.01); every element is a function of (seed, tensor name, element index) alone
+(``random_init``), so values depend neither on the order of generation nor on the device that draws.
 """
 from __future__ import annotations
 
-import hashlib
+import fnmatch
 import json
 import os
 from typing import Dict, List, Tuple
@@ -64,47 +64,62 @@ def _param_dtype(model_dtype: torch.dtype, stored: List[torch.dtype]) -> torch.d
 
 def load_weights(model, source) -> None:
     """Fill every parameter of ``model`` from ``source`` (``names()``, ``info(name)``,
-    ``tensor(name)``), on the model's device."""
+    ``tensor(name)``), on the model's device.  Parts that name the same checkpoint tensor as the whole
+    of a parameter (a head tied to the embedding) share one device tensor."""
     wanted = model.tensor_sources()
-    by_name: Dict[str, Tuple[object, object]] = {}
+    by_name: Dict[str, List[Tuple[object, object]]] = {}
     for part, src in wanted:
-        by_name[src.name] = (part, src)
+        by_name.setdefault(src.name, []).append((part, src))
     have = set(source.names())
-    ignorable = set(model.ignorable_tensor_names())
+    ignorable = tuple(getattr(model.plan, "ignorable_tensors", ()))
     missing = sorted(n for n in by_name if n not in have)
-    unexpected = sorted(n for n in have if n not in by_name and n not in ignorable
-                        and not n.endswith("rotary_emb.inv_freq"))
+    unexpected = sorted(n for n in have if n not in by_name and not any(fnmatch.fnmatchcase(n, pat) for pat in ignorable))
     wrong = []
-    for n, (_, src) in by_name.items():
+    for n, users in by_name.items():
         if n in have:
             dt, shape = source.info(n)
-            if tuple(shape) != tuple(src.shape):
-                wrong.append(f"{n}: stored {tuple(shape)}, the model wants {tuple(src.shape)}")
-            elif dt not in _FLOAT16 + _FLOAT32 + _INTS:
+            for _, src in users:
+                if tuple(shape) != tuple(src.shape):
+                    wrong.append(f"{n}: stored {tuple(shape)}, the model wants {tuple(src.shape)}")
+            if dt not in _FLOAT16 + _FLOAT32 + _INTS:
                 wrong.append(f"{n}: element type {dt} is not loadable")
     if missing or unexpected or wrong:
-        raise WeightError(missing, unexpected, sorted(wrong))
+        raise WeightError(missing, unexpected, sorted(set(wrong)))
 
     # element type of each parameter from the storage types of its tensors
     stored: Dict[Tuple[int, str], List[torch.dtype]] = {}
     for part, src in wanted:
         stored.setdefault((id(part), src.param), []).append(source.info(src.name)[0])
     parts = {id(p): p for p, _ in wanted}
-    for (pid, pname), dts in stored.items():
-        part = parts[pid]
-        shape = part.param_shapes()[pname]
-        part.params[pname] = torch.empty(shape, dtype=_param_dtype(model.dtype, dts), device=model.device)
-    for part in model.all_parts():
-        for pname in part.param_shapes():
-            if pname not in part.params:
-                raise WeightError([f"(no tensor fills parameter {pname} of {part.prefix})"], [], [])
+
+    def whole(part, src) -> bool:
+        return src.row0 == 0 and tuple(src.shape) == tuple(part.param_shapes()[src.param])
+
+    shared: Dict[str, torch.Tensor] = {}   # checkpoint tensor -> the device tensor that holds all of it
+    filled = set()
     for part, src in wanted:
+        if whole(part, src) and src.name in shared:
+            part.params[src.param] = shared[src.name]
+            filled.add((id(part), src.param))
+            continue
+        key = (id(part), src.param)
+        if src.param not in part.params or key not in filled:
+            shape = part.param_shapes()[src.param]
+            part.params[src.param] = torch.empty(shape, dtype=_param_dtype(model.dtype, stored[key]),
+                                                 device=model.device)
+            filled.add(key)
         dest = part.params[src.param]
         flat = dest.view(-1, dest.shape[-1]) if dest.dim() >= 2 else dest
         t = source.tensor(src.name)
         n0 = src.shape[0]
         flat[src.row0 : src.row0 + n0].copy_(t.reshape(flat[src.row0 : src.row0 + n0].shape)
                                              .to(device=model.device, dtype=dest.dtype))
+        if whole(part, src):
+            shared[src.name] = dest
+    for part in model.all_parts():
+        for pname in part.param_shapes():
+            if (id(part), pname) not in filled:
+                raise WeightError([f"(no tensor fills parameter {pname} of {part.prefix})"], [], [])
     model.loaded = True
 
 
@@ -112,23 +127,7 @@ def load_weights(model, source) -> None:
 # random weights
 
 
-def _tensor_seed(seed: int, name: str) -> int:
-    h = hashlib.sha256(f"{seed}:{name}".encode()).digest()
-    return int.from_bytes(h[:8], "little") & 0x7FFFFFFFFFFFFFFF
-
-
-def random_tensor(seed: int, name: str, shape, init: str, dtype: torch.dtype, device="cpu") -> torch.Tensor:
-    """The random-weights mode's value of tensor ``name``: float32 draws, rounded to ``dtype``."""
-    g = torch.Generator(device=device)
-    g.manual_seed(_tensor_seed(seed, name))
-    t = torch.randn(tuple(shape), generator=g, dtype=torch.float32, device=device)
-    if init == "norm":
-        t = 1.0 + 0.01 * t
-    elif init in ("linear", "bias"):
-        t = 0.02 * t
-    else:
-        raise ValueError(f"unknown init kind {init!r}")
-    return t.to(dtype)
+from .random_init import random_tensor  # noqa: E402  (the draw itself: same bits on every device)
 
 
 class RandomSource:
@@ -149,8 +148,11 @@ class RandomSource:
         return random_tensor(self.seed, name, s.shape, s.init, self.dtype, self.device)
 
 
-def write_random_model(raw_config: dict, seed: int, out_dir: str, dtype: torch.dtype = torch.bfloat16) -> str:
-    """Write ``out_dir/config.json`` and ``out_dir/model.safetensors`` with seeded random weights."""
+def write_random_model(raw_config: dict, seed: int, out_dir: str, dtype: torch.dtype = torch.bfloat16,
+                       device="cpu") -> str:
+    """Write ``out_dir/config.json`` and ``out_dir/model.safetensors`` with seeded random weights.
+    ``device``: where the values are drawn (the same bits everywhere; a GPU draws a large model in
+    seconds where the host takes minutes)."""
     from ..config.base import arch_name_of
     from ..models.model import Model
 
@@ -160,12 +162,14 @@ def write_random_model(raw_config: dict, seed: int, out_dir: str, dtype: torch.d
     os.makedirs(out_dir, exist_ok=True)
     with open(os.path.join(out_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(raw_config, f, indent=1)
-    sources = [s for _, s in model.tensor_sources()]
-    by_name = {s.name: s for s in sources}
+    by_name = {}
+    for _, s in model.tensor_sources():
+        by_name.setdefault(s.name, s)   # a tensor that two parts name (a tied head) is written once
+    sources = list(by_name.values())
     write_safetensors(
         os.path.join(out_dir, "model.safetensors"),
         [(s.name, tuple(s.shape), dtype) for s in sources],
-        lambda n: random_tensor(seed, n, by_name[n].shape, by_name[n].init, dtype),
+        lambda n: random_tensor(seed, n, by_name[n].shape, by_name[n].init, dtype, device).cpu(),
         metadata={"format": "pt", "seed": str(seed)},
     )
     return out_dir

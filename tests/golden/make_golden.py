@@ -6,16 +6,25 @@ random qwen2moe models.
 
 Builds the reference's library on the CPU (CUDA and Vulkan switched off), compiles
 ref_harness.cpp against it, writes each case's weights (drawn exactly as the random-weights
-mode of the engine draws them: torch.randn seeded by sha256(seed:name)) in the tensor names
+mode of the engine draws them: locus_b200.weights.random_init, a function of seed, tensor name
+and element index) in the tensor names
 and layouts the reference reads (GGUF names, experts stacked [E][I][H]), runs the harness
 and stores config, seed, tensor list, tokens and logits.  tests/test_plain.py regenerates the
 same weights and compares the plain implementation with these logits.
 
-Cases: what the reference can express for this architecture -- every layer a mixture of
+Model cases: what the reference can express for this architecture -- every layer a mixture of
 experts, no renormalisation of the top-k weights, gated shared expert, q/k/v bias, head size
 hidden / heads, tied or untied head.
+
+Selection cases: the reference's ``moe_select`` (src/locus/model/llama.cpp:900-980) called directly on
+rows of router logits with the options that its qwen2moe loader fixes (renormalised top-k weights:
+llama.cpp:966-978; a weight scale; sigmoid scores; a selection bias; group-limited routing); the
+picked experts and their weights are stored and compared with ``plain.moe_select``.
+
+It also times the reference's CPU forward on the model cases (batched prefill of the case's tokens
+repeated to 128, then 32 greedy decode steps; scalar and avx2 backends) and stores the tokens per
+second under "timing": the only speed of the reference for this architecture that can be had here.
 """
-import hashlib
 import json
 import os
 import struct
@@ -44,11 +53,31 @@ CASES = [
 ]
 
 
+SELECT_CASES = [
+    # name, E, k, renorm, scoring, groups, groups used, bias, scale, rows
+    ("tiny-B router: 12 experts top-3, renormalised", 12, 3, True, "softmax", 1, 1, False, 1.0, 48),
+    ("8 experts top-2, renormalised, scale 2.5", 8, 2, True, "softmax", 1, 1, False, 2.5, 32),
+    ("60 experts top-4, plain softmax", 60, 4, False, "softmax", 1, 1, False, 1.0, 32),
+    ("16 experts top-4, sigmoid scores, selection bias, renormalised", 16, 4, True, "sigmoid", 1, 1, True, 1.0, 32),
+    ("32 experts top-6 in 3 of 8 groups, sigmoid, bias", 32, 6, True, "sigmoid", 8, 3, True, 1.5, 32),
+    ("24 experts top-5 in 2 of 4 groups, softmax", 24, 5, False, "softmax", 4, 2, False, 1.0, 32),
+]
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from locus_b200.weights.random_init import random_tensor  # noqa: E402
+
+
 def draw(seed, name, shape, init):
-    g = torch.Generator().manual_seed(int.from_bytes(hashlib.sha256(f"{seed}:{name}".encode()).digest()[:8], "little")
-                                      & 0x7FFFFFFFFFFFFFFF)
-    t = torch.randn(tuple(shape), generator=g, dtype=torch.float32)
-    return (1.0 + 0.01 * t) if init == "norm" else 0.02 * t
+    return random_tensor(seed, name, shape, init, torch.float32)
+
+
+def select_inputs(case_index, E, rows, has_bias):
+    """Router logits (and the bias) of a selection case: seeded draws, some rows with exact ties."""
+    logits = random_tensor(100 + case_index, "router_logits", (rows, E), "linear", torch.float32) * 100.0
+    logits[1, : min(E, 4)] = 0.75      # a tie among the first experts: the lowest index wins
+    logits[2, :] = 0.0                  # everything ties
+    bias = random_tensor(100 + case_index, "selection_bias", (E,), "linear", torch.float32) * 10.0 if has_bias else None
+    return logits, bias
 
 
 def tensor_list(cfg):
@@ -153,13 +182,54 @@ def main():
                 f.write(struct.pack("<I", len(dims)) + struct.pack(f"<{len(dims)}Q", *dims))
                 f.write(t.contiguous().numpy().astype("<f4").tobytes())
             f.write(struct.pack("<I", len(tokens)) + struct.pack(f"<{len(tokens)}i", *tokens))
-        out = subprocess.check_output([exe, path]).decode().split("\n")
+        out = subprocess.check_output([exe, "logits", path]).decode().split("\n")
         n, V = (int(x) for x in out[0].split())
         logits = [[float(x) for x in out[1 + i].split()] for i in range(n)]
         assert all(len(r) == V for r in logits)
         golden["cases"].append({"name": case["name"], "seed": case["seed"], "config": cfg, "tokens": tokens,
                                 "tensors": [[n, s, i] for n, s, i in tl], "logits": logits})
         print(f"{case['name']}: {n} positions x {V} logits")
+        # the reference's speed on this model: 128 prompt tokens in one batched prefill, 32 decode steps
+        long_tokens = (tokens * (128 // len(tokens) + 1))[:128]
+        tpath = os.path.join(build, "case_time.bin")
+        with open(path, "rb") as f:
+            blob = f.read()
+        with open(tpath, "wb") as f:
+            f.write(blob[: len(blob) - 4 - 4 * len(tokens)])
+            f.write(struct.pack("<I", len(long_tokens)) + struct.pack(f"<{len(long_tokens)}i", *long_tokens))
+        for backend in ("scalar", "avx2"):
+            best = None
+            for _ in range(3):
+                res = subprocess.check_output([exe, "time", tpath, backend, "32"]).decode().split()
+                if res[0] == "unavailable":
+                    break
+                n_pre, t_pre, n_dec, t_dec = int(res[0]), float(res[1]), int(res[2]), float(res[3])
+                cur = {"prefill_tokens": n_pre, "prefill_tok_s": n_pre / t_pre, "decode_tokens": n_dec,
+                       "decode_tok_s": n_dec / t_dec}
+                if best is None or cur["decode_tok_s"] > best["decode_tok_s"]:
+                    best = cur
+            if best is not None:
+                golden.setdefault("timing", []).append(dict(best, case=case["name"], backend=backend,
+                                                            threads=os.cpu_count()))
+                print(f"  {backend}: prefill {best['prefill_tok_s']:.0f} tok/s, decode {best['decode_tok_s']:.0f} tok/s")
+    golden["select"] = []
+    for ci, (name, E, k, renorm, scoring, groups, used, has_bias, scale, rows) in enumerate(SELECT_CASES):
+        logits, bias = select_inputs(ci, E, rows, has_bias)
+        path = os.path.join(build, "select.bin")
+        with open(path, "wb") as f:
+            f.write(struct.pack("<7I", E, k, int(renorm), 1 if scoring == "softmax" else 2, groups, used, int(has_bias)))
+            f.write(struct.pack("<f", scale))
+            if has_bias:
+                f.write(bias.numpy().astype("<f4").tobytes())
+            f.write(struct.pack("<I", rows))
+            f.write(logits.contiguous().numpy().astype("<f4").tobytes())
+        lines = [l.split() for l in subprocess.check_output([exe, "select", path]).decode().strip().split("\n")]
+        assert len(lines) == rows and all(len(l) == 2 * k for l in lines)
+        golden["select"].append({"name": name, "index": ci, "n_experts": E, "top_k": k, "renorm": renorm,
+                                 "score_fn": scoring, "n_group": groups, "n_group_used": used, "bias": has_bias,
+                                 "scale": scale, "rows": rows, "ids": [[int(x) for x in l[:k]] for l in lines],
+                                 "weights": [[float(x) for x in l[k:]] for l in lines]})
+        print(f"select: {name}: {rows} rows")
     with open(os.path.join(HERE, "golden.json"), "w") as f:
         json.dump(golden, f)
     print("wrote", os.path.join(HERE, "golden.json"))

@@ -68,17 +68,46 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: int = 0
     return out
 
 
-def moe_select(router_logits: torch.Tensor, top_k: int, norm_topk: bool, scale: float = 1.0):
-    """src/locus/model/llama.cpp:900-980 (softmax gating, no bias, one group): softmax over
-    all experts, k rounds of arg-max with strict '>' (ties to the lowest index), weight =
-    p / wsum * scale, wsum = sum of the picked p when renormalising, else 1.
+def moe_select(router_logits: torch.Tensor, top_k: int, norm_topk: bool, scale: float = 1.0,
+               score_fn: str = "softmax", sel_bias: Optional[torch.Tensor] = None, n_group: int = 1,
+               n_group_used: int = 1):
+    """src/locus/model/llama.cpp:900-980: scores = softmax over all experts (llama.cpp:903-904) or a
+    sigmoid of each logit (:905-909); selection scores = scores + bias (:913-918); with groups, a group's
+    score is the sum of its two best selection scores and all but the best ``n_group_used`` groups are
+    masked to -1e30 (:919-951); k rounds of arg-max with strict '>' (ties to the lowest index, :952-965);
+    weight = score / wsum * scale, wsum = sum of the picked scores when renormalising, else 1 (:966-978).
     One token: router_logits [E] -> (ids [k], weights [k]) in pick order."""
-    p = softmax(router_logits)
+    E = router_logits.shape[0]
+    p = softmax(router_logits) if score_fn == "softmax" else 1.0 / (1.0 + torch.exp(-router_logits))
     sel = p.clone()
+    if sel_bias is not None:
+        sel = sel + sel_bias.to(sel.dtype)
+    if n_group > 1:
+        per = E // n_group
+        gscore = []
+        for g in range(n_group):
+            top1 = top2 = -1e30
+            for e in range(g * per, (g + 1) * per):
+                v = float(sel[e])
+                if v > top1:
+                    top1, top2 = v, top1
+                elif v > top2:
+                    top2 = v
+            gscore.append(top1 + (top2 if per > 1 else 0.0))
+        keep: List[int] = []
+        for _ in range(n_group_used):
+            best = -1
+            for g in range(n_group):
+                if g not in keep and (best < 0 or gscore[g] > gscore[best]):
+                    best = g
+            keep.append(best)
+        for e in range(E):
+            if e // per not in keep:
+                sel[e] = -1e30
     picked: List[int] = []
     for _ in range(top_k):
         best = -1
-        for e in range(sel.shape[0]):
+        for e in range(E):
             if e in picked:
                 continue
             if best < 0 or sel[e] > sel[best]:
@@ -167,19 +196,27 @@ def attention_block(h: torch.Tensor, W: Dict[str, torch.Tensor], prefix: str, cf
     return o @ W[f"{prefix}.o_proj.weight"].T
 
 
-class _CastOnRead(dict):
+class _CastOnRead:
     """The checkpoint's tensors, converted to the working type when read (a large model converted
-    as a whole would not fit in memory)."""
+    as a whole would not fit in memory).  ``weights`` may be any mapping, also one that makes a
+    tensor only when it is asked for."""
 
     def __init__(self, weights, dtype):
-        super().__init__(weights)
+        self.weights = weights
         self.dtype = dtype
 
     def __getitem__(self, name):
-        return super().__getitem__(name).to(self.dtype)
+        return self.weights[name].to(self.dtype)
+
+    def __contains__(self, name):
+        return name in self.weights
 
     def get(self, name, default=None):
-        return self[name] if name in self else default
+        return self[name] if name in self.weights else default
+
+    def rows(self, name, idx):
+        """Rows ``idx`` of a matrix, without converting the rest of it."""
+        return self.weights[name][idx].to(self.dtype)
 
 
 def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
@@ -191,7 +228,7 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens: Sequence[int],
     ``forced_routing``: {"model.layers.N.mlp": [experts of token 0, of token 1, ...]}."""
     W = _CastOnRead(weights, dtype)
     eps = cfg["rms_norm_eps"]
-    x = W["model.embed_tokens.weight"][torch.tensor(list(tokens), dtype=torch.long)]
+    x = W.rows("model.embed_tokens.weight", torch.tensor(list(tokens), dtype=torch.long))
     for l in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{l}"
         h = rmsnorm(x, W[f"{p}.input_layernorm.weight"], eps)

@@ -213,3 +213,66 @@ def test_tied_head_tolerates_a_stored_head(tmp_path):
 
     load_weights(model, WithHead())
     assert model.loaded
+
+
+def test_tied_head_and_embedding_are_one_tensor_and_the_plan_says_what_to_ignore(tmp_path):
+    model = _cpu_model("B")
+    src = RandomSource(model, 1, torch.bfloat16)
+    assert src.names().count("model.embed_tokens.weight") == 1
+
+    class WithLeftovers:
+        def names(self):
+            return src.names() + ["lm_head.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
+
+        info, tensor = src.info, src.tensor
+
+    load_weights(model, WithLeftovers())
+    assert model.head.params["weight"].data_ptr() == model.embedding.params["table"].data_ptr()
+    assert model.param_bytes() == sum(t.numel() * 2 for _, s in {s.name: (0, s) for _, s in model.tensor_sources()}.items()
+                                      for t in [torch.empty(s[1].shape, device="meta")])
+    # an untied model has a head of its own, and a stored tensor that its plan does not name is an error
+    a = _cpu_model("A")
+    srca = RandomSource(a, 0, torch.bfloat16)
+
+    class Extra:
+        def names(self):
+            return srca.names() + ["model.layers.0.self_attn.rotary_emb.inv_freq", "model.extra"]
+
+        info, tensor = srca.info, srca.tensor
+
+    with pytest.raises(WeightError) as ei:
+        load_weights(a, Extra())
+    assert ei.value.unexpected == ["model.extra"]
+    load_weights(a, srca)
+    assert a.head.params["weight"].data_ptr() != a.embedding.params["table"].data_ptr()
+
+
+def test_random_draws_are_a_function_of_seed_name_and_index():
+    from locus_b200.weights import random_init as R
+
+    key = R.tensor_key(7, "some.tensor")
+    whole = R.normal_slice(key, 0, 5000)
+    parts = torch.cat([R.normal_slice(key, 0, 1), R.normal_slice(key, 1, 1233), R.normal_slice(key, 1234, 3766)])
+    assert torch.equal(whole, parts)                      # any cut, any order
+    assert not torch.equal(whole, R.normal_slice(R.tensor_key(7, "other.tensor"), 0, 5000))
+    u = R.uniform_slice(key, 0, 200000)
+    assert 0.0 < float(u.min()) and float(u.max()) < 1.0 and abs(float(u.mean()) - 0.5) < 0.005
+    z = R.normal_slice(key, 0, 200000)
+    assert abs(float(z.mean())) < 0.01 and abs(float(z.std()) - 1.0) < 0.01
+    assert abs(float((z.abs() < 1.0).double().mean()) - 0.6827) < 0.01 and float(z.abs().max()) > 3.5
+    # the logarithm made of exact operations agrees with the library's to the last bits
+    x = torch.cat([u[:1000], torch.tensor([2.0 ** -53, 1e-300, 0.02425, 0.999999, 7.5], dtype=torch.float64)])
+    assert float(((R._log(x) - torch.log(x)).abs() / torch.log(x).abs()).max()) < 1e-14
+    assert float(R._log(torch.ones(1, dtype=torch.float64))) == 0.0
+    # a tensor larger than one slice is the slices side by side
+    old, R.SLICE = R.SLICE, 1000
+    try:
+        t = R.random_tensor(3, "w", (7, 500), "linear", torch.float32)
+    finally:
+        R.SLICE = old
+    assert torch.equal(t, R.random_tensor(3, "w", (7, 500), "linear", torch.float32))
+    assert torch.equal(R.random_tensor(3, "w", (7, 500), "linear", torch.bfloat16), t.to(torch.bfloat16))
+    n = R.random_tensor(3, "n", (4000,), "norm", torch.float32)
+    assert abs(float(n.mean()) - 1.0) < 0.002 and abs(float(n.std()) - 0.01) < 0.002
+    with pytest.raises(ValueError, match="init kind"):
+        R.random_tensor(3, "w", (2,), "uniform", torch.float32)

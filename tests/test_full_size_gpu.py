@@ -49,7 +49,7 @@ class FullCase:
         from locus_b200.weights.loader import write_random_model
         import locus_b200.models  # noqa: F401
 
-        self.dir = write_random_model(FULL, 3, str(tmp / "full"), torch.bfloat16)
+        self.dir = write_random_model(FULL, 3, str(tmp / "full"), torch.bfloat16, device="cuda:0")
         self.cfg, self.weights = plain.load_folder(self.dir)
         self.tokens = {rid: random_tokens(n, FULL["vocab_size"], 40 + n) for rid, n in LENGTHS.items()}
         self.positions = {}

@@ -173,7 +173,7 @@ def test_attention_part_whole_then_in_portions(dtype, nh, nkv, hd, window):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_embedding_and_head_parts(dtype):
     emb = make_part("embedding", PartSpec("embedding", {"vocab": 331, "hidden": 56}), "e")
-    head = make_part("head", PartSpec("linear", {"vocab": 331, "hidden": 56, "tied": False}), "h")
+    head = make_part("head", PartSpec("linear", {"vocab": 331, "hidden": 56}), "h")
     We, Wh = fill(emb, dtype), fill(head, dtype, seed=2)
     toks = torch.tensor([0, 330, 17, 17, 5], dtype=torch.int32, device=DEV)
     x = torch.empty(5, 56, device=DEV)
@@ -183,5 +183,5 @@ def test_embedding_and_head_parts(dtype):
     logits = torch.empty(5, 331, device=DEV)
     head.forward(hrows.to(DEV), logits)
     close(logits, hrows.double() @ Wh["h.weight"].T, dtype, "head")
-    tied = make_part("head", PartSpec("linear", {"vocab": 331, "hidden": 56, "tied": True}), "t")
-    assert tied.sources() == [] and tied.param_shapes() == {}
+    tied = make_part("head", PartSpec("linear", {"vocab": 331, "hidden": 56, "tied_to": "e.weight"}), "t")
+    assert [s.name for s in tied.sources()] == ["e.weight"]  # the loader gives both parts one device tensor

@@ -5,6 +5,7 @@ sampling helpers, and the golden logits that the reference's own C++ code produc
 import json
 import math
 import os
+import sys
 
 import pytest
 import torch
@@ -143,15 +144,39 @@ def test_golden_logits_of_the_reference():
         pytest.skip("no golden file committed")
     with open(path) as f:
         golden = json.load(f)
+    from locus_b200.weights.random_init import random_tensor
+
     for case in golden["cases"]:
         cfg = case["config"]
-        W = {}
-        import hashlib
-        for name, shape, init in case["tensors"]:
-            g = torch.Generator().manual_seed(int.from_bytes(hashlib.sha256(f"{case['seed']}:{name}".encode()).digest()[:8], "little") & 0x7FFFFFFFFFFFFFFF)
-            t = torch.randn(tuple(shape), generator=g, dtype=torch.float32)
-            W[name] = (1.0 + 0.01 * t) if init == "norm" else 0.02 * t
+        W = {name: random_tensor(case["seed"], name, shape, init, torch.float32) for name, shape, init in case["tensors"]}
         ref = torch.tensor(case["logits"], dtype=torch.float64)
         got = plain.forward(cfg, W, case["tokens"], torch.float32)
         scale = float(ref.abs().max())
         assert float((got.double() - ref).abs().max()) <= 2e-5 * scale, case["name"]
+
+
+def test_golden_selections_of_the_reference():
+    """The reference's own moe_select (src/locus/model/llama.cpp:900-980), called directly by
+    tests/golden/ref_harness.cpp with the options its qwen2moe loader fixes: renormalised weights
+    (tiny-B's norm_topk_prob), a weight scale, sigmoid scores, a selection bias, groups."""
+    path = os.path.join(HERE, "golden", "golden.json")
+    if not os.path.isfile(path):
+        pytest.skip("no golden file committed")
+    with open(path) as f:
+        golden = json.load(f)
+    sys.path.insert(0, os.path.join(HERE, "golden"))
+    from make_golden import select_inputs
+
+    assert len(golden["select"]) >= 6
+    for case in golden["select"]:
+        E, k = case["n_experts"], case["top_k"]
+        logits, bias = select_inputs(case["index"], E, case["rows"], case["bias"])
+        for r in range(case["rows"]):
+            ids, w = plain.moe_select(logits[r], k, case["renorm"], case["scale"], case["score_fn"], bias,
+                                      case["n_group"], case["n_group_used"])
+            assert ids == case["ids"][r], (case["name"], r)
+            ref = torch.tensor(case["weights"][r], dtype=torch.float64)
+            got = torch.tensor([float(x) for x in w], dtype=torch.float64)
+            assert float((got - ref).abs().max()) <= 2e-6 * max(1.0, float(ref.abs().max())), (case["name"], r)
+            if case["renorm"]:
+                assert abs(float(got.sum()) - case["scale"]) < 1e-5

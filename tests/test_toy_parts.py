@@ -75,7 +75,7 @@ def toy_plan(cfg):
                      embedding=PartSpec("embedding", {"vocab": cfg["vocab"], "hidden": H, "prefix": "toy.embed"}),
                      layers=layers, order=order,
                      final_norm=PartSpec("rmsnorm", {"width": H, "eps": cfg["eps"], "prefix": "toy.norm"}),
-                     head=PartSpec("linear", {"vocab": cfg["vocab"], "hidden": H, "tied": True, "prefix": "toy.head"}),
+                     head=PartSpec("linear", {"vocab": cfg["vocab"], "hidden": H, "tied_to": "toy.embed.weight", "prefix": "toy.head"}),
                      config=cfg)
 
 

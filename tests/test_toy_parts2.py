@@ -129,7 +129,7 @@ def toy2_plan(cfg):
                      embedding=PartSpec("embedding", {"vocab": cfg["vocab"], "hidden": H, "prefix": "toy2.embed"}),
                      layers=layers, order=[LayerCall(i) for i in range(4)],
                      final_norm=PartSpec("rmsnorm", {"width": H, "eps": cfg["eps"], "prefix": "toy2.norm"}),
-                     head=PartSpec("linear", {"vocab": cfg["vocab"], "hidden": H, "tied": False, "prefix": "toy2.head"}),
+                     head=PartSpec("linear", {"vocab": cfg["vocab"], "hidden": H, "prefix": "toy2.head"}),
                      config=cfg)
 
 
