@@ -401,53 +401,238 @@ def test_pool_sized_by_a_share_of_free_memory(tmp_path_factory):
         Engine.from_model_dir(c.dir, dtype="bfloat16", kv_fraction=1.5)
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_trace_run_program(case, dtype, tmp_path):
-    """bin/trace_run as a program: a mixed trace with a pool of 4 x 64-token pages short of
-    what all requests together need, so pages are used again."""
-    if case.name == "C":
-        pytest.skip("one windowed and two plain configurations are enough for the program test")
-    out = tmp_path / "out"
-    rids = list(case.tokens)[:4]
-    lens = {r: len(case.tokens[r]) for r in rids}
-    max_tokens = sum(sorted((-(-n // 64) * 64 for n in lens.values()), reverse=True)[:2])
-    steps, fed = [], {}
-    # two requests at a time, portions beside single tokens
-    pairs = [rids[:2], rids[2:]]
-    step_no = 0
-    lines = []
-    expect = {}
-    for pair in pairs:
-        live = list(pair)
-        while live:
-            entries, end = [], []
-            for j, rid in enumerate(list(live)):
-                a = fed.get(rid, 0)
-                n = min(lens[rid] - a, 1 if (step_no + j) % 3 == 0 else 11)
-                want = list(range(n)) if n <= 2 else [0, n - 1]
-                entries.append({"id": rid, "tokens": case.tokens[rid][a : a + n], "want": want})
-                expect.setdefault(step_no, []).extend((rid, a + w) for w in want)
-                fed[rid] = a + n
-                if fed[rid] == lens[rid]:
-                    end.append(rid)
-                    live.remove(rid)
-            lines.append(json.dumps({"step": step_no, "entries": entries, "end": end}))
-            step_no += 1
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", case.dir, "--dtype", dtype,
-                           "--out", str(out), "--max-tokens", str(max_tokens)], input="\n".join(lines) + "\n",
-                          capture_output=True, text=True, timeout=600)
-    assert proc.returncode == 0, proc.stderr[-2000:]
-    assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(step_no)]
+def replay_program(case, dtype, steps, out_dir, *, max_tokens, page_tokens=64, max_live=4, extra=()):
+    """Run ``steps`` (lists of (request, n new tokens), every fed position wanted) through bin/trace_run as a
+    program.  Returns ({rid: [T, V] logits}, returncode, stderr) and leaves the engine's expert choices in
+    ``case.routed`` as ``run_trace`` does."""
     import numpy as np
+
+    lines, layout, fed = [], [], {}
+    for no, step in enumerate(steps):
+        entries, end, spans = [], [], []
+        for rid, n in step:
+            a = fed.get(rid, 0)
+            base = rid.split("/")[-1]
+            entries.append({"id": rid, "tokens": case.tokens[base][a : a + n], "want": list(range(n))})
+            spans.append((rid, a, n))
+            fed[rid] = a + n
+            if fed[rid] == len(case.tokens[base]):
+                end.append(rid)
+        lines.append(json.dumps({"step": no, "entries": entries, "end": end}))
+        layout.append(spans)
+    dt_name = "float32" if dtype == torch.float32 else "bfloat16"
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", case.dir, "--dtype", dt_name, "--out",
+           str(out_dir), "--max-tokens", str(max_tokens), "--page-tokens", str(page_tokens), "--max-live", str(max_live),
+           "--dump-routing", *extra]
+    proc = subprocess.run(cmd, input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=900)
+    if proc.returncode != 0:
+        return None, proc.returncode, proc.stderr
+    assert [l for l in proc.stdout.split("\n") if l.startswith("done")] == [f"done {i}" for i in range(len(steps))]
     V = case.cfg["vocab_size"]
-    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
-    for s, wants in expect.items():
-        arr = torch.from_numpy(np.fromfile(out / f"{s}.f32", dtype="<f4").reshape(-1, V).copy())
-        assert arr.shape[0] == len(wants)
-        for row, (rid, pos) in enumerate(wants):
-            ref = case.ref(rid)
-            if pos in case.near_ties(rid, NEAR_TIE[tdt]):
-                continue  # either expert is right there; the program cannot tell us which it took
-            scale = float(ref.abs().max())
-            err = float((arr[row].double() - ref[pos]).abs().max())
-            assert err <= TOL[tdt][0] * scale, f"step {s} {rid}@{pos}: {err:.3e}"
+    got, routed = {}, {}
+    for no, spans in enumerate(layout):
+        arr = torch.from_numpy(np.fromfile(os.path.join(str(out_dir), f"{no}.f32"), dtype="<f4").reshape(-1, V).copy())
+        with open(os.path.join(str(out_dir), f"{no}.route.json")) as f:
+            route = json.load(f)
+        assert arr.shape[0] == sum(n for _, _, n in spans)
+        row = 0
+        for rid, a, n in spans:
+            got.setdefault(rid, []).append(arr[row : row + n])
+            for prefix, ids in route.items():
+                d = routed.setdefault(rid, {}).setdefault(prefix, {})
+                for i in range(n):
+                    d[a + i] = ids[row + i]
+            row += n
+    case.routed = routed
+    return {rid: torch.cat(parts) for rid, parts in got.items()}, 0, proc.stderr
+
+
+def check_program(case, got, dtype, what):
+    """``check`` for request ids of the form <mode>/<request>: same tokens, same oracle."""
+    tol_max, tol_mean = TOL[dtype]
+    for rid, lg in got.items():
+        base = rid.split("/")[-1]
+        assert lg.shape[0] == len(case.tokens[base]), f"{what} {rid}: {lg.shape[0]} rows"
+        ref, _ = case.ref_following(base, case.routed.get(rid), NEAR_TIE[dtype])
+        scale = float(ref.abs().max())
+        err = (lg.double() - ref).abs()
+        assert torch.isfinite(lg).all(), f"{what} {case.name}/{rid}: logits are not finite"
+        assert float(err.max()) <= tol_max * scale, (
+            f"{what} {case.name}/{rid}: max error {float(err.max()):.3e} > {tol_max * scale:.3e}; first position "
+            f"above the bound: {int((err.max(dim=1).values > tol_max * scale).nonzero()[0])}")
+        assert float(err.mean()) <= tol_mean * scale, f"{what} {case.name}/{rid}: mean error {float(err.mean()):.3e}"
+
+
+def four_modes(case):
+    """The four ways of replaying the same requests, one after the other in one trace: whole; most of it in one step
+    and the last 32 tokens one by one; portions of changing size down to two tokens; mixed, up to four live."""
+    rids = list(case.tokens)
+    steps = [[("whole/" + r, len(case.tokens[r]))] for r in rids]
+    for r in rids:
+        n = len(case.tokens[r])
+        head = max(0, n - 32)
+        if head:
+            steps.append([("tail/" + r, head)])
+        steps += [[("tail/" + r, 1)]] * (n - head)
+    sizes = [2, 16, 3, 17, 2, 31, 64, 5, 2, 15, 33, 1, 2, 48]
+    for r in rids:
+        a, i = 0, 0
+        while a < len(case.tokens[r]):
+            n = min(sizes[i % len(sizes)], len(case.tokens[r]) - a)
+            steps.append([("cut/" + r, n)])
+            a, i = a + n, i + 1
+    steps += [[("mixed/" + r, n) for r, n in step] for step in mixed_steps(case)]
+    return steps
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_run_program_in_four_modes(case, dtype, tmp_path):
+    """bin/trace_run as a program (its own process, the engine's model, step function, cache and kernels): the
+    four ways of cutting in one trace, in a pool that holds just the four largest requests, so that every page
+    is used again and again; pages of 64 tokens, and of 16 for the configuration with the window."""
+    if case.name == "C" and dtype == torch.float32:
+        pytest.skip("the windowed configuration replays in bfloat16; A and B in both element types")
+    P = 16 if case.name == "C" else 64
+    lens = sorted((len(t) for t in case.tokens.values()), reverse=True)
+    max_tokens = sum(-(-n // P) * P for n in lens[:4])
+    got, code, err = replay_program(case, dtype, four_modes(case), tmp_path / "out", max_tokens=max_tokens, page_tokens=P)
+    assert code == 0, err[-2000:]
+    assert len(got) == 4 * len(case.tokens)
+    check_program(case, got, dtype, "trace_run")
+
+
+def test_trace_run_program_options_and_refusals(tmp_path_factory):
+    """Pages of 16 tokens with two live requests; a pool that runs out ends the program with a message and 2,
+    as does a third live request when --max-live is 2."""
+    case = Case("A", tmp_path_factory.mktemp("models_tr"))
+    r = list(case.tokens)
+    n3, n4 = len(case.tokens[r[3]]), len(case.tokens[r[4]])
+    steps = [[(r[3], 30), (r[4], 2)], [(r[3], n3 - 30), (r[4], 100)], [(r[4], n4 - 102), (r[2], len(case.tokens[r[2]]))]]
+    need = -(-n3 // 16) * 16 + -(-n4 // 16) * 16
+    out = tmp_path_factory.mktemp("trace_out")
+    got, code, err = replay_program(case, torch.float32, steps, out / "ok", max_tokens=need, page_tokens=16, max_live=2)
+    assert code == 0, err[-2000:]
+    check_program(case, got, torch.float32, "trace_run, pages of 16")
+    got, code, err = replay_program(case, torch.float32, steps, out / "short", max_tokens=need - 16, page_tokens=16,
+                                    max_live=2)
+    assert code == 2 and "out of cache pages" in err
+    three = [[(r[0], 2), (r[1], 2), (r[2], 2)]]
+    got, code, err = replay_program(case, torch.float32, three, out / "live", max_tokens=256, page_tokens=16, max_live=2)
+    assert code == 2 and "--max-live 2" in err
+
+
+def _sampled(eng, prompts_and_seeds, n_new, sp, watch):
+    """Submit the requests in order and run; returns the watched request's tokens and its record."""
+    ids = [eng.submit(p, n_new, sp, seed) for p, seed in prompts_and_seeds]
+    eng.run_to_completion()
+    recs = [eng.get(i) for i in ids]
+    assert all(r.status.value == "done" for r in recs), [r.error for r in recs]
+    out = (list(recs[watch].generated), recs[watch].preemptions)
+    for i in ids:
+        eng.release(i)
+    assert eng.cache.free_pages() == eng.cache.total_pages()
+    return out
+
+
+def test_sampled_tokens_do_not_depend_on_batching_chunking_or_preemption(tmp_path_factory):
+    """tiny-B's workload: 24 samples at temperature 0.8 with seed 1.  The same request gives the same tokens alone,
+    beside three others, with its prompt cut into portions of 16, and after it was preempted and recomputed: the
+    draw is keyed by (seed, index of the generated token) and the logits by nothing but the request's own tokens."""
+    from locus_b200.engine.engine import Engine
+    from locus_b200.sampling.sampler import SamplingParams
+
+    case = Case("B", tmp_path_factory.mktemp("models_smp"))
+    sp = SamplingParams(temperature=0.8)
+    r = list(case.tokens)
+    mine = case.tokens[r[3]][:41]
+    others = [case.tokens[r[5]][:60], case.tokens[r[4]][:30], case.tokens[r[2]][:25]]
+
+    def engine(**kw):
+        args = dict(dtype="float32", ctx=1024, page_tokens=16, max_batch_tokens=256, chunk=256, max_running=4,
+                    decode_headroom=0)
+        args.update(kw)
+        return Engine.from_model_dir(case.dir, **args)
+
+    alone, _ = _sampled(engine(), [(mine, 1)], 24, sp, 0)
+    assert len(alone) == 24 and len(set(alone)) > 4   # sampled, not a constant
+    greedy, _ = _sampled(engine(), [(mine, 1)], 24, SamplingParams(), 0)
+    assert greedy != alone
+    beside, _ = _sampled(engine(), [(others[0], 7), (mine, 1), (others[1], 8), (others[2], 9)], 24, sp, 1)
+    assert beside == alone
+    chunked, _ = _sampled(engine(max_batch_tokens=32, chunk=16), [(others[1], 5), (mine, 1)], 24, sp, 1)
+    assert chunked == alone
+    # a pool of 8 pages: the two requests cannot both finish in it; the newest (ours) is preempted and recomputed
+    small = engine(ctx=8 * 16, max_batch_tokens=32, chunk=16)
+    again, n_pre = _sampled(small, [(others[0], 7), (mine, 1)], 24, sp, 1)
+    assert n_pre > 0 and small.sched.counters["failed"] == 0
+    assert again == alone
+    other_seed, _ = _sampled(engine(), [(mine, 2)], 24, sp, 0)
+    assert other_seed != alone
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_released_midway_and_fed_again_from_the_start(case, dtype):
+    """What preemption does to a request (src/locus/engine/engine.cpp:230-239 of the reference): its pages go back
+    mid-way, others take them, later it is fed again from position 0 on pages that others have used (poisoned with
+    NaN in between).  Every position's logits of every feeding against the plain implementation."""
+    from locus_b200.engine.step import StepEntry
+
+    rids = list(case.tokens)
+    victim, other, third = rids[-1], rids[-2], rids[-3]
+    nv, no, nt = (len(case.tokens[x]) for x in (victim, other, third))
+    P = 16
+    runner, cache = make_runner(case, dtype, page_tokens=P, n_pages=-(-nv // P) + -(-no // P))
+    cut = (2 * nv) // 3
+    seen = []
+    for part in runner.model.all_parts():
+        if hasattr(part, "observer"):
+            part.observer = lambda prefix, ids, wts: seen.append((prefix, ids.cpu().tolist()))
+    feedings = {}   # name -> (request, {position: logits row}, {prefix: {position: experts}})
+
+    def feed(name, rid, seq, a, n):
+        seen.clear()
+        assert cache.ensure_capacity(seq, n), f"out of pages feeding {name}"
+        lg = runner.step([StepEntry(seq, case.tokens[rid][a : a + n], list(range(n)))]).float().cpu()
+        _, rows, routed = feedings.setdefault(name, (rid, {}, {}))
+        for i in range(n):
+            rows[a + i] = lg[i].clone()
+        for prefix, ids in seen:
+            routed.setdefault(prefix, {}).update({a + i: ids[i] for i in range(n)})
+
+    v = cache.open("victim")
+    feed("first", victim, v, 0, cut // 2)
+    o = cache.open("other")
+    feed("other", other, o, 0, no // 2)
+    feed("first", victim, v, cut // 2, cut - cut // 2)       # the victim is two thirds through ...
+    held = v.pages_held(0)
+    cache.release(v)                                          # ... and loses everything
+    cache.check_invariants()
+    feed("other", other, o, no // 2, no - no // 2)            # the other grows into the freed pages
+    t = cache.open("third")
+    feed("third", third, t, 0, nt)
+    cache.release(t)
+    v = cache.open("victim")                                  # readmitted: from position 0, in portions, then token by token
+    a = 0
+    for n in (cut // 3, 2, cut - cut // 3 - 2):
+        feed("again", victim, v, a, n)
+        a += n
+    cache.release(o)
+    while a < nv:
+        n = 1 if nv - a <= 8 else min(19, nv - a - 8)
+        feed("again", victim, v, a, n)
+        a += n
+    assert held > 0
+    cache.release(v)
+    assert cache.free_pages() == cache.total_pages()
+    cache.check_invariants()
+    tol_max, tol_mean = TOL[dtype]
+    for name, (rid, rows, routed) in feedings.items():
+        ref, _ = case.ref_following(rid, routed, NEAR_TIE[dtype])
+        places = sorted(rows)
+        assert places == list(range(len(places))) and (name == "first") == (len(places) < len(case.tokens[rid]))
+        got = torch.stack([rows[p] for p in places]).double()
+        assert torch.isfinite(got).all(), f"{name}: logits are not finite (a stale or poisoned page was read)"
+        err = (got - ref[: len(places)]).abs()
+        scale = float(ref.abs().max())
+        assert float(err.max()) <= tol_max * scale, f"{name}: max error {float(err.max()):.3e} at {int(err.max(dim=1).values.argmax())}"
+        assert float(err.mean()) <= tol_mean * scale, name
