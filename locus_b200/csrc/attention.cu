@@ -36,6 +36,21 @@ struct AttnArgs {
 #define CHUNK_TK 32
 #define DEC_SPLIT 128
 
+// Error word of this module: set by a kernel that was launched with arguments that do not fit the batch it
+// finds on the device (1: max_splits does not cover the longest context of a decode step); the kernel still
+// ends in order and leaves its counters zero, but the output of the affected requests is incomplete.
+__device__ int g_attn_error = 0;
+
+extern "C" int locus_attn_error() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_attn_error, sizeof(int)) != cudaSuccess) return -1;
+    if (v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_attn_error, &zero, sizeof(int));
+    }
+    return v;
+}
+
 template <typename T>
 __device__ __forceinline__ const T* kv_row(const AttnArgs& a, const int* table, int t, int kvh,
                                             int which) {
@@ -213,6 +228,11 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     const int k1 = min(p, (split + 1) * DEC_SPLIT - 1);  // inclusive
     const int tid = threadIdx.x;
     const size_t part = (static_cast<size_t>(item) * a.nh + h) * a.max_splits + split;
+    // The grid has max_splits blocks per (request, head).  If the caller's max_splits does not reach the split of
+    // position p, the keys beyond it are not read: say so, and count and merge only the splits that exist, so that
+    // the counter still returns to zero.
+    const bool short_grid = p / DEC_SPLIT >= a.max_splits;
+    if (short_grid && split == 0 && h == 0 && tid == 0) atomicExch(&g_attn_error, 1);
     if (k0 > k1) return;  // a split without keys: neither written nor read
     const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
     for (int d = tid; d < hd; d += 128)
@@ -311,7 +331,7 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
     // The block that finishes last among the splits of this (request, head) merges them: a counter per
     // (request, head), zero before the launch and zero again after it.  The merge adds the splits in
     // ascending order whichever block runs it.
-    const int s0 = t_lo / DEC_SPLIT, s1 = p / DEC_SPLIT;  // the splits that hold keys: all of them count
+    const int s0 = t_lo / DEC_SPLIT, s1 = min(p / DEC_SPLIT, a.max_splits - 1);  // the splits that hold keys: all of them count
     __shared__ int last_sh;
     __syncthreads();  // every thread's partial results are written ...
     if (tid == 0) {

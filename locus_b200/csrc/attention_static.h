@@ -28,6 +28,11 @@
 //    that completes leaves them zero.  Because the arrays are shared, two calls whose
 //    kernels can overlap on the GPU (different streams, or different host threads) race;
 //    order them on one stream or with events.
+//  * max_splits must cover the longest context of the batch (longest position / 128 + 1).  The context
+//    lengths live on the device, so the host cannot check this; a kernel that finds a longer context
+//    reads only the keys that its splits cover, sets the module's error word (locus_attn_error()
+//    returns 1 and clears it; the read synchronises) and still leaves the counters zero, so later
+//    calls are not affected.  The output of that call is incomplete and must be discarded.
 //  * It calls no cudaMalloc / cudaFree and no allocating library routine; inputs and outputs
 //    are the caller's.
 #pragma once
@@ -50,6 +55,9 @@ int locus_attn_decode_static(const void* q, int dt, const void* pool, void* out,
                              int table_stride, const int* items, int n_items, int nh, int nkv, int hd,
                              int page_tokens, int window, float scale, int max_splits,
                              cudaStream_t stream);
+
+// 0, or the code that a kernel of this module recorded since the last call (then cleared).
+int locus_attn_error(void);
 
 #ifdef __cplusplus
 }

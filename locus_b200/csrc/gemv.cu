@@ -123,7 +123,7 @@ __device__ __forceinline__ void gemv_body(const GemvArgs& a, const TW* __restric
 }
 
 template <typename TX, typename TW, bool DUAL>
-__global__ void __launch_bounds__(32 * GV_WARPS) gemv_kernel(GemvArgs a) {
+__global__ void __launch_bounds__(32 * GV_WARPS) rowstream_kernel(GemvArgs a) {
     int row0, rows;
     const TW* W = static_cast<const TW*>(a.w);
     const TW* W2 = static_cast<const TW*>(a.w2);
@@ -184,9 +184,9 @@ static int launch(const GemvArgs& a, int tiles, bool dual, cudaStream_t stream) 
     if (grid.x == 0 || grid.y == 0) return 0;
     if (grid.y > 65535) return LOCUS_ERR_UNSUPPORTED;
     if (dual) {
-        gemv_kernel<TX, TW, true><<<grid, 32 * GV_WARPS, 0, stream>>>(a);
+        rowstream_kernel<TX, TW, true><<<grid, 32 * GV_WARPS, 0, stream>>>(a);
     } else {
-        gemv_kernel<TX, TW, false><<<grid, 32 * GV_WARPS, 0, stream>>>(a);
+        rowstream_kernel<TX, TW, false><<<grid, 32 * GV_WARPS, 0, stream>>>(a);
     }
     return locus_launch_status();
 }

@@ -214,6 +214,11 @@ class ModelRunner:
             if code:
                 raise RuntimeError(f"tensor-core kernel fault: a pipeline wait ran out (code {code}: "
                                    "1 = loader, 2 = MMA issuer, 3 = epilogue); results since the last check are invalid")
+        if self.device.type == "cuda" and "attention" in K._LIBS:
+            code = K.attn_error()
+            if code:
+                raise RuntimeError(f"decode attention fault (code {code}): the step's split count did not cover its "
+                                   "longest context; results since the last check are invalid")
         if self.device.type == "cuda" and "attention_tc" in K._LIBS:
             code = K.attn_tc_error()
             if code:

@@ -618,16 +618,31 @@ def attn_tc_error() -> int:
     return int(_lib("attention_tc").locus_attn_tc_error())
 
 
+def attn_error() -> int:
+    """Error word of the attention module (0 = fine; 1 = a decode step's ``max_splits`` did not cover its
+    longest context); reading it synchronises the device and clears it."""
+    return int(_lib("attention").locus_attn_error())
+
+
 DECODE_SPLIT = 128
 
 
-def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype, max_splits: int, device) -> int:
-    """How many partial results the scratch of :func:`attn_decode` should hold for batches of up to
-    ``max_items`` requests: for the streaming kernel (rows of 128, 256 or 512 bytes) one per
-    (request, head) plus eight rounds of the grid's warps, so that short batches can be cut finely;
-    for other head sizes one per (request, head, split)."""
+def decode_streams(head_dim: int, dtype: torch.dtype, page_tokens: int, max_items: int) -> bool:
+    """Whether :func:`attn_decode` runs the streaming kernel (the condition of csrc/attention.cu): rows of
+    128, 256 or 512 bytes, pages that are a multiple of that row size's chunk of 32, 16 or 8 keys, and at
+    most 1024 requests."""
     row_bytes = head_dim * (4 if dtype == torch.float32 else 2)
-    if row_bytes in (128, 256, 512) and max_items <= 1024:
+    return row_bytes in (128, 256, 512) and page_tokens % (4096 // row_bytes) == 0 and max_items <= 1024
+
+
+def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype, max_splits: int, device,
+                 page_tokens: int = 64) -> int:
+    """How many partial results the scratch of :func:`attn_decode` should hold for batches of up to
+    ``max_items`` requests: for the streaming kernel (:func:`decode_streams`) one per
+    (request, head) plus eight rounds of the grid's warps, so that short batches can be cut finely;
+    for other head and page sizes one per (request, head, split), ``max_splits`` being the splits of the
+    longest context that the cache allows."""
+    if decode_streams(head_dim, dtype, page_tokens, max_items):
         try:
             n_sm = torch.cuda.get_device_properties(device).multi_processor_count
         except Exception:  # no GPU (host tests with emulated kernels)

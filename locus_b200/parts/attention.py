@@ -113,7 +113,10 @@ class Attention(Mixer):
                 K.attn_chunk(q, cache.pool, o, items=batch.chunk_items, n_items=batch.n_chunk_items, **common)
         if batch.n_decode_items:
             n = batch.n_decode_items
-            units = K.decode_units(rt.max_segments, self.n_heads, self.head_dim, q.dtype, batch.max_splits, rt.device)
+            # scratch sized once, for the longest context that the block table can describe
+            cap_splits = (gb.block_table.shape[1] * gb.page_tokens - 1) // K.DECODE_SPLIT + 1
+            units = K.decode_units(rt.max_segments, self.n_heads, self.head_dim, q.dtype,
+                                   max(cap_splits, batch.max_splits), rt.device, gb.page_tokens)
             part_o = rt.buf("attention.part_o", (units * self.head_dim,), torch.float32)
             part_ml = rt.buf("attention.part_ml", (2 * units,), torch.float32)
             counters = rt.shared_object(

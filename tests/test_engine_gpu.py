@@ -513,7 +513,8 @@ def test_trace_run_program_options_and_refusals(tmp_path_factory):
     got, code, err = replay_program(case, torch.float32, steps, out / "ok", max_tokens=need, page_tokens=16, max_live=2)
     assert code == 0, err[-2000:]
     check_program(case, got, torch.float32, "trace_run, pages of 16")
-    got, code, err = replay_program(case, torch.float32, steps, out / "short", max_tokens=need - 16, page_tokens=16,
+    # ten pages: the second step wants 4 + 7
+    got, code, err = replay_program(case, torch.float32, steps, out / "short", max_tokens=160, page_tokens=16,
                                     max_live=2)
     assert code == 2 and "out of cache pages" in err
     three = [[(r[0], 2), (r[1], 2), (r[2], 2)]]

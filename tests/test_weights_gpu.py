@@ -111,7 +111,10 @@ def test_all_24_layers_against_the_plain_implementation():
                 kth = min(float(probs[e]) for e in ids)
                 for e in eng:
                     assert float(probs[e]) >= kth * (1 - NEAR_TIE), (prefix, pos, e, float(probs[e]), kth)
-    assert n_diff < 0.02 * 24 * 302, f"{n_diff} choices differ"
+    # How many may differ: the 4th and 5th best of 60 router logits (sigma 0.9 with these weights) lie about 0.09
+    # apart on average, the engine's logits carry an error of sigma 0.007 (bfloat16 activations), so a swap is
+    # expected at about 0.8 * 0.007 / 0.09 = 6 % of the (layer, position) pairs; far more would be a fault.
+    assert n_diff < 0.10 * 24 * 302, f"{n_diff} choices differ"
     tol_max, tol_mean = TOL[dtype]
     scale = float(ref.abs().max())
     err = (got - ref).abs()

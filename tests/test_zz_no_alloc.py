@@ -6,8 +6,10 @@ lock, or in a host that got a fixed memory budget and no allocator), or they are
 programs without a tensor library.  ``locus_attn_decode_static`` keeps the scratch in a
 fixed 4 MiB device array inside the library instead.  This test calls it twice in a row
 (the second call finds the first call's leftovers in the shared array) and compares each
-result with the regular entry point's, checks that device memory does not move, and that a
-call too large for the array is refused.  The file sorts last so that a run that stops at
+result with the regular entry point's and with the plain float64 attention of
+``tests/emulated_kernels.py``, checks that device memory does not move, that a call too large
+for the array is refused, and that a call whose ``max_splits`` does not cover its longest
+context reports it and leaves the shared counters usable.  The file sorts last so that a run that stops at
 the first failure has already run every other test.
 """
 import ctypes
@@ -15,6 +17,8 @@ import math
 
 import pytest
 import torch
+
+import emulated_kernels as EK
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -90,6 +94,49 @@ def test_static_scratch_entry_point_matches_the_regular_one_twice(dtype):
         err = float((outs[i].double() - ref).abs().max())
         assert math.isfinite(err) and err <= tol * float(ref.abs().max()), (i, err)
         assert float(outs[i].abs().max()) > 0
+        plain = _plain(cases[i], nh, nkv, hd, P, 0)
+        err = float((outs[i].double().cpu() - plain).abs().max())
+        assert err <= tol * float(plain.abs().max()), (i, err)
+    assert lib.locus_attn_error() == 0
+
+
+def _plain(c, nh, nkv, hd, P, window):
+    """The float64 attention of tests/emulated_kernels.py on host copies of the case."""
+    EK.PRECISE = True
+    try:
+        ref = torch.zeros(c["q"].shape[0], nh * hd, dtype=torch.float64)
+        EK.attn_decode(c["q"].cpu(), c["pool"].cpu(), ref, seg_q0=c["seg_q0"].cpu(), seg_qn=c["seg_qn"].cpu(),
+                       seg_ctx=c["seg_ctx"].cpu(), block_table=c["table"].cpu(), items=c["items"].cpu(),
+                       n_items=c["q"].shape[0], n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=window,
+                       scale=1.0 / math.sqrt(hd), part_o=None, part_ml=None, counters=None, max_splits=1 << 20)
+    finally:
+        EK.PRECISE = False
+    return ref
+
+
+def test_too_few_splits_are_reported_and_do_not_poison_later_calls():
+    """``max_splits`` below what the longest context needs: the host cannot see the context lengths, so the kernel
+    notices, sets the module's error word, merges the splits that exist and returns its counters to zero.  The
+    next, correct call through the shared counters is right."""
+    from locus_b200.csrc import build
+
+    lib = build.load("attention")
+    nh, nkv, hd, P = 4, 2, 64, 16          # bfloat16 rows of 128 bytes with pages of 16: the split kernel
+    c = _case(torch.bfloat16, 21, 3, nh, nkv, hd, P, [700, 40, 300])
+    out = torch.zeros(3, nh * hd, dtype=torch.bfloat16, device=DEV)
+    assert lib.locus_attn_error() == 0
+    assert _call(lib, True, c, out, nh, nkv, hd, P, 0, 3) == 0     # 700 // 128 + 1 = 6 splits are needed
+    torch.cuda.synchronize()
+    assert lib.locus_attn_error() == 1 and lib.locus_attn_error() == 0   # reported once, then cleared
+    plain = _plain(c, nh, nkv, hd, P, 0)
+    err = (out.double().cpu() - plain).abs().max(dim=1).values
+    assert float(err[1]) <= 1.2e-2 * float(plain.abs().max())   # the request that fits its splits is right
+    assert torch.isfinite(out.float()).all()
+    out.zero_()
+    assert _call(lib, True, c, out, nh, nkv, hd, P, 0, 6) == 0
+    torch.cuda.synchronize()
+    assert lib.locus_attn_error() == 0
+    assert float((out.double().cpu() - plain).abs().max()) <= 1.2e-2 * float(plain.abs().max())
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
