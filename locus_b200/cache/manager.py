@@ -72,7 +72,9 @@ class _Group:
         self.gid = gid
         self.spec = spec
         self.calls: List[int] = []
-        self.pool: Optional[torch.Tensor] = None
+        self.n_pages = 0
+        self.pool: Optional[torch.Tensor] = None    # [calls, pages, planes, kv heads, page_tokens, head_dim]
+        self.extra: Optional[torch.Tensor] = None   # [calls, pages, page_tokens, extra_width]
 
 
 class _StateSlots:
@@ -94,11 +96,13 @@ class CacheManager:
     def __init__(self, needs: Sequence[Tuple[Optional[PagedKvSpec], Optional[StateSpec], Optional[int]]], *,
                  page_tokens: int, n_pages: int, n_state_slots: int, max_seq_tokens: int,
                  dtype: torch.dtype = torch.float32, device="cpu", allocate_device: bool = True,
-                 poison: bool = False) -> None:
+                 poison: bool = False, max_step_tokens: int = 0) -> None:
         """``needs``: per entry of the model's run order, what its mixer keeps and whose cache
-        it reads.  ``n_pages``: pages of every group.  ``poison``: fill pages with NaN when
-        they are created and when they are given back (tests: a read of a stale or unwritten
-        slot then shows in the logits)."""
+        it reads.  ``n_pages``: pages of a group that keeps all tokens.  ``max_step_tokens`` > 0: the most
+        tokens that one step feeds to one request; a group with a window then gets only the pages that
+        ``n_state_slots`` requests can hold at once (window + step, rounded up to pages, plus one each)
+        instead of ``n_pages``.  ``poison``: fill pages with NaN when they are created and when they are
+        given back (tests: a read of a stale or unwritten slot then shows in the logits)."""
         if page_tokens <= 0 or n_pages < 0 or n_state_slots <= 0:
             raise ValueError("page_tokens and n_state_slots must be positive")
         self.page_tokens = page_tokens
@@ -132,8 +136,15 @@ class CacheManager:
             self._call_index.append(len(g.calls))
             g.calls.append(i)
         self._lib = native.lib()
+        self.max_step_tokens = max(0, int(max_step_tokens))
+        for g in self.groups:
+            g.n_pages = n_pages
+            if g.spec.window > 0 and self.max_step_tokens > 0:
+                per_request = -(-(g.spec.window + self.max_step_tokens) // page_tokens) + 1
+                g.n_pages = min(n_pages, n_state_slots * per_request)
         windows = (ctypes.c_int * max(1, len(self.groups)))(*[g.spec.window for g in self.groups])
-        self._core = self._lib.locus_cache_new(len(self.groups), windows, page_tokens, n_pages, n_state_slots,
+        group_pages = (ctypes.c_int * max(1, len(self.groups)))(*[g.n_pages for g in self.groups])
+        self._core = self._lib.locus_cache_new(len(self.groups), windows, page_tokens, group_pages, n_state_slots,
                                                max_seq_tokens)
         if not self._core:
             raise ValueError("the native cache could not be created from these sizes")
@@ -153,16 +164,21 @@ class CacheManager:
                 self._state.append(None)
         if allocate_device:
             for g in self.groups:
-                shape = (len(g.calls), n_pages, 2, g.spec.n_kv_heads, page_tokens, g.spec.head_dim)
+                shape = (len(g.calls), g.n_pages, g.spec.planes, g.spec.n_kv_heads, page_tokens, g.spec.head_dim)
                 g.pool = torch.empty(shape, dtype=dtype, device=self.device)
+                if g.spec.extra_width > 0:
+                    g.extra = torch.empty((len(g.calls), g.n_pages, page_tokens, g.spec.extra_width), dtype=dtype,
+                                          device=self.device)
                 if poison:
                     g.pool.fill_(float("nan"))
+                    if g.extra is not None:
+                        g.extra.fill_(float("nan"))
         self._live: Dict[object, SeqCache] = {}
 
     # -- geometry -----------------------------------------------------------
     def bytes_per_token(self) -> int:
         el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.calls) * 2 * g.spec.n_kv_heads * g.spec.head_dim * el for g in self.groups)
+        return sum(len(g.calls) * g.spec.elements_per_token() * el for g in self.groups)
 
     def pages_for(self, n_tokens: int) -> int:
         return -(-n_tokens // self.page_tokens)
@@ -173,8 +189,21 @@ class CacheManager:
             return self._lib.locus_cache_free_pages(self._core, gid)
         return min((self._lib.locus_cache_free_pages(self._core, g.gid) for g in self.groups), default=self.n_pages)
 
-    def total_pages(self) -> int:
-        return self.n_pages
+    def total_pages(self, gid: Optional[int] = None) -> int:
+        """Pages of one group's pool, or the smallest pool over all groups (so that an idle cache has
+        ``free_pages() == total_pages()``)."""
+        if gid is not None:
+            return self.groups[gid].n_pages
+        return min((g.n_pages for g in self.groups), default=self.n_pages)
+
+    def pages_needed(self, gid: int, n_tokens: int, step_tokens: int = 0) -> int:
+        """Pages that a request of ``n_tokens`` tokens holds in group ``gid`` at most when no step feeds it
+        more than ``step_tokens`` tokens (0: unknown): all of them, or what covers the window and a step."""
+        return self._lib.locus_cache_pages_needed(self._core, gid, n_tokens, step_tokens)
+
+    def fits_when_empty(self, n_tokens: int, step_tokens: int = 0) -> bool:
+        """Whether a request of ``n_tokens`` tokens fits the pools when nothing else is held."""
+        return all(self.pages_needed(g.gid, n_tokens, step_tokens) <= g.n_pages for g in self.groups)
 
     def layer_caches(self) -> List[LayerCache]:
         out = []
@@ -182,8 +211,11 @@ class CacheManager:
             pool = None
             if gid is not None and self.groups[gid].pool is not None:
                 pool = self.groups[gid].pool[self._call_index[i]]
+            extra = None
+            if gid is not None and self.groups[gid].extra is not None:
+                extra = self.groups[gid].extra[self._call_index[i]]
             out.append(LayerCache(group=gid, pool=pool, page_tokens=self.page_tokens,
-                                  state=self._state[i], writes=self._call_writes[i]))
+                                  state=self._state[i], writes=self._call_writes[i], extra=extra))
         return out
 
     # -- requests -----------------------------------------------------------
@@ -229,6 +261,8 @@ class CacheManager:
                 g = self.groups[pairs[i]]
                 if g.pool is not None:
                     g.pool[:, pairs[i + 1]].fill_(float("nan"))
+                    if g.extra is not None:
+                        g.extra[:, pairs[i + 1]].fill_(float("nan"))
 
     def get(self, seq_id) -> Optional[SeqCache]:
         return self._live.get(seq_id)
@@ -294,6 +328,8 @@ class CacheManager:
             g = self.groups[self._freed[2 * i]]
             if g.pool is not None:
                 g.pool[:, self._freed[2 * i + 1]].fill_(float("nan"))
+                if g.extra is not None:
+                    g.extra[:, self._freed[2 * i + 1]].fill_(float("nan"))
 
     def _not_open(self, seq: SeqCache) -> None:
         raise CacheError(f"request {seq.seq_id!r} is not open in this cache")

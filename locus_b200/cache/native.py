@@ -27,7 +27,9 @@ def lib() -> ctypes.CDLL:
             "locus_pool_allocate": (c_int, [c_void_p]),
             "locus_pool_release": (c_int, [c_void_p, c_int]),
             "locus_pool_retain": (c_int, [c_void_p, c_int]),
-            "locus_cache_new": (c_void_p, [c_int, P_INT, c_int, c_int, c_int, c_int]),
+            "locus_cache_new": (c_void_p, [c_int, P_INT, c_int, P_INT, c_int, c_int]),
+            "locus_cache_total_pages": (c_int, [c_void_p, c_int]),
+            "locus_cache_pages_needed": (c_int, [c_void_p, c_int, c_int, c_int]),
             "locus_cache_delete": (None, [c_void_p]),
             "locus_cache_table_width": (c_int, [c_void_p]),
             "locus_cache_free_pages": (c_int, [c_void_p, c_int]),
@@ -45,8 +47,9 @@ def lib() -> ctypes.CDLL:
             "locus_cache_release": (c_int, [c_void_p, c_int64, P_INT, c_int]),
             "locus_cache_check": (c_int, [c_void_p, P_INT]),
             "locus_step_build": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-                                         c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p,
-                                         c_void_p]),
+                                         c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
+            "locus_plan_query_tiles": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_int64]),
+            "locus_plan_segments_with": (c_int, [c_int, c_void_p, c_int, c_void_p, c_int64]),
         }
         sig.update({
             "locus_sched_new": (c_void_p, [c_void_p, c_int, c_int, c_int, c_int, c_int]),

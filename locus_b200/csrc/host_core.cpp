@@ -62,7 +62,7 @@ struct Seq {
 inline int pages_of(int tokens, int page_tokens) { return (tokens + page_tokens - 1) / page_tokens; }
 
 struct Cache {
-    int page_tokens, n_pages, max_seq_tokens, table_width;
+    int page_tokens, n_pages, max_seq_tokens, table_width;  // n_pages: of the largest group
     std::vector<int> window;  // per group, 0 = all keys
     std::vector<Pool> pools;
     Pool slots;
@@ -71,15 +71,25 @@ struct Cache {
     std::vector<uint32_t> stamp;  // scratch of step assembly: which step saw a request last
     uint32_t step_no = 0;
 
-    Cache(int n_groups, const int* windows, int page_tokens_, int n_pages_, int n_slots, int max_seq)
-        : page_tokens(page_tokens_), n_pages(n_pages_), max_seq_tokens(max_seq),
+    Cache(int n_groups, const int* windows, int page_tokens_, const int* group_pages, int n_slots, int max_seq)
+        : page_tokens(page_tokens_), n_pages(0), max_seq_tokens(max_seq),
           table_width(pages_of(max_seq, page_tokens_) > 0 ? pages_of(max_seq, page_tokens_) : 1), slots(n_slots) {
         for (int g = 0; g < n_groups; ++g) {
             window.push_back(windows[g]);
-            pools.emplace_back(n_pages_);
+            pools.emplace_back(group_pages[g]);
+            n_pages = group_pages[g] > n_pages ? group_pages[g] : n_pages;
         }
     }
     int n_groups() const { return static_cast<int>(pools.size()); }
+    // Pages that a request of n_tokens tokens holds in group g at most, when no step feeds it more than
+    // step_tokens at once: all of them, or in a group with a window those that cover the window and the step.
+    int pages_needed(int g, int n_tokens, int step_tokens) const {
+        const int all = pages_of(n_tokens, page_tokens);
+        const int w = window[static_cast<size_t>(g)];
+        if (w <= 0 || step_tokens <= 0) return all;
+        const int span = pages_of(w + step_tokens, page_tokens) + 1;
+        return all < span ? all : span;
+    }
 
     Seq* find(int64_t handle) {
         const uint32_t idx = static_cast<uint32_t>(handle & 0xffffffff);
@@ -130,10 +140,17 @@ int locus_pool_retain(void* p, int i) {
 }
 
 // ---- cache ---------------------------------------------------------------------------------
-void* locus_cache_new(int n_groups, const int* windows, int page_tokens, int n_pages, int n_state_slots,
+// group_pages: pages of every group's pool (groups with a window may hold fewer than the others).
+void* locus_cache_new(int n_groups, const int* windows, int page_tokens, const int* group_pages, int n_state_slots,
                       int max_seq_tokens) {
-    if (n_groups < 0 || page_tokens <= 0 || n_pages < 0 || n_state_slots <= 0) return nullptr;
-    return new Cache(n_groups, windows, page_tokens, n_pages, n_state_slots, max_seq_tokens);
+    if (n_groups < 0 || page_tokens <= 0 || n_state_slots <= 0) return nullptr;
+    for (int g = 0; g < n_groups; ++g)
+        if (group_pages[g] < 0) return nullptr;
+    return new Cache(n_groups, windows, page_tokens, group_pages, n_state_slots, max_seq_tokens);
+}
+int locus_cache_total_pages(void* c, int gid) { return as_cache(c)->pools[static_cast<size_t>(gid)].total(); }
+int locus_cache_pages_needed(void* c, int gid, int n_tokens, int step_tokens) {
+    return as_cache(c)->pages_needed(gid, n_tokens, step_tokens);
 }
 void locus_cache_delete(void* c) { delete as_cache(c); }
 int locus_cache_table_width(void* c) { return as_cache(c)->table_width; }
@@ -267,7 +284,8 @@ int locus_cache_release(void* cv, int64_t h, int* freed, int cap) {
 int locus_cache_check(void* cv, int* detail) {
     Cache* c = as_cache(cv);
     for (int g = 0; g < c->n_groups(); ++g) {
-        std::vector<int> held(static_cast<size_t>(c->n_pages), 0);
+        const int n_pages = c->pools[static_cast<size_t>(g)].total();
+        std::vector<int> held(static_cast<size_t>(n_pages), 0);
         int distinct = 0;
         for (const Seq& s : c->seqs) {
             if (!s.open) continue;
@@ -275,7 +293,7 @@ int locus_cache_check(void* cv, int* detail) {
                 if (page >= 0 && held[static_cast<size_t>(page)]++ == 0) ++distinct;
         }
         const Pool& pool = c->pools[static_cast<size_t>(g)];
-        for (int page = 0; page < c->n_pages; ++page) {
+        for (int page = 0; page < n_pages; ++page) {
             const int n = held[static_cast<size_t>(page)];
             if (n > 1) { detail[0] = g; detail[1] = page; detail[2] = n; return 1; }
             if (n == 1 && pool.refs[static_cast<size_t>(page)] != 1) {
@@ -304,13 +322,13 @@ int locus_cache_check(void* cv, int* detail) {
 // The descriptors of one step, written back to back into out (int32) in this order, with
 // (offset, length) of each in layout:
 //   0 tokens[T]  1 positions[T]  2 seg_q0[S]  3 seg_qn[S]  4 seg_ctx[S]  5 state_slots[S]
-//   6 want_rows[n_want]  7 chunk_items[2 * n] (segment, first query of a tile of chunk_tile queries;
-//   segments with more than one new token)  8 decode_items[n] (segments with one new token)
-//   9 chunk_items of tiles of mma_tile queries  then per group g: 10 + 2g slots[T] (page *
-//   page_tokens + offset of each new token), 11 + 2g block table [S, table_width] (-1 padded).
-// info: T, n_want, longest context after the step, n chunk items, n decode items, n mma items,
-//       and on an error the offending entry and a value (for codes 5 and 9 the index, within the
-//       entry, of the token or wanted place).
+//   6 want_rows[n_want]  then per group g: 7 + 2g slots[T] (page * page_tokens + offset of each new
+//   token), 8 + 2g block table [S, table_width] (-1 padded).
+// Nothing here knows what a mixer's kernels want beyond that: work lists of tiles and the like are planned
+// by the parts themselves (they may use the helpers at the end of this section) and ride behind these
+// descriptors in the same buffer.
+// info: T, n_want, longest context after the step, and on an error the offending entry [6] and a value
+//       [7] (for codes 5 and 9 the index, within the entry, of the token or wanted place).
 // Checks before anything is written that could be launched: 0 ok; 1 no entries; 2 more entries than
 // max_segments; 3 a request twice; 4 an entry without tokens; 5 token outside the vocabulary;
 // 6 beyond max_positions; 7 request not open; 8 capacity not ensured; 9 wanted place outside the
@@ -318,8 +336,7 @@ int locus_cache_check(void* cv, int* detail) {
 // already given back; 13 out too small.
 int locus_step_build(void* cv, int n_entries, const int64_t* handles, const int* counts, const int64_t* tokens,
                      const int* want_counts, const int64_t* wants, int vocab, int max_positions, int max_tokens,
-                     int max_segments, int max_wanted, int chunk_tile, int mma_tile, int* out, int64_t out_cap,
-                     int* layout, int* info) {
+                     int max_segments, int max_wanted, int* out, int64_t out_cap, int* layout, int* info) {
     Cache* c = as_cache(cv);
     info[6] = info[7] = 0;
     if (n_entries <= 0) return 1;
@@ -329,7 +346,7 @@ int locus_step_build(void* cv, int n_entries, const int64_t* handles, const int*
         for (auto& s : c->stamp) s = 0;
         c->step_no = 1;
     }
-    int64_t T = 0, n_want = 0, n_chunk = 0, n_chunk_mma = 0, n_decode = 0;
+    int64_t T = 0, n_want = 0;
     {
         const int64_t* tok = tokens;
         const int64_t* wnt = wants;
@@ -350,12 +367,6 @@ int locus_step_build(void* cv, int n_entries, const int64_t* handles, const int*
                 if (wnt[i] < 0 || wnt[i] >= n) { info[7] = i; return 9; }
             T += n;
             n_want += want_counts[e];
-            if (n == 1) {
-                n_decode += 1;
-            } else {
-                n_chunk += (n + chunk_tile - 1) / chunk_tile;
-                n_chunk_mma += (n + mma_tile - 1) / mma_tile;
-            }
             tok += n;
             wnt += want_counts[e];
         }
@@ -363,19 +374,20 @@ int locus_step_build(void* cv, int n_entries, const int64_t* handles, const int*
     if (T > max_tokens) { info[7] = static_cast<int>(T); return 10; }
     if (n_want > max_wanted) { info[7] = static_cast<int>(n_want); return 11; }
     const int S = n_entries, G = c->n_groups(), W = c->table_width;
-    const int64_t lens[10] = {T, T, S, S, S, S, n_want, 2 * n_chunk, n_decode, 2 * n_chunk_mma};
+    const int F = 7;
+    const int64_t lens[F] = {T, T, S, S, S, S, n_want};
     int64_t off = 0;
-    for (int f = 0; f < 10; ++f) {
+    for (int f = 0; f < F; ++f) {
         layout[2 * f] = static_cast<int>(off);
         layout[2 * f + 1] = static_cast<int>(lens[f]);
         off += lens[f];
     }
     for (int g = 0; g < G; ++g) {
-        layout[2 * (10 + 2 * g)] = static_cast<int>(off);
-        layout[2 * (10 + 2 * g) + 1] = static_cast<int>(T);
+        layout[2 * (F + 2 * g)] = static_cast<int>(off);
+        layout[2 * (F + 2 * g) + 1] = static_cast<int>(T);
         off += T;
-        layout[2 * (11 + 2 * g)] = static_cast<int>(off);
-        layout[2 * (11 + 2 * g) + 1] = S * W;
+        layout[2 * (F + 1 + 2 * g)] = static_cast<int>(off);
+        layout[2 * (F + 1 + 2 * g) + 1] = S * W;
         off += static_cast<int64_t>(S) * W;
     }
     if (off > out_cap) return 13;
@@ -386,9 +398,6 @@ int locus_step_build(void* cv, int n_entries, const int64_t* handles, const int*
     int* o_ctx = out + layout[8];
     int* o_slot = out + layout[10];
     int* o_want = out + layout[12];
-    int* o_chunk = out + layout[14];
-    int* o_dec = out + layout[16];
-    int* o_mma = out + layout[18];
     int row = 0, longest = 0;
     const int64_t* tok = tokens;
     const int64_t* wnt = wants;
@@ -406,22 +415,16 @@ int locus_step_build(void* cv, int n_entries, const int64_t* handles, const int*
             o_pos[row + i] = ctx + i;
         }
         if (ctx + n > longest) longest = ctx + n;
-        if (n == 1) {
-            *o_dec++ = e;
-        } else {
-            for (int q = 0; q < n; q += chunk_tile) { *o_chunk++ = e; *o_chunk++ = q; }
-            for (int q = 0; q < n; q += mma_tile) { *o_mma++ = e; *o_mma++ = q; }
-        }
         for (int g = 0; g < G; ++g) {
             const auto& t = s->tables[static_cast<size_t>(g)];
-            int* o_slots = out + layout[2 * (10 + 2 * g)] + row;
+            int* o_slots = out + layout[2 * (F + 2 * g)] + row;
             for (int i = 0; i < n; ++i) {
                 const int pos = ctx + i;
                 const int page = t[static_cast<size_t>(pos / P)];
                 if (page < 0) { info[6] = e; info[7] = pos; return 12; }
                 o_slots[i] = page * P + pos % P;
             }
-            int* o_table = out + layout[2 * (11 + 2 * g)] + static_cast<int64_t>(e) * W;
+            int* o_table = out + layout[2 * (F + 1 + 2 * g)] + static_cast<int64_t>(e) * W;
             const int len = static_cast<int>(t.size());
             if (len > 0) std::memcpy(o_table, t.data(), sizeof(int) * static_cast<size_t>(len));
             for (int i = len; i < W; ++i) o_table[i] = -1;
@@ -433,10 +436,36 @@ int locus_step_build(void* cv, int n_entries, const int64_t* handles, const int*
     info[0] = static_cast<int>(T);
     info[1] = static_cast<int>(n_want);
     info[2] = longest;
-    info[3] = static_cast<int>(n_chunk);
-    info[4] = static_cast<int>(n_decode);
-    info[5] = static_cast<int>(n_chunk_mma);
     return 0;
+}
+
+// Helpers for parts that plan work lists over the segments of a step.  seg_qn: new tokens per segment.
+// Tiles of `tile` queries over every segment with at least min_new new tokens, as pairs (segment, first
+// query of the tile) in segment order; returns the number of pairs, or -1 when out (cap ints) is too small.
+int locus_plan_query_tiles(int n_seg, const int* seg_qn, int tile, int min_new, int* out, int64_t cap) {
+    if (tile <= 0) return -1;
+    int64_t n = 0;
+    for (int s = 0; s < n_seg; ++s) {
+        if (seg_qn[s] < min_new) continue;
+        for (int q = 0; q < seg_qn[s]; q += tile) {
+            if (2 * n + 1 >= cap) return -1;
+            out[2 * n] = s;
+            out[2 * n + 1] = q;
+            ++n;
+        }
+    }
+    return static_cast<int>(n);
+}
+
+// The segments with exactly `new_tokens` new tokens, in order; returns their number, or -1 when out is too small.
+int locus_plan_segments_with(int n_seg, const int* seg_qn, int new_tokens, int* out, int64_t cap) {
+    int64_t n = 0;
+    for (int s = 0; s < n_seg; ++s) {
+        if (seg_qn[s] != new_tokens) continue;
+        if (n >= cap) return -1;
+        out[n++] = s;
+    }
+    return static_cast<int>(n);
 }
 
 }  // extern "C"
@@ -485,10 +514,11 @@ struct Sched {
         events.push_back(rid);
         events.push_back(arg);
     }
-    int free_pages() const {
-        int least = cache->n_pages;
-        for (const Pool& p : cache->pools) least = std::min(least, p.n_free());
-        return least;
+    // whether every group has free pages for a request of n_tokens tokens (fed at most `chunk` at a time)
+    bool room_for(int n_tokens) const {
+        for (int g = 0; g < cache->n_groups(); ++g)
+            if (cache->pages_needed(g, n_tokens, chunk) > cache->pools[static_cast<size_t>(g)].n_free()) return false;
+        return true;
     }
     void give_back(SReq& r) {
         if (r.handle < 0) return;
@@ -561,8 +591,7 @@ int locus_sched_admit(void* sv) {
     while (!s->waiting.empty() && static_cast<int>(s->running.size()) < s->max_running) {
         const int64_t rid = s->waiting.front();
         SReq& r = s->reqs[rid];
-        const int want = pages_of(r.stream_len + s->headroom, s->cache->page_tokens);
-        if (want > s->free_pages() || s->cache->slots.n_free() == 0) break;  // nobody overtakes the front
+        if (!s->room_for(r.stream_len + s->headroom) || s->cache->slots.n_free() == 0) break;  // nobody overtakes the front
         s->waiting.pop_front();
         r.handle = locus_cache_open(s->cache);
         r.status = ST_RUNNING;

@@ -135,14 +135,14 @@ class StepBatch:
     state_slots: torch.Tensor # int32 [n_seg] per-request state slot
     want_rows: torch.Tensor   # int32 [n_want] rows whose logits are returned
     n_want: int
-    chunk_items: torch.Tensor # int32 [n_chunk_items, 2] (segment, first query of a 16-token tile)
-    n_chunk_items: int
-    chunk_items64: torch.Tensor  # the same portions cut into 64-token tiles (tensor-core kernel)
-    n_chunk_items64: int
-    decode_items: torch.Tensor  # int32 [n_decode_items] segments with one new token
-    n_decode_items: int
-    max_splits: int           # split count that covers the longest context (decode kernel)
+    longest: int = 0          # the longest context of the step, its new tokens included
+    # True: the step may be replayed with other lengths (a CUDA graph), so nothing that is launched may
+    # depend on ``longest`` or on other lengths known only to the host
+    static_shapes: bool = False
     groups: Dict[int, GroupBatch] = field(default_factory=dict)
+    # what the parts' own step plans (parts.base.StepPlan) wrote, by the plan's key: device tensors of the
+    # work lists by name, and the plain numbers the plan returned
+    plans: Dict[Tuple, Dict[str, object]] = field(default_factory=dict)
     # host copies, for parts that plan on the host
     host_seg_q0: List[int] = field(default_factory=list)
     host_seg_qn: List[int] = field(default_factory=list)
@@ -156,7 +156,8 @@ class LayerCache:
     descriptors of its group, and its per-request state (if it has any)."""
 
     group: Optional[int]              # cache group id, key into StepBatch.groups
-    pool: Optional[torch.Tensor]      # [n_pages, 2, n_kv_heads, page_tokens, head_dim]
+    pool: Optional[torch.Tensor]      # [n_pages, planes (K, V or K alone), n_kv_heads, page_tokens, head_dim]
     page_tokens: int
     state: Optional[torch.Tensor]     # [n_state_slots, *StateSpec.shape]
     writes: bool = True               # False: the call reads another call's cache
+    extra: Optional[torch.Tensor] = None  # [n_pages, page_tokens, extra_width] per-token fields beside the rows

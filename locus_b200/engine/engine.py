@@ -72,7 +72,7 @@ class Engine:
         n_pages = -(-ctx // page_tokens)
         cache = CacheManager(model.cache_needs(), page_tokens=page_tokens, n_pages=n_pages,
                              n_state_slots=max_running, max_seq_tokens=max_seq_tokens, dtype=model.dtype,
-                             device=model.device)
+                             device=model.device, max_step_tokens=min(chunk, max_batch_tokens))
         max_tokens = max(max_batch_tokens, max_running)
         runner = ModelRunner(model, cache, max_tokens=max_tokens, max_segments=max_running,
                              max_wanted=max_running, use_graphs=use_graphs)

@@ -183,9 +183,11 @@ class Scheduler:
         if n_prompt + 1 > self.cache.max_seq_tokens:
             return (f"prompt length {n_prompt} exceeds the cache's limit of "
                     f"{self.cache.max_seq_tokens} tokens per request")
-        want = self.cache.pages_for(n_prompt + self.cfg.decode_headroom)
-        if want > self.cache.total_pages():
-            return f"prompt needs {want} cache pages but the pool holds only {self.cache.total_pages()}"
+        n = n_prompt + self.cfg.decode_headroom
+        for g in self.cache.groups:
+            want = self.cache.pages_needed(g.gid, n, self.cfg.chunk)
+            if want > g.n_pages:
+                return f"prompt needs {want} cache pages but the pool holds only {g.n_pages}"
         return ""
 
     def submit(self, prompt: Sequence[int], max_new_tokens: int, sampling: SamplingParams = GREEDY,
@@ -230,7 +232,7 @@ class Scheduler:
         if not self.waiting:
             return False
         r = self.requests[self.waiting[0]]
-        return self.cache.pages_for(r.stream_len() + self.cfg.decode_headroom) <= self.cache.total_pages()
+        return self.cache.fits_when_empty(r.stream_len() + self.cfg.decode_headroom, self.cfg.chunk)
 
     def idle(self) -> bool:
         return not self.running and not self.waiting

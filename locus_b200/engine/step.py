@@ -26,10 +26,7 @@ import torch
 
 from ..cache.manager import CacheError, CacheManager, SeqCache
 from .. import kernels as K
-from ..kernels import DECODE_SPLIT
 from .batch import GroupBatch, Runtime, StepBatch
-
-CHUNK_TILE = 16  # queries per work item of the chunk attention kernel
 
 
 class StepError(ValueError):
@@ -59,7 +56,7 @@ class _BuildArgs:
 
 
 class ModelRunner:
-    _N_FIELDS = 10  # fields of a step before the per-group ones (csrc/host_core.cpp: locus_step_build)
+    _N_FIELDS = 7  # fields of a step before the per-group ones (csrc/host_core.cpp: locus_step_build)
 
     def __init__(self, model, cache: CacheManager, *, max_tokens: int, max_segments: int,
                  max_wanted: Optional[int] = None, use_graphs: bool = False) -> None:
@@ -75,8 +72,13 @@ class ModelRunner:
         self.layer_caches = cache.layer_caches()
         G = len(cache.groups)
         W = cache.table_width
-        items_max = max_tokens // CHUNK_TILE + max_segments + 1
-        size = (max_tokens * (2 + G) + max_segments * (5 + G * W) + self.max_wanted + 4 * items_max)
+        # the parts' own step plans (work lists of their kernels), one of each kind, behind the descriptors
+        self.plans = {}
+        for part in model.all_parts():
+            for pl in (part.step_plans() if hasattr(part, "step_plans") else []):
+                self.plans.setdefault(pl.key, pl)
+        self._plan_caps = {key: int(pl.capacity(max_tokens, max_segments)) for key, pl in self.plans.items()}
+        size = (max_tokens * (2 + G) + max_segments * (4 + G * W) + self.max_wanted + sum(self._plan_caps.values()))
         # two pinned staging buffers, used in turn: a buffer is rewritten only after the copy
         # that read it has finished (its event), so steps may be queued without a host sync
         on_gpu = self.device.type == "cuda"
@@ -96,7 +98,7 @@ class ModelRunner:
         self.stats = {"steps": 0, "tokens": 0, "graph_replays": 0, "h2d_bytes": 0}
 
     # ------------------------------------------------------------------
-    def _build(self, entries: Sequence[StepEntry], fixed_splits: bool) -> StepBatch:
+    def _build(self, entries: Sequence[StepEntry], fixed_shapes: bool) -> StepBatch:
         """Check the entries and write the step's descriptors: one native call that reads the
         requests' page tables where they live and fills the pinned staging buffer, then one
         copy to the device."""
@@ -133,7 +135,7 @@ class ModelRunner:
         host = self._hosts[turn]
         code = cache._lib.locus_step_build(
             cache._core, n_seg, a.p_handles, a.p_counts, a.p_tokens, a.p_want_counts, a.p_wants, plan.vocab_size,
-            plan.max_positions, self.max_tokens, self.max_segments, self.max_wanted, CHUNK_TILE, K.MMA_QUERY_TILE,
+            plan.max_positions, self.max_tokens, self.max_segments, self.max_wanted,
             self._host_ptrs[turn], host.numel(), a.p_layout, a.p_info)
         info = a.info
         if code:
@@ -141,6 +143,26 @@ class ModelRunner:
         self._host_turn ^= 1
         layout = a.layout
         off = int(layout[-2]) + int(layout[-1])
+        hn = self._host_np[turn]
+
+        def hseg(i):
+            return hn[layout[2 * i] : layout[2 * i] + layout[2 * i + 1]]
+
+        # every distinct plan of the model's parts writes its work lists behind the descriptors
+        planned = []
+        if self.plans:
+            seg_q0, seg_qn, seg_ctx = hseg(2), hseg(3), hseg(4)
+            for key, pl in self.plans.items():
+                cap = self._plan_caps[key]
+                res = pl.build(seg_q0, seg_qn, seg_ctx, hn[off : off + cap])
+                used = 0
+                for name, v in res.items():
+                    if isinstance(v, tuple):
+                        if v[0] < 0 or v[1] < 0 or v[0] + v[1] > cap:
+                            raise StepError(f"step plan {key!r}: list {name!r} lies outside the plan's capacity of {cap}")
+                        used = max(used, v[0] + v[1])
+                planned.append((key, off, tuple(sorted(res.items()))))
+                off += used
         self._dev[:off].copy_(host[:off], non_blocking=True)
         if self._host_events[turn] is not None:
             self._host_events[turn].record()
@@ -149,35 +171,39 @@ class ModelRunner:
 
         # the device views of a layout are made once: steps of the same shape (every decode step of
         # a batch size) have the same layout
-        key = layout.tobytes()
+        key = (layout.tobytes(), tuple(planned))
         views = self._views.get(key)
         if views is None:
             if len(self._views) > 256:
                 self._views.clear()
-            views = [self._dev[int(layout[2 * i]) : int(layout[2 * i]) + int(layout[2 * i + 1])]
-                     for i in range(len(layout) // 2)]
-            views[7], views[9] = views[7].view(-1, 2), views[9].view(-1, 2)
+            fields = [self._dev[int(layout[2 * i]) : int(layout[2 * i]) + int(layout[2 * i + 1])]
+                      for i in range(len(layout) // 2)]
             W = cache.table_width
             for gi in range(len(cache.groups)):
-                views[self._N_FIELDS + 2 * gi + 1] = views[self._N_FIELDS + 2 * gi + 1].view(n_seg, W)
+                fields[self._N_FIELDS + 2 * gi + 1] = fields[self._N_FIELDS + 2 * gi + 1].view(n_seg, W)
+            plans = {}
+            for pkey, base, items in planned:
+                d = {}
+                for name, v in items:
+                    if isinstance(v, tuple):
+                        t = self._dev[base + v[0] : base + v[0] + v[1]]
+                        d[name] = t.view(*v[2]) if len(v) > 2 and v[2] else t
+                    else:
+                        d[name] = v
+                plans[pkey] = d
+            views = (fields, plans)
             self._views[key] = views
-        hn = self._host_np[turn]
-
-        def hv(i):
-            return hn[layout[2 * i] : layout[2 * i] + layout[2 * i + 1]].tolist()
-
-        longest = int(info[2])
-        max_splits = (cache.max_seq_tokens - 1) // DECODE_SPLIT + 1 if fixed_splits else (longest - 1) // DECODE_SPLIT + 1
+        fields, plans = views
         batch = StepBatch(
-            T=int(info[0]), n_seg=n_seg, tokens=views[0], positions=views[1], seg_q0=views[2], seg_qn=views[3],
-            seg_ctx=views[4], state_slots=views[5], want_rows=views[6], n_want=int(info[1]),
-            chunk_items=views[7], n_chunk_items=int(info[3]), chunk_items64=views[9], n_chunk_items64=int(info[5]),
-            decode_items=views[8], n_decode_items=int(info[4]), max_splits=max_splits,
-            host_seg_q0=hv(2), host_seg_qn=hv(3), host_seg_ctx=hv(4), host_state_slots=hv(5),
+            T=int(info[0]), n_seg=n_seg, tokens=fields[0], positions=fields[1], seg_q0=fields[2], seg_qn=fields[3],
+            seg_ctx=fields[4], state_slots=fields[5], want_rows=fields[6], n_want=int(info[1]),
+            longest=cache.max_seq_tokens if fixed_shapes else int(info[2]), static_shapes=fixed_shapes, plans=plans,
+            host_seg_q0=hseg(2).tolist(), host_seg_qn=hseg(3).tolist(), host_seg_ctx=hseg(4).tolist(),
+            host_state_slots=hseg(5).tolist(),
         )
         for gi, g in enumerate(cache.groups):
-            batch.groups[g.gid] = GroupBatch(block_table=views[self._N_FIELDS + 2 * gi + 1],
-                                             slots=views[self._N_FIELDS + 2 * gi], page_tokens=cache.page_tokens)
+            batch.groups[g.gid] = GroupBatch(block_table=fields[self._N_FIELDS + 2 * gi + 1],
+                                             slots=fields[self._N_FIELDS + 2 * gi], page_tokens=cache.page_tokens)
         return batch
 
     def _raise_build_error(self, code: int, entries, at: int, value: int) -> None:
@@ -232,7 +258,7 @@ class ModelRunner:
         The requests' token counts are advanced."""
         decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
         graphed = self.use_graphs and decode_only and self.device.type == "cuda"
-        batch = self._build(entries, fixed_splits=graphed)
+        batch = self._build(entries, fixed_shapes=graphed)
         before = K.launches
         if graphed:
             key = len(entries)

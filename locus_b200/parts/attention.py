@@ -20,7 +20,41 @@ from typing import Optional
 import torch
 
 from .. import kernels as K
-from .base import Mixer, PagedKvSpec, PartSpec, TensorSource, make_part, register_mixer
+from .base import Mixer, PagedKvSpec, PartSpec, StepPlan, TensorSource, make_part, register_mixer
+
+CHUNK_TILE = 16  # queries per work item of the CUDA-core chunk kernel
+
+
+class AttentionTiles(StepPlan):
+    """The work lists of this file's attention kernels: tiles of 16 queries (CUDA-core kernel) and of 64 queries
+    (tensor-core kernels) over the segments with more than one new token, and the segments with exactly one
+    (the decode kernel).  One plan serves every attention layer of a model.  The lists are made by two small
+    native helpers (csrc/host_core.cpp: ``locus_plan_query_tiles``, ``locus_plan_segments_with``)."""
+
+    key = ("attention.tiles", CHUNK_TILE, K.MMA_QUERY_TILE)
+
+    def __init__(self) -> None:
+        from ..cache import native
+
+        self._lib = native.lib()
+
+    def capacity(self, max_tokens: int, max_segments: int) -> int:
+        tiles = max_tokens // CHUNK_TILE + max_tokens // K.MMA_QUERY_TILE + 2 * max_segments
+        return 2 * tiles + max_segments
+
+    def build(self, seg_q0, seg_qn, seg_ctx, out):
+        n_seg, qn, cap = len(seg_qn), seg_qn.ctypes.data, len(out)
+        base = out.ctypes.data
+        n16 = self._lib.locus_plan_query_tiles(n_seg, qn, CHUNK_TILE, 2, base, cap)
+        o64 = 2 * max(n16, 0)
+        n64 = self._lib.locus_plan_query_tiles(n_seg, qn, K.MMA_QUERY_TILE, 2, base + 4 * o64, cap - o64)
+        o1 = o64 + 2 * max(n64, 0)
+        n1 = self._lib.locus_plan_segments_with(n_seg, qn, 1, base + 4 * o1, cap - o1)
+        if n16 < 0 or n64 < 0 or n1 < 0:
+            raise ValueError("attention: the step has more tiles than the plan's capacity holds")
+        return {"chunk_items": (0, 2 * n16, (-1, 2)), "n_chunk_items": n16,
+                "chunk_items64": (o64, 2 * n64, (-1, 2)), "n_chunk_items64": n64,
+                "decode_items": (o1, n1, None), "n_decode_items": n1}
 
 
 class Attention(Mixer):
@@ -70,6 +104,9 @@ class Attention(Mixer):
     def cache_needs(self):
         return PagedKvSpec(self.n_kv_heads, self.head_dim, self.window), None
 
+    def step_plans(self):
+        return [AttentionTiles()]
+
     # -- forward ------------------------------------------------------------
     def forward(self, h, batch, cache, residual, rt) -> None:
         T = batch.T
@@ -93,38 +130,42 @@ class Attention(Mixer):
                       block_table=gb.block_table, n_heads=self.n_heads, n_kv_heads=self.n_kv_heads,
                       head_dim=self.head_dim, page_tokens=gb.page_tokens, window=self.window,
                       scale=self.scale)
-        if batch.n_chunk_items:
+        tiles = batch.plans[AttentionTiles.key]
+        # splits of 128 keys that cover the longest context (all that the block table can describe when the
+        # step's launches must not depend on its lengths)
+        cap_splits = (gb.block_table.shape[1] * gb.page_tokens - 1) // K.DECODE_SPLIT + 1
+        max_splits = cap_splits if batch.static_shapes else min(cap_splits, (max(batch.longest, 1) - 1) // K.DECODE_SPLIT + 1)
+        if tiles["n_chunk_items"]:
             if K.attn_chunk_tc_takes(q, self.head_dim, gb.page_tokens, T):
-                K.attn_chunk_tc(q, cache.pool, o, items=batch.chunk_items64, n_items=batch.n_chunk_items64, **common)
+                K.attn_chunk_tc(q, cache.pool, o, items=tiles["chunk_items64"], n_items=tiles["n_chunk_items64"], **common)
             elif K.attn_chunk_mma_takes(q, self.head_dim):
                 # few 64-query tiles behind a long context: the keys of every tile are cut into ranges
-                keys = batch.max_splits * K.DECODE_SPLIT
+                keys = max_splits * K.DECODE_SPLIT
                 if self.window > 0:
                     keys = min(keys, self.window + K.MMA_QUERY_TILE)
-                n_splits = K.attn_chunk_mma_splits(batch.n_chunk_items64, self.n_heads, keys)
+                n_splits = K.attn_chunk_mma_splits(tiles["n_chunk_items64"], self.n_heads, keys)
                 part_o = part_ml = None
                 if n_splits > 1:
                     n_o, n_ml = K.attn_chunk_mma_scratch(self.head_dim)
                     part_o = rt.buf("attention.chunk_part_o", (n_o,), torch.float32)
                     part_ml = rt.buf("attention.chunk_part_ml", (n_ml,), torch.float32)
-                K.attn_chunk_mma(q, cache.pool, o, items=batch.chunk_items64, n_items=batch.n_chunk_items64,
+                K.attn_chunk_mma(q, cache.pool, o, items=tiles["chunk_items64"], n_items=tiles["n_chunk_items64"],
                                  n_splits=n_splits, part_o=part_o, part_ml=part_ml, **common)
             else:
-                K.attn_chunk(q, cache.pool, o, items=batch.chunk_items, n_items=batch.n_chunk_items, **common)
-        if batch.n_decode_items:
-            n = batch.n_decode_items
+                K.attn_chunk(q, cache.pool, o, items=tiles["chunk_items"], n_items=tiles["n_chunk_items"], **common)
+        if tiles["n_decode_items"]:
+            n = tiles["n_decode_items"]
             # scratch sized once, for the longest context that the block table can describe
-            cap_splits = (gb.block_table.shape[1] * gb.page_tokens - 1) // K.DECODE_SPLIT + 1
-            units = K.decode_units(rt.max_segments, self.n_heads, self.head_dim, q.dtype,
-                                   max(cap_splits, batch.max_splits), rt.device, gb.page_tokens)
+            units = K.decode_units(rt.max_segments, self.n_heads, self.head_dim, q.dtype, cap_splits, rt.device,
+                                   gb.page_tokens)
             part_o = rt.buf("attention.part_o", (units * self.head_dim,), torch.float32)
             part_ml = rt.buf("attention.part_ml", (2 * units,), torch.float32)
             counters = rt.shared_object(
                 ("attention.counters", rt.max_segments * self.n_heads),
                 lambda: torch.zeros(rt.max_segments * self.n_heads, dtype=torch.int32, device=rt.device),
             )
-            K.attn_decode(q, cache.pool, o, items=batch.decode_items, n_items=n, part_o=part_o,
-                          part_ml=part_ml, counters=counters, max_splits=batch.max_splits, **common)
+            K.attn_decode(q, cache.pool, o, items=tiles["decode_items"], n_items=n, part_o=part_o,
+                          part_ml=part_ml, counters=counters, max_splits=max_splits, **common)
         K.linear(o, self.params["wo"], residual, bias=self.params.get("bo"), accumulate=True)
 
 

@@ -95,11 +95,24 @@ class TensorSource:
 
 @dataclass(frozen=True)
 class PagedKvSpec:
-    """Keys and values of every token, in pages; ``window`` > 0: only the last ``window``."""
+    """What a mixer keeps per token, in pages: a key row of ``n_kv_heads * head_dim`` elements, a value row
+    of the same width unless ``has_v`` is off (a mixer that keeps one row per token: keys only, or a latent),
+    and ``extra_width`` further elements per token in a tensor of their own (per-token fields beside the
+    rows, as the reference appends them to its cache row, src/locus/model/arch.cpp:539-542).  ``window`` > 0:
+    only the last ``window`` tokens are kept; pages behind the window go back while the request lives."""
 
     n_kv_heads: int
     head_dim: int
     window: int = 0
+    has_v: bool = True
+    extra_width: int = 0
+
+    @property
+    def planes(self) -> int:
+        return 2 if self.has_v else 1
+
+    def elements_per_token(self) -> int:
+        return self.planes * self.n_kv_heads * self.head_dim + self.extra_width
 
 
 @dataclass(frozen=True)
@@ -181,11 +194,37 @@ class RotaryTable:
     interleaved: bool
 
 
+class StepPlan:
+    """Work lists that a part wants for every step, planned on the host from the step's segments: which
+    tiles of queries its kernels run, which segments take which kernel, and the like.  The step function knows
+    nothing of their meaning: it asks every distinct plan of the model (distinct by ``key``) once per step to
+    write its lists behind the step's descriptors, into the same pinned buffer, so that they reach the device
+    in the step's one copy; the part finds them as ``batch.plans[key]``.
+
+    ``capacity(max_tokens, max_segments)``: the most int32 values the plan writes for any step.
+    ``build(seg_q0, seg_qn, seg_ctx, out)``: the three arguments are host arrays (numpy int32 views of the
+    pinned buffer, one entry per segment); write the lists into ``out`` (numpy int32, ``capacity`` long) and
+    return ``{name: (offset in out, length, trailing shape or None)}`` for lists and ``{name: int}`` for plain
+    numbers (counts) that the part wants back."""
+
+    key: Tuple = ()
+
+    def capacity(self, max_tokens: int, max_segments: int) -> int:
+        raise NotImplementedError
+
+    def build(self, seg_q0, seg_qn, seg_ctx, out) -> Dict[str, Any]:
+        raise NotImplementedError
+
+
 class Mixer(Part):
     """Mixes information across the tokens of a request (attention here)."""
 
     def cache_needs(self) -> Tuple[Optional[PagedKvSpec], Optional[StateSpec]]:
         return None, None
+
+    def step_plans(self) -> List[StepPlan]:
+        """Host-planned work lists this mixer wants for every step (see :class:`StepPlan`)."""
+        return []
 
     def forward(self, h: torch.Tensor, batch: "StepBatch", cache: "LayerCache",
                 residual: torch.Tensor, rt: "Runtime") -> None:

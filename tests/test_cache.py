@@ -188,3 +188,54 @@ def test_a_closed_request_stays_closed_when_its_record_is_used_again():
     c.release(b)
     c.check_invariants()
     assert c.free_pages() == 4 and c.state_slots.free == 3
+
+
+def test_a_window_group_gets_a_pool_of_its_own_size():
+    """With the step size known, a group with a window holds what the live requests can hold at once (window + step,
+    in pages, plus one each), not as many pages as a group that keeps everything; requests are admitted against
+    each group's own need."""
+    c = CacheManager(_needs(window=20), page_tokens=16, n_pages=40, n_state_slots=3, max_seq_tokens=256,
+                     dtype=torch.float32, device="cpu", max_step_tokens=32)
+    full, win = c.groups
+    assert (full.n_pages, win.n_pages) == (40, 3 * (-(-(20 + 32) // 16) + 1)) and win.pool.shape[1] == 15
+    assert c.total_pages(0) == 40 and c.total_pages(1) == 15 and c.total_pages() == 15 == c.free_pages()
+    assert c.pages_needed(0, 200, 32) == 13 and c.pages_needed(1, 200, 32) == 5 and c.pages_needed(1, 30, 32) == 2
+    assert c.fits_when_empty(256, 32) and not c.fits_when_empty(41 * 16, 32)
+    # three requests of 200 tokens, fed 32 at a time: the window group never runs out
+    seqs = [c.open(i) for i in range(3)]
+    for a in range(0, 200, 32):
+        for s in seqs:
+            n = min(32, 200 - a)
+            assert c.ensure_capacity(s, n)
+            c.commit(s, n)
+            assert s.pages_held(1) <= 5
+        c.check_invariants()
+    assert c.free_pages(0) == 40 - 3 * 13
+    for s in seqs:
+        c.release(s)
+    assert c.free_pages(0) == 40 and c.free_pages(1) == 15
+    c.check_invariants()
+    # without a step size the window group is as large as the others
+    d = CacheManager(_needs(window=20), page_tokens=16, n_pages=40, n_state_slots=3, max_seq_tokens=256,
+                     dtype=torch.float32, device="cpu")
+    assert [g.n_pages for g in d.groups] == [40, 40]
+
+
+def test_rows_without_values_and_fields_beside_the_rows():
+    spec = PagedKvSpec(2, 16, 0, has_v=False, extra_width=3)
+    assert spec.planes == 1 and spec.elements_per_token() == 2 * 16 + 3
+    c = CacheManager([(spec, None, None), (PagedKvSpec(2, 16), None, None)], page_tokens=16, n_pages=4,
+                     n_state_slots=2, max_seq_tokens=64, dtype=torch.bfloat16, device="cpu", poison=True)
+    assert len(c.groups) == 2
+    assert c.groups[0].pool.shape == (1, 4, 1, 2, 16, 16) and c.groups[0].extra.shape == (1, 4, 16, 3)
+    assert c.groups[1].pool.shape == (1, 4, 2, 2, 16, 16) and c.groups[1].extra is None
+    assert c.bytes_per_token() == 2 * ((2 * 16 + 3) + 2 * 2 * 16)
+    lay = c.layer_caches()
+    assert lay[0].extra.shape == (4, 16, 3) and lay[1].extra is None and lay[0].pool.shape == (4, 1, 2, 16, 16)
+    s = c.open("r")
+    assert c.ensure_capacity(s, 20)
+    page = s.tables[0][0]
+    lay[0].extra[page] = 1.0
+    c.commit(s, 20)
+    c.release(s)
+    assert torch.isnan(lay[0].extra[page].float()).all()   # fields are poisoned with their page

@@ -152,9 +152,10 @@ def test_step_descriptors_match_a_plain_assembly(tmp_path):
     import random
 
     import locus_b200.kernels as K
-    from locus_b200.engine.step import CHUNK_TILE
+    from locus_b200.parts.attention import CHUNK_TILE, AttentionTiles
 
     cfg, W, model, cache, runner = setup("C", tmp_path, n_pages=40, page=16, max_tokens=96)
+    assert list(runner.plans) == [AttentionTiles.key]   # every attention layer shares the one plan
     assert any(g.spec.window > 0 for g in cache.groups) and any(g.spec.window == 0 for g in cache.groups)
     rng = random.Random(4)
     names = ["a", "b", "c", "d"]
@@ -171,13 +172,15 @@ def test_step_descriptors_match_a_plain_assembly(tmp_path):
         if not entries:
             continue
         want, want_groups = plain_descriptors(cache, entries, CHUNK_TILE, K.MMA_QUERY_TILE)
-        batch = runner._build(entries, fixed_splits=False)
+        batch = runner._build(entries, fixed_shapes=False)
+        tiles = batch.plans[AttentionTiles.key]   # the attention part's own work lists ride in the same buffer
         for k, v in want.items():
-            got = getattr(batch, k)
+            got = tiles[k] if k in tiles else getattr(batch, k)
             assert got.tolist() == v, (it, k)
         assert (batch.T, batch.n_seg, batch.n_want) == (len(want["tokens"]), len(entries), len(want["want_rows"]))
-        assert (batch.n_chunk_items, batch.n_chunk_items64, batch.n_decode_items) == (
+        assert (tiles["n_chunk_items"], tiles["n_chunk_items64"], tiles["n_decode_items"]) == (
             len(want["chunk_items"]), len(want["chunk_items64"]), len(want["decode_items"]))
+        assert batch.longest == max(e.seq.n_tokens + len(e.tokens) for e in entries) and not batch.static_shapes
         assert batch.host_seg_q0 == want["seg_q0"] and batch.host_seg_ctx == want["seg_ctx"]
         assert batch.host_seg_qn == want["seg_qn"] and batch.host_state_slots == want["state_slots"]
         for gid, g in want_groups.items():

@@ -1,6 +1,8 @@
 """The engine at the layer sizes of Qwen1.5-MoE-A2.7B (hidden 2048, 16 heads of 128, 60 experts of
-1408 with 4 picked, a shared expert of 5632, the vocabulary of 151,936; two layers of them) against
-the plain implementation in float64, in float32 and in bfloat16.
+1408 with 4 picked, a shared expert of 5632, the vocabulary of 151,936; two layers of them) and of
+Qwen2-57B-A14B (hidden 3584, 28 query heads on 4 key/value heads, 64 experts of 2560 with 8 picked, a
+shared expert of 20480; two layers) against the plain implementation in float64, in float32 and in
+bfloat16.
 
 The tiny configurations cannot reach what these sizes reach: the tensor-core products with their
 real tile shapes and token boxes, the tcgen05 attention kernel under sixteen heads, sixty experts
@@ -26,17 +28,32 @@ FULL = {
     "mlp_only_layers": [], "hidden_act": "silu", "eos_token_id": -1,
 }
 # Two experts whose probabilities in the oracle are this close (relative) may be swapped by the engine.
-# In bfloat16 the router reads activations rounded to 8 bits of mantissa.  Measured against the oracle at
-# this width, the engine's probabilities of the picked experts are off by 0.3% on average in the first
-# layer (1.5% at most among 2,400) and by 0.45% in the second: a logit error of sigma = 0.004 to 0.005, so
-# that the difference of two logits has sigma = 0.007 and a swap at a gap of 2% is a 3-sigma event, seen
-# about once among the 2,000 choices of this test.  3% is a little over 4 sigma.
+# In bfloat16 the router reads activations rounded to 8 bits of mantissa.  The bound is a little over four
+# sigma of the difference of two probabilities' errors, from the error of the engine's probabilities of the
+# picked experts against the oracle, measured at each size (400 tokens, two layers):
+#   A2.7B sizes:    rms 0.40 % in the first layer, 0.52 % in the second (largest of 3,200: 2.2 %): the
+#                   difference of two has sigma 0.7 %, a swap at a gap of 2 % is a 3-sigma event that shows up
+#                   about once among the 2,000 choices of this test; bound 3 %;
+#   57B-A14B sizes: rms 0.69 % and 1.08 % (largest of 6,400: 4.5 %; router logits of sigma 1.2 instead of 0.9
+#                   over a hidden size of 3584, eight picks of 64): sigma of the difference 1.5 %, bound 6.5 %.
+# In float32 the bound is the rounding of float32 sums.
 NEAR_TIE = {torch.float32: 1e-5, torch.bfloat16: 3e-2}
-LENGTHS = {"r0": 600, "r1": 331, "r2": 70}
-# the same requests cut two ways; (request, new tokens) per step
-WHOLE = [[("r0", 600)], [("r1", 331)], [("r2", 70)]]
-MIXED = [[("r0", 300), ("r2", 40)], [("r0", 256), ("r1", 77)], [("r0", 40), ("r1", 250), ("r2", 28)],
-         [("r0", 2), ("r1", 2), ("r2", 1)], [("r0", 1), ("r1", 1), ("r2", 1)], [("r0", 1), ("r1", 1)]]
+NEAR_TIE_57B = {torch.float32: 1e-5, torch.bfloat16: 6.5e-2}
+FULL57 = dict(FULL, hidden_size=3584, num_attention_heads=28, num_key_value_heads=4, num_experts=64,
+              num_experts_per_tok=8, moe_intermediate_size=2560, shared_expert_intermediate_size=20480,
+              intermediate_size=18944, max_position_embeddings=32768)
+# per size: configuration, weight seed, request lengths, and the same requests cut two ways ((request, new
+# tokens) per step): whole, and in portions beside one another and token by token
+SIZES = {
+    "a27b": dict(cfg=FULL, seed=3, near_tie=NEAR_TIE, lengths={"r0": 600, "r1": 331, "r2": 70},
+                 whole=[[("r0", 600)], [("r1", 331)], [("r2", 70)]],
+                 mixed=[[("r0", 300), ("r2", 40)], [("r0", 256), ("r1", 77)], [("r0", 40), ("r1", 250), ("r2", 28)],
+                        [("r0", 2), ("r1", 2), ("r2", 1)], [("r0", 1), ("r1", 1), ("r2", 1)], [("r0", 1), ("r1", 1)]]),
+    "57b-a14b": dict(cfg=FULL57, seed=4, near_tie=NEAR_TIE_57B, lengths={"r0": 400, "r1": 200, "r2": 70},
+                     whole=[[("r0", 400)], [("r1", 200)], [("r2", 70)]],
+                     mixed=[[("r0", 220), ("r2", 40)], [("r0", 158), ("r1", 50)], [("r0", 20), ("r1", 147), ("r2", 28)],
+                            [("r0", 1), ("r1", 2), ("r2", 1)], [("r0", 1), ("r1", 1), ("r2", 1)]]),
+}
 
 
 def wanted(n):
@@ -45,15 +62,18 @@ def wanted(n):
 
 
 class FullCase:
-    def __init__(self, tmp):
+    def __init__(self, tmp, size):
         from locus_b200.weights.loader import write_random_model
         import locus_b200.models  # noqa: F401
 
-        self.dir = write_random_model(FULL, 3, str(tmp / "full"), torch.bfloat16, device="cuda:0")
+        spec = SIZES[size]
+        self.lengths, self.whole, self.mixed, self.near_tie = spec["lengths"], spec["whole"], spec["mixed"], spec["near_tie"]
+        LENGTHS = self.lengths
+        self.dir = write_random_model(spec["cfg"], spec["seed"], str(tmp / "full"), torch.bfloat16, device="cuda:0")
         self.cfg, self.weights = plain.load_folder(self.dir)
-        self.tokens = {rid: random_tokens(n, FULL["vocab_size"], 40 + n) for rid, n in LENGTHS.items()}
+        self.tokens = {rid: random_tokens(n, spec["cfg"]["vocab_size"], 40 + n) for rid, n in LENGTHS.items()}
         self.positions = {}
-        for steps in (WHOLE, MIXED):
+        for steps in (self.whole, self.mixed):
             fed = {}
             for step in steps:
                 for rid, n in step:
@@ -104,9 +124,13 @@ class FullCase:
         return lg
 
 
-@pytest.fixture(scope="module")
-def full(tmp_path_factory):
-    return FullCase(tmp_path_factory.mktemp("full_size"))
+@pytest.fixture(scope="module", params=sorted(SIZES))
+def full(request, tmp_path_factory):
+    case = FullCase(tmp_path_factory.mktemp("full_size_" + request.param.replace("-", "_")), request.param)
+    yield case
+    import shutil
+
+    shutil.rmtree(case.dir, ignore_errors=True)   # up to 10 GB of weights
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -122,7 +146,8 @@ def test_full_layer_sizes(full, dtype):
     cache = CacheManager(model.cache_needs(), page_tokens=64, n_pages=18, n_state_slots=4, max_seq_tokens=1024,
                          dtype=dtype, device="cuda:0", poison=True)
     runner = ModelRunner(model, cache, max_tokens=640, max_segments=4)
-    for steps in (WHOLE, MIXED):
+    LENGTHS = full.lengths
+    for steps in (full.whole, full.mixed):
         seen = []
         for part in model.all_parts():
             if hasattr(part, "observer"):
@@ -154,7 +179,7 @@ def test_full_layer_sizes(full, dtype):
         assert cache.free_pages() == cache.total_pages()
         tol_max, tol_mean = TOL[dtype]
         for rid in LENGTHS:
-            ref = full.following(rid, routed[rid], NEAR_TIE[dtype])
+            ref = full.following(rid, routed[rid], full.near_tie[dtype])
             places = full.positions[rid]
             mine = torch.stack([got[rid][p] for p in places if p in got[rid]]).double()
             ref = ref[[i for i, p in enumerate(places) if p in got[rid]]]

@@ -133,14 +133,26 @@ def _batch(cache, seq, n, rt):
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
     table = seq.tables[0] + [-1] * (cache.table_width - len(seq.tables[0]))
     slots = [seq.tables[0][p // P] * P + p % P for p in range(ctx, ctx + n)]
-    items16 = [(0, o) for o in range(0, n, 16)] if n > 1 else []
-    items64 = [(0, o) for o in range(0, n, K.MMA_QUERY_TILE)] if n > 1 else []
+    import numpy as np
+
+    from locus_b200.parts.attention import AttentionTiles
+
+    # the part's own step plan, built as the step function builds it: lists into a host buffer, then to the device
+    plan = AttentionTiles()
+    host = np.zeros(plan.capacity(n, 1), dtype=np.int32)
+    res = plan.build(np.array([0], dtype=np.int32), np.array([n], dtype=np.int32), np.array([ctx], dtype=np.int32), host)
+    dev = torch.from_numpy(host).to(DEV)
+    tiles = {}
+    for name, v in res.items():
+        if isinstance(v, tuple):
+            t = dev[v[0] : v[0] + v[1]]
+            tiles[name] = t.view(*v[2]) if v[2] else t
+        else:
+            tiles[name] = v
+    assert tiles["n_decode_items"] == (1 if n == 1 else 0) and tiles["n_chunk_items64"] == (-(-n // K.MMA_QUERY_TILE) if n > 1 else 0)
     b = StepBatch(T=n, n_seg=1, tokens=i32([0] * n), positions=i32(list(range(ctx, ctx + n))), seg_q0=i32([0]),
                   seg_qn=i32([n]), seg_ctx=i32([ctx]), state_slots=i32([0]), want_rows=i32([]), n_want=0,
-                  chunk_items=i32(items16).view(-1, 2), n_chunk_items=len(items16),
-                  chunk_items64=i32(items64).view(-1, 2), n_chunk_items64=len(items64),
-                  decode_items=i32([0] if n == 1 else []), n_decode_items=1 if n == 1 else 0,
-                  max_splits=(ctx + n - 1) // K.DECODE_SPLIT + 1)
+                  longest=ctx + n, plans={AttentionTiles.key: tiles})
     b.groups[0] = GroupBatch(block_table=i32(table).view(1, -1), slots=i32(slots), page_tokens=P)
     return b
 

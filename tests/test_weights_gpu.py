@@ -38,7 +38,8 @@ A27B = {
     "intermediate_size": 5632, "qkv_bias": True, "tie_word_embeddings": False, "use_sliding_window": False,
     "mlp_only_layers": [], "hidden_act": "silu", "eos_token_id": -1,
 }
-NEAR_TIE = 3e-2   # see tests/test_full_size_gpu.py: what bfloat16 activations do to the router's probabilities
+# see tests/test_full_size_gpu.py: what bfloat16 activations do to the router's probabilities
+NEAR_TIE = {torch.bfloat16: 3e-2, torch.float32: 1e-5}
 
 
 class DrawnOnRead:
@@ -58,10 +59,12 @@ class DrawnOnRead:
         return self.draw(self.src[name])
 
 
-def test_all_24_layers_against_the_plain_implementation():
-    """A 300-token prompt in one step (tcgen05 attention, grouped expert products), then two decode steps from
-    the cache, through all 24 layers in bfloat16; the plain implementation follows the engine's expert choices
-    (checked to be near-ties where they differ from its own) and compares logits at sampled positions."""
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_all_24_layers_against_the_plain_implementation(dtype):
+    """A 300-token prompt in one step (in bfloat16: tcgen05 attention, grouped expert products on the tensor
+    cores; in float32: the CUDA-core path, 57 GB of weights), then two decode steps from the cache, through all
+    24 layers; the plain implementation follows the engine's expert choices (checked to be near-ties where they
+    differ from its own) and compares logits at sampled positions."""
     import locus_b200.models  # noqa: F401
     from locus_b200.cache import CacheManager
     from locus_b200.config import find_arch
@@ -69,11 +72,11 @@ def test_all_24_layers_against_the_plain_implementation():
     from locus_b200.models.model import Model
     from locus_b200.weights.loader import RandomSource, load_weights
 
-    seed, dtype = 2, torch.bfloat16
+    seed = 2
     entry = find_arch("Qwen2MoeForCausalLM")
     model = Model(entry.build_plan(entry.parse_config(A27B)), dtype, DEV)
     load_weights(model, RandomSource(model, seed, dtype, DEV))
-    assert abs(model.param_bytes() / 1e9 - 28.63) < 0.05
+    assert abs(model.param_bytes() / 1e9 - (28.63 if dtype == torch.bfloat16 else 57.26)) < 0.1
     cache = CacheManager(model.cache_needs(), page_tokens=64, n_pages=6, n_state_slots=2, max_seq_tokens=384,
                          dtype=dtype, device=DEV, poison=True)
     runner = ModelRunner(model, cache, max_tokens=320, max_segments=2)
@@ -110,11 +113,11 @@ def test_all_24_layers_against_the_plain_implementation():
                 n_diff += 1
                 kth = min(float(probs[e]) for e in ids)
                 for e in eng:
-                    assert float(probs[e]) >= kth * (1 - NEAR_TIE), (prefix, pos, e, float(probs[e]), kth)
+                    assert float(probs[e]) >= kth * (1 - NEAR_TIE[dtype]), (prefix, pos, e, float(probs[e]), kth)
     # How many may differ: the 4th and 5th best of 60 router logits (sigma 0.9 with these weights) lie about 0.09
     # apart on average, the engine's logits carry an error of sigma 0.007 (bfloat16 activations), so a swap is
     # expected at about 0.8 * 0.007 / 0.09 = 6 % of the (layer, position) pairs; far more would be a fault.
-    assert n_diff < 0.10 * 24 * 302, f"{n_diff} choices differ"
+    assert n_diff < (0.10 * 24 * 302 if dtype == torch.bfloat16 else 4), f"{n_diff} choices differ"
     tol_max, tol_mean = TOL[dtype]
     scale = float(ref.abs().max())
     err = (got - ref).abs()
