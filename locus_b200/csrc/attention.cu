@@ -11,6 +11,7 @@
 // size that is a multiple of 16 up to 256, any number of heads and any group ratio.
 // Cache layout of one layer: [n_pages][2 (K, V)][nkv][page_tokens][hd].
 #include "common.cuh"
+#include "attn_ranges.cuh"
 
 struct AttnArgs {
     const void* q;            // [T, nh * hd]
@@ -396,8 +397,6 @@ __global__ void __launch_bounds__(128) attn_decode_split_kernel(AttnArgs a) {
 #define DS_LOADS 8        // load instructions per chunk
 #define DS_OVERHEAD 64    // fixed cost of a range, in keys
 #define DS_MERGE 2        // cost of merging one more range, in keys
-#define DS_CAND 256       // candidate range lengths looked at
-#define DS_MAX_ITEMS 1024
 
 // a 16-byte load of cache data that is read once: no line of L1 is spent on it
 __device__ __forceinline__ uint4 ld_once(const uint4* p) {
@@ -423,63 +422,15 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
     const int hd = a.hd, P = a.page_tokens;
 
     // ---- how the batch is cut into ranges (the same result in every block) ----
-    __shared__ int s_first[DS_MAX_ITEMS];   // first key of item i, rounded down to 32
-    __shared__ int s_nkeys[DS_MAX_ITEMS];   // keys from there to the query's own position
-    __shared__ int s_pref[DS_MAX_ITEMS + 1];  // ranges of the items before i
-    __shared__ int s_seg[DS_MAX_ITEMS], s_pos[DS_MAX_ITEMS], s_row[DS_MAX_ITEMS];  // segment, position, row of q / out
-    __shared__ unsigned long long s_best[DS_WARPS];
-    __shared__ int s_len;
-    int longest = 0;
-    for (int i = tid; i < n_items; i += blockDim.x) {
-        const int seg = a.items[i];
-        const int p = a.seg_ctx[seg];
-        const int t_lo = a.window > 0 ? max(0, p - a.window + 1) : 0;
-        const int first = t_lo & ~31;
-        s_first[i] = first;
-        s_nkeys[i] = p - first + 1;
-        s_seg[i] = seg;
-        s_pos[i] = p;
-        s_row[i] = a.seg_q0[seg];
-    }
-    __syncthreads();
-    for (int i = 0; i < n_items; ++i) longest = max(longest, s_nkeys[i]);
+    __shared__ KeyRanges kr;
     const int n_warps = gridDim.x * DS_WARPS;
-    {
-        // candidates: multiples of `step` keys; a thread looks at two of them
-        const int step = 32 * ((longest + 32 * DS_CAND - 1) / (32 * DS_CAND));
-        unsigned long long best = ~0ull;
-        for (int c = tid; c < DS_CAND; c += blockDim.x) {
-            const int len = step * (c + 1);
-            if (len - step >= longest && c > 0) break;  // longer than any context: same cut as the one before
-            long long units = 0;
-            for (int i = 0; i < n_items; ++i) units += (s_nkeys[i] + len - 1) / len;
-            units *= a.nh;
-            if (units > max_units) continue;  // the scratch does not hold that many partial results
-            const long long rounds = (units + n_warps - 1) / n_warps;
-            // the merge of a (request, head) runs in one warp and grows with its number of ranges
-            const unsigned long long cost = static_cast<unsigned long long>(rounds) * (len + cost_range) +
-                                            cost_merge * static_cast<unsigned long long>((longest + len - 1) / len);
-            best = min(best, (cost << 24) | static_cast<unsigned>(c));  // ties: the shorter range
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, o));
-        if (lane == 0) s_best[warp] = best;
-        __syncthreads();
-        if (tid == 0) {
-            unsigned long long b = s_best[0];
-            for (int w = 1; w < DS_WARPS; ++w) b = min(b, s_best[w]);
-            // nothing fits (a scratch smaller than one range per (request, head)): refused on the host
-            s_len = b == ~0ull ? 0 : step * (static_cast<int>(b & 0xffffff) + 1);
-            int acc = 0;
-            const int len = max(32, s_len);
-            for (int i = 0; i < n_items; ++i) {
-                s_pref[i] = acc;
-                acc += (s_nkeys[i] + len - 1) / len;
-            }
-            s_pref[n_items] = acc;
-        }
-        __syncthreads();
-    }
+    plan_key_ranges(kr, a.items, a.seg_ctx, a.seg_q0, a.window, n_items, a.nh, max_units, n_warps, cost_range, cost_merge);
+    int* const s_first = kr.first;
+    int* const s_pref = kr.pref;
+    int* const s_seg = kr.seg;
+    int* const s_pos = kr.pos;
+    int* const s_row = kr.row;
+    const int s_len = kr.len;
     const int len = s_len;
     if (len == 0) return;
     const int n_ranges = s_pref[n_items];

@@ -40,7 +40,8 @@ HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
 HEADERS = ["common.cuh"]
 
 # module name -> further headers its library depends on
-MODULE_HEADERS: Dict[str, List[str]] = {"attention": ["attention_static.h"]}
+MODULE_HEADERS: Dict[str, List[str]] = {"attention": ["attention_static.h", "attn_ranges.cuh"],
+                                        "attention_gqa": ["attn_ranges.cuh"]}
 
 # module name -> extra nvcc flags
 MODULE_FLAGS: Dict[str, List[str]] = {}

@@ -245,6 +245,11 @@ class ModelRunner:
             if code:
                 raise RuntimeError(f"decode attention fault (code {code}): the step's split count did not cover its "
                                    "longest context; results since the last check are invalid")
+        if self.device.type == "cuda" and "attention_gqa" in K._LIBS:
+            code = K.attn_gqa_error()
+            if code:
+                raise RuntimeError(f"grouped-query decode attention fault (code {code}): a wait for a bulk copy ran out; "
+                                   "results since the last check are invalid")
         if self.device.type == "cuda" and "attention_tc" in K._LIBS:
             code = K.attn_tc_error()
             if code:

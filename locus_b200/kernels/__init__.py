@@ -624,7 +624,35 @@ def attn_error() -> int:
     return int(_lib("attention").locus_attn_error())
 
 
+def attn_gqa_error() -> int:
+    """Error word of the grouped-query decode attention module (0 = fine; 1 = a wait for a bulk copy ran out);
+    reading it synchronises the device and clears it."""
+    return int(_lib("attention_gqa").locus_attn_gqa_error())
+
+
 DECODE_SPLIT = 128
+
+
+USE_GQA_DECODE = True   # tests switch it off to run grouped-query models on the per-head kernels
+# The range cut's cost model of the grouped-query kernel, in keys (csrc/attn_ranges.cuh): the fixed cost of a range,
+# and the cost of merging one more range per query head of the group (the merging warp takes the group's heads two
+# at a time).  Measured at 28 heads on 4, 8,192 keys: with 2 x 7 = 14 keys per range a call takes 50 / 51 / 52 /
+# 65 / 196 us at 1 / 4 / 8 / 16 / 64 requests (2: 51 / 52 / 51 / 66 / 202; 35: 75 / 76 / 74 / 75 / 196).
+GQA_COST_RANGE, GQA_COST_MERGE_PER_HEAD = 64, 2
+# Fewer (request, key/value head) pairs than this: the per-head kernels, which cut the work G times finer (at 28
+# heads on 4 and 8,192 keys: 25 / 37 / 55 / 96 us at 1 / 2 / 4 / 8 requests against 50 / 50 / 51 / 52).
+GQA_MIN_UNITS = 16
+
+
+def attn_decode_gqa_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, head_dim: int, page_tokens: int,
+                          n_items: int) -> bool:
+    """Whether :func:`attn_decode` runs the grouped-query kernel (csrc/attention_gqa.cu): bfloat16, 2 to 16
+    query heads per key/value head, head size 64 or 128, pages of a multiple of 16 tokens, and enough
+    (request, key/value head) pairs to fill the GPU with whole groups."""
+    g = n_heads // max(1, n_kv_heads)
+    return (USE_GQA_DECODE and USE_TENSOR_CORES and dtype == torch.bfloat16 and n_heads % max(1, n_kv_heads) == 0
+            and 2 <= g <= 16 and head_dim in (64, 128) and page_tokens % 16 == 0 and n_items <= 1024
+            and n_items * n_kv_heads >= GQA_MIN_UNITS)
 
 
 def decode_streams(head_dim: int, dtype: torch.dtype, page_tokens: int, max_items: int) -> bool:
@@ -636,18 +664,25 @@ def decode_streams(head_dim: int, dtype: torch.dtype, page_tokens: int, max_item
 
 
 def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype, max_splits: int, device,
-                 page_tokens: int = 64) -> int:
+                 page_tokens: int = 64, n_kv_heads: int = 0) -> int:
     """How many partial results the scratch of :func:`attn_decode` should hold for batches of up to
-    ``max_items`` requests: for the streaming kernel (:func:`decode_streams`) one per
-    (request, head) plus eight rounds of the grid's warps, so that short batches can be cut finely;
-    for other head and page sizes one per (request, head, split), ``max_splits`` being the splits of the
-    longest context that the cache allows."""
+    ``max_items`` requests.  The streaming kernels (:func:`decode_streams`, :func:`attn_decode_gqa_takes`) want
+    one per (request, head) plus eight rounds of the grid's warps, so that short batches can be cut finely; the
+    split kernel (other head and page sizes; and the small batches of a grouped-query model whose rows the
+    per-head streaming kernel does not take) wants one per (request, head, split), ``max_splits`` being the
+    splits of the longest context that the cache allows."""
+    try:
+        n_sm = torch.cuda.get_device_properties(device).multi_processor_count
+    except Exception:  # no GPU (host tests with emulated kernels)
+        n_sm = 148
+    streaming = max_items * n_heads + 8 * 16 * n_sm
     if decode_streams(head_dim, dtype, page_tokens, max_items):
-        try:
-            n_sm = torch.cuda.get_device_properties(device).multi_processor_count
-        except Exception:  # no GPU (host tests with emulated kernels)
-            n_sm = 148
-        return max_items * n_heads + 8 * 16 * n_sm
+        return streaming
+    if n_kv_heads > 0 and attn_decode_gqa_takes(dtype, n_heads, n_kv_heads, head_dim, page_tokens,
+                                                max(max_items, GQA_MIN_UNITS)):
+        # batches below GQA_MIN_UNITS pairs go to the split kernel
+        small = min(max_items, max(0, -(-GQA_MIN_UNITS // n_kv_heads) - 1))
+        return max(streaming, small * n_heads * max_splits)
     return max_items * n_heads * max_splits
 
 
@@ -675,6 +710,16 @@ def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q
     _need(pool.numel() * pool.element_size() < (64 << 30), "attn_decode: a layer's cache pool of 64 GiB or more")
     _i32(counters, "counters")
     _need(counters.numel() >= n_items * n_heads, "attn_decode: counters too small")
+    if attn_decode_gqa_takes(q.dtype, n_heads, n_kv_heads, head_dim, page_tokens, n_items):
+        # several query heads per key/value head: the kernel that reads every cache row once for its whole group
+        code = _lib("attention_gqa").locus_attn_decode_gqa(
+            _p(q), _p(pool), _p(out), _p(seg_q0), _p(seg_ctx), _p(block_table), I(block_table.shape[1]), _p(items),
+            I(n_items), I(n_heads), I(n_kv_heads), I(head_dim), I(page_tokens), I(window), F(scale), _p(part_o),
+            _p(part_ml), _p(counters), ctypes.c_longlong(max_units), I(GQA_COST_RANGE),
+            I(GQA_COST_MERGE_PER_HEAD * (n_heads // n_kv_heads)), _stream()
+        )
+        _check(code, "attn_decode", f"(grouped queries; heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
+        return
     code = _lib("attention").locus_attn_decode(
         _p(q), I(dtype_code(q.dtype)), _p(pool), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
         _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads),

@@ -99,7 +99,7 @@ class Attention(Mixer):
         return out
 
     def kernel_modules(self, dtype):
-        return ["elementwise", "gemm_simt", "gemv", "attention"] + (["gemm_skinny", "gemm_tc", "attention_mma", "attention_tc"] if dtype == torch.bfloat16 else [])
+        return ["elementwise", "gemm_simt", "gemv", "attention"] + (["gemm_skinny", "gemm_tc", "attention_mma", "attention_tc", "attention_gqa"] if dtype == torch.bfloat16 else [])
 
     def cache_needs(self):
         return PagedKvSpec(self.n_kv_heads, self.head_dim, self.window), None
@@ -157,7 +157,7 @@ class Attention(Mixer):
             n = tiles["n_decode_items"]
             # scratch sized once, for the longest context that the block table can describe
             units = K.decode_units(rt.max_segments, self.n_heads, self.head_dim, q.dtype, cap_splits, rt.device,
-                                   gb.page_tokens)
+                                   gb.page_tokens, self.n_kv_heads)
             part_o = rt.buf("attention.part_o", (units * self.head_dim,), torch.float32)
             part_ml = rt.buf("attention.part_ml", (2 * units,), torch.float32)
             counters = rt.shared_object(

@@ -517,6 +517,56 @@ def test_attn_decode(dtype, nh, nkv, hd, P, window):
         assert int(counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("nh,nkv,hd,P,window", [(28, 4, 128, 64, 0), (6, 2, 64, 16, 0), (12, 1, 128, 16, 0), (32, 2, 64, 32, 0),
+                                                (14, 2, 128, 64, 333), (8, 4, 64, 48, 40), (16, 1, 128, 64, 0)])
+def test_attn_decode_grouped_queries(nh, nkv, hd, P, window, monkeypatch):
+    """Several query heads per key/value head: the kernel that serves a whole group from one pass over the keys
+    (tensor cores, csrc/attention_gqa.cu), against the plain attention and against the per-head kernel; groups of
+    2 to 16 heads, both head sizes, windows, contexts from one key to thousands, lengths that end anywhere in a
+    chunk of 16 keys."""
+    segs = [(0, 1), (15, 1), (16, 1), (255, 1), (1000, 1), (2047, 1), (33, 1), (4200, 1)]
+    dtype = torch.bfloat16
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=nh + hd, n_pages=sum(-(-(c + 1) // P) for c, _ in segs) + 2)
+    monkeypatch.setattr(K, "GQA_MIN_UNITS", 1)   # also the batches that the engine would give to the per-head kernels
+    assert K.attn_decode_gqa_takes(dtype, nh, nkv, hd, P, len(segs))
+    items = torch.tensor([3, 0, 7, 1, 2, 4, 6, 5], dtype=torch.int32)   # items in another order than the segments
+    max_splits = 4200 // K.DECODE_SPLIT + 1
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=window, scale=1 / math.sqrt(hd))
+    units = K.decode_units(len(segs), nh, hd, dtype, max_splits, DEV, P, nkv)
+    part_o = torch.full((units * hd,), float("nan"), device=DEV)
+    part_ml = torch.full((2 * units,), float("nan"), device=DEV)
+    counters = torch.zeros(len(segs) * nh, dtype=torch.int32, device=DEV)
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.attn_decode(q, pool, ref, items=items, n_items=len(segs), part_o=None, part_ml=None, counters=None,
+                   max_splits=max_splits, **meta, **kw)
+    outs = {}
+    for gqa in (True, False):
+        K.USE_GQA_DECODE = gqa
+        try:
+            for again in range(2):
+                out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
+                pu = part_o if gqa else torch.full((len(segs) * nh * max_splits * hd,), float("nan"), device=DEV)
+                pm = part_ml if gqa else torch.full((2 * len(segs) * nh * max_splits,), float("nan"), device=DEV)
+                K.attn_decode(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=len(segs), part_o=pu,
+                              part_ml=pm, counters=counters, max_splits=max_splits, **_dev(meta), **kw)
+                close(out, ref, dtype, f"attn_decode, grouped queries ({'group' if gqa else 'per head'} kernel)")
+                assert int(counters.abs().sum()) == 0
+            outs[gqa] = out
+        finally:
+            K.USE_GQA_DECODE = True
+    # a scratch that holds just one partial result per (request, head): one range each, still right
+    tight_o = torch.full((len(segs) * nh * hd,), float("nan"), device=DEV)
+    tight_ml = torch.full((2 * len(segs) * nh,), float("nan"), device=DEV)
+    out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
+    K.attn_decode(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=len(segs), part_o=tight_o, part_ml=tight_ml,
+                  counters=counters, max_splits=max_splits, **_dev(meta), **kw)
+    close(out, ref, dtype, "attn_decode, grouped queries, one range per request")
+    monkeypatch.undo()
+    assert K.attn_decode_gqa_takes(dtype, 28, 4, 128, 64, 4) and not K.attn_decode_gqa_takes(dtype, 28, 4, 128, 64, 3)
+    assert not K.attn_decode_gqa_takes(torch.float32, nh, nkv, hd, P, 64) and not K.attn_decode_gqa_takes(dtype, 4, 4, hd, P, 64)
+    assert not K.attn_decode_gqa_takes(dtype, 34, 2, hd, P, 64) and not K.attn_decode_gqa_takes(dtype, nh, nkv, 96, P, 64)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [0, 3000])
 def test_attn_decode_long_contexts(dtype, window):
