@@ -177,6 +177,8 @@ def main() -> int:
     raw = dict(conf["raw"], num_hidden_layers=args.layers)
     if max(ctx, PREFILL_TOKENS) > raw["max_position_embeddings"]:
         raw["max_position_embeddings"] = max(ctx, PREFILL_TOKENS)  # a longer synthetic context than the model was trained for
+    if args.trace:
+        raw["max_position_embeddings"] = max(raw["max_position_embeddings"], 8192)
     entry = find_arch("Qwen2MoeForCausalLM")
     cfg = entry.parse_config(raw)
     t0 = time.time()
@@ -195,9 +197,10 @@ def main() -> int:
                             allocate_device=False).bytes_per_token() * P
     free, _ = torch.cuda.mem_get_info()
     n_pages = min(pages_wanted, int((free - (12 << 30)) // per_page))
+    TRACE_CONTEXT = 8192   # the trace's requests hold up to 4,096 + 512 tokens
+    max_seq = max(ctx, PREFILL_TOKENS, TRACE_CONTEXT if args.trace else 0)
     cache = CacheManager(model.cache_needs(), page_tokens=P, n_pages=n_pages, n_state_slots=max_b,
-                         max_seq_tokens=max(ctx, PREFILL_TOKENS),
-                         dtype=dtype, device=dev)
+                         max_seq_tokens=max_seq, dtype=dtype, device=dev)
     for g in cache.groups:  # synthetic cache contents for the steps that start from an adopted context
         flat = g.pool.view(-1)
         step = 1 << 28
@@ -383,7 +386,10 @@ def main() -> int:
         sec = time.perf_counter() - t1
         eng.check_device_errors()
         recs = [eng.get(r) for r in rids]
-        assert all(r.status.value == "done" and len(r.generated) == n for r, n in zip(recs, news)), "a trace request failed"
+        bad = [(r.id, r.status.value, r.error, len(r.generated), n) for r, n in zip(recs, news)
+               if r.status.value != "done" or len(r.generated) != n]
+        if bad:
+            raise SystemExit(f"bench.py: trace requests failed: {bad[:4]}")
         gen_tokens = sum(news)
         trace = {"requests": n_req, "prompt_tokens": sum(lens), "generated_tokens": gen_tokens, "steps": n_steps,
                  "seconds": sec, "tokens_per_s": (sum(lens) + gen_tokens) / sec, "generated_per_s": gen_tokens / sec,

@@ -14,6 +14,7 @@
 // every load is a full 16-byte vector of one row.  The order of the sum of an element
 // depends on K only.
 #include "common.cuh"
+#include "route_select.cuh"
 
 #define SK_WARPS 8
 #define SK_ROWS 16
@@ -38,6 +39,17 @@ struct SkinnyArgs {
     const int* tile_rows;
     const int* n_tiles;
     long long w_expert_stride;
+    // Optional tail (the router of a decode-sized batch): when route_counter is set, `out` holds float32 router
+    // logits [T, ldo] of all T = M tokens (one row tile), and the block that finishes last selects every token's
+    // experts from them and lays the pairs out by expert (route_select.cuh), all in this launch.  The counter is
+    // zero before the launch and zero after it.
+    int* route_counter;
+    int* route_ids;
+    float* route_wts;
+    float* route_gamma;
+    int route_experts, route_has_gate;
+    RouteOpts route_opts;
+    RouteLayoutOut route_layout;
 };
 
 __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
@@ -50,7 +62,7 @@ __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uin
 
 __device__ __forceinline__ uint4 ld_stream(const bf16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
 
-template <int NT, bool DUAL>
+template <int NT, bool DUAL, bool ROUTE = false>
 __global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
     pdl_entry();
     extern __shared__ float red[];  // [SK_WARPS][(DUAL ? 2 : 1)][NT][16 * 8]
@@ -173,15 +185,38 @@ __global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
             st_dyn(a.out, a.out_dt, o, v);
         }
     }
+    if (ROUTE) {
+        // the block that writes its logits last routes: selection and expert layout from the complete logits
+        __shared__ int is_last;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            is_last = atomicAdd(a.route_counter, 1) == static_cast<int>(gridDim.x) - 1;
+            if (is_last) *a.route_counter = 0;
+        }
+        __syncthreads();
+        if (!is_last) return;
+        __threadfence();
+        route_small_block(red, static_cast<const float*>(a.out), static_cast<int>(a.ldo), a.route_ids, a.route_wts,
+                          a.route_gamma, a.M, a.route_experts, a.route_has_gate, a.route_opts, a.route_layout);
+    }
 }
 
 template <int NT>
-static int launch(const SkinnyArgs& a, int tiles, bool dual, cudaStream_t stream) {
+static int launch(const SkinnyArgs& a, int tiles, bool dual, cudaStream_t stream, size_t smem_tail = 0) {
     dim3 grid(ceil_div(a.N, SK_ROWS), tiles);
     if (grid.x == 0 || grid.y == 0) return 0;
     if (grid.y > 65535) return LOCUS_ERR_UNSUPPORTED;
-    const size_t smem = sizeof(float) * SK_WARPS * (dual ? 2 : 1) * NT * 128;
-    if (dual) {
+    size_t smem = sizeof(float) * SK_WARPS * (dual ? 2 : 1) * NT * 128;
+    if (smem_tail > smem) smem = smem_tail;
+    if (smem > 200 * 1024) return LOCUS_ERR_UNSUPPORTED;
+    if (a.route_counter != nullptr) {
+        if (dual || NT > 2) return LOCUS_ERR_UNSUPPORTED;
+        constexpr int NTR = NT > 2 ? 2 : NT;
+        if (smem > 48 * 1024)
+            cudaFuncSetAttribute(skinny_kernel<NTR, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        locus_launch(skinny_kernel<NTR, false, true>, grid, 32 * SK_WARPS, smem, stream, a);
+    } else if (dual) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(skinny_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         locus_launch(skinny_kernel<NT, true>, grid, 32 * SK_WARPS, smem, stream, a);
@@ -213,9 +248,43 @@ extern "C" int locus_gemm_skinny(const void* x, const void* w, const void* w2, c
     a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows; a.x_row_div = x_row_div;
     a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldo = ldo; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.w_expert_stride = w_expert_stride;
+    a.route_counter = nullptr;
     const int tiles = tile_expert ? max_tiles : ceil_div(M, tile_tokens);
     const bool dual = w2 != nullptr;
     if (tile_tokens == 8) return launch<1>(a, tiles, dual, stream);
     if (tile_tokens == 16) return launch<2>(a, tiles, dual, stream);
     return launch<4>(a, tiles, dual, stream);
+}
+
+// The router of a decode-sized batch in one launch: logits[t, e] = w_all[e] . h[t] for the E (+1 with a gate) rows of
+// w_all by the kernel above -- the same kernel, and the same order of every sum, as locus_gemm_skinny gives for any
+// number of tokens -- and in its last block the selection (locus_router_select) and the expert layout
+// (locus_moe_sort) of route_select.cuh.  T <= 16 tokens (one row tile), T * k <= RS_MAX_PAIRS, E <= RS_MAX_E.
+// counter: one int, zero before the call and zero after it.
+extern "C" int locus_router_fused_small(const void* h, const void* w_all, float* logits, int ld, int* counter, int* ids,
+                                        float* wts, float* gamma, int T, int H, long long ldh, int E, int k, int has_gate,
+                                        int renorm, float scale, int score_fn, const float* sel_bias, int n_group,
+                                        int n_group_used, int tile_m, int* counts, int* offsets, int* sorted_pair,
+                                        int* pair_pos, int* tile_expert, int* tile_row0, int* tile_rows, int* n_tiles,
+                                        cudaStream_t stream) {
+    if (T <= 0) return 0;
+    const RouteOpts o{k, renorm, score_fn, n_group, n_group_used, scale, sel_bias};
+    const int n_rows = E + (has_gate ? 1 : 0);
+    if (!route_opts_ok(o, E) || ld < n_rows || tile_m <= 0 || counter == nullptr) return LOCUS_ERR_UNSUPPORTED;
+    if (T > 16 || E > RS_MAX_E || static_cast<long long>(T) * k > RS_MAX_PAIRS) return LOCUS_ERR_UNSUPPORTED;
+    if (H <= 0 || H % 8 != 0 || ldh % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(w_all)) & 15) return LOCUS_ERR_UNSUPPORTED;
+    SkinnyArgs a;
+    a.x = static_cast<const bf16*>(h); a.w = static_cast<const bf16*>(w_all); a.w2 = nullptr;
+    a.bias = nullptr; a.bias_dt = 0; a.out = logits; a.out_dt = LOCUS_DT_F32; a.accumulate = 0;
+    a.row_scale = nullptr; a.scale_rows = nullptr; a.x_rows = nullptr; a.x_row_div = 1;
+    a.M = T; a.N = n_rows; a.K = H; a.ldx = ldh; a.ldo = ld; a.tile_expert = nullptr; a.tile_row0 = nullptr;
+    a.tile_rows = nullptr; a.n_tiles = nullptr; a.w_expert_stride = 0;
+    a.route_counter = counter; a.route_ids = ids; a.route_wts = wts; a.route_gamma = gamma;
+    a.route_experts = E; a.route_has_gate = has_gate; a.route_opts = o;
+    a.route_layout = RouteLayoutOut{tile_m, counts, offsets, sorted_pair, pair_pos, tile_expert, tile_row0, tile_rows, n_tiles};
+    const size_t tail = route_small_smem(SK_WARPS, T, E, k);
+    // the same row tile that locus_gemm_skinny's callers use for this many tokens
+    if (T <= 8) return launch<1>(a, 1, false, stream, tail);
+    return launch<2>(a, 1, false, stream, tail);
 }

@@ -747,12 +747,13 @@ def _route_rule(score_fn: str, sel_bias: Optional[torch.Tensor], n_group: int, n
 
 class RouterScratch:
     """Scratch of :func:`router_topk`: the router logits of a step and one counter per tile of
-    8 tokens (zero between launches)."""
+    8 tokens (zero between launches); ``fused_counter``: the counter of :func:`route_fused_small`."""
 
     def __init__(self, max_tokens: int, n_logits: int, device) -> None:
         self.max_tokens, self.n_logits = max_tokens, n_logits
         self.logits = torch.empty(max_tokens * n_logits, dtype=torch.float32, device=device)
         self.counters = torch.zeros((max_tokens + 7) // 8, dtype=torch.int32, device=device)
+        self.fused_counter = torch.zeros(1, dtype=torch.int32, device=device)
 
 
 def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.Tensor],
@@ -879,6 +880,43 @@ def route_small(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch
         _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _stream()
     )
     _check(code, "route_small", f"(T={n_tokens}, E={n_experts}, k={top_k})")
+
+
+def route_fused_small(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor, n_experts: int, has_gate: bool,
+                      ids: torch.Tensor, wts: torch.Tensor, gamma: Optional[torch.Tensor], layout: ExpertLayout,
+                      counter: torch.Tensor, *, n_tokens: int, top_k: int, renorm: bool, scale: float = 1.0,
+                      tile_m: Optional[int] = None, score_fn: str = "softmax", sel_bias: Optional[torch.Tensor] = None,
+                      n_group: int = 1, n_group_used: int = 1) -> None:
+    """:func:`router_logits` followed by :func:`route_small` in ONE launch, for batches that ``route_small_takes``:
+    the same logits (the same kernel computes them), picks, weights and layout.  ``counter``: one int32 that is
+    zero before the call and zero after it."""
+    _need(route_small_takes(n_tokens, top_k, n_experts), "route_fused_small: batch too large")
+    _cuda_c(h, "h")
+    _cuda_c(w_all, "w_all")
+    T, H = n_tokens, h.shape[1]
+    n = n_experts + (1 if has_gate else 0)
+    _need(h.shape[0] >= T and w_all.shape[0] == n and w_all.shape[1] == H, "route_fused_small: shapes")
+    _need(h.dtype == torch.bfloat16 and w_all.dtype == torch.bfloat16 and H % 8 == 0, "route_fused_small: bfloat16, H % 8 == 0")
+    _need(logits.is_cuda and logits.dtype == torch.float32 and logits.shape[0] >= T and logits.shape[1] >= n
+          and logits.stride(1) == 1, "route_fused_small: logits must be float32 [T, >= rows of w_all]")
+    _i32(ids, "ids")
+    _i32(counter, "counter")
+    _need(wts.dtype == torch.float32 and wts.numel() >= T * top_k and ids.numel() >= T * top_k,
+          "route_fused_small: ids / wts too small")
+    _need(T * top_k <= layout.sorted_pair.numel() and layout.n_experts == n_experts, "route_fused_small: layout does not fit")
+    if has_gate:
+        _need(gamma is not None and gamma.dtype == torch.float32 and gamma.numel() >= T, "route_fused_small: gamma")
+    if tile_m is not None:
+        _need(tile_m >= layout.MIN_TILE, f"route_fused_small: tiles of at least {layout.MIN_TILE} rows")
+        layout.tile_m = tile_m
+    code = _lib("gemm_skinny").locus_router_fused_small(
+        _p(h), _p(w_all), _p(logits), I(logits.stride(0)), _p(counter), _p(ids), _p(wts), _p(gamma), I(T), I(H),
+        LL(h.stride(0)), I(n_experts), I(top_k), I(1 if has_gate else 0), I(1 if renorm else 0), F(scale),
+        *_route_rule(score_fn, sel_bias, n_group, n_group_used, n_experts, "route_fused_small"), I(layout.tile_m),
+        _p(layout.counts), _p(layout.offsets), _p(layout.sorted_pair), _p(layout.pair_pos), _p(layout.tile_expert),
+        _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _stream()
+    )
+    _check(code, "route_fused_small", f"(T={T}, E={n_experts}, k={top_k})")
 
 
 def moe_combine(x: torch.Tensor, pair_out: torch.Tensor, pair_pos: torch.Tensor, top_k: int) -> None:

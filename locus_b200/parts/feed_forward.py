@@ -155,13 +155,13 @@ class SparseMoe(FeedForward):
         if self._router_all is not None and K.USE_TENSOR_CORES:
             # bfloat16: router (and gate) logits on the tensor cores, one kernel for every batch shape
             logits = self._scratch.logits.view(rt.max_tokens, self.E + 1)
-            K.router_logits(h, self._router_all, logits)
             if K.route_small_takes(T, self.k, self.E):
-                # a decode-sized batch: selection and the expert layout in one launch
-                K.route_small(logits, self.E, self.shared_gate, ids, wts, gamma, lay, n_tokens=T, tile_m=tile,
-                              **self._rule)
+                # a decode-sized batch: logits, selection and the expert layout in one launch
+                K.route_fused_small(h, self._router_all, logits, self.E, self.shared_gate, ids, wts, gamma, lay,
+                                    self._scratch.fused_counter, n_tokens=T, tile_m=tile, **self._rule)
                 sorted_already = True
             else:
+                K.router_logits(h, self._router_all, logits)
                 K.router_select(logits, self.E, self.shared_gate, ids, wts, gamma, n_tokens=T, **self._rule)
         else:
             K.router_topk(h, self.params["router"], self.params.get("shared_gate"), ids, wts, gamma,

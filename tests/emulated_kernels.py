@@ -235,6 +235,12 @@ def route_small(logits, n_experts, has_gate, ids, wts, gamma, layout, *, n_token
     moe_sort(ids, n_tokens * top_k, layout, tile_m)
 
 
+def route_fused_small(h, w_all, logits, n_experts, has_gate, ids, wts, gamma, layout, counter, *, n_tokens, tile_m=None,
+                      **rule):
+    router_logits(h[:n_tokens], w_all, logits)
+    route_small(logits, n_experts, has_gate, ids, wts, gamma, layout, n_tokens=n_tokens, tile_m=tile_m, **rule)
+
+
 def moe_sort(ids, n_pairs, layout, tile_m=None):
     if tile_m is not None:
         layout.tile_m = tile_m
@@ -322,7 +328,7 @@ def sample(logits, *, temperature, top_k, top_p, min_p, seeds, counters, out, ke
 
 
 _NAMES = ["embed_rows", "rmsnorm", "rmsnorm_adds", "attn_chunk_tc_takes", "linear", "rope_kv_write", "attn_chunk", "attn_chunk_mma", "attn_decode", "router_topk", "router_logits", "router_select",
-          "moe_sort", "route_small", "route_small_takes", "moe_combine", "gather_rows", "apply_penalties", "sample"]
+          "moe_sort", "route_small", "route_small_takes", "route_fused_small", "moe_combine", "gather_rows", "apply_penalties", "sample"]
 
 
 def install(monkeypatch) -> None:

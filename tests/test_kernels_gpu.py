@@ -263,6 +263,38 @@ def test_route_small_is_select_then_sort(T, E, k, tile, gate, renorm):
     assert not K.route_small_takes(17, k, E) and not K.route_small_takes(T, k, 513)
 
 
+@pytest.mark.parametrize("T,H,E,k,gate,tile", [(1, 64, 4, 2, True, 8), (8, 2048, 60, 4, True, 8), (16, 200, 64, 8, False, 16),
+                                               (9, 3584, 64, 8, True, 128), (5, 72, 512, 6, False, 8)])
+def test_router_in_one_launch_is_logits_then_route_small(T, H, E, k, gate, tile):
+    """Logits, selection and layout of a decode-sized batch in one launch give, bit for bit, what the two launches give
+    (the same kernel computes the logits; the last block routes), twice in a row (the counter returns to zero)."""
+    g = torch.Generator().manual_seed(T * 7 + E)
+    h = (torch.randn(T, H, generator=g)).to(torch.bfloat16).to(DEV)
+    n = E + (1 if gate else 0)
+    w_all = (torch.randn(n, H, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
+    rule = dict(top_k=k, renorm=True, scale=1.25)
+    ids2, wts2, gamma2 = torch.full((T * k,), -1, dtype=torch.int32, device=DEV), torch.zeros(T * k, device=DEV), torch.zeros(T, device=DEV)
+    logits2 = torch.zeros(T, E + 1, device=DEV)
+    lay2 = K.ExpertLayout(T * k, E, 64, DEV)
+    K.router_logits(h, w_all, logits2)
+    K.route_small(logits2, E, gate, ids2, wts2, gamma2 if gate else None, lay2, n_tokens=T, tile_m=tile, **rule)
+    counter = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for again in range(2):
+        ids1, wts1, gamma1 = torch.full((T * k,), -1, dtype=torch.int32, device=DEV), torch.zeros(T * k, device=DEV), torch.zeros(T, device=DEV)
+        logits1 = torch.zeros(T, E + 1, device=DEV)
+        lay1 = K.ExpertLayout(T * k, E, 64, DEV)
+        K.route_fused_small(h, w_all, logits1, E, gate, ids1, wts1, gamma1 if gate else None, lay1, counter, n_tokens=T,
+                            tile_m=tile, **rule)
+        assert torch.equal(logits1[:, :n], logits2[:, :n])
+        assert torch.equal(ids1, ids2) and torch.equal(wts1, wts2) and torch.equal(gamma1, gamma2)
+        n_tiles = int(lay2.n_tiles.cpu())
+        assert int(lay1.n_tiles.cpu()) == n_tiles and int(counter.cpu()) == 0
+        for name in ("counts", "offsets", "sorted_pair", "pair_pos"):
+            assert torch.equal(getattr(lay1, name), getattr(lay2, name)), name
+        for name in ("tile_expert", "tile_row0", "tile_rows"):
+            assert torch.equal(getattr(lay1, name)[:n_tiles], getattr(lay2, name)[:n_tiles]), name
+
+
 def test_router_ties_go_to_lowest_index():
     h = torch.ones(2, 16)
     wr = torch.zeros(6, 16)
