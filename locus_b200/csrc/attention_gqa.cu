@@ -18,12 +18,12 @@
 //                       (the rows of O^T are a permutation of the head dimension, undone at the store).
 // Keeping the memory busy: the K rows and the V rows of a chunk of 16 keys are two runs of 16 x hd x 2 bytes, each
 // contiguous in a page.  One lane of the warp asks for each run with ONE bulk copy (cp.async.bulk, global to shared
-// memory, completion counted on an mbarrier of the warp's own), three chunks deep; the warp reads the fragments back
+// memory, completion counted on an mbarrier of the warp's own), two chunks deep; the warp reads the fragments back
 // when the chunk's turn comes.  (Copies of 16 bytes per lane were bound first by the number of requests to the L2,
 // then, coalesced, by their 200 instructions of address arithmetic per chunk: 465 instructions per chunk at two
 // warps per scheduler.)  Rows of V that belong to no live key (before a window's start, behind the range's end) are
-// zeroed in shared memory before use: unwritten cache may hold any bits, and 0 x NaN is NaN.  One block of eight
-// warps per SM, 24 KB of copies in flight per warp; a warp synchronises only with itself.  Every wait on a barrier
+// zeroed in shared memory before use: unwritten cache may hold any bits, and 0 x NaN is NaN.  One block of ten
+// warps per SM, 16 KB of copies in flight per warp; a warp synchronises only with itself.  Every wait on a barrier
 // is bounded: when the limit runs out the warp records it in the module's error word and leaves.
 // The cut of the batch into ranges, the partial results, the counters and the ordered merge are those of the
 // streaming kernel (attn_ranges.cuh; ranges x key/value heads are the units of work).
@@ -48,8 +48,16 @@ struct GqaArgs {
     int* counters;            // [n_items * nh], zero between launches (one per (request, kv head) is used)
 };
 
-#define GQ_WARPS 8    // warps of a block; one block per SM
-#define GQ_STAGES 3   // chunks of 16 keys whose copies are in flight per warp
+// Warps of a block (one block per SM) and chunks of 16 keys whose copies are in flight per warp.  Shared memory
+// (8 KB per chunk at head size 128) allows 8 x 3, 10 x 2, 12 x 2 or 6 x 4; measured at 28 heads on 4 and 8,192 keys,
+// 64 / 8 requests: 202 / 52 us, 184 / 56, 190 / 58, 231 / 47.  More warps hide the latency of a chunk's chain of
+// dependent instructions better than a deeper ring does.
+#ifndef GQ_WARPS
+#define GQ_WARPS 10
+#endif
+#ifndef GQ_STAGES
+#define GQ_STAGES 2
+#endif
 
 #define GQ_WAIT_LIMIT 2000000000LL   // cycles a warp waits for a copy before it gives up (about a second)
 
