@@ -413,7 +413,6 @@ struct false_tag { static constexpr bool value = false; };
 template <typename T, int LPK>
 __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(AttnArgs a, int n_items, int max_units,
                                                                               int cost_range, int cost_merge) {
-    pdl_entry();
     pdl_trigger();  // every block of this grid is resident from the start
     constexpr int VEC = 16 / sizeof(T);   // elements of a lane
     constexpr int KPL = 32 / LPK;         // key rows of a load instruction
@@ -424,7 +423,11 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
     // ---- how the batch is cut into ranges (the same result in every block) ----
     __shared__ KeyRanges kr;
     const int n_warps = gridDim.x * DS_WARPS;
+    // The cut reads only the step's descriptors, which were on the device before the step's first kernel: under
+    // programmatic dependent launch it is made while the kernel in front of this one (which writes q and the newest
+    // keys and values) still runs; the wait for that kernel comes after it.
     plan_key_ranges(kr, a.items, a.seg_ctx, a.seg_q0, a.window, n_items, a.nh, max_units, n_warps, cost_range, cost_merge);
+    bool waited = false;  // whether this warp has waited for the kernel in front (every path does before it leaves)
     int* const s_first = kr.first;
     int* const s_pref = kr.pref;
     int* const s_seg = kr.seg;
@@ -432,7 +435,10 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
     int* const s_row = kr.row;
     const int s_len = kr.len;
     const int len = s_len;
-    if (len == 0) return;
+    if (len == 0) {
+        pdl_entry();
+        return;
+    }
     const int n_ranges = s_pref[n_items];
     const long long n_units = static_cast<long long>(n_ranges) * a.nh;
 
@@ -458,13 +464,6 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
         const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
         const T* pool = static_cast<const T*>(a.pool) + static_cast<size_t>(kvh) * P * hd + d0;
 
-        float q[VEC];
-        {
-            float raw[VEC];
-            Vec<T>::load(static_cast<const T*>(a.q) + (static_cast<size_t>(row) * a.nh + h) * hd + d0, raw);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) q[i] = raw[i] * qscale;
-        }
         float m = -INFINITY, l = 0.f, acc[VEC];
 #pragma unroll
         for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
@@ -489,9 +488,30 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
         uint4 kreg[DS_LOADS], vreg[DS_LOADS];
         int page_next = page_of(k_begin + CHUNK), page_next2 = page_of(k_begin + 2 * CHUNK);
         unsigned base = chunk_base(k_begin, page_of(k_begin));
+        // Keys before the request's own position were written by earlier steps: a first chunk that ends before that
+        // position is asked for before the wait for the kernel in front, which writes q and the newest key and value.
+        const bool early = !waited && k_begin + CHUNK <= p;
+        if (early) {
 #pragma unroll
-        for (int g = 0; g < DS_LOADS; ++g)
-            kreg[g] = live(k_begin, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+            for (int g = 0; g < DS_LOADS; ++g)
+                kreg[g] = live(k_begin, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+        }
+        if (!waited) {
+            pdl_entry();
+            waited = true;
+        }
+        if (!early) {
+#pragma unroll
+            for (int g = 0; g < DS_LOADS; ++g)
+                kreg[g] = live(k_begin, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+        }
+        float q[VEC];
+        {
+            float raw[VEC];
+            Vec<T>::load(static_cast<const T*>(a.q) + (static_cast<size_t>(row) * a.nh + h) * hd + d0, raw);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) q[i] = raw[i] * qscale;
+        }
         // One chunk: FAST when this chunk and the next lie wholly inside the range (the steady state), so
         // that no load and no score needs a check of its own.
         auto chunk = [&](int k0, auto fast_tag) {
@@ -616,6 +636,7 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
             dst[3] = from_f<T>(o.w * inv);
         }
     }
+    if (!waited) pdl_entry();  // a warp without work: the grid must not finish before the kernel in front has
 }
 
 // The two constants of the streaming kernel's cost model (in keys); a switch for measurements.

@@ -147,7 +147,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 template <int HD, bool WIDE>
 __global__ void __launch_bounds__(32 * GQ_WARPS, 1) attn_decode_gqa_kernel(GqaArgs a, int n_items, long long max_units,
                                                                            int cost_range, int cost_merge) {
-    pdl_entry();
     pdl_trigger();  // every block of this grid is resident from the start
     constexpr int KS = HD / 16;      // k-steps of a score tile
     constexpr int NL = HD / 32;      // 16-byte pieces of a lane per key row (keys)
@@ -177,6 +176,8 @@ __global__ void __launch_bounds__(32 * GQ_WARPS, 1) attn_decode_gqa_kernel(GqaAr
     // a unit (range, kv head) leaves G partial results: the scratch holds max_units of them
     const int len = plan_key_ranges(kr, a.items, a.seg_ctx, a.seg_q0, a.window, n_items, a.nkv, max_units / G, n_warps,
                                     cost_range, cost_merge);
+    // (the cut read only the step's descriptors; q and the newest keys and values come from the kernel in front)
+    pdl_entry();
     if (len == 0) return;
     const int n_ranges = kr.pref[n_items];
     const long long n_units = static_cast<long long>(n_ranges) * a.nkv;

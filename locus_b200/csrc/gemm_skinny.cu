@@ -39,6 +39,10 @@ struct SkinnyArgs {
     const int* tile_rows;
     const int* n_tiles;
     long long w_expert_stride;
+    // The tile list was written by a kernel that finished before the kernel in front of this one started (the
+    // second product of the experts: the list comes from the router, the kernel in front is the first product):
+    // the block may read it, and ask for its first weights, before it waits for the kernel in front.
+    int lists_ready;
     // Optional tail (the router of a decode-sized batch): when route_counter is set, `out` holds float32 router
     // logits [T, ldo] of all T = M tokens (one row tile), and the block that finishes last selects every token's
     // experts from them and lays the pairs out by expert (route_select.cuh), all in this launch.  The counter is
@@ -64,14 +68,22 @@ __device__ __forceinline__ uint4 ld_stream(const bf16* p) { return __ldcs(reinte
 
 template <int NT, bool DUAL, bool ROUTE = false>
 __global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
-    pdl_entry();
     extern __shared__ float red[];  // [SK_WARPS][(DUAL ? 2 : 1)][NT][16 * 8]
+    // Under programmatic dependent launch this block may be resident while the kernel in front of it still runs.
+    // The weights do not depend on that kernel, so a plain product asks for its first weights before it waits;
+    // a grouped product learns its expert from the tile list, which the kernel in front may have written.
+    const bool grouped = a.tile_expert != nullptr;
+    const bool wait_first = grouped && !a.lists_ready;
+    if (wait_first) pdl_entry();
     int tok0, ntok;
     const bf16* W = a.w;
     const bf16* W2 = a.w2;
-    if (a.tile_expert != nullptr) {
+    if (grouped) {
         const int tile = blockIdx.y;
-        if (tile >= *a.n_tiles) return;
+        if (tile >= *a.n_tiles) {
+            if (!wait_first) pdl_entry();  // the grid must not finish before the kernel in front has
+            return;
+        }
         const long long e = a.tile_expert[tile];
         tok0 = a.tile_row0[tile];
         ntok = a.tile_rows[tile];
@@ -91,6 +103,26 @@ __global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
     const bf16* wh = W + r_hi * K;
     const bf16* ul = DUAL ? W2 + r_lo * K : nullptr;
     const bf16* uh = DUAL ? W2 + r_hi * K : nullptr;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    // this warp's k-steps: 32 elements each, interleaved with the other warps'; four steps at a time
+    constexpr int STEP = 32, STRIDE = STEP * SK_WARPS, UNROLL = 4;
+    uint4 al[UNROLL], ah[UNROLL], bl[DUAL ? UNROLL : 1], bh[DUAL ? UNROLL : 1];
+    auto load_weights = [&](int kb) {
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int k = kb + u * STRIDE + q * 8;
+            const bool in = k < K;  // K is a multiple of 8: a chunk is inside or outside as a whole
+            al[u] = in ? ld_stream(wl + k) : zero;
+            ah[u] = in ? ld_stream(wh + k) : zero;
+            if (DUAL) {
+                bl[u] = in ? ld_stream(ul + k) : zero;
+                bh[u] = in ? ld_stream(uh + k) : zero;
+            }
+        }
+    };
+    const int kb_first = warp * STEP;
+    if (kb_first < K) load_weights(kb_first);
+    if (!wait_first) pdl_entry();
     // token rows of this lane, one per 8-wide tile
     const bf16* xr[NT];
 #pragma unroll
@@ -112,22 +144,8 @@ __global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
             c[j][i] = 0.f;
             if (DUAL) c2[j][i] = 0.f;
         }
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    // this warp's k-steps: 32 elements each, interleaved with the other warps'; four steps at a time
-    constexpr int STEP = 32, STRIDE = STEP * SK_WARPS, UNROLL = 4;
-    for (int kb = warp * STEP; kb < K; kb += STRIDE * UNROLL) {
-        uint4 al[UNROLL], ah[UNROLL], bl[DUAL ? UNROLL : 1], bh[DUAL ? UNROLL : 1];
-#pragma unroll
-        for (int u = 0; u < UNROLL; ++u) {
-            const int k = kb + u * STRIDE + q * 8;
-            const bool in = k < K;  // K is a multiple of 8: a chunk is inside or outside as a whole
-            al[u] = in ? ld_stream(wl + k) : zero;
-            ah[u] = in ? ld_stream(wh + k) : zero;
-            if (DUAL) {
-                bl[u] = in ? ld_stream(ul + k) : zero;
-                bh[u] = in ? ld_stream(uh + k) : zero;
-            }
-        }
+    for (int kb = kb_first; kb < K; kb += STRIDE * UNROLL) {
+        if (kb != kb_first) load_weights(kb);
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             const int k = kb + u * STRIDE + q * 8;
@@ -235,7 +253,7 @@ extern "C" int locus_gemm_skinny(const void* x, const void* w, const void* w2, c
                                  const int* scale_rows, const int* x_rows, int x_row_div, int M, int N, int K,
                                  long long ldx, long long ldo, int tile_tokens, const int* tile_expert,
                                  const int* tile_row0, const int* tile_rows, const int* n_tiles, int max_tiles,
-                                 long long w_expert_stride, cudaStream_t stream) {
+                                 long long w_expert_stride, int lists_ready, cudaStream_t stream) {
     if (N <= 0 || K <= 0 || K % 8 != 0 || ldx % 8 != 0) return LOCUS_ERR_UNSUPPORTED;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(w2)) & 15)
         return LOCUS_ERR_UNSUPPORTED;
@@ -248,6 +266,7 @@ extern "C" int locus_gemm_skinny(const void* x, const void* w, const void* w2, c
     a.row_scale = row_scale; a.scale_rows = scale_rows; a.x_rows = x_rows; a.x_row_div = x_row_div;
     a.M = M; a.N = N; a.K = K; a.ldx = ldx; a.ldo = ldo; a.tile_expert = tile_expert; a.tile_row0 = tile_row0;
     a.tile_rows = tile_rows; a.n_tiles = n_tiles; a.w_expert_stride = w_expert_stride;
+    a.lists_ready = lists_ready;
     a.route_counter = nullptr;
     const int tiles = tile_expert ? max_tiles : ceil_div(M, tile_tokens);
     const bool dual = w2 != nullptr;
@@ -279,7 +298,7 @@ extern "C" int locus_router_fused_small(const void* h, const void* w_all, float*
     a.bias = nullptr; a.bias_dt = 0; a.out = logits; a.out_dt = LOCUS_DT_F32; a.accumulate = 0;
     a.row_scale = nullptr; a.scale_rows = nullptr; a.x_rows = nullptr; a.x_row_div = 1;
     a.M = T; a.N = n_rows; a.K = H; a.ldx = ldh; a.ldo = ld; a.tile_expert = nullptr; a.tile_row0 = nullptr;
-    a.tile_rows = nullptr; a.n_tiles = nullptr; a.w_expert_stride = 0;
+    a.tile_rows = nullptr; a.n_tiles = nullptr; a.w_expert_stride = 0; a.lists_ready = 0;
     a.route_counter = counter; a.route_ids = ids; a.route_wts = wts; a.route_gamma = gamma;
     a.route_experts = E; a.route_has_gate = has_gate; a.route_opts = o;
     a.route_layout = RouteLayoutOut{tile_m, counts, offsets, sorted_pair, pair_pos, tile_expert, tile_row0, tile_rows, n_tiles};

@@ -353,14 +353,17 @@ def tc_error() -> int:
 def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[torch.Tensor] = None,
            bias: Optional[torch.Tensor] = None, accumulate: bool = False,
            row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None,
-           x_rows: Optional[torch.Tensor] = None, x_row_div: int = 1, layout: Optional[ExpertLayout] = None, n_rows: Optional[int] = None) -> None:
+           x_rows: Optional[torch.Tensor] = None, x_row_div: int = 1, layout: Optional[ExpertLayout] = None,
+           n_rows: Optional[int] = None, lists_ready: bool = False) -> None:
     """out = x . w^T with float32 accumulation on CUDA cores (see csrc/gemm_simt.cu).
 
     ``w2``: out = silu(x . w^T) * (x . w2^T).  ``bias`` [N] is added, ``row_scale`` [M]
     multiplies the row (``scale_rows``: row m uses row_scale[scale_rows[m]]), ``accumulate`` adds the result into the float32 ``out``.
     ``x_rows``: logical row m reads x[x_rows[m] // x_row_div].  ``layout``: grouped product,
     ``w`` is [E, N, K] and logical rows are the expert-sorted pairs of the layout.
-    ``n_rows``: number of logical rows (default: rows of ``out``).
+    ``n_rows``: number of logical rows (default: rows of ``out``).  ``lists_ready``: the layout was filled by a
+    kernel that finished before the kernel in front of this one started (the experts' second product), so a
+    kernel launched with programmatic dependent launch may read it before it waits for the one in front.
     """
     _cuda_c(x, "x")
     _cuda_c(w, "w")
@@ -404,7 +407,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
             _p(x), _p(w), _p(w2), _p(bias), I(dtype_code(bias.dtype) if bias is not None else 0), _p(out),
             I(dtype_code(out.dtype)), I(1 if accumulate else 0), _p(row_scale), _p(scale_rows), _p(x_rows),
             I(x_row_div), I(M), I(N), I(K), LL(x.stride(0)), LL(out.stride(0)), I(tile), _p(te), _p(t0), _p(tr),
-            _p(nt), I(max_tiles), LL(stride), _stream()
+            _p(nt), I(max_tiles), LL(stride), I(1 if (lists_ready and layout is not None) else 0), _stream()
         )
         _check(code, "linear", f"(skinny; M={M}, N={N}, K={K}, tile {tile})")
         return
@@ -803,7 +806,7 @@ def router_logits(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor) ->
     tile = 8 if T <= 8 else (16 if T <= 16 else 32)
     code = _lib("gemm_skinny").locus_gemm_skinny(
         _p(h), _p(w_all), None, None, I(0), _p(logits), I(0), I(0), None, None, None, I(1), I(T), I(n), I(H),
-        LL(h.stride(0)), LL(logits.stride(0)), I(tile), None, None, None, None, I(0), LL(0), _stream()
+        LL(h.stride(0)), LL(logits.stride(0)), I(tile), None, None, None, None, I(0), LL(0), I(0), _stream()
     )
     _check(code, "router_logits", f"(T={T}, H={H}, rows {n})")
 

@@ -189,7 +189,7 @@ class SparseMoe(FeedForward):
             K.linear(xs, self.params["gate_exps"], act, w2=self.params["up_exps"], layout=lay, n_rows=n_pairs)
         pair_out = rt.rows("moe.pair_out", self.hidden, torch.float32, n_pairs, per_token=self.k)
         K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts,
-                 scale_rows=lay.sorted_pair)
+                 scale_rows=lay.sorted_pair, lists_ready=True)
         if overlap:
             rt.join()
         if self.shared is not None and not overlap:

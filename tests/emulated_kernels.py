@@ -47,7 +47,7 @@ class ExpertLayout(K.ExpertLayout):
     pass
 
 
-def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, scale_rows=None, x_rows=None,
+def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, scale_rows=None, x_rows=None, lists_ready=False,
            x_row_div=1, layout=None, n_rows=None):
     M = out.shape[0] if n_rows is None else n_rows
     if M == 0:
