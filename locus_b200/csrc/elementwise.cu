@@ -67,7 +67,7 @@ template <typename TW, typename TO>
 __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x, const TW* __restrict__ w,
                                                           float eps, TO* __restrict__ out,
                                                           const int* __restrict__ rows, int H,
-                                                          const float* __restrict__ add_src,
+                                                          const void* __restrict__ add_src, int add_bf16,
                                                           const int* __restrict__ add_pos, int add_k) {
     pdl_entry();
     pdl_trigger();
@@ -83,8 +83,16 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x,
         if (add_src != nullptr) {
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int s = 0; s < add_k; ++s) {
-                const float4 p = reinterpret_cast<const float4*>(
-                    add_src + static_cast<size_t>(add_pos[r * add_k + s]) * H)[j];
+                const size_t at = static_cast<size_t>(add_pos[r * add_k + s]) * H;
+                float4 p;
+                if (add_bf16) {
+                    const uint2 raw = reinterpret_cast<const uint2*>(static_cast<const bf16*>(add_src) + at)[j];
+                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+                    p = make_float4(lo.x, lo.y, hi.x, hi.y);
+                } else {
+                    p = reinterpret_cast<const float4*>(static_cast<const float*>(add_src) + at)[j];
+                }
                 acc.x += p.x; acc.y += p.y; acc.z += p.z; acc.w += p.w;
             }
             t.x += acc.x; t.y += acc.y; t.z += acc.z; t.w += acc.w;
@@ -131,21 +139,23 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x,
     }
 }
 
-// add_src / add_pos / add_k: see rmsnorm_f32_kernel; only with float32 x, H a multiple of 4, 16-byte
-// aligned x and add_src.
+// add_src (float32 or bfloat16 rows, add_dt) / add_pos / add_k: see rmsnorm_f32_kernel; only with float32 x, H a
+// multiple of 4, 16-byte aligned x and add_src.
 extern "C" int locus_rmsnorm(void* x, int x_dt, const void* w, int w_dt, float eps, void* out,
-                             int out_dt, const int* rows, int n_rows, int H, const float* add_src,
+                             int out_dt, const int* rows, int n_rows, int H, const void* add_src, int add_dt,
                              const int* add_pos, int add_k, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     const bool fast = x_dt == LOCUS_DT_F32 && H % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
     if (add_src != nullptr &&
-        (!fast || add_pos == nullptr || add_k <= 0 || (reinterpret_cast<uintptr_t>(add_src) & 15)))
+        (!fast || add_pos == nullptr || add_k <= 0 || (reinterpret_cast<uintptr_t>(add_src) & 15) ||
+         (add_dt != LOCUS_DT_F32 && add_dt != LOCUS_DT_BF16)))
         return LOCUS_ERR_UNSUPPORTED;
+    const int add_bf16 = add_dt == LOCUS_DT_BF16 ? 1 : 0;
     if (fast) {
         float* xf = static_cast<float*>(x);
 #define NORM_LAUNCH(TW, TO)                                                                             \
         locus_launch(rmsnorm_f32_kernel<TW, TO>, n_rows, 256, 0, stream, xf, static_cast<const TW*>(w), eps,      \
-                     static_cast<TO*>(out), rows, H, add_src, add_pos, add_k)
+                     static_cast<TO*>(out), rows, H, add_src, add_bf16, add_pos, add_k)
         if (w_dt == LOCUS_DT_BF16 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(bf16, bf16);
         else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_F32) NORM_LAUNCH(float, float);
         else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(float, bf16);
@@ -321,7 +331,8 @@ extern "C" int locus_rope_kv_write(const void* qkv, int dt, const int* positions
 // Routed-expert combine: x[t, :] += sum over slot = 0..k-1 (in that order) of
 // pair_out[pair_pos[t * k + slot], :].  The routing weight is already applied to
 // pair_out.  No atomics: the sum order is the selection order, for every batch.
-__global__ void moe_combine_kernel(float* __restrict__ x, const float* __restrict__ pair_out,
+template <typename TP>
+__global__ void moe_combine_kernel(float* __restrict__ x, const TP* __restrict__ pair_out,
                                    const int* __restrict__ pair_pos, int k, int H) {
     pdl_entry();
     pdl_trigger();
@@ -329,16 +340,22 @@ __global__ void moe_combine_kernel(float* __restrict__ x, const float* __restric
     for (int j = threadIdx.x; j < H; j += blockDim.x) {
         float acc = 0.f;
         for (int s = 0; s < k; ++s) {
-            acc += pair_out[static_cast<size_t>(pair_pos[t * k + s]) * H + j];
+            acc += to_f(pair_out[static_cast<size_t>(pair_pos[t * k + s]) * H + j]);
         }
         x[static_cast<size_t>(t) * H + j] += acc;
     }
 }
 
-extern "C" int locus_moe_combine(float* x, const float* pair_out, const int* pair_pos, int T,
+// pair_out: float32 or bfloat16 rows (pair_dt); the sum is float32 either way.
+extern "C" int locus_moe_combine(float* x, const void* pair_out, int pair_dt, const int* pair_pos, int T,
                                  int k, int H, cudaStream_t stream) {
     if (T <= 0) return 0;
-    locus_launch(moe_combine_kernel, T, 256, 0, stream, x, pair_out, pair_pos, k, H);
+    if (pair_dt == LOCUS_DT_F32)
+        locus_launch(moe_combine_kernel<float>, T, 256, 0, stream, x, static_cast<const float*>(pair_out), pair_pos, k, H);
+    else if (pair_dt == LOCUS_DT_BF16)
+        locus_launch(moe_combine_kernel<bf16>, T, 256, 0, stream, x, static_cast<const bf16*>(pair_out), pair_pos, k, H);
+    else
+        return LOCUS_ERR_UNSUPPORTED;
     return locus_launch_status();
 }
 

@@ -175,12 +175,13 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor,
         _need(rmsnorm_adds(x), "rmsnorm: cannot fold the expert sum into these rows")
         _cuda_c(add_src, "pair_out")
         _i32(add_pos, "pair_pos")
-        _need(add_src.dtype == torch.float32 and add_src.shape[-1] == H
+        _need(add_src.dtype in (torch.float32, torch.bfloat16) and add_src.shape[-1] == H
               and add_pos.numel() >= (n if rows is None else x.shape[0]) * add_k,
               "rmsnorm: expert sum of another shape")
     code = _lib("elementwise").locus_rmsnorm(
         _p(x), I(dtype_code(x.dtype)), _p(w), I(dtype_code(w.dtype)), F(eps), _p(out),
-        I(dtype_code(out.dtype)), _p(rows), I(n), I(H), _p(add_src), _p(add_pos), I(add_k), _stream()
+        I(dtype_code(out.dtype)), _p(rows), I(n), I(H), _p(add_src),
+        I(dtype_code(add_src.dtype) if add_src is not None else 0), _p(add_pos), I(add_k), _stream()
     )
     _check(code, "rmsnorm")
 
@@ -923,15 +924,17 @@ def route_fused_small(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor
 
 
 def moe_combine(x: torch.Tensor, pair_out: torch.Tensor, pair_pos: torch.Tensor, top_k: int) -> None:
-    """x[t] += sum over slots (in slot order) of pair_out[pair_pos[t * k + slot]]."""
+    """x[t] += sum over slots (in slot order) of pair_out[pair_pos[t * k + slot]] (float32 or bfloat16 rows;
+    the sum is float32)."""
     _cuda_c(x, "x")
     _cuda_c(pair_out, "pair_out")
     _i32(pair_pos, "pair_pos")
     T, H = x.shape
-    _need(x.dtype == torch.float32 and pair_out.dtype == torch.float32, "moe_combine: float32 only")
+    _need(x.dtype == torch.float32 and pair_out.dtype in (torch.float32, torch.bfloat16),
+          "moe_combine: float32 x, float32 or bfloat16 pair rows")
     _need(pair_out.shape[-1] == H, "moe_combine: width mismatch")
-    code = _lib("elementwise").locus_moe_combine(_p(x), _p(pair_out), _p(pair_pos), I(T), I(top_k), I(H),
-                                                 _stream())
+    code = _lib("elementwise").locus_moe_combine(_p(x), _p(pair_out), I(dtype_code(pair_out.dtype)), _p(pair_pos), I(T),
+                                                 I(top_k), I(H), _stream())
     _check(code, "moe_combine")
 
 

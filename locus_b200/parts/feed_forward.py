@@ -187,7 +187,10 @@ class SparseMoe(FeedForward):
             xs = rt.rows("moe.x_sorted", self.hidden, rt.dtype, n_pairs, per_token=self.k)
             K.gather_rows(h, lay.sorted_pair, self.k, xs, n_pairs)
             K.linear(xs, self.params["gate_exps"], act, w2=self.params["up_exps"], layout=lay, n_rows=n_pairs)
-        pair_out = rt.rows("moe.pair_out", self.hidden, torch.float32, n_pairs, per_token=self.k)
+        # the experts' weighted outputs, one row per (token, slot): in the model's element type (in bfloat16 a row is
+        # rounded once more, like every activation between kernels; their sum, the residual stream, stays float32)
+        pair_dt = torch.bfloat16 if (all_bf16 and rt.dtype == torch.bfloat16) else torch.float32
+        pair_out = rt.rows("moe.pair_out", self.hidden, pair_dt, n_pairs, per_token=self.k)
         K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts,
                  scale_rows=lay.sorted_pair, lists_ready=True)
         if overlap:

@@ -270,7 +270,7 @@ def moe_combine(x, pair_out, pair_pos, top_k):
     for t in range(T):
         acc = torch.zeros_like(x[t])
         for s in range(top_k):
-            acc = acc + pair_out[int(pair_pos[t * top_k + s])]
+            acc = acc + pair_out[int(pair_pos[t * top_k + s])].to(acc.dtype)
         x[t] += acc
 
 

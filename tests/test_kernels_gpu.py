@@ -70,16 +70,20 @@ def test_rmsnorm_folds_the_expert_sum(dtype, H, k):
     the plain norm, and leaves the same sum in x."""
     T = 6
     x = rnd(T, H, seed=1, scale=3.0).to(DEV)
-    pair_out = rnd(T * k, H, seed=2, scale=2.0).to(DEV)
+    # the experts' rows are float32 in a float32 model and bfloat16 in a bfloat16 one; the sum is float32 either way
+    pair_out = rnd(T * k, H, seed=2, scale=2.0).to(dtype).to(DEV)
     pair_pos = torch.randperm(T * k, generator=torch.Generator().manual_seed(3)).to(torch.int32).to(DEV)
     w = (rnd(H, dtype=dtype, seed=4) + 1).to(DEV)
     assert K.rmsnorm_adds(x)
+    xr = x.cpu().double()
+    EK.moe_combine(xr, pair_out.cpu().double(), pair_pos.cpu(), k)
     x2, out2 = x.clone(), torch.empty(T, H, dtype=dtype, device=DEV)
     K.moe_combine(x2, pair_out, pair_pos, k)
     K.rmsnorm(x2, w, 1e-6, out2)
     x1, out1 = x.clone(), torch.empty(T, H, dtype=dtype, device=DEV)
     K.rmsnorm(x1, w, 1e-6, out1, add=(pair_out, pair_pos, k))
     assert torch.equal(x1, x2) and torch.equal(out1, out2)
+    close(x1, xr, torch.float32, "x + the experts' sum")
     assert not K.rmsnorm_adds(torch.zeros(2, 6))
     # with a gather of rows (one of them named twice) the sum shows in the output alone
     rows = torch.tensor([4, 1, 4], dtype=torch.int32, device=DEV)
