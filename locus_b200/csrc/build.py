@@ -17,6 +17,7 @@ import os
 import shutil
 import subprocess
 import sys
+import re
 import tempfile
 import threading
 import time
@@ -37,11 +38,7 @@ NVCC_FLAGS = [
 
 HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
 
-HEADERS = ["common.cuh"]
-
-# module name -> further headers its library depends on
-MODULE_HEADERS: Dict[str, List[str]] = {"attention": ["attention_static.h", "attn_ranges.cuh"],
-                                        "attention_gqa": ["attn_ranges.cuh"]}
+_INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
 
 # module name -> extra nvcc flags
 MODULE_FLAGS: Dict[str, List[str]] = {}
@@ -96,12 +93,22 @@ def _is_host_module(name: str) -> bool:
     return os.path.isfile(os.path.join(CSRC_DIR, name + ".cpp"))
 
 
+def source_files(name: str) -> List[str]:
+    """The module's source file and every file of this folder that it includes with quotes, directly or through
+    another one, in the order met: what a library's name is hashed over."""
+    files = [name + (".cpp" if _is_host_module(name) else ".cu")]
+    for f in files:  # grows while it is walked
+        with open(os.path.join(CSRC_DIR, f), "r", encoding="utf-8") as fh:
+            for inc in _INCLUDE.findall(fh.read()):
+                if inc not in files and os.path.isfile(os.path.join(CSRC_DIR, inc)):
+                    files.append(inc)
+    return files
+
+
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    if _is_host_module(name):
-        files, flags = [name + ".cpp"], HOST_FLAGS
-    else:
-        files, flags = [name + ".cu"] + HEADERS + MODULE_HEADERS.get(name, []), NVCC_FLAGS + MODULE_FLAGS.get(name, [])
+    files = source_files(name)
+    flags = HOST_FLAGS if _is_host_module(name) else NVCC_FLAGS + MODULE_FLAGS.get(name, [])
     for f in files:
         with open(os.path.join(CSRC_DIR, f), "rb") as fh:
             h.update(fh.read())

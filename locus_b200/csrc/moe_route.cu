@@ -210,17 +210,20 @@ __global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ i
                                                         int* __restrict__ offsets, int* __restrict__ sorted_pair,
                                                         int* __restrict__ pair_pos, int* __restrict__ tile_expert,
                                                         int* __restrict__ tile_row0, int* __restrict__ tile_rows,
-                                                        int* __restrict__ n_tiles) {
+                                                        int* __restrict__ n_tiles, int tile2_m,
+                                                        int* __restrict__ tile2_expert, int* __restrict__ tile2_row0,
+                                                        int* __restrict__ tile2_rows, int* __restrict__ n_tiles2) {
     pdl_entry();
     __shared__ int s_off;
     __shared__ int warp_cnt[8];
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     if (threadIdx.x == 0) {
-        int off = 0, tile = 0;
+        int off = 0, tile = 0, tile2 = 0;
         for (int j = 0; j < e; ++j) {
             off += counts[j];
             tile += (counts[j] + tile_m - 1) / tile_m;
+            if (tile2_m > 0) tile2 += (counts[j] + tile2_m - 1) / tile2_m;
         }
         s_off = off;
         offsets[e] = off;
@@ -230,6 +233,15 @@ __global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ i
             tile_expert[tile + i] = e;
             tile_row0[tile + i] = off + i * tile_m;
             tile_rows[tile + i] = min(tile_m, mine - i * tile_m);
+        }
+        if (tile2_m > 0) {  // the same rows in tiles of another size (for a product with another token tile)
+            const int nt2 = (mine + tile2_m - 1) / tile2_m;
+            for (int i = 0; i < nt2; ++i) {
+                tile2_expert[tile2 + i] = e;
+                tile2_row0[tile2 + i] = off + i * tile2_m;
+                tile2_rows[tile2 + i] = min(tile2_m, mine - i * tile2_m);
+            }
+            if (e == E - 1) *n_tiles2 = tile2 + nt2;
         }
         if (e == E - 1) {
             offsets[E] = off + mine;
@@ -259,14 +271,18 @@ __global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ i
     }
 }
 
+// tile2_m > 0: a second tile list over the same layout, with tiles of tile2_m rows (tile2_* and n_tiles2).
 extern "C" int locus_moe_sort(const int* ids, int n_pairs, int E, int tile_m, int* counts,
                               int* offsets, int* sorted_pair, int* pair_pos, int* tile_expert,
-                              int* tile_row0, int* tile_rows, int* n_tiles, cudaStream_t stream) {
+                              int* tile_row0, int* tile_rows, int* n_tiles, int tile2_m, int* tile2_expert,
+                              int* tile2_row0, int* tile2_rows, int* n_tiles2, cudaStream_t stream) {
     if (n_pairs <= 0) return 0;
-    if (E <= 0 || tile_m <= 0) return LOCUS_ERR_UNSUPPORTED;
+    if (E <= 0 || tile_m <= 0 || tile2_m < 0) return LOCUS_ERR_UNSUPPORTED;
+    if (tile2_m > 0 && (tile2_expert == nullptr || tile2_row0 == nullptr || tile2_rows == nullptr || n_tiles2 == nullptr))
+        return LOCUS_ERR_UNSUPPORTED;
     locus_launch(moe_count_kernel, E, 256, 0, stream, ids, n_pairs, counts);
     locus_launch(moe_fill_kernel, E, 256, 0, stream, ids, n_pairs, E, counts, tile_m, offsets, sorted_pair, pair_pos,
-                 tile_expert, tile_row0, tile_rows, n_tiles);
+                 tile_expert, tile_row0, tile_rows, n_tiles, tile2_m, tile2_expert, tile2_row0, tile2_rows, n_tiles2);
     return locus_launch_status();
 }
 

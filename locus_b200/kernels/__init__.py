@@ -206,10 +206,17 @@ class ExpertLayout:
         self.tile_row0 = torch.zeros(self.max_tiles, **i32)
         self.tile_rows = torch.zeros(self.max_tiles, **i32)
         self.n_tiles = torch.zeros(1, **i32)
+        # a second tile list over the same rows, with tiles of tile2_m rows (0: none; see moe_sort)
+        self.tile2_m = 0
+        self.tile2_expert = torch.zeros(self.max_tiles, **i32)
+        self.tile2_row0 = torch.zeros(self.max_tiles, **i32)
+        self.tile2_rows = torch.zeros(self.max_tiles, **i32)
+        self.n_tiles2 = torch.zeros(1, **i32)
 
-    def tiles_for(self, n_pairs: int) -> int:
-        """Upper bound of the number of row tiles when ``n_pairs`` pairs are routed."""
-        return min(self.max_tiles, n_pairs // self.tile_m + min(n_pairs, self.n_experts) + 1)
+    def tiles_for(self, n_pairs: int, tile_m: Optional[int] = None) -> int:
+        """Upper bound of the number of row tiles (of ``tile_m`` rows, default the layout's) when ``n_pairs``
+        pairs are routed."""
+        return min(self.max_tiles, n_pairs // (tile_m or self.tile_m) + min(n_pairs, self.n_experts) + 1)
 
 
 # Tests switch this off to run the CUDA-core product on bfloat16 inputs.
@@ -336,6 +343,16 @@ def _split_scratch(device) -> torch.Tensor:
     return t
 
 
+def expert_second_tile(n_pairs: int, n_experts: int) -> int:
+    """Row tile of the experts' SECOND product (one accumulator per tile: 256 token rows fit the tensor memory)
+    when it pays to walk the layout in larger tiles than the first product's 128, else 0.  With 137 rows per expert
+    on average half of the experts need a second 128-row tile, which costs nearly what a full one costs (the tile
+    waits for the same weights): measured at 60 x (2048 -> 2048), 4 picks, 2,048 tokens 122 us with 128-row tiles and
+    110 us with 256-row tiles, at 64 x (3584 -> 2560), 8 picks 396 and 351 us; at 512 tokens (34 rows per expert)
+    87 and 95 us."""
+    return 256 if n_pairs >= 96 * n_experts else 0
+
+
 def expert_tile(n_pairs: int, n_experts: int) -> int:
     """Row tile of a grouped product on the tensor cores.  Always the full 128 rows: a tile reads its
     tokens through a box that fits the rows it really has (16 to 256), so a tile with few rows costs little,
@@ -355,7 +372,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
            bias: Optional[torch.Tensor] = None, accumulate: bool = False,
            row_scale: Optional[torch.Tensor] = None, scale_rows: Optional[torch.Tensor] = None,
            x_rows: Optional[torch.Tensor] = None, x_row_div: int = 1, layout: Optional[ExpertLayout] = None,
-           n_rows: Optional[int] = None, lists_ready: bool = False) -> None:
+           n_rows: Optional[int] = None, lists_ready: bool = False, second_tiles: bool = False) -> None:
     """out = x . w^T with float32 accumulation on CUDA cores (see csrc/gemm_simt.cu).
 
     ``w2``: out = silu(x . w^T) * (x . w2^T).  ``bias`` [N] is added, ``row_scale`` [M]
@@ -365,6 +382,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
     ``n_rows``: number of logical rows (default: rows of ``out``).  ``lists_ready``: the layout was filled by a
     kernel that finished before the kernel in front of this one started (the experts' second product), so a
     kernel launched with programmatic dependent launch may read it before it waits for the one in front.
+    ``second_tiles``: a grouped product on the tensor cores walks the layout's second tile list (``moe_sort`` with
+    ``tile2_m``) instead of the first.
     """
     _cuda_c(x, "x")
     _cuda_c(w, "w")
@@ -431,7 +450,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, w2: Optional[
         return
     if tensor_cores_take(x, w, x_rows):
         # bfloat16 x bfloat16: tcgen05 kernel (csrc/gemm_tc.cu)
-        if layout is not None:
+        if layout is not None and second_tiles and layout.tile2_m > 0:
+            TN, splits, scratch = layout.tile2_m, 1, None
+            te, t0, tr, nt = layout.tile2_expert, layout.tile2_row0, layout.tile2_rows, layout.n_tiles2
+            max_tiles = layout.tiles_for(M, layout.tile2_m)
+        elif layout is not None:
             TN, splits, scratch = layout.tile_m, 1, None
             te, t0, tr, nt = layout.tile_expert, layout.tile_row0, layout.tile_rows, layout.n_tiles
             max_tiles = layout.tiles_for(M)
@@ -832,18 +855,23 @@ def router_select(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: tor
     _check(code, "router_select", f"(E={n_experts}, k={top_k})")
 
 
-def moe_sort(ids: torch.Tensor, n_pairs: int, layout: ExpertLayout, tile_m: Optional[int] = None) -> None:
+def moe_sort(ids: torch.Tensor, n_pairs: int, layout: ExpertLayout, tile_m: Optional[int] = None,
+             tile2_m: int = 0) -> None:
     """Fill ``layout`` from the picked experts ``ids`` (first ``n_pairs`` entries), with row
-    tiles of ``tile_m`` rows (default: the layout's)."""
+    tiles of ``tile_m`` rows (default: the layout's).  ``tile2_m`` > 0: also a second tile list over the same
+    rows with tiles of that size, for a product that runs with another token tile (``linear(..., second_tiles=True)``)."""
     _i32(ids, "ids")
     _need(n_pairs <= layout.sorted_pair.numel(), "moe_sort: layout too small")
     if tile_m is not None:
         _need(tile_m >= layout.MIN_TILE, f"moe_sort: tiles of at least {layout.MIN_TILE} rows")
         layout.tile_m = tile_m
+    _need(tile2_m == 0 or tile2_m >= layout.MIN_TILE, f"moe_sort: tiles of at least {layout.MIN_TILE} rows")
+    layout.tile2_m = tile2_m
     code = _lib("moe_route").locus_moe_sort(
         _p(ids), I(n_pairs), I(layout.n_experts), I(layout.tile_m), _p(layout.counts),
         _p(layout.offsets), _p(layout.sorted_pair), _p(layout.pair_pos), _p(layout.tile_expert),
-        _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), _stream()
+        _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), I(tile2_m), _p(layout.tile2_expert),
+        _p(layout.tile2_row0), _p(layout.tile2_rows), _p(layout.n_tiles2), _stream()
     )
     _check(code, "moe_sort")
 
@@ -876,6 +904,7 @@ def route_small(logits: torch.Tensor, n_experts: int, has_gate: bool, ids: torch
     if tile_m is not None:
         _need(tile_m >= layout.MIN_TILE, f"route_small: tiles of at least {layout.MIN_TILE} rows")
         layout.tile_m = tile_m
+    layout.tile2_m = 0  # this call writes the first tile list only: a second list of an earlier call is stale now
     code = _lib("moe_route").locus_route_small(
         _p(logits), I(logits.stride(0)), _p(ids), _p(wts), _p(gamma), I(n_tokens), I(n_experts), I(top_k),
         I(1 if has_gate else 0), I(1 if renorm else 0), F(scale),
@@ -913,6 +942,7 @@ def route_fused_small(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor
     if tile_m is not None:
         _need(tile_m >= layout.MIN_TILE, f"route_fused_small: tiles of at least {layout.MIN_TILE} rows")
         layout.tile_m = tile_m
+    layout.tile2_m = 0  # as in route_small: no second tile list
     code = _lib("gemm_skinny").locus_router_fused_small(
         _p(h), _p(w_all), _p(logits), I(logits.stride(0)), _p(counter), _p(ids), _p(wts), _p(gamma), I(T), I(H),
         LL(h.stride(0)), I(n_experts), I(top_k), I(1 if has_gate else 0), I(1 if renorm else 0), F(scale),

@@ -177,7 +177,9 @@ class SparseMoe(FeedForward):
                 self.shared.forward(h, batch, residual, rt, row_scale=gamma)
         act = rt.rows(f"moe.act{self.I}", self.I, rt.dtype, n_pairs, per_token=self.k)
         if not sorted_already:
-            K.moe_sort(ids, n_pairs, lay, tile)
+            # the second product of the tensor-core path may walk the layout in larger tiles
+            tile2 = K.expert_second_tile(n_pairs, self.E) if (all_bf16 and not streamed) else 0
+            K.moe_sort(ids, n_pairs, lay, tile, tile2)
         if streamed or not all_bf16:
             # few rows per expert (or no tensor-core form): the kernels gather the token rows themselves
             K.linear(h, self.params["gate_exps"], act, w2=self.params["up_exps"], x_rows=lay.sorted_pair,
@@ -192,7 +194,7 @@ class SparseMoe(FeedForward):
         pair_dt = torch.bfloat16 if (all_bf16 and rt.dtype == torch.bfloat16) else torch.float32
         pair_out = rt.rows("moe.pair_out", self.hidden, pair_dt, n_pairs, per_token=self.k)
         K.linear(act, self.params["down_exps"], pair_out, layout=lay, n_rows=n_pairs, row_scale=wts,
-                 scale_rows=lay.sorted_pair, lists_ready=True)
+                 scale_rows=lay.sorted_pair, lists_ready=True, second_tiles=True)
         if overlap:
             rt.join()
         if self.shared is not None and not overlap:

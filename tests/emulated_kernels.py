@@ -48,6 +48,7 @@ class ExpertLayout(K.ExpertLayout):
 
 
 def linear(x, w, out, *, w2=None, bias=None, accumulate=False, row_scale=None, scale_rows=None, x_rows=None, lists_ready=False,
+           second_tiles=False,
            x_row_div=1, layout=None, n_rows=None):
     M = out.shape[0] if n_rows is None else n_rows
     if M == 0:
@@ -241,13 +242,14 @@ def route_fused_small(h, w_all, logits, n_experts, has_gate, ids, wts, gamma, la
     route_small(logits, n_experts, has_gate, ids, wts, gamma, layout, n_tokens=n_tokens, tile_m=tile_m, **rule)
 
 
-def moe_sort(ids, n_pairs, layout, tile_m=None):
+def moe_sort(ids, n_pairs, layout, tile_m=None, tile2_m=0):
     if tile_m is not None:
         layout.tile_m = tile_m
+    layout.tile2_m = tile2_m
     E, tm = layout.n_experts, layout.tile_m
     idl = ids[:n_pairs].tolist()
     pos = 0
-    tile = 0
+    tile = tile2 = 0
     for e in range(E):
         mine = [p for p, x in enumerate(idl) if x == e]
         layout.counts[e] = len(mine)
@@ -257,12 +259,19 @@ def moe_sort(ids, n_pairs, layout, tile_m=None):
             layout.tile_row0[tile] = pos + i
             layout.tile_rows[tile] = min(tm, len(mine) - i)
             tile += 1
+        for i in range(0, len(mine), tile2_m) if tile2_m else ():
+            layout.tile2_expert[tile2] = e
+            layout.tile2_row0[tile2] = pos + i
+            layout.tile2_rows[tile2] = min(tile2_m, len(mine) - i)
+            tile2 += 1
         for p in mine:
             layout.sorted_pair[pos] = p
             layout.pair_pos[p] = pos
             pos += 1
     layout.offsets[E] = pos
     layout.n_tiles[0] = tile
+    if tile2_m:
+        layout.n_tiles2[0] = tile2
 
 
 def moe_combine(x, pair_out, pair_pos, top_k):

@@ -144,6 +144,16 @@ def test_moe_sort_layout(T, E, k):
         assert torch.equal(getattr(lay, name).cpu(), getattr(ref, name)), name
     for name in ("tile_expert", "tile_row0", "tile_rows"):
         assert torch.equal(getattr(lay, name).cpu()[:n_tiles], getattr(ref, name)[:n_tiles]), name
+    # a second tile list over the same rows, in tiles of another size
+    K.moe_sort(ids.to(DEV), T * k, lay, 16, 40)
+    EK.moe_sort(ids, T * k, ref, 16, 40)
+    n1, n2 = int(ref.n_tiles), int(ref.n_tiles2)
+    assert (int(lay.n_tiles.cpu()), int(lay.n_tiles2.cpu())) == (n1, n2) and n2 <= lay.tiles_for(T * k, 40) and n2 <= n1
+    for name in ("tile_expert", "tile_row0", "tile_rows"):
+        assert torch.equal(getattr(lay, name).cpu()[:n1], getattr(ref, name)[:n1]), name
+    for name in ("tile2_expert", "tile2_row0", "tile2_rows"):
+        assert torch.equal(getattr(lay, name).cpu()[:n2], getattr(ref, name)[:n2]), name
+    assert int(lay.tile2_rows.cpu()[:n2].sum()) == T * k
 
 
 @pytest.mark.parametrize("xdt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
@@ -852,6 +862,18 @@ def test_linear_grouped_tensor_cores_every_tile(tile):
     ref_out = torch.empty(T * k, H, dtype=torch.float64)
     EK.linear(act.cpu(), wd, ref_out, layout=ref_lay, n_rows=T * k, row_scale=wts, scale_rows=ref_lay.sorted_pair)
     close(pair_out, ref_out, dt, f"grouped down, tile {tile}")
+    if tile == 128:
+        # the second product over the same layout in tiles of 256 rows (the crowded expert has 180): the same rows out
+        K.moe_sort(ids.to(DEV), T * k, lay, tile, 256)
+        assert int(lay.n_tiles2.cpu()) < int(lay.n_tiles.cpu())
+        out2 = torch.full((T * k, H), float("nan"), device=DEV)
+        K.linear(act, wd.to(DEV), out2, layout=lay, n_rows=T * k, row_scale=wts.to(DEV), scale_rows=lay.sorted_pair,
+                 second_tiles=True)
+        close(out2, ref_out, dt, "grouped down, second tile list of 256 rows")
+        bf = torch.full((T * k, H), float("nan"), dtype=dt, device=DEV)   # and into rows of the model's element type
+        K.linear(act, wd.to(DEV), bf, layout=lay, n_rows=T * k, row_scale=wts.to(DEV), scale_rows=lay.sorted_pair,
+                 second_tiles=True)
+        close(bf, ref_out, dt, "grouped down, bfloat16 rows")
     assert K.tc_error() == 0
 
 

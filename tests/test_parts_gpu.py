@@ -84,6 +84,30 @@ def test_dense_mlp_part(dtype, inter, shape):
     close(x, ref, dtype, "dense mlp adds into the residual")
 
 
+def _moe_step(part, W, cfg, dtype, rt, T, seed):
+    """One forward of the part on T random rows against the plain block, following the part's picks where the
+    oracle has a near-tie (see test_engine_gpu.py)."""
+    H, k = part.hidden, cfg["num_experts_per_tok"]
+    picked = []
+    part.observer = lambda prefix, ids, wts: picked.append(ids.cpu().tolist())
+    g = torch.Generator().manual_seed(seed)
+    h = torch.randn(T, H, generator=g).to(dtype)
+    x0 = torch.randn(T, H, generator=g)
+    x = x0.clone().to(DEV)
+    part.forward(h.to(DEV), None, x, rt)
+    aux = {}
+    plain.moe_block(h.double(), W, "f", cfg, aux=aux)
+    forced = []
+    for t in range(T):
+        ids, probs = aux["f"][t]
+        if sorted(picked[0][t]) != sorted(ids):
+            kth = min(float(probs[e]) for e in ids)
+            assert all(float(probs[e]) >= kth * (1 - (1e-5 if dtype == torch.float32 else 1e-2)) for e in picked[0][t])
+        forced.append(picked[0][t])
+    ref = x0.double() + plain.moe_block(h.double(), W, "f", cfg, forced=forced)
+    close(x, ref, dtype, f"sparse moe E={part.E} k={k} T={T}")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("E,k,norm,I,Is,T", [(8, 2, False, 32, 64, 5), (12, 3, True, 48, 0, 70), (60, 4, False, 40, 96, 300)])
 def test_sparse_moe_part(dtype, E, k, norm, I, Is, T):
@@ -93,25 +117,25 @@ def test_sparse_moe_part(dtype, E, k, norm, I, Is, T):
     W = fill(part, dtype, seed=3)
     rt = rt_for(dtype, max_tokens=320)
     part.bind(rt)
-    picked = []
-    part.observer = lambda prefix, ids, wts: picked.append(ids.cpu().tolist())
-    h = torch.randn(T, H).to(dtype)
-    x0 = torch.randn(T, H)
-    x = x0.clone().to(DEV)
-    part.forward(h.to(DEV), None, x, rt)
     cfg = {"num_experts_per_tok": k, "norm_topk_prob": norm, "shared_expert_intermediate_size": Is}
-    aux = {}
-    plain.moe_block(h.double(), W, "f", cfg, aux=aux)
-    # follow the part's routing where it is a near-tie in the oracle (see test_engine_gpu.py)
-    forced = []
-    for t in range(T):
-        ids, probs = aux["f"][t]
-        if sorted(picked[0][t]) != sorted(ids):
-            kth = min(float(probs[e]) for e in ids)
-            assert all(float(probs[e]) >= kth * (1 - (1e-5 if dtype == torch.float32 else 1e-2)) for e in picked[0][t])
-        forced.append(picked[0][t])
-    ref = x0.double() + plain.moe_block(h.double(), W, "f", cfg, forced=forced)
-    close(x, ref, dtype, f"sparse moe E={E} k={k}")
+    _moe_step(part, W, cfg, dtype, rt, T, 0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sparse_moe_part_steps_of_every_size_on_one_layout(dtype):
+    """The expert layout is shared by the steps: a step with many rows per expert (which, in bfloat16, leaves a
+    second tile list of 256 rows), then steps that sort in other ways (one launch for up to 16 tokens, tiles of 8
+    rows for up to 8, the general sort above), each of which must not see the lists of the step before."""
+    H, E, k, I = 72, 4, 4, 48
+    assert K.expert_second_tile(100 * k, E) == 256 and K.expert_second_tile(40 * k, E) == 0
+    part = make_part("feed_forward", PartSpec("sparse_moe", {"hidden": H, "n_experts": E, "top_k": k, "norm_topk": True,
+                                                              "expert_intermediate": I, "shared_intermediate": 32}), "f")
+    W = fill(part, dtype, seed=4)
+    rt = rt_for(dtype, max_tokens=320)
+    part.bind(rt)
+    cfg = {"num_experts_per_tok": k, "norm_topk_prob": True, "shared_expert_intermediate_size": 32}
+    for i, T in enumerate([100, 16, 300, 3, 40, 12, 120, 17]):
+        _moe_step(part, W, cfg, dtype, rt, T, 10 + i)
 
 
 def _attention_case(dtype, nh, nkv, hd, window, H=80, P=16):
