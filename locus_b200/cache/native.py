@@ -49,6 +49,7 @@ def lib() -> ctypes.CDLL:
             "locus_step_build": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                          c_int, c_int, c_int, c_int, c_void_p, c_int64, c_void_p, c_void_p]),
             "locus_plan_query_tiles": (c_int, [c_int, c_void_p, c_int, c_int, c_void_p, c_int64]),
+            "locus_sort_tiles_by_position": (None, [c_int, c_void_p, c_void_p]),
             "locus_plan_segments_with": (c_int, [c_int, c_void_p, c_int, c_void_p, c_int64]),
         }
         sig.update({

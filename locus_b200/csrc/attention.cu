@@ -75,8 +75,10 @@ __global__ void __launch_bounds__(128) attn_chunk_kernel(AttnArgs a) {
     float* l_s = m_s + CHUNK_BQ;                   // [BQ]
     float* al_s = l_s + CHUNK_BQ;                  // [BQ]
 
-    const int seg = a.items[2 * blockIdx.x], qoff = a.items[2 * blockIdx.x + 1];
-    const int h = blockIdx.y;
+    // the late tiles of a prompt see the most keys: the grid takes them first, for all heads (its fast index)
+    const int item = gridDim.y - 1 - blockIdx.y;
+    const int seg = a.items[2 * item], qoff = a.items[2 * item + 1];
+    const int h = blockIdx.x;
     const int kvh = h / (a.nh / a.nkv);
     const int nq = min(CHUNK_BQ, a.seg_qn[seg] - qoff);
     const int row0 = a.seg_q0[seg] + qoff;
@@ -672,12 +674,12 @@ extern "C" int locus_attn_chunk(const void* q, int dt, const void* pool, void* o
                                 float scale, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     if (int e = check_common(nh, nkv, hd, page_tokens, window)) return e;
-    if (nh > 65535) return LOCUS_ERR_UNSUPPORTED;
+    if (n_items > 65535) return LOCUS_ERR_UNSUPPORTED;
     AttnArgs a = make_args(q, pool, out, seg_q0, seg_qn, seg_ctx, block_table, table_stride, items,
                            nh, nkv, hd, page_tokens, window, scale);
     const size_t smem = sizeof(float) * (CHUNK_BQ * hd + CHUNK_TK * (hd + 1) + CHUNK_TK * hd +
                                          CHUNK_BQ * (CHUNK_TK + 1) + 3 * CHUNK_BQ);
-    dim3 grid(n_items, nh);
+    dim3 grid(nh, n_items);
     if (dt == LOCUS_DT_F32) {
         cudaFuncSetAttribute(attn_chunk_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         attn_chunk_kernel<float><<<grid, 128, smem, stream>>>(a);

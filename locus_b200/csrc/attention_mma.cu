@@ -90,10 +90,10 @@ __global__ void __launch_bounds__(128) attn_chunk_mma_kernel(MmaAttnArgs a) {
     bf16* sV = sK + 2 * MK * LDS;                      // [2][MK][LDS]
 
     // Items are listed in ascending position; the late tiles of a prompt see the most keys, so the grid
-    // takes them first and the short ones fill the tail.
-    const int item = gridDim.x - 1 - blockIdx.x;
+    // takes them first, for all heads (the heads are the grid's fast index), and the short ones fill the tail.
+    const int item = gridDim.y - 1 - blockIdx.y;
     const int seg = a.items[2 * item], qoff = a.items[2 * item + 1];
-    const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+    const int h = blockIdx.x, kvh = h / (a.nh / a.nkv);
     const int nq = min(MQ, a.seg_qn[seg] - qoff);
     const int row0 = a.seg_q0[seg] + qoff;
     const int p0 = a.seg_ctx[seg] + qoff;
@@ -365,7 +365,8 @@ static int launch(const MmaAttnArgs& a, int n_items, cudaStream_t stream) {
             return static_cast<int>(cudaGetLastError());
         set = true;
     }
-    dim3 grid(n_items, a.nh, a.n_splits);
+    if (n_items > 65535) return LOCUS_ERR_UNSUPPORTED;
+    dim3 grid(a.nh, n_items, a.n_splits);
     attn_chunk_mma_kernel<HD><<<grid, 128, smem, stream>>>(a);
     if (a.n_splits > 1)
         attn_chunk_merge_kernel<<<dim3((MQ * (HD / 2) + 127) / 128, n_items, a.nh), 128, 0, stream>>>(a, HD);

@@ -153,11 +153,12 @@ __global__ void __launch_bounds__(320, 1)
 attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, TcAttnArgs a) {
     extern __shared__ __align__(1024) uint8_t at_raw[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    // the late tiles of a prompt see the most keys: the grid takes them first
-    const int item = gridDim.x - 1 - blockIdx.x;
+    // the late tiles of a prompt see the most keys: the grid takes them first, for all heads (the heads are the
+    // fast index of the grid, so that the blocks go out longest first and the last SMs to finish hold short ones)
+    const int item = gridDim.y - 1 - blockIdx.y;
     const int seg = a.items[2 * item], qoff = a.items[2 * item + 1];
     if (qoff & 64) return;  // items are tiles of 64 queries; a block takes an even one and its upper neighbour
-    const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
+    const int h = blockIdx.x, kvh = h / (a.nh / a.nkv);
     const int nq = min(AT_MQ, a.seg_qn[seg] - qoff);
     const int row0 = a.seg_q0[seg] + qoff;
     const int p0 = a.seg_ctx[seg] + qoff;
@@ -489,7 +490,8 @@ extern "C" int locus_attn_chunk_tc(const void* q, long long T, const void* pool,
             return static_cast<int>(cudaGetLastError());
         set = true;
     }
-    dim3 grid(n_items, nh);
+    if (n_items > 65535) return LOCUS_ERR_UNSUPPORTED;
+    dim3 grid(nh, n_items);
     attn_chunk_tc_kernel<<<grid, 320, smem, stream>>>(map_q, map_kv, a);
     return locus_launch_status();
 }

@@ -457,6 +457,22 @@ int locus_plan_query_tiles(int n_seg, const int* seg_qn, int tile, int min_new, 
     return static_cast<int>(n);
 }
 
+// Orders n query tiles (segment, first query) by the position of their first query, seg_ctx[segment] + first
+// query, ascending and stable: the attention kernels walk the list from its end, so the tiles that see the most
+// keys go out first and the short ones fill the tail, whichever requests they belong to.
+void locus_sort_tiles_by_position(int n, int* items, const int* seg_ctx) {
+    if (n <= 1) return;
+    std::vector<std::pair<int, int>> v(n);
+    for (int i = 0; i < n; ++i) v[i] = {items[2 * i], items[2 * i + 1]};
+    std::stable_sort(v.begin(), v.end(), [&](const std::pair<int, int>& a, const std::pair<int, int>& b) {
+        return seg_ctx[a.first] + a.second < seg_ctx[b.first] + b.second;
+    });
+    for (int i = 0; i < n; ++i) {
+        items[2 * i] = v[i].first;
+        items[2 * i + 1] = v[i].second;
+    }
+}
+
 // The segments with exactly `new_tokens` new tokens, in order; returns their number, or -1 when out is too small.
 int locus_plan_segments_with(int n_seg, const int* seg_qn, int new_tokens, int* out, int64_t cap) {
     int64_t n = 0;

@@ -29,7 +29,9 @@ class AttentionTiles(StepPlan):
     """The work lists of this file's attention kernels: tiles of 16 queries (CUDA-core kernel) and of 64 queries
     (tensor-core kernels) over the segments with more than one new token, and the segments with exactly one
     (the decode kernel).  One plan serves every attention layer of a model.  The lists are made by two small
-    native helpers (csrc/host_core.cpp: ``locus_plan_query_tiles``, ``locus_plan_segments_with``)."""
+    native helpers (csrc/host_core.cpp: ``locus_plan_query_tiles``, ``locus_plan_segments_with``).  The tiles are
+    listed by the position of their first query, ascending, across requests: the kernels walk a list from its end,
+    so the tiles with the most keys start first (``locus_sort_tiles_by_position``)."""
 
     key = ("attention.tiles", CHUNK_TILE, K.MMA_QUERY_TILE)
 
@@ -52,6 +54,9 @@ class AttentionTiles(StepPlan):
         n1 = self._lib.locus_plan_segments_with(n_seg, qn, 1, base + 4 * o1, cap - o1)
         if n16 < 0 or n64 < 0 or n1 < 0:
             raise ValueError("attention: the step has more tiles than the plan's capacity holds")
+        ctx = seg_ctx.ctypes.data
+        self._lib.locus_sort_tiles_by_position(n16, base, ctx)
+        self._lib.locus_sort_tiles_by_position(n64, base + 4 * o64, ctx)
         return {"chunk_items": (0, 2 * n16, (-1, 2)), "n_chunk_items": n16,
                 "chunk_items64": (o64, 2 * n64, (-1, 2)), "n_chunk_items64": n64,
                 "decode_items": (o1, n1, None), "n_decode_items": n1}

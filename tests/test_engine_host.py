@@ -143,6 +143,9 @@ def plain_descriptors(cache, entries, chunk_tile, mma_tile):
         for gid, row in e.seq.tables.items():
             groups[gid]["slots"] += [row[p // P] * P + p % P for p in range(ctx, ctx + n)]
             groups[gid]["table"].append(row + [-1] * (W - len(row)))
+    # tiles by the position of their first query, ascending; ties keep the order of the requests
+    for k in ("chunk_items", "chunk_items64"):
+        out[k] = sorted(out[k], key=lambda sq: out["seg_ctx"][sq[0]] + sq[1])
     return out, groups
 
 
