@@ -46,7 +46,24 @@ struct TcAttnArgs {
     const int* items;
     int nh, nkv, page_tokens, window;
     float scale;
+    // Ranges of key tiles per block of queries (1: a block writes the result itself).  With more, a block takes
+    // one range (blockIdx.z) and leaves, per query row of the step and head, its unnormalised sum, its running
+    // maximum (base 2, scaled) and its denominator; attn_chunk_tc_merge_kernel adds the ranges up in ascending order.
+    int n_splits;
+    float* part_o;    // [row][head][split][128]
+    float* part_ml;   // [row][head][split][2]
 };
+
+// Key tiles of a block of nq queries whose first sits at position p0: the first tile's first position and their
+// number, and how they are cut into ranges (the same in both kernels).
+__device__ __forceinline__ void at_tiles(int p0, int nq, int window, int n_splits, int& first_tile, int& n_tiles,
+                                         int& per_split) {
+    const int t_hi = p0 + nq - 1;
+    const int t_lo = window > 0 ? max(0, p0 - window + 1) : 0;
+    first_tile = (t_lo / AT_MK) * AT_MK;
+    n_tiles = (t_hi - first_tile) / AT_MK + 1;
+    per_split = (n_tiles + n_splits - 1) / n_splits;
+}
 
 __device__ __forceinline__ uint32_t at_smem(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -165,8 +182,13 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int t_hi = p0 + nq - 1;
     const int t_lo = a.window > 0 ? max(0, p0 - a.window + 1) : 0;
     const int P = a.page_tokens;
-    const int first_tile = (t_lo / AT_MK) * AT_MK;
-    const int n_tiles = (t_hi - first_tile) / AT_MK + 1;
+    // this block's range of the key tiles (all of them when the keys are not cut)
+    int first_tile, n_tiles_all, per_split;
+    at_tiles(p0, nq, a.window, a.n_splits, first_tile, n_tiles_all, per_split);
+    const int split = blockIdx.z;
+    first_tile += split * per_split * AT_MK;
+    const int n_tiles = max(0, min(per_split, n_tiles_all - split * per_split));
+    if (n_tiles == 0) return;  // the merge counts the live ranges the same way
     const int* table = a.block_table + static_cast<size_t>(seg) * a.table_stride;
 
     // shared memory: Q, K[2], V[2], P[2] (each a tile of two swizzled halves), then the barriers.  That is
@@ -406,7 +428,15 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (!add_sum(n_tiles - 1, alpha_prev)) ok = false;
         {
             const float l = l_run + with_partner(n_tiles & 1, l_run);
-            if (ok && r < nq) {
+            if (a.n_splits > 1) {
+                if (ok && r < nq) {
+                    const size_t unit = (static_cast<size_t>(row0 + r) * a.nh + h) * a.n_splits + split;
+                    float* po = a.part_o + unit * AT_HD + 64 * half;
+#pragma unroll
+                    for (int d = 0; d < 64; d += 4) *reinterpret_cast<float4*>(po + d) = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
+                    if (half == 0) *reinterpret_cast<float2*>(a.part_ml + unit * 2) = make_float2(m_run, l);
+                }
+            } else if (ok && r < nq) {
                 const float inv = 1.0f / l;
                 bf16* dst = a.out + (static_cast<size_t>(row0 + r) * a.nh + h) * AT_HD + 64 * half;
 #pragma unroll
@@ -427,6 +457,56 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
     }
+}
+
+#define AT_MAX_SPLITS 16
+
+// out[row][head] = sum over the live ranges s (ascending) of o_s 2^(m_s - M) / sum of l_s 2^(m_s - M), M = max m_s.
+// One thread per (query row, four adjacent dimensions) of a block of queries and a head; the loads of all ranges
+// are issued together (the loops are unrolled over the most ranges there can be).
+__global__ void __launch_bounds__(128) attn_chunk_tc_merge_kernel(TcAttnArgs a) {
+    const int item = blockIdx.y, h = blockIdx.z;
+    const int seg = a.items[2 * item], qoff = a.items[2 * item + 1];
+    if (qoff & 64) return;
+    const int nq = min(AT_MQ, a.seg_qn[seg] - qoff);
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nq * (AT_HD / 4)) return;
+    const int r = i / (AT_HD / 4), d = (i - r * (AT_HD / 4)) * 4;
+    const int row = a.seg_q0[seg] + qoff + r;
+    int first_tile, n_tiles, per_split;
+    at_tiles(a.seg_ctx[seg] + qoff, nq, a.window, a.n_splits, first_tile, n_tiles, per_split);
+    const int live = (n_tiles + per_split - 1) / per_split;
+    const size_t unit0 = (static_cast<size_t>(row) * a.nh + h) * a.n_splits;
+    float2 ml[AT_MAX_SPLITS];
+    float4 v[AT_MAX_SPLITS];
+#pragma unroll
+    for (int s = 0; s < AT_MAX_SPLITS; ++s) {
+        ml[s] = make_float2(-INFINITY, 0.f);
+        v[s] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (s < live) {
+            ml[s] = *reinterpret_cast<const float2*>(a.part_ml + (unit0 + s) * 2);
+            v[s] = *reinterpret_cast<const float4*>(a.part_o + (unit0 + s) * AT_HD + d);
+        }
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < AT_MAX_SPLITS; ++s) M = fmaxf(M, ml[s].x);
+    float L = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < AT_MAX_SPLITS; ++s) {
+        const float w = ml[s].x == -INFINITY ? 0.f : exp2f(ml[s].x - M);
+        L += ml[s].y * w;
+        acc.x += v[s].x * w;
+        acc.y += v[s].y * w;
+        acc.z += v[s].z * w;
+        acc.w += v[s].w * w;
+    }
+    const float inv = 1.0f / L;
+    uint2 pk;
+    pk.x = at_pack(acc.x * inv, acc.y * inv);
+    pk.y = at_pack(acc.z * inv, acc.w * inv);
+    *reinterpret_cast<uint2*>(a.out + (static_cast<size_t>(row) * a.nh + h) * AT_HD + d) = pk;
 }
 
 // ---------------------------------------------------------------------------
@@ -464,11 +544,18 @@ static bool at_make_map(CUtensorMap* map, const void* ptr, long long rows, long 
 // q, out [T, nh * 128] bfloat16; pool: one layer's pages [n_pages][2][nkv][page_tokens][128] bfloat16;
 // items: [n_items, 2] = (segment, first query of a 64-query tile), a segment's tiles in ascending order.
 // Head size 128 and pages of a multiple of 64 tokens only (LOCUS_ERR_UNSUPPORTED otherwise).
+// n_splits > 1: the key tiles of every block are cut into that many ranges (at most 16); part_o holds
+// T * nh * n_splits * 128 floats, part_ml T * nh * n_splits * 2; a second launch merges.
 extern "C" int locus_attn_chunk_tc(const void* q, long long T, const void* pool, long long n_pages, void* out,
                                    const int* seg_q0, const int* seg_qn, const int* seg_ctx, const int* block_table,
                                    int table_stride, const int* items, int n_items, int nh, int nkv, int hd,
-                                   int page_tokens, int window, float scale, cudaStream_t stream) {
+                                   int page_tokens, int window, float scale, int n_splits, float* part_o,
+                                   float* part_ml, cudaStream_t stream) {
     if (n_items <= 0) return 0;
+    if (n_splits < 1 || n_splits > AT_MAX_SPLITS) return LOCUS_ERR_UNSUPPORTED;
+    if (n_splits > 1 && (part_o == nullptr || part_ml == nullptr ||
+                         ((reinterpret_cast<uintptr_t>(part_o) | reinterpret_cast<uintptr_t>(part_ml)) & 15)))
+        return LOCUS_ERR_UNSUPPORTED;
     if (hd != AT_HD || page_tokens <= 0 || page_tokens % 64 != 0 || window < 0) return LOCUS_ERR_UNSUPPORTED;
     if (nh <= 0 || nkv <= 0 || nh % nkv != 0 || nh > 65535) return LOCUS_ERR_UNSUPPORTED;
     const long long pool_rows = n_pages * 2 * nkv * page_tokens;
@@ -483,6 +570,7 @@ extern "C" int locus_attn_chunk_tc(const void* q, long long T, const void* pool,
     a.out = static_cast<bf16*>(out); a.seg_q0 = seg_q0; a.seg_qn = seg_qn; a.seg_ctx = seg_ctx;
     a.block_table = block_table; a.table_stride = table_stride; a.items = items; a.nh = nh; a.nkv = nkv;
     a.page_tokens = page_tokens; a.window = window; a.scale = scale;
+    a.n_splits = n_splits; a.part_o = part_o; a.part_ml = part_ml;
     const size_t smem = 7 * AT_TILE_BYTES + 160 + 2 * 2 * 128 * 4;
     static bool set = false;
     if (!set) {
@@ -491,8 +579,10 @@ extern "C" int locus_attn_chunk_tc(const void* q, long long T, const void* pool,
         set = true;
     }
     if (n_items > 65535) return LOCUS_ERR_UNSUPPORTED;
-    dim3 grid(nh, n_items);
+    dim3 grid(nh, n_items, n_splits);
     attn_chunk_tc_kernel<<<grid, 320, smem, stream>>>(map_q, map_kv, a);
+    if (n_splits > 1)
+        attn_chunk_tc_merge_kernel<<<dim3(AT_MQ * (AT_HD / 4) / 128, n_items, nh), 128, 0, stream>>>(a);
     return locus_launch_status();
 }
 

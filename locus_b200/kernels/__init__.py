@@ -609,35 +609,79 @@ def attn_chunk_mma(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, se
 
 
 TC_ATTN_HEAD_DIM = 128   # the tcgen05 attention kernel: this head size, pages of a multiple of 64 tokens
-TC_ATTN_MIN_TOKENS = 256  # portions of fewer new tokens in a step stay with the mma.sync kernel
+TC_ATTN_MIN_TOKENS = 256  # from this many new tokens in a step on, the tcgen05 kernel takes every portion
 
 
-def attn_chunk_tc_takes(q: torch.Tensor, head_dim: int, page_tokens: int, n_tokens: int) -> bool:
-    """Whether the tcgen05 kernel of prompt portions takes this step: bfloat16, head size 128, pages of
-    a multiple of 64 tokens, and enough new tokens to fill blocks of 128 queries."""
-    return (USE_TENSOR_CORES and q.dtype == torch.bfloat16 and head_dim == TC_ATTN_HEAD_DIM
-            and page_tokens % 64 == 0 and n_tokens >= TC_ATTN_MIN_TOKENS)
+def attn_chunk_tc_takes(q: torch.Tensor, head_dim: int, page_tokens: int, n_tokens: int, max_ctx: int = 0) -> bool:
+    """Whether the tcgen05 kernel of prompt portions takes this step: bfloat16, head size 128, pages of a
+    multiple of 64 tokens, and either enough new tokens to fill blocks of 128 queries or a context long enough
+    that the kernel's faster walk over the keys (cut into ranges, :func:`attn_chunk_tc_splits`) outweighs its
+    start-up.  Measured at 16 heads against the mma.sync kernel, both with their key ranges: 128 new tokens
+    behind 1,000 / 4,000 / 30,000 cached ones 18.6 / 20.4 / 59.6 us against 15.0 / 31.5 / 153.8 us; 16 new tokens
+    14.2 / 16.4 / 53.9 us against 9.0 / 17.4 / 89.4 us."""
+    if not (USE_TENSOR_CORES and q.dtype == torch.bfloat16 and head_dim == TC_ATTN_HEAD_DIM and page_tokens % 64 == 0):
+        return False
+    return n_tokens >= TC_ATTN_MIN_TOKENS or max_ctx >= (2048 if n_tokens >= 128 else 4096)
+
+
+TC_ATTN_MAX_SPLITS = 16
+TC_ATTN_QUERY_BLOCK = 128   # queries of a block of the tcgen05 kernel (two of the 64-query tiles of its item list)
+
+
+def attn_chunk_tc_splits(n_items: int, n_heads: int, max_ctx: int) -> int:
+    """Ranges the key tiles of every block of :func:`attn_chunk_tc` are cut into.  A block takes 128 queries of one
+    head, a block per SM: a portion of a few hundred tokens behind a long context makes fewer blocks than the GPU
+    has SMs, each walking thousands of keys alone.  Then the keys are cut so that about every SM has a block, down
+    to four tiles of 128 keys per range (a block's start and end cost about four tiles' time)."""
+    blocks = -(-n_items // 2) * n_heads
+    n_sm = _sm_count()
+    tiles = -(-max_ctx // TC_ATTN_QUERY_BLOCK)
+    if 2 * blocks > n_sm or tiles < 8:
+        return 1
+    return max(1, min(TC_ATTN_MAX_SPLITS, n_sm // blocks, tiles // 4))
+
+
+def attn_chunk_tc_scratch() -> Tuple[int, int]:
+    """Floats of the two scratch buffers (sums; maxima and denominators) that :func:`attn_chunk_tc` needs for any
+    cut that :func:`attn_chunk_tc_splits` chooses: one partial result per (token, head, range), and the ranges
+    never outnumber SMs / blocks while a block holds at most 128 tokens of a head."""
+    units = TC_ATTN_QUERY_BLOCK * _sm_count()
+    return units * TC_ATTN_HEAD_DIM, units * 2
 
 
 def attn_chunk_tc(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
                   seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
                   items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,
-                  page_tokens: int, window: int, scale: float) -> None:
+                  page_tokens: int, window: int, scale: float, n_splits: int = 1,
+                  part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None) -> None:
     """Attention of portions of prompts with tcgen05 tensor cores (scores and sums in tensor memory):
-    ``items`` as for :func:`attn_chunk_mma` (tiles of 64 queries, a segment's tiles in ascending order;
-    a block takes two)."""
+    ``items`` as for :func:`attn_chunk_mma` (tiles of 64 queries; a block takes an even one and the 64 queries
+    behind it).  ``n_splits`` > 1 (:func:`attn_chunk_tc_splits`) with scratch of :func:`attn_chunk_tc_scratch`
+    floats: the key tiles of every block are cut into that many ranges, merged in ascending order by a second
+    kernel."""
     _cuda_c(q, "q")
     _cuda_c(out, "out")
     _cuda_c(pool, "pool")
     _i32(block_table, "block_table")
     _i32(items, "items")
     _need(q.dtype == pool.dtype == out.dtype == torch.bfloat16, "attn_chunk_tc: bfloat16 only")
+    _need(1 <= n_splits <= TC_ATTN_MAX_SPLITS, f"attn_chunk_tc: 1 to {TC_ATTN_MAX_SPLITS} key ranges")
+    if n_splits > 1:
+        units = q.shape[0] * n_heads * n_splits
+        n_o, n_ml = units * TC_ATTN_HEAD_DIM, units * 2
+        _need(part_o is not None and part_ml is not None and part_o.dtype == part_ml.dtype == torch.float32
+              and part_o.is_cuda and part_ml.is_cuda and part_o.numel() >= n_o and part_ml.numel() >= n_ml,
+              "attn_chunk_tc: scratch too small for these ranges")
     code = _lib("attention_tc").locus_attn_chunk_tc(
         _p(q), LL(q.shape[0]), _p(pool), LL(pool.shape[0]), _p(out), _p(seg_q0), _p(seg_qn), _p(seg_ctx),
         _p(block_table), I(block_table.shape[1]), _p(items), I(n_items), I(n_heads), I(n_kv_heads), I(head_dim),
-        I(page_tokens), I(window), F(scale), _stream()
+        I(page_tokens), I(window), F(scale), I(n_splits), _p(part_o if n_splits > 1 else None),
+        _p(part_ml if n_splits > 1 else None), _stream()
     )
-    _check(code, "attn_chunk_tc", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim}, pages of {page_tokens})")
+    if n_splits > 1 and code == 0:
+        _count_launches(1)
+    _check(code, "attn_chunk_tc", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim}, pages of {page_tokens}, "
+                                  f"{n_splits} key ranges)")
 
 
 def attn_tc_error() -> int:

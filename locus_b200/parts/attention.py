@@ -141,13 +141,20 @@ class Attention(Mixer):
         cap_splits = (gb.block_table.shape[1] * gb.page_tokens - 1) // K.DECODE_SPLIT + 1
         max_splits = cap_splits if batch.static_shapes else min(cap_splits, (max(batch.longest, 1) - 1) // K.DECODE_SPLIT + 1)
         if tiles["n_chunk_items"]:
-            if K.attn_chunk_tc_takes(q, self.head_dim, gb.page_tokens, T):
-                K.attn_chunk_tc(q, cache.pool, o, items=tiles["chunk_items64"], n_items=tiles["n_chunk_items64"], **common)
+            # few query tiles behind a long context: the keys of every tile are cut into ranges
+            keys = max_splits * K.DECODE_SPLIT
+            if self.window > 0:
+                keys = min(keys, self.window + K.TC_ATTN_QUERY_BLOCK)
+            if K.attn_chunk_tc_takes(q, self.head_dim, gb.page_tokens, T, keys):
+                n_splits = K.attn_chunk_tc_splits(tiles["n_chunk_items64"], self.n_heads, keys)
+                part_o = part_ml = None
+                if n_splits > 1:
+                    n_o, n_ml = K.attn_chunk_tc_scratch()
+                    part_o = rt.buf("attention.chunk_tc_part_o", (n_o,), torch.float32)
+                    part_ml = rt.buf("attention.chunk_tc_part_ml", (n_ml,), torch.float32)
+                K.attn_chunk_tc(q, cache.pool, o, items=tiles["chunk_items64"], n_items=tiles["n_chunk_items64"],
+                                n_splits=n_splits, part_o=part_o, part_ml=part_ml, **common)
             elif K.attn_chunk_mma_takes(q, self.head_dim):
-                # few 64-query tiles behind a long context: the keys of every tile are cut into ranges
-                keys = max_splits * K.DECODE_SPLIT
-                if self.window > 0:
-                    keys = min(keys, self.window + K.MMA_QUERY_TILE)
                 n_splits = K.attn_chunk_mma_splits(tiles["n_chunk_items64"], self.n_heads, keys)
                 part_o = part_ml = None
                 if n_splits > 1:

@@ -168,11 +168,16 @@ def bench_attn_chunk(args) -> None:
     tile = K.MMA_QUERY_TILE if mma else 16
     items = torch.tensor([(0, o) for o in range(0, T, tile)], dtype=torch.int32, device="cuda:0")
 
-    tc = mma and not args.mma_sync and K.attn_chunk_tc_takes(q, args.head_dim, args.page_tokens, T)
+    tc = mma and not args.mma_sync and K.attn_chunk_tc_takes(q, args.head_dim, args.page_tokens, T, ctx + T)
 
     extra = {}
     n_splits = 1
-    if mma and not tc:
+    if tc:
+        n_splits = K.attn_chunk_tc_splits(items.shape[0], args.heads, ctx + T) if args.key_ranges < 0 else args.key_ranges
+        if n_splits > 1:
+            n_o, n_ml = T * args.heads * n_splits * args.head_dim, T * args.heads * n_splits * 2
+            extra = dict(n_splits=n_splits, part_o=torch.empty(n_o, device="cuda:0"), part_ml=torch.empty(n_ml, device="cuda:0"))
+    elif mma:
         n_splits = K.attn_chunk_mma_splits(items.shape[0], args.heads, ctx + T) if args.key_ranges < 0 else args.key_ranges
         if n_splits > 1:
             n_o, n_ml = K.attn_chunk_mma_scratch(args.head_dim)
@@ -185,7 +190,7 @@ def bench_attn_chunk(args) -> None:
     us = _time(fn, args.iters, args.graph)
     flops = 4.0 * args.heads * args.head_dim * (T * ctx + T * (T + 1) / 2)
     print(f"attn_chunk tokens={T} ctx={ctx} heads={args.heads}/{args.kv_heads} head_dim={args.head_dim} "
-          f"{'tcgen05' if tc else (f'mma.sync, {n_splits} key ranges' if mma else 'cuda cores')}: {us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
+          f"{f'tcgen05, {n_splits} key ranges' if tc else (f'mma.sync, {n_splits} key ranges' if mma else 'cuda cores')}: {us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
 
 
 def main(argv=None) -> int:
@@ -219,7 +224,7 @@ def main(argv=None) -> int:
                     help="linear: with --token-tile, parts along K (0 = not split)")
     ap.add_argument("--cuda-cores", action="store_true", help="attn_chunk: the CUDA-core kernel")
     ap.add_argument("--key-ranges", type=int, default=-1,
-                    help="attn_chunk, mma.sync kernel: ranges the keys are cut into (default: the engine's choice)")
+                    help="attn_chunk, tensor-core kernels: ranges the keys are cut into (default: the engine's choice)")
     ap.add_argument("--mma-sync", action="store_true", help="attn_chunk: the mma.sync kernel where tcgen05 would run")
     args = ap.parse_args(argv)
     if args.skinny_rows >= 0:

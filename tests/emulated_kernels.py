@@ -24,7 +24,7 @@ def embed_rows(tokens, table, out):
     out.copy_(table[tokens.long()].to(out.dtype))
 
 
-def attn_chunk_tc_takes(q, head_dim, page_tokens, n_tokens):
+def attn_chunk_tc_takes(q, head_dim, page_tokens, n_tokens, max_ctx=0):
     return False
 
 

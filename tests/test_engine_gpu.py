@@ -38,12 +38,12 @@ REQUESTS = {  # name -> (length, seed); lengths straddle page edges (16 and 64) 
 
 
 class Case:
-    def __init__(self, name, tmp):
+    def __init__(self, name, tmp, raw=None, requests=None):
         self.name = name
-        self.dir = make_model_dir(tmp, name, torch.bfloat16)
+        self.dir = make_model_dir(tmp, name, torch.bfloat16, raw=raw)
         self.cfg, self.weights = plain.load_folder(self.dir)
         self.tokens = {f"r{i}": random_tokens(n, self.cfg["vocab_size"], 100 * s + n)
-                       for i, (n, s) in enumerate(REQUESTS[name])}
+                       for i, (n, s) in enumerate(requests or REQUESTS[name])}
         self._ref = {}
 
     def ref(self, rid):
@@ -204,6 +204,33 @@ def test_long_portions_with_head_size_128(dtype, tmp_path_factory):
         K.attn_chunk_tc = orig
     assert (len(used) > 0) == (dtype == torch.bfloat16)
     assert K.attn_tc_error() == 0 if dtype == torch.bfloat16 else True
+
+
+def test_short_portions_behind_a_long_context_with_head_size_128(tmp_path_factory):
+    """A prompt of 4,400 tokens: most of it in one step, then portions of 100, 17, 64 and 2 tokens and single
+    tokens behind more than 4,000 cached ones, a second request beside them.  In bfloat16 the short portions run on
+    the tcgen05 attention kernel with the keys of every block cut into ranges that a second launch merges."""
+    import locus_b200.kernels as K
+    from tiny_configs import config
+
+    raw = config("D")
+    raw["max_position_embeddings"] = 8192
+    case = Case("D", tmp_path_factory.mktemp("models_d_long"), raw=raw, requests=[(4400, 7), (40, 3)])
+    ranges = []
+    orig = K.attn_chunk_tc
+    K.attn_chunk_tc = lambda *a, **k: (ranges.append((a[0].shape[0], k.get("n_splits", 1))), orig(*a, **k))[1]
+    try:
+        runner, cache = make_runner(case, torch.bfloat16, page_tokens=64, n_pages=80, max_tokens=4224, max_seq=8192)
+        steps = [[("r0", 4200)], [("r0", 100), ("r1", 38)], [("r0", 17), ("r1", 1)], [("r0", 64), ("r1", 1)], [("r0", 2)]]
+        steps += [[("r0", 1)]] * (4400 - 4383)
+        got = run_trace(runner, cache, case, steps)
+        check(case, got, torch.bfloat16, "short portions behind a long context")
+        assert cache.free_pages() == cache.total_pages()
+    finally:
+        K.attn_chunk_tc = orig
+    assert K.attn_tc_error() == 0
+    # the long first step in one range; every short portion behind it in several
+    assert ranges[0] == (4200, 1) and all(n > 1 for t, n in ranges if t < 200) and sum(t < 200 for t, n in ranges) >= 8
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -529,12 +529,66 @@ def test_attn_chunk_tcgen05(nh, nkv, P, window):
     kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=window, scale=1 / math.sqrt(hd))
     assert K.attn_chunk_tc_takes(q.to(DEV), hd, P, T)
     assert not K.attn_chunk_tc_takes(q.to(DEV), hd, 48, T) and not K.attn_chunk_tc_takes(q.to(DEV), 64, P, T)
+    assert not K.attn_chunk_tc_takes(q.to(DEV), hd, P, 100, 1500) and K.attn_chunk_tc_takes(q.to(DEV), hd, P, 16, 5000)
     out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
     K.attn_chunk_tc(q.to(DEV), pool.to(DEV), out, items=items_t.to(DEV), n_items=len(items), **_dev(meta), **kw)
     assert K.attn_tc_error() == 0
     ref = torch.zeros(T, nh * hd, dtype=torch.float64)
     EK.attn_chunk(q, torch.nan_to_num(pool, nan=1e4), ref, items=items_t, n_items=len(items), **meta, **kw)
     close(out, ref, dtype, "attn_chunk_tc")
+    # the key tiles of every block cut into ranges (more ranges than most blocks have tiles) and merged by a second
+    # launch; the items in another order (the kernel walks the list from its end, whatever the order)
+    order = torch.randperm(len(items), generator=torch.Generator().manual_seed(3))
+    shuffled = items_t[order].contiguous()
+    for n_splits, its in ((2, items_t), (3, shuffled), (16, items_t)):
+        part_o = torch.full((T * nh * n_splits * hd,), float("nan"), device=DEV)
+        part_ml = torch.full((T * nh * n_splits * 2,), float("nan"), device=DEV)
+        out_s = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        before = K.launches
+        K.attn_chunk_tc(q.to(DEV), pool.to(DEV), out_s, items=its.to(DEV), n_items=len(items), n_splits=n_splits,
+                        part_o=part_o, part_ml=part_ml, **_dev(meta), **kw)
+        assert K.launches - before == 2 and K.attn_tc_error() == 0
+        close(out_s, ref, dtype, f"attn_chunk_tc in {n_splits} key ranges")
+    with pytest.raises(K.KernelError):
+        K.attn_chunk_tc(q.to(DEV), pool.to(DEV), out, items=items_t.to(DEV), n_items=len(items), n_splits=2,
+                        part_o=part_o[:8], part_ml=part_ml, **_dev(meta), **kw)
+    with pytest.raises(K.KernelError):
+        K.attn_chunk_tc(q.to(DEV), pool.to(DEV), out, items=items_t.to(DEV), n_items=len(items), n_splits=17,
+                        part_o=part_o, part_ml=part_ml, **_dev(meta), **kw)
+    n_sm = torch.cuda.get_device_properties(0).multi_processor_count
+    assert K.attn_chunk_tc_splits(64, 16, 100000) == 1 and K.attn_chunk_tc_splits(4, 16, 600) == 1
+    assert 1 < K.attn_chunk_tc_splits(4, 16, 30000) <= min(K.TC_ATTN_MAX_SPLITS, n_sm // 32)
+    # the scratch of attn_chunk_tc_scratch holds every cut that attn_chunk_tc_splits chooses
+    for n_items, heads in ((2, 1), (4, 16), (5, 7), (16, 4), (3, 40)):
+        sp = K.attn_chunk_tc_splits(n_items, heads, 1 << 20)
+        assert 64 * n_items * heads * sp * hd <= K.attn_chunk_tc_scratch()[0], (n_items, heads, sp)
+
+
+def test_attn_chunk_tcgen05_one_far_key_among_thousands_in_ranges():
+    """A portion of 256 tokens behind 6,000 cached ones, the keys cut into ranges: one key far back (in an early
+    range) is made to carry nearly all the weight of some queries, so that a range whose maximum or denominator
+    were lost in the merge would show."""
+    dtype, hd, nh, nkv, P = torch.bfloat16, 128, 2, 1, 64
+    segs = [(6000, 256)]
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=5, n_pages=100)
+    far = 777
+    page, off = int(meta["block_table"][0, far // P]), far % P
+    pool[page, 0, 0, off] = pool[page, 0, 0, off] * 0 + 4.0      # a large key ...
+    q[::3] = q[::3] * 0 + 0.5                                     # ... that every third query points at
+    items_t = torch.tensor([(0, o) for o in range(0, 256, K.MMA_QUERY_TILE)], dtype=torch.int32)
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=0, scale=1 / math.sqrt(hd))
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.attn_chunk(q, pool, ref, items=items_t, n_items=len(items_t), **meta, **kw)
+    v_far = pool[page, 1, 0, off].double()
+    assert float((ref[0, :hd] - v_far).abs().max()) < 1e-2 * float(v_far.abs().max())   # the far key does dominate
+    for n_splits in (1, 5, 12):
+        part_o = torch.full((T * nh * n_splits * hd,), float("nan"), device=DEV)
+        part_ml = torch.full((T * nh * n_splits * 2,), float("nan"), device=DEV)
+        out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        K.attn_chunk_tc(q.to(DEV), pool.to(DEV), out, items=items_t.to(DEV), n_items=len(items_t), n_splits=n_splits,
+                        part_o=part_o, part_ml=part_ml, **_dev(meta), **kw)
+        assert K.attn_tc_error() == 0
+        close(out, ref, dtype, f"far key, {n_splits} key ranges")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
