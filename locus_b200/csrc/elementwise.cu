@@ -63,12 +63,43 @@ __global__ void rmsnorm_kernel(const void* __restrict__ x, int x_dt, const void*
 // (the outputs of a row's experts, the sum that moe_combine_kernel forms, in the same order), written
 // back to x, then the norm of the new row.  With rows the sum goes into the norm only and x stays as
 // it was (a row may be named twice, and nobody reads the other rows' sums).
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void put4(float* p, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void put4(bf16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = pk;
+}
+// dst[c .. c + 3] = t * scale * w[c .. c + 3], every element rounded once as from_f does
+template <typename TW, typename TO>
+__device__ __forceinline__ void store4(TO* dst, const TW* w, int c, float4 t, float scale, bool wide) {
+    if (wide) {
+        const float4 g = load4(w + c);
+        put4(dst + c, t.x * scale * g.x, t.y * scale * g.y, t.z * scale * g.z, t.w * scale * g.w);
+    } else {
+        dst[c] = from_f<TO>(t.x * scale * to_f(w[c]));
+        dst[c + 1] = from_f<TO>(t.y * scale * to_f(w[c + 1]));
+        dst[c + 2] = from_f<TO>(t.z * scale * to_f(w[c + 2]));
+        dst[c + 3] = from_f<TO>(t.w * scale * to_f(w[c + 3]));
+    }
+}
+
 template <typename TW, typename TO>
 __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x, const TW* __restrict__ w,
                                                           float eps, TO* __restrict__ out,
                                                           const int* __restrict__ rows, int H,
                                                           const void* __restrict__ add_src, int add_bf16,
-                                                          const int* __restrict__ add_pos, int add_k) {
+                                                          const int* __restrict__ add_pos, int add_k, int vec_io) {
     pdl_entry();
     pdl_trigger();
     __shared__ float warp_part[8];
@@ -128,15 +159,14 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x,
     __syncthreads();
     const float scale = scale_s;
     TO* dst = out + static_cast<size_t>(i) * H;
-    for (int j = threadIdx.x; j < n4; j += 256) {
-        const int u = j >> 8;
-        const float4 t = u < 4 ? v[u] : fetch_again(j);
-        const int c = j << 2;
-        dst[c] = from_f<TO>(t.x * scale * to_f(w[c]));
-        dst[c + 1] = from_f<TO>(t.y * scale * to_f(w[c + 1]));
-        dst[c + 2] = from_f<TO>(t.z * scale * to_f(w[c + 2]));
-        dst[c + 3] = from_f<TO>(t.w * scale * to_f(w[c + 3]));
+    // four weights in, four results out, each as one access where the rows are aligned for it (checked by the host)
+    const bool wide = vec_io;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int j = threadIdx.x + u * 256;
+        if (j < n4) store4(dst, w, j << 2, v[u], scale, wide);
     }
+    for (int j = threadIdx.x + 1024; j < n4; j += 256) store4(dst, w, j << 2, fetch_again(j), scale, wide);
 }
 
 // add_src (float32 or bfloat16 rows, add_dt) / add_pos / add_k: see rmsnorm_f32_kernel; only with float32 x, H a
@@ -151,11 +181,13 @@ extern "C" int locus_rmsnorm(void* x, int x_dt, const void* w, int w_dt, float e
          (add_dt != LOCUS_DT_F32 && add_dt != LOCUS_DT_BF16)))
         return LOCUS_ERR_UNSUPPORTED;
     const int add_bf16 = add_dt == LOCUS_DT_BF16 ? 1 : 0;
+    // weights and output rows start on 16-byte boundaries (H % 4 == 0 keeps every row of out aligned for 4 elements)
+    const int vec_io = ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 ? 1 : 0;
     if (fast) {
         float* xf = static_cast<float*>(x);
 #define NORM_LAUNCH(TW, TO)                                                                             \
         locus_launch(rmsnorm_f32_kernel<TW, TO>, n_rows, 256, 0, stream, xf, static_cast<const TW*>(w), eps,      \
-                     static_cast<TO*>(out), rows, H, add_src, add_bf16, add_pos, add_k)
+                     static_cast<TO*>(out), rows, H, add_src, add_bf16, add_pos, add_k, vec_io)
         if (w_dt == LOCUS_DT_BF16 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(bf16, bf16);
         else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_F32) NORM_LAUNCH(float, float);
         else if (w_dt == LOCUS_DT_F32 && out_dt == LOCUS_DT_BF16) NORM_LAUNCH(float, bf16);

@@ -202,11 +202,15 @@ __global__ void __launch_bounds__(256) moe_count_kernel(const int* __restrict__ 
     }
 }
 
-// One block per expert.  Each of the 8 warps takes a contiguous eighth of the pairs: it counts its
-// matches, the block adds the warps' counts in order, then every warp ranks its own matches with
-// ballots -- no block-wide barrier inside the loops.  Positions are ascending in p (stable).
+// One block per expert.  Each of the 8 warps takes a contiguous eighth of the pairs.  With COUNT the block first
+// counts every expert's pairs itself, per warp, in shared memory (E blocks each read the ids once from L2: cheaper
+// than a launch of its own for the counts, which every block needs for its offset) and writes its own expert's
+// count; without, the counts come from moe_count_kernel.  The block adds the warps' counts in order, then every
+// warp ranks its own matches with ballots -- no block-wide barrier inside the loops.  Positions are ascending
+// in p (stable).
+template <bool COUNT>
 __global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ ids, int n_pairs, int E,
-                                                        const int* __restrict__ counts, int tile_m,
+                                                        int* __restrict__ counts, int tile_m,
                                                         int* __restrict__ offsets, int* __restrict__ sorted_pair,
                                                         int* __restrict__ pair_pos, int* __restrict__ tile_expert,
                                                         int* __restrict__ tile_row0, int* __restrict__ tile_rows,
@@ -214,47 +218,82 @@ __global__ void __launch_bounds__(256) moe_fill_kernel(const int* __restrict__ i
                                                         int* __restrict__ tile2_expert, int* __restrict__ tile2_row0,
                                                         int* __restrict__ tile2_rows, int* __restrict__ n_tiles2) {
     pdl_entry();
+    extern __shared__ int hist[];  // COUNT: [8 warps][E] pairs of a warp's eighth per expert, then [E] totals
     __shared__ int s_off;
     __shared__ int warp_cnt[8];
     const int e = blockIdx.x;
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    if (threadIdx.x == 0) {
-        int off = 0, tile = 0, tile2 = 0;
-        for (int j = 0; j < e; ++j) {
-            off += counts[j];
-            tile += (counts[j] + tile_m - 1) / tile_m;
-            if (tile2_m > 0) tile2 += (counts[j] + tile2_m - 1) / tile2_m;
-        }
-        s_off = off;
-        offsets[e] = off;
-        const int mine = counts[e];
-        const int nt = (mine + tile_m - 1) / tile_m;
-        for (int i = 0; i < nt; ++i) {
-            tile_expert[tile + i] = e;
-            tile_row0[tile + i] = off + i * tile_m;
-            tile_rows[tile + i] = min(tile_m, mine - i * tile_m);
-        }
-        if (tile2_m > 0) {  // the same rows in tiles of another size (for a product with another token tile)
-            const int nt2 = (mine + tile2_m - 1) / tile2_m;
-            for (int i = 0; i < nt2; ++i) {
-                tile2_expert[tile2 + i] = e;
-                tile2_row0[tile2 + i] = off + i * tile2_m;
-                tile2_rows[tile2 + i] = min(tile2_m, mine - i * tile2_m);
-            }
-            if (e == E - 1) *n_tiles2 = tile2 + nt2;
-        }
-        if (e == E - 1) {
-            offsets[E] = off + mine;
-            *n_tiles = tile + nt;
-        }
-    }
     const int per = ((n_pairs + 7) / 8 + 31) & ~31;  // pairs per warp, a multiple of 32
     const int p_begin = wid * per, p_end = min(n_pairs, p_begin + per);
-    int c = 0;
-    for (int p = p_begin + lane; p < p_end; p += 32) c += (ids[p] == e);
+    const int* cnt = counts;
+    if (COUNT) {
+        for (int i = threadIdx.x; i < 8 * E; i += blockDim.x) hist[i] = 0;
+        __syncthreads();
+        for (int p = p_begin + lane; p < p_end; p += 32) {
+            const int id = ids[p];
+            if (id >= 0 && id < E) atomicAdd(&hist[wid * E + id], 1);
+        }
+        __syncthreads();
+        int* tot = hist + 8 * E;
+        for (int j = threadIdx.x; j < E; j += blockDim.x) {
+            int c = 0;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
-    if (lane == 0) warp_cnt[wid] = c;
+            for (int w = 0; w < 8; ++w) c += hist[w * E + j];
+            tot[j] = c;
+        }
+        __syncthreads();
+        cnt = tot;
+        if (threadIdx.x == 0) counts[e] = tot[e];
+    }
+    if (wid == 0) {
+        // rows and tiles of the experts before this one
+        int off = 0, tile = 0, tile2 = 0;
+        for (int j = lane; j < e; j += 32) {
+            const int c = cnt[j];
+            off += c;
+            tile += (c + tile_m - 1) / tile_m;
+            if (tile2_m > 0) tile2 += (c + tile2_m - 1) / tile2_m;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            off += __shfl_xor_sync(0xffffffffu, off, o);
+            tile += __shfl_xor_sync(0xffffffffu, tile, o);
+            tile2 += __shfl_xor_sync(0xffffffffu, tile2, o);
+        }
+        if (lane == 0) {
+            s_off = off;
+            offsets[e] = off;
+            const int mine = cnt[e];
+            const int nt = (mine + tile_m - 1) / tile_m;
+            for (int i = 0; i < nt; ++i) {
+                tile_expert[tile + i] = e;
+                tile_row0[tile + i] = off + i * tile_m;
+                tile_rows[tile + i] = min(tile_m, mine - i * tile_m);
+            }
+            if (tile2_m > 0) {  // the same rows in tiles of another size (for a product with another token tile)
+                const int nt2 = (mine + tile2_m - 1) / tile2_m;
+                for (int i = 0; i < nt2; ++i) {
+                    tile2_expert[tile2 + i] = e;
+                    tile2_row0[tile2 + i] = off + i * tile2_m;
+                    tile2_rows[tile2 + i] = min(tile2_m, mine - i * tile2_m);
+                }
+                if (e == E - 1) *n_tiles2 = tile2 + nt2;
+            }
+            if (e == E - 1) {
+                offsets[E] = off + mine;
+                *n_tiles = tile + nt;
+            }
+        }
+    }
+    if (COUNT) {
+        if (lane == 0) warp_cnt[wid] = hist[wid * E + e];
+    } else {
+        int c = 0;
+        for (int p = p_begin + lane; p < p_end; p += 32) c += (ids[p] == e);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) c += __shfl_xor_sync(0xffffffffu, c, o);
+        if (lane == 0) warp_cnt[wid] = c;
+    }
     __syncthreads();
     int pos = s_off;
     for (int w = 0; w < wid; ++w) pos += warp_cnt[w];
@@ -280,9 +319,17 @@ extern "C" int locus_moe_sort(const int* ids, int n_pairs, int E, int tile_m, in
     if (E <= 0 || tile_m <= 0 || tile2_m < 0) return LOCUS_ERR_UNSUPPORTED;
     if (tile2_m > 0 && (tile2_expert == nullptr || tile2_row0 == nullptr || tile2_rows == nullptr || n_tiles2 == nullptr))
         return LOCUS_ERR_UNSUPPORTED;
-    locus_launch(moe_count_kernel, E, 256, 0, stream, ids, n_pairs, counts);
-    locus_launch(moe_fill_kernel, E, 256, 0, stream, ids, n_pairs, E, counts, tile_m, offsets, sorted_pair, pair_pos,
-                 tile_expert, tile_row0, tile_rows, n_tiles, tile2_m, tile2_expert, tile2_row0, tile2_rows, n_tiles2);
+    const size_t hist = sizeof(int) * 9 * static_cast<size_t>(E);
+    if (hist <= 40 * 1024) {  // one launch: every block counts for itself
+        locus_launch(moe_fill_kernel<true>, E, 256, hist, stream, ids, n_pairs, E, counts, tile_m, offsets, sorted_pair,
+                     pair_pos, tile_expert, tile_row0, tile_rows, n_tiles, tile2_m, tile2_expert, tile2_row0, tile2_rows,
+                     n_tiles2);
+    } else {
+        locus_launch(moe_count_kernel, E, 256, 0, stream, ids, n_pairs, counts);
+        locus_launch(moe_fill_kernel<false>, E, 256, 0, stream, ids, n_pairs, E, counts, tile_m, offsets, sorted_pair,
+                     pair_pos, tile_expert, tile_row0, tile_rows, n_tiles, tile2_m, tile2_expert, tile2_row0, tile2_rows,
+                     n_tiles2);
+    }
     return locus_launch_status();
 }
 

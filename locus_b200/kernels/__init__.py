@@ -90,9 +90,10 @@ class stream_scope:
         return False
 
 
-# kernels launched through this module since import (several entry points launch two)
+# kernels launched through this module since import (some entry points launch two and count the second themselves)
 launches = 0
-_LAUNCHES_OF = {"moe_sort": 2}
+_LAUNCHES_OF = {}
+MOE_SORT_ONE_LAUNCH_EXPERTS = 40 * 1024 // (9 * 4)   # up to this many experts moe_sort is one launch, else two
 
 
 def _count_launches(n: int) -> None:
@@ -917,6 +918,8 @@ def moe_sort(ids: torch.Tensor, n_pairs: int, layout: ExpertLayout, tile_m: Opti
         _p(layout.tile_row0), _p(layout.tile_rows), _p(layout.n_tiles), I(tile2_m), _p(layout.tile2_expert),
         _p(layout.tile2_row0), _p(layout.tile2_rows), _p(layout.n_tiles2), _stream()
     )
+    if code == 0 and layout.n_experts > MOE_SORT_ONE_LAUNCH_EXPERTS:
+        _count_launches(1)
     _check(code, "moe_sort")
 
 

@@ -128,8 +128,11 @@ def _route(T, E, k, seed):
     return ids
 
 
-@pytest.mark.parametrize("T,E,k", [(1, 4, 2), (50, 7, 3), (300, 60, 4), (9, 5, 5)])
+@pytest.mark.parametrize("T,E,k", [(1, 4, 2), (50, 7, 3), (300, 60, 4), (9, 5, 5), (2100, 60, 4), (200, 1500, 3)])
 def test_moe_sort_layout(T, E, k):
+    """(With up to MOE_SORT_ONE_LAUNCH_EXPERTS experts every block counts all experts' pairs itself; beyond, a
+    launch of its own counts.)"""
+    assert 60 < K.MOE_SORT_ONE_LAUNCH_EXPERTS < 1500
     ids = _route(T, E, k, T)
     if T == 9:
         ids[:] = 2  # every pair on one expert; others empty
