@@ -446,6 +446,9 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
 
     const int grp = lane / LPK, sub = lane % LPK;  // which row of a load, which 16 bytes of the row
     const int d0 = sub * VEC;
+    // A row of hd elements takes hd / VEC lanes; LPK is that number rounded up to a power of two (head sizes like
+    // 96 or 48), and the lanes behind the row's end neither load nor store: they carry zeros through the sums.
+    const bool active = d0 < hd;
     const float qscale = a.scale * 1.4426950408889634f;  // scores in base 2
     const int pshift = (P & (P - 1)) == 0 ? __ffs(P) - 1 : -1;  // pages of 2^k tokens: shifts instead of divisions
     const size_t v_off = static_cast<size_t>(a.nkv) * P * hd;  // V row = K row + v_off
@@ -484,6 +487,10 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
         };
         auto live = [&](int k0, int g) -> bool {
             const int t = k0 + g * KPL + grp;
+            return active && t >= t_lo && t < k_end;
+        };
+        auto t_live = [&](int k0, int g) -> bool {  // the key itself, whatever this lane's part of its row
+            const int t = k0 + g * KPL + grp;
             return t >= t_lo && t < k_end;
         };
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
@@ -510,7 +517,9 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
         float q[VEC];
         {
             float raw[VEC];
-            Vec<T>::load(static_cast<const T*>(a.q) + (static_cast<size_t>(row) * a.nh + h) * hd + d0, raw);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) raw[i] = 0.f;
+            if (active) Vec<T>::load(static_cast<const T*>(a.q) + (static_cast<size_t>(row) * a.nh + h) * hd + d0, raw);
 #pragma unroll
             for (int i = 0; i < VEC; ++i) q[i] = raw[i] * qscale;
         }
@@ -521,7 +530,7 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
             // V of this chunk
 #pragma unroll
             for (int g = 0; g < DS_LOADS; ++g)
-                vreg[g] = (FAST || live(k0, g)) ? ld_once(pool4 + v_units + base + g * KPL * row_units) : zero4;
+                vreg[g] = ((FAST && active) || live(k0, g)) ? ld_once(pool4 + v_units + base + g * KPL * row_units) : zero4;
             // scores of this chunk
             float sc[DS_LOADS];
 #pragma unroll
@@ -533,7 +542,7 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
                 for (int i = 0; i < VEC; ++i) dot = fmaf(q[i], kf[i], dot);
 #pragma unroll
                 for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                sc[g] = (FAST || live(k0, g)) ? dot : -INFINITY;
+                sc[g] = (FAST || t_live(k0, g)) ? dot : -INFINITY;
             }
             // K of the next chunk, and the block-table entry of the chunk after the next two
             base = chunk_base(k0 + CHUNK, page_next);
@@ -541,7 +550,7 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
             page_next2 = page_of(k0 + 3 * CHUNK);
 #pragma unroll
             for (int g = 0; g < DS_LOADS; ++g)
-                kreg[g] = (FAST || live(k0 + CHUNK, g)) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+                kreg[g] = ((FAST && active) || live(k0 + CHUNK, g)) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
             // running softmax of this lane group, then the weighted sum
             float mx = m;
 #pragma unroll
@@ -587,7 +596,7 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
             for (int i = 0; i < VEC; ++i) acc[i] = low ? acc[i] * wa + acc_o[i] * wb : acc_o[i] * wb + acc[i] * wa;
             m = mx;
         }
-        if (grp == 0) {
+        if (grp == 0 && active) {
             float* po = a.part_o + static_cast<size_t>(u) * hd + d0;
 #pragma unroll
             for (int i = 0; i < VEC; i += 4) *reinterpret_cast<float4*>(po + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
@@ -711,10 +720,12 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
     a.part_o = part_o; a.part_ml = part_ml; a.counters = counters; a.max_splits = max_splits;
     if (counters == nullptr) return LOCUS_ERR_UNSUPPORTED;
     if (max_units < static_cast<long long>(n_items) * nh) return LOCUS_ERR_UNSUPPORTED;
-    // rows of 128, 256 or 512 bytes: the streaming kernel on a fixed grid
-    const int lpk = hd * (dt == LOCUS_DT_F32 ? 4 : 2) / 16;
+    // rows of 64 to 512 bytes: the streaming kernel on a fixed grid, 8, 16 or 32 lanes to a row (the row's 16-byte
+    // pieces rounded up to a power of two: a head of 96 bfloat16 elements takes 12 of 16 lanes)
+    const int pieces = hd * (dt == LOCUS_DT_F32 ? 4 : 2) / 16;
+    const int lpk = pieces < 4 ? 0 : pieces <= 8 ? 8 : pieces <= 16 ? 16 : pieces <= 32 ? 32 : 0;
     const int chunk_keys = lpk > 0 ? DS_LOADS * 32 / lpk : 1;
-    if ((dt == LOCUS_DT_F32 || dt == LOCUS_DT_BF16) && (lpk == 8 || lpk == 16 || lpk == 32) && n_items <= DS_MAX_ITEMS &&
+    if ((dt == LOCUS_DT_F32 || dt == LOCUS_DT_BF16) && lpk > 0 && n_items <= DS_MAX_ITEMS &&
         page_tokens % chunk_keys == 0) {
         static int n_sm = 0;
         if (n_sm == 0) {

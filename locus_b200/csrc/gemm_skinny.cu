@@ -105,7 +105,9 @@ __global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
     const bf16* uh = DUAL ? W2 + r_hi * K : nullptr;
     const uint4 zero = make_uint4(0, 0, 0, 0);
     // this warp's k-steps: 32 elements each, interleaved with the other warps'; four steps at a time
-    constexpr int STEP = 32, STRIDE = STEP * SK_WARPS, UNROLL = 4;
+    // (the router's launch is a handful of blocks whose whole share of the weights fits eight steps per warp: they
+    // are all asked for at once, before the wait for the kernel in front)
+    constexpr int STEP = 32, STRIDE = STEP * SK_WARPS, UNROLL = ROUTE ? 8 : 4;
     uint4 al[UNROLL], ah[UNROLL], bl[DUAL ? UNROLL : 1], bh[DUAL ? UNROLL : 1];
     auto load_weights = [&](int kb) {
 #pragma unroll

@@ -729,10 +729,11 @@ def attn_decode_gqa_takes(dtype: torch.dtype, n_heads: int, n_kv_heads: int, hea
 
 def decode_streams(head_dim: int, dtype: torch.dtype, page_tokens: int, max_items: int) -> bool:
     """Whether :func:`attn_decode` runs the streaming kernel (the condition of csrc/attention.cu): rows of
-    128, 256 or 512 bytes, pages that are a multiple of that row size's chunk of 32, 16 or 8 keys, and at
-    most 1024 requests."""
-    row_bytes = head_dim * (4 if dtype == torch.float32 else 2)
-    return row_bytes in (128, 256, 512) and page_tokens % (4096 // row_bytes) == 0 and max_items <= 1024
+    64 to 512 bytes (8, 16 or 32 lanes to a row: its 16-byte pieces rounded up to a power of two), pages that
+    are a multiple of that lane count's chunk of 32, 16 or 8 keys, and at most 1024 requests."""
+    pieces = head_dim * (4 if dtype == torch.float32 else 2) // 16
+    lanes = 0 if pieces < 4 else 8 if pieces <= 8 else 16 if pieces <= 16 else 32 if pieces <= 32 else 0
+    return lanes > 0 and page_tokens % (256 // lanes) == 0 and max_items <= 1024
 
 
 def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype, max_splits: int, device,

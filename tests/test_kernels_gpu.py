@@ -598,7 +598,8 @@ def test_attn_chunk_tcgen05_one_far_key_among_thousands_in_ranges():
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 4, 16, 16, 0), (6, 2, 32, 64, 0), (5, 1, 48, 16, 0),
                                                 (16, 16, 128, 64, 0), (2, 1, 256, 64, 0), (4, 2, 64, 16, 300),
                                                 (4, 2, 128, 64, 300), (8, 8, 64, 32, 50), (6, 3, 32, 32, 0),
-                                                (4, 4, 80, 16, 7)])
+                                                (4, 4, 80, 16, 7), (8, 8, 96, 64, 0), (4, 2, 48, 64, 20),
+                                                (3, 3, 112, 32, 0), (2, 2, 192, 16, 0)])
 def test_attn_decode(dtype, nh, nkv, hd, P, window):
     segs = [(0, 1), (255, 1), (256, 1), (700, 1), (31, 1)]
     pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=hd + 1, n_pages=100)
