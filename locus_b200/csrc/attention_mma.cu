@@ -16,8 +16,8 @@
 // that run as blocks of their own (blockIdx.z) and leave unnormalised sums, running maxima and
 // denominators in a scratch; attn_chunk_merge_kernel adds the ranges up in ascending order.
 //
-// Head sizes: multiples of 16 up to 128 (template instances 16, 32, 48, 64, 96, 128); other
-// sizes are refused and the caller uses the CUDA-core kernel.  Rows in shared memory are
+// Head sizes: every multiple of 16 up to 256 (a template instance each); other sizes are refused and the
+// caller uses the CUDA-core kernel.  Rows in shared memory are
 // padded by 16 bytes so that ldmatrix reads no bank twice.
 #include "common.cuh"
 
@@ -395,8 +395,18 @@ extern "C" int locus_attn_chunk_mma(const void* q, const void* pool, void* out, 
         case 32: return launch<32>(a, n_items, stream);
         case 48: return launch<48>(a, n_items, stream);
         case 64: return launch<64>(a, n_items, stream);
+        case 80: return launch<80>(a, n_items, stream);
         case 96: return launch<96>(a, n_items, stream);
+        case 112: return launch<112>(a, n_items, stream);
         case 128: return launch<128>(a, n_items, stream);
+        case 144: return launch<144>(a, n_items, stream);
+        case 160: return launch<160>(a, n_items, stream);
+        case 176: return launch<176>(a, n_items, stream);
+        case 192: return launch<192>(a, n_items, stream);
+        case 208: return launch<208>(a, n_items, stream);
+        case 224: return launch<224>(a, n_items, stream);
+        case 240: return launch<240>(a, n_items, stream);
+        case 256: return launch<256>(a, n_items, stream);
         default: return LOCUS_ERR_UNSUPPORTED;
     }
 }

@@ -546,7 +546,7 @@ def attn_chunk(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0
     _check(code, "attn_chunk", f"(heads {n_heads}/{n_kv_heads}, head_dim {head_dim})")
 
 
-MMA_HEAD_DIMS = (16, 32, 48, 64, 96, 128)
+MMA_HEAD_DIMS = tuple(range(16, 257, 16))
 MMA_QUERY_TILE = 64
 
 

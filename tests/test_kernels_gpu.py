@@ -479,7 +479,11 @@ def test_attn_chunk(dtype, nh, nkv, hd, P, window):
 
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 4, 16, 16, 0), (6, 2, 32, 16, 0), (5, 1, 48, 64, 0),
                                                 (2, 2, 64, 16, 0), (3, 1, 96, 64, 0), (4, 2, 128, 64, 0),
-                                                (4, 2, 64, 16, 20), (2, 1, 32, 64, 1), (2, 2, 128, 16, 100)])
+                                                (4, 2, 64, 16, 20), (2, 1, 32, 64, 1), (2, 2, 128, 16, 100),
+                                                (2, 1, 80, 16, 0), (3, 3, 112, 64, 30), (2, 2, 144, 16, 0),
+                                                (2, 1, 160, 64, 0), (2, 2, 176, 16, 0), (4, 2, 192, 32, 50),
+                                                (2, 2, 208, 16, 0), (2, 1, 224, 64, 0), (2, 2, 240, 16, 0),
+                                                (2, 1, 256, 64, 0)])
 def test_attn_chunk_tensor_cores(nh, nkv, hd, P, window):
     """Portions of 2 to 200 tokens at contexts that straddle the 64-key tiles and the pages."""
     dtype = torch.bfloat16
