@@ -412,8 +412,8 @@ __device__ __forceinline__ uint4 ld_once(const uint4* p) {
 struct true_tag { static constexpr bool value = true; };
 struct false_tag { static constexpr bool value = false; };
 
-template <typename T, int LPK>
-__global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(AttnArgs a, int n_items, int max_units,
+template <typename T, int LPK, bool DEEP, bool PADDED>
+__global__ void __launch_bounds__(32 * DS_WARPS, DEEP ? 2 : 4) attn_decode_stream_kernel(AttnArgs a, int n_items, int max_units,
                                                                               int cost_range, int cost_merge) {
     pdl_trigger();  // every block of this grid is resident from the start
     constexpr int VEC = 16 / sizeof(T);   // elements of a lane
@@ -446,9 +446,11 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
 
     const int grp = lane / LPK, sub = lane % LPK;  // which row of a load, which 16 bytes of the row
     const int d0 = sub * VEC;
-    // A row of hd elements takes hd / VEC lanes; LPK is that number rounded up to a power of two (head sizes like
-    // 96 or 48), and the lanes behind the row's end neither load nor store: they carry zeros through the sums.
-    const bool active = d0 < hd;
+    // A row of hd elements takes hd / VEC lanes.  PADDED: LPK is that number rounded up to a power of two (head
+    // sizes like 96 or 48), and the lanes behind the row's end neither load nor store: they carry zeros through
+    // the sums.  (A template parameter: at large batches the kernel is bound by instruction issue, and the
+    // predicate on every load costs a tenth of its time.)
+    const bool active = PADDED ? d0 < hd : true;
     const float qscale = a.scale * 1.4426950408889634f;  // scores in base 2
     const int pshift = (P & (P - 1)) == 0 ? __ffs(P) - 1 : -1;  // pages of 2^k tokens: shifts instead of divisions
     const size_t v_off = static_cast<size_t>(a.nkv) * P * hd;  // V row = K row + v_off
@@ -494,89 +496,157 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
             return t >= t_lo && t < k_end;
         };
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
-        uint4 kreg[DS_LOADS], vreg[DS_LOADS];
-        int page_next = page_of(k_begin + CHUNK), page_next2 = page_of(k_begin + 2 * CHUNK);
-        unsigned base = chunk_base(k_begin, page_of(k_begin));
-        // Keys before the request's own position were written by earlier steps: a first chunk that ends before that
-        // position is asked for before the wait for the kernel in front, which writes q and the newest key and value.
-        const bool early = !waited && k_begin + CHUNK <= p;
-        if (early) {
-#pragma unroll
-            for (int g = 0; g < DS_LOADS; ++g)
-                kreg[g] = live(k_begin, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
-        }
-        if (!waited) {
-            pdl_entry();
-            waited = true;
-        }
-        if (!early) {
-#pragma unroll
-            for (int g = 0; g < DS_LOADS; ++g)
-                kreg[g] = live(k_begin, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
-        }
         float q[VEC];
-        {
+        auto load_q = [&]() {
             float raw[VEC];
 #pragma unroll
             for (int i = 0; i < VEC; ++i) raw[i] = 0.f;
             if (active) Vec<T>::load(static_cast<const T*>(a.q) + (static_cast<size_t>(row) * a.nh + h) * hd + d0, raw);
 #pragma unroll
             for (int i = 0; i < VEC; ++i) q[i] = raw[i] * qscale;
-        }
-        // One chunk: FAST when this chunk and the next lie wholly inside the range (the steady state), so
-        // that no load and no score needs a check of its own.
-        auto chunk = [&](int k0, auto fast_tag) {
-            constexpr bool FAST = decltype(fast_tag)::value;
-            // V of this chunk
-#pragma unroll
-            for (int g = 0; g < DS_LOADS; ++g)
-                vreg[g] = ((FAST && active) || live(k0, g)) ? ld_once(pool4 + v_units + base + g * KPL * row_units) : zero4;
-            // scores of this chunk
-            float sc[DS_LOADS];
-#pragma unroll
-            for (int g = 0; g < DS_LOADS; ++g) {
-                float kf[VEC];
-                Vec<T>::unpack(kreg[g], kf);
-                float dot = 0.f;
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) dot = fmaf(q[i], kf[i], dot);
-#pragma unroll
-                for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                sc[g] = (FAST || t_live(k0, g)) ? dot : -INFINITY;
-            }
-            // K of the next chunk, and the block-table entry of the chunk after the next two
-            base = chunk_base(k0 + CHUNK, page_next);
-            page_next = page_next2;
-            page_next2 = page_of(k0 + 3 * CHUNK);
-#pragma unroll
-            for (int g = 0; g < DS_LOADS; ++g)
-                kreg[g] = ((FAST && active) || live(k0 + CHUNK, g)) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
-            // running softmax of this lane group, then the weighted sum
-            float mx = m;
-#pragma unroll
-            for (int g = 0; g < DS_LOADS; ++g) mx = fmaxf(mx, sc[g]);
-            if (FAST || mx != -INFINITY) {
-                const float corr = exp2f(m - mx);  // 0 on the first live chunk
-                l *= corr;
-#pragma unroll
-                for (int i = 0; i < VEC; ++i) acc[i] *= corr;
+        };
+        if constexpr (DEEP) {
+            // Few requests: a warp's time is the latency of its chain of chunks, not bandwidth.  K and V of TWO
+            // chunks are kept in flight (twice the registers, half the blocks per SM): while one chunk is worked on
+            // the next is already under way and the one after that is asked for as soon as registers are free.
+            uint4 kb[2][DS_LOADS], vb[2][DS_LOADS];
+            auto issue = [&](int slot, int k0) {
+                const unsigned cb = chunk_base(k0, page_of(k0));
 #pragma unroll
                 for (int g = 0; g < DS_LOADS; ++g) {
-                    const float pr = exp2f(sc[g] - mx);  // 0 for a key that is not there
-                    l += pr;
-                    float vf[VEC];
-                    Vec<T>::unpack(vreg[g], vf);
-#pragma unroll
-                    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(pr, vf[i], acc[i]);
+                    const bool lv = live(k0, g);
+                    kb[slot][g] = lv ? ld_once(pool4 + cb + g * KPL * row_units) : zero4;
+                    vb[slot][g] = lv ? ld_once(pool4 + v_units + cb + g * KPL * row_units) : zero4;
                 }
-                m = mx;
+            };
+            auto consume = [&](int slot, int k0) {
+                float sc[DS_LOADS];
+#pragma unroll
+                for (int g = 0; g < DS_LOADS; ++g) {
+                    float kf[VEC];
+                    Vec<T>::unpack(kb[slot][g], kf);
+                    float dot = 0.f;
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) dot = fmaf(q[i], kf[i], dot);
+#pragma unroll
+                    for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                    sc[g] = t_live(k0, g) ? dot : -INFINITY;
+                }
+                float mx = m;
+#pragma unroll
+                for (int g = 0; g < DS_LOADS; ++g) mx = fmaxf(mx, sc[g]);
+                if (mx != -INFINITY) {
+                    const float corr = exp2f(m - mx);  // 0 on the first live chunk
+                    l *= corr;
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) acc[i] *= corr;
+#pragma unroll
+                    for (int g = 0; g < DS_LOADS; ++g) {
+                        const float pr = exp2f(sc[g] - mx);  // 0 for a key that is not there
+                        l += pr;
+                        float vf[VEC];
+                        Vec<T>::unpack(vb[slot][g], vf);
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) acc[i] = fmaf(pr, vf[i], acc[i]);
+                    }
+                    m = mx;
+                }
+            };
+            // chunks that end before the request's own position hold old keys and values only: asked for before the
+            // wait for the kernel in front, which writes q and the newest key and value
+            const bool early0 = !waited && k_begin + CHUNK <= p, early1 = !waited && k_begin + 2 * CHUNK <= p;
+            if (early0) issue(0, k_begin);
+            if (early1) issue(1, k_begin + CHUNK);
+            if (!waited) {
+                pdl_entry();
+                waited = true;
             }
-        };
-        for (int k0 = k_begin; k0 < k_end; k0 += CHUNK) {
-            if (k0 >= t_lo && k0 + 2 * CHUNK <= k_end) {
-                chunk(k0, true_tag());
-            } else {
-                chunk(k0, false_tag());
+            if (!early0) issue(0, k_begin);
+            if (!early1) issue(1, k_begin + CHUNK);
+            load_q();
+            for (int k0 = k_begin; k0 < k_end; k0 += 2 * CHUNK) {
+                consume(0, k0);
+                issue(0, k0 + 2 * CHUNK);
+                consume(1, k0 + CHUNK);
+                issue(1, k0 + 3 * CHUNK);
+            }
+        } else {
+            uint4 kreg[DS_LOADS], vreg[DS_LOADS];
+            int page_next = page_of(k_begin + CHUNK), page_next2 = page_of(k_begin + 2 * CHUNK);
+            unsigned base = chunk_base(k_begin, page_of(k_begin));
+            // Keys before the request's own position were written by earlier steps: a first chunk that ends before that
+            // position is asked for before the wait for the kernel in front, which writes q and the newest key and value.
+            const bool early = !waited && k_begin + CHUNK <= p;
+            if (early) {
+#pragma unroll
+                for (int g = 0; g < DS_LOADS; ++g)
+                    kreg[g] = live(k_begin, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+            }
+            if (!waited) {
+                pdl_entry();
+                waited = true;
+            }
+            if (!early) {
+#pragma unroll
+                for (int g = 0; g < DS_LOADS; ++g)
+                    kreg[g] = live(k_begin, g) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+            }
+            load_q();
+            // One chunk: FAST when this chunk and the next lie wholly inside the range (the steady state), so
+            // that no load and no score needs a check of its own.
+            auto chunk = [&](int k0, auto fast_tag) {
+                constexpr bool FAST = decltype(fast_tag)::value;
+                // V of this chunk
+#pragma unroll
+                for (int g = 0; g < DS_LOADS; ++g)
+                    vreg[g] = ((FAST && active) || live(k0, g)) ? ld_once(pool4 + v_units + base + g * KPL * row_units) : zero4;
+                // scores of this chunk
+                float sc[DS_LOADS];
+#pragma unroll
+                for (int g = 0; g < DS_LOADS; ++g) {
+                    float kf[VEC];
+                    Vec<T>::unpack(kreg[g], kf);
+                    float dot = 0.f;
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) dot = fmaf(q[i], kf[i], dot);
+#pragma unroll
+                    for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                    sc[g] = (FAST || t_live(k0, g)) ? dot : -INFINITY;
+                }
+                // K of the next chunk, and the block-table entry of the chunk after the next two
+                base = chunk_base(k0 + CHUNK, page_next);
+                page_next = page_next2;
+                page_next2 = page_of(k0 + 3 * CHUNK);
+#pragma unroll
+                for (int g = 0; g < DS_LOADS; ++g)
+                    kreg[g] = ((FAST && active) || live(k0 + CHUNK, g)) ? ld_once(pool4 + base + g * KPL * row_units) : zero4;
+                // running softmax of this lane group, then the weighted sum
+                float mx = m;
+#pragma unroll
+                for (int g = 0; g < DS_LOADS; ++g) mx = fmaxf(mx, sc[g]);
+                if (FAST || mx != -INFINITY) {
+                    const float corr = exp2f(m - mx);  // 0 on the first live chunk
+                    l *= corr;
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) acc[i] *= corr;
+#pragma unroll
+                    for (int g = 0; g < DS_LOADS; ++g) {
+                        const float pr = exp2f(sc[g] - mx);  // 0 for a key that is not there
+                        l += pr;
+                        float vf[VEC];
+                        Vec<T>::unpack(vreg[g], vf);
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) acc[i] = fmaf(pr, vf[i], acc[i]);
+                    }
+                    m = mx;
+                }
+            };
+            for (int k0 = k_begin; k0 < k_end; k0 += CHUNK) {
+                if (k0 >= t_lo && k0 + 2 * CHUNK <= k_end) {
+                    chunk(k0, true_tag());
+                } else {
+                    chunk(k0, false_tag());
+                }
             }
         }
         // merge the lane groups (ascending group order is kept by always putting the lower group first)
@@ -652,6 +722,14 @@ __global__ void __launch_bounds__(32 * DS_WARPS, 4) attn_decode_stream_kernel(At
 
 // The two constants of the streaming kernel's cost model (in keys); a switch for measurements.
 static int g_ds_cost_range = DS_OVERHEAD, g_ds_cost_merge = DS_MERGE;
+// Up to this many (request, head) pairs, or pairs x splits of 128 keys of the longest context, the variant with two
+// chunks in flight runs (16 heads, 4,000 cached tokens: 20.4 -> 17.4 us at one request, 32.0 -> 30.0 at four, equal at
+// eight, 90.7 -> 95.9 at sixteen; 500 cached tokens at eight requests: 21.5 -> 17.2 us); g_ds_deep forces it on (1)
+// or off (0) for measurements (-1: by these bounds).
+#define DS_DEEP_PAIRS 64
+#define DS_DEEP_SPLITS 2048
+static int g_ds_deep = -1;
+extern "C" void locus_attn_decode_set_deep(int deep) { g_ds_deep = deep; }
 extern "C" void locus_attn_decode_set_cost(int range_overhead, int merge_per_range) {
     g_ds_cost_range = range_overhead;
     g_ds_cost_merge = merge_per_range;
@@ -736,17 +814,27 @@ extern "C" int locus_attn_decode(const void* q, int dt, const void* pool, void* 
                 return static_cast<int>(cudaGetLastError());
             }
         }
-        const dim3 sgrid(n_sm * 4);
+        // few (request, head) pairs: the variant with two chunks in flight per warp on half the blocks (see the kernel)
+        const long long pairs = static_cast<long long>(n_items) * nh;
+        const bool deep = g_ds_deep >= 0 ? g_ds_deep != 0 : (pairs <= DS_DEEP_PAIRS || pairs * max_splits <= DS_DEEP_SPLITS);
+        const dim3 sgrid(n_sm * (deep ? 2 : 4));
         const int units = static_cast<int>(max_units < (1 << 30) ? max_units : (1 << 30));
+#define DS_LAUNCH(TT, L)                                                                                               \
+        do {                                                                                                           \
+            if (deep) locus_launch(attn_decode_stream_kernel<TT, L, true, true>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge); \
+            else if (pieces != L) locus_launch(attn_decode_stream_kernel<TT, L, false, true>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge); \
+            else locus_launch(attn_decode_stream_kernel<TT, L, false, false>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge); \
+        } while (0)
         if (dt == LOCUS_DT_F32) {
-            if (lpk == 8) locus_launch(attn_decode_stream_kernel<float, 8>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
-            else if (lpk == 16) locus_launch(attn_decode_stream_kernel<float, 16>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
-            else locus_launch(attn_decode_stream_kernel<float, 32>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
+            if (lpk == 8) DS_LAUNCH(float, 8);
+            else if (lpk == 16) DS_LAUNCH(float, 16);
+            else DS_LAUNCH(float, 32);
         } else {
-            if (lpk == 8) locus_launch(attn_decode_stream_kernel<bf16, 8>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
-            else if (lpk == 16) locus_launch(attn_decode_stream_kernel<bf16, 16>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
-            else locus_launch(attn_decode_stream_kernel<bf16, 32>, sgrid, 32 * DS_WARPS, 0, stream, a, n_items, units, g_ds_cost_range, g_ds_cost_merge);
+            if (lpk == 8) DS_LAUNCH(bf16, 8);
+            else if (lpk == 16) DS_LAUNCH(bf16, 16);
+            else DS_LAUNCH(bf16, 32);
         }
+#undef DS_LAUNCH
         return locus_launch_status();
     }
     if (max_units < static_cast<long long>(n_items) * nh * max_splits) return LOCUS_ERR_UNSUPPORTED;

@@ -759,6 +759,13 @@ def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype
     return max_items * n_heads * max_splits
 
 
+def attn_decode_variant(deep: Optional[bool]) -> None:
+    """Force the streaming decode kernel's variant with two chunks in flight per warp on (True) or off (False), or
+    leave the choice to the library (None: by the number of (request, head) pairs and the longest context).  For
+    tests and measurements."""
+    _lib("attention").locus_attn_decode_set_deep(I(-1 if deep is None else 1 if deep else 0))
+
+
 def attn_decode(q: torch.Tensor, pool: torch.Tensor, out: torch.Tensor, *, seg_q0: torch.Tensor,
                 seg_qn: torch.Tensor, seg_ctx: torch.Tensor, block_table: torch.Tensor,
                 items: torch.Tensor, n_items: int, n_heads: int, n_kv_heads: int, head_dim: int,

@@ -617,12 +617,18 @@ def test_attn_decode(dtype, nh, nkv, hd, P, window):
     ref = torch.zeros(T, nh * hd, dtype=torch.float64)
     EK.attn_decode(q, pool, ref, items=items, n_items=len(segs), part_o=None, part_ml=None, counters=None,
                    max_splits=max_splits, **meta, **kw)
-    for again in range(2):  # the second call finds the counters as the first left them: zero
-        out.zero_()
-        K.attn_decode(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=len(segs), part_o=part_o,
-                      part_ml=part_ml, counters=counters, max_splits=max_splits, **_dev(meta), **kw)
-        close(out, ref, dtype, "attn_decode")
-        assert int(counters.abs().sum()) == 0
+    # the second call finds the counters as the first left them: zero.  Where the streaming kernel runs, its two
+    # variants (one or two chunks in flight per warp; the library picks by the batch) are both forced in turn
+    try:
+        for deep in (None, False, True):
+            K.attn_decode_variant(deep)
+            out.zero_()
+            K.attn_decode(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=len(segs), part_o=part_o,
+                          part_ml=part_ml, counters=counters, max_splits=max_splits, **_dev(meta), **kw)
+            close(out, ref, dtype, f"attn_decode (two chunks in flight: {deep})")
+            assert int(counters.abs().sum()) == 0
+    finally:
+        K.attn_decode_variant(None)
 
 
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(28, 4, 128, 64, 0), (6, 2, 64, 16, 0), (12, 1, 128, 16, 0), (32, 2, 64, 32, 0),
