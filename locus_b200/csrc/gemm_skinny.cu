@@ -67,7 +67,7 @@ __device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uin
 __device__ __forceinline__ uint4 ld_stream(const bf16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
 
 template <int NT, bool DUAL, bool ROUTE = false>
-__global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
+__global__ void __launch_bounds__(32 * SK_WARPS, ROUTE ? 1 : (NT == 1 ? 4 : ((NT == 4 && DUAL) ? 2 : 3))) skinny_kernel(SkinnyArgs a) {
     extern __shared__ float red[];  // [SK_WARPS][(DUAL ? 2 : 1)][NT][16 * 8]
     // Under programmatic dependent launch this block may be resident while the kernel in front of it still runs.
     // The weights do not depend on that kernel, so a plain product asks for its first weights before it waits;
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(32 * SK_WARPS) skinny_kernel(SkinnyArgs a) {
     // this warp's k-steps: 32 elements each, interleaved with the other warps'; four steps at a time
     // (the router's launch is a handful of blocks whose whole share of the weights fits eight steps per warp: they
     // are all asked for at once, before the wait for the kernel in front)
-    constexpr int STEP = 32, STRIDE = STEP * SK_WARPS, UNROLL = ROUTE ? 8 : 4;
+    constexpr int STEP = 32, STRIDE = STEP * SK_WARPS, UNROLL = ROUTE ? 8 : (DUAL ? 2 : 4);
     uint4 al[UNROLL], ah[UNROLL], bl[DUAL ? UNROLL : 1], bh[DUAL ? UNROLL : 1];
     auto load_weights = [&](int kb) {
 #pragma unroll
