@@ -27,7 +27,7 @@ __device__ __forceinline__ u64 mix64(u64 z) {
 __device__ __forceinline__ u64 fixed_weight(float logit, float mx, float inv_t) {
     // exp in float32, at most 1.0; 2^40 fixed point (a weight below 2^-40 counts as 0)
     const float w = expf((logit - mx) * inv_t);
-    return static_cast<u64>(static_cast<double>(w) * 1099511627776.0);
+    return __float2ull_rz(w * 1099511627776.0f);  // w * 2^40 is exact in float32: the value the double product gives
 }
 
 // Penalties on the tokens of the history window (src/locus/model/sampling.cpp:16-43 of the
@@ -85,6 +85,62 @@ __device__ u64 block_sum_u64(u64 v, u64* scratch) {
     return tot;
 }
 
+// Histogram updates without a fight over the popular bins.  Logits cluster: the tokens of a row fall into a few of
+// a pass's 256 bins (all into one, in the passes over the weights), and 150,000 atomic additions to a few
+// shared-memory words take milliseconds.  So every warp has a histogram of its own (32 x 256 words, added up
+// after the pass), a thread gathers a run of equal bins in registers and adds it when the bin changes, and what
+// it holds at the end goes out as one addition per warp when the whole warp holds the same bin.  The sums are
+// integers: the result is the same whatever the order.
+struct RunAcc {
+    int bin;
+    u64 sum;
+};
+__device__ __forceinline__ void run_add(RunAcc& acc, u64* hist, int bin, u64 val) {
+    if (bin != acc.bin) {
+        if (acc.sum != 0) atomicAdd(&hist[acc.bin], acc.sum);
+        acc.bin = bin;
+        acc.sum = 0;
+    }
+    acc.sum += val;
+}
+__device__ __forceinline__ void run_flush(RunAcc& acc, u64* hist) {  // all threads of the warp call it
+    int same = 0;
+    __match_all_sync(0xffffffffu, acc.bin, &same);
+    if (same) {
+        u64 v = acc.sum;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if ((threadIdx.x & 31) == 0 && v != 0) atomicAdd(&hist[acc.bin], v);
+    } else if (acc.sum != 0) {
+        atomicAdd(&hist[acc.bin], acc.sum);
+    }
+    acc.bin = 0;
+    acc.sum = 0;
+}
+
+// f(i, row[i]) for the elements [begin, end) of a row, spread over `nt` threads of which this is `t`.  With `vec`
+// (the row starts on a 16-byte boundary and begin is a multiple of 4) four elements come with one load: one block
+// reads a whole row of the vocabulary, and what bounds it is the number of loads it has in flight.
+template <typename F>
+__device__ __forceinline__ void row_each(const float* __restrict__ row, int begin, int end, int t, int nt, bool vec, F f) {
+    if (vec) {
+        const float4* r4 = reinterpret_cast<const float4*>(row + begin);
+        const int n4 = (end - begin) >> 2;
+#pragma unroll 2
+        for (int j = t; j < n4; j += nt) {
+            const float4 v = r4[j];
+            const int i = begin + 4 * j;
+            f(i, v.x);
+            f(i + 1, v.y);
+            f(i + 2, v.z);
+            f(i + 3, v.w);
+        }
+        for (int i = begin + 4 * n4 + t; i < end; i += nt) f(i, row[i]);
+    } else {
+        for (int i = begin + t; i < end; i += nt) f(i, row[i]);
+    }
+}
+
 struct SampleRow {
     float temperature;
     int top_k;
@@ -100,26 +156,29 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
     const u64* __restrict__ seeds, const u64* __restrict__ counters, int* __restrict__ out_token,
     int* __restrict__ kept_count) {
     pdl_entry();
+    extern __shared__ u64 warp_hist[];  // [SAMPLE_THREADS / 32][256]
     __shared__ u64 scratch[SAMPLE_THREADS / 32];
     __shared__ u64 hist[256];
     __shared__ float wmax[32];
     __shared__ int widx[32];
     __shared__ unsigned sel_prefix;
     __shared__ u64 sel_above;
-    __shared__ int found;
+    __shared__ u64 seg_total[SAMPLE_THREADS / 32];
+    __shared__ u64 seg_count[SAMPLE_THREADS / 32];
     const int r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
     const float* row = logits + r * row_stride;
+    u64* const mine = warp_hist + wid * 256;
 
     // ---- maximum and its first index (the greedy answer)
+    const bool vec = (reinterpret_cast<uintptr_t>(row) & 15) == 0;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
-        const float v = row[i];
-        if (v > best) {
+    row_each(row, 0, V, tid, SAMPLE_THREADS, vec, [&](int i, float v) {
+        if (v > best || (v == best && i < best_i)) {
             best = v;
             best_i = i;
         }
-    }
+    });
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -167,12 +226,20 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
         u64 above = 0;  // tokens known to be above the current prefix bucket
         for (int pass = 0; pass < 4; ++pass) {
             const int shift = 24 - 8 * pass;
-            if (tid < 256) hist[tid] = 0;
+            for (int i = tid; i < SAMPLE_THREADS / 32 * 256; i += SAMPLE_THREADS) warp_hist[i] = 0;
             __syncthreads();
-            for (int i = tid; i < V; i += SAMPLE_THREADS) {
-                const unsigned k = order_key(row[i]);
+            RunAcc acc{0, 0};
+            row_each(row, 0, V, tid, SAMPLE_THREADS, vec, [&](int, float v) {
+                const unsigned k = order_key(v);
                 const bool match = pass == 0 || (k >> (shift + 8)) == (prefix >> (shift + 8));
-                if (match) atomicAdd(&hist[(k >> shift) & 255u], 1ULL);
+                if (match) run_add(acc, mine, static_cast<int>((k >> shift) & 255u), 1ULL);
+            });
+            run_flush(acc, mine);
+            __syncthreads();
+            if (tid < 256) {
+                u64 c = 0;
+                for (int w = 0; w < SAMPLE_THREADS / 32; ++w) c += warp_hist[w * 256 + tid];
+                hist[tid] = c;
             }
             __syncthreads();
             if (tid == 0) {
@@ -192,31 +259,36 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
         key_thr = prefix;
     }
 
-    // ---- total weight of the top-k survivors
-    u64 part = 0;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
-        const float v = row[i];
-        if (order_key(v) >= key_thr) part += fixed_weight(v, mx, inv_t);
-    }
-    const u64 total = block_sum_u64(part, scratch);
-
     // ---- top-p: smallest weight w_thr such that the tokens with weight >= w_thr hold at
     // least top_p of the total; radix select on the fixed-point weights by mass
     u64 w_thr = 0;
     const float tp = top_p[r];
     if (tp < 1.0f) {
+        // total weight of the top-k survivors
+        u64 part = 0;
+        row_each(row, 0, V, tid, SAMPLE_THREADS, vec, [&](int, float v) {
+            if (order_key(v) >= key_thr) part += fixed_weight(v, mx, inv_t);
+        });
+        const u64 total = block_sum_u64(part, scratch);
         const u64 target = static_cast<u64>(static_cast<double>(tp) * static_cast<double>(total));
         u64 prefix = 0, above = 0;
         for (int pass = 0; pass < 6; ++pass) {  // 48-bit weights (<= 2^40), 8 bits a pass
             const int shift = 40 - 8 * pass;
-            if (tid < 256) hist[tid] = 0;
+            for (int i = tid; i < SAMPLE_THREADS / 32 * 256; i += SAMPLE_THREADS) warp_hist[i] = 0;
             __syncthreads();
-            for (int i = tid; i < V; i += SAMPLE_THREADS) {
-                const float v = row[i];
-                if (order_key(v) < key_thr) continue;
+            RunAcc acc{0, 0};
+            row_each(row, 0, V, tid, SAMPLE_THREADS, vec, [&](int, float v) {
+                if (order_key(v) < key_thr) return;
                 const u64 w = fixed_weight(v, mx, inv_t);
                 const bool match = pass == 0 || (w >> (shift + 8)) == (prefix >> (shift + 8));
-                if (match) atomicAdd(&hist[(w >> shift) & 255ULL], w);
+                if (match) run_add(acc, mine, static_cast<int>((w >> shift) & 255ULL), w);
+            });
+            run_flush(acc, mine);
+            __syncthreads();
+            if (tid < 256) {
+                u64 c = 0;
+                for (int w = 0; w < SAMPLE_THREADS / 32; ++w) c += warp_hist[w * 256 + tid];
+                hist[tid] = c;
             }
             __syncthreads();
             if (tid == 0) {
@@ -243,60 +315,100 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
         if (m_thr > w_thr) w_thr = m_thr;
     }
 
-    // ---- kept total and count
-    u64 kpart = 0, cpart = 0;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
-        const float v = row[i];
-        if (order_key(v) < key_thr) continue;
+    // ---- kept weight and count of every warp's own stretch of the row (warp w holds the tokens
+    // [w * seg, (w + 1) * seg), seg a multiple of 128: a lane takes four neighbours at a time)
+    const int seg = ((V + SAMPLE_THREADS / 32 - 1) / (SAMPLE_THREADS / 32) + 127) & ~127;
+    const int seg0 = min(V, wid * seg), seg1 = min(V, seg0 + seg);
+    auto kept_weight = [&](int i, float v, bool& kept) -> u64 {  // a kept token may weigh 0 (below 2^-40 of the largest)
+        kept = false;
+        if (order_key(v) < key_thr) return 0;
         const u64 w = fixed_weight(v, mx, inv_t);
-        if (w >= w_thr || i == arg) {
-            kpart += w;
-            cpart += 1;
+        kept = w >= w_thr || i == arg;
+        return kept ? w : 0;
+    };
+    {
+        u64 kpart = 0, cpart = 0;
+        row_each(row, seg0, seg1, lane, 32, vec, [&](int i, float v) {
+            bool kept;
+            kpart += kept_weight(i, v, kept);
+            cpart += kept;
+        });
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            kpart += __shfl_xor_sync(0xffffffffu, kpart, o);
+            cpart += __shfl_xor_sync(0xffffffffu, cpart, o);
+        }
+        if (lane == 0) {
+            seg_total[wid] = kpart;
+            seg_count[wid] = cpart;
         }
     }
-    const u64 kept_total = block_sum_u64(kpart, scratch);
-    const u64 kept_n = block_sum_u64(cpart, scratch);
+    __syncthreads();
+    u64 kept_total = 0, kept_n = 0, before = 0;
+    for (int w = 0; w < SAMPLE_THREADS / 32; ++w) {
+        if (w < wid) before += seg_total[w];
+        kept_total += seg_total[w];
+        kept_n += seg_count[w];
+    }
     if (tid == 0 && kept_count) kept_count[r] = static_cast<int>(kept_n);
 
-    // ---- draw: u in [0, 1) from (seed, counter); first index whose running sum exceeds it
+    // ---- draw: u in [0, 1) from (seed, counter); first index whose running sum exceeds it.  The warp whose
+    // stretch holds the goal walks it 128 tokens at a time (a lane four neighbours, the next four already asked
+    // for); nobody else has anything left to do.
     const u64 bits = mix64(mix64(seeds[r]) ^ (counters[r] * 0xd1342543de82ef95ULL + 1ULL));
     const double u = static_cast<double>(bits >> 11) * (1.0 / 9007199254740992.0);
     u64 goal = static_cast<u64>(u * static_cast<double>(kept_total));
-    if (goal >= kept_total) goal = kept_total - 1;
-    if (tid == 0) found = arg;  // fallback (kept_total of 0 cannot happen: arg weighs 2^40)
-    u64 running = 0;
-    __syncthreads();
-    for (int base = 0; base < V; base += SAMPLE_THREADS) {
-        const int i = base + tid;
-        u64 w = 0;
-        if (i < V) {
-            const float v = row[i];
-            if (order_key(v) >= key_thr) {
-                const u64 ww = fixed_weight(v, mx, inv_t);
-                if (ww >= w_thr || i == arg) w = ww;
-            }
+    if (goal >= kept_total) goal = kept_total - 1;  // (a kept total of 0 cannot happen: arg weighs 2^40)
+    if (!(before <= goal && goal < before + seg_total[wid])) return;
+    u64 running = before;
+    int found = arg;
+    auto load4 = [&](int i0, float* v) {  // the tokens i0 .. i0 + 3 (zeros of no weight behind the stretch's end)
+        if (vec && i0 + 3 < seg1) {
+            const float4 t = *reinterpret_cast<const float4*>(row + i0);
+            v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[e] = i0 + e < seg1 ? row[i0 + e] : -INFINITY;
         }
-        // inclusive scan over the block
-        u64 inc = w;
+    };
+    float cur[4], nxt[4];
+    load4(seg0 + 4 * lane, cur);
+    for (int base = seg0; base < seg1; base += 128) {
+        const int i0 = base + 4 * lane;
+        load4(i0 + 128, nxt);
+        u64 w[4], mine_sum = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            bool kept = false;
+            w[e] = i0 + e < seg1 ? kept_weight(i0 + e, cur[e], kept) : 0;
+            mine_sum += w[e];
+        }
+        u64 inc = mine_sum;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
             const u64 up = __shfl_up_sync(0xffffffffu, inc, o);
             if (lane >= o) inc += up;
         }
-        __syncthreads();
-        if (lane == 31) scratch[wid] = inc;
-        __syncthreads();
-        u64 before = running;
-        for (int w2 = 0; w2 < wid; ++w2) before += scratch[w2];
-        u64 chunk_total = 0;
-        for (int w2 = 0; w2 < SAMPLE_THREADS / 32; ++w2) chunk_total += scratch[w2];
-        const u64 hi = before + inc, lo = hi - w;
-        if (w > 0 && lo <= goal && goal < hi) found = i;  // exactly one thread overall
-        running += chunk_total;
-        if (running > goal) break;  // uniform across the block
+        const u64 hi = running + inc, lo = hi - mine_sum;
+        const bool here = mine_sum > 0 && lo <= goal && goal < hi;  // at most one lane
+        const unsigned hit = __ballot_sync(0xffffffffu, here);
+        if (hit != 0) {
+            if (here) {
+                u64 at = lo;
+                int e = 0;
+                for (; e < 3; ++e) {
+                    if (goal < at + w[e]) break;
+                    at += w[e];
+                }
+                out_token[r] = i0 + e;
+            }
+            return;
+        }
+        running += __shfl_sync(0xffffffffu, inc, 31);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) cur[e] = nxt[e];
     }
-    __syncthreads();
-    if (tid == 0) out_token[r] = found;
+    if (lane == 0) out_token[r] = found;
 }
 
 extern "C" int locus_sample(const float* logits, long long row_stride, int R, int V,
@@ -305,7 +417,14 @@ extern "C" int locus_sample(const float* logits, long long row_stride, int R, in
                             int* out_token, int* kept_count, cudaStream_t stream) {
     if (R <= 0) return 0;
     if (V <= 0) return LOCUS_ERR_UNSUPPORTED;
-    locus_launch(sample_kernel, R, SAMPLE_THREADS, 0, stream, logits, row_stride, V, temperature, top_k, top_p, min_p,
+    const size_t smem = sizeof(u64) * (SAMPLE_THREADS / 32) * 256;  // a histogram per warp
+    static bool set = false;
+    if (!set) {
+        if (cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+            return static_cast<int>(cudaGetLastError());
+        set = true;
+    }
+    locus_launch(sample_kernel, R, SAMPLE_THREADS, smem, stream, logits, row_stride, V, temperature, top_k, top_p, min_p,
                  seeds, counters, out_token, kept_count);
     return locus_launch_status();
 }

@@ -62,13 +62,21 @@ class Sampler:
         self.max_rows = max_rows
         self._pin = self.device.type == "cuda"
         R = max_rows
-        # float block: temperature, top_p, min_p, repeat, freq, presence; int block: top_k; long block: seed, counter
-        self._hf = torch.zeros(6 * R, dtype=torch.float32, pin_memory=self._pin)
-        self._df = torch.zeros(6 * R, dtype=torch.float32, device=self.device)
-        self._hi = torch.zeros(R, dtype=torch.int32, pin_memory=self._pin)
-        self._di = torch.zeros(R, dtype=torch.int32, device=self.device)
-        self._hl = torch.zeros(2 * R, dtype=torch.int64, pin_memory=self._pin)
-        self._dl = torch.zeros(2 * R, dtype=torch.int64, device=self.device)
+        # One packed block of per-row parameters, host (pinned) and device, so that a step uploads them with one
+        # copy: int64 seed, counter; float32 temperature, top_p, min_p, repeat, frequency, presence; int32 top_k.
+        self._block_bytes = (2 * 8 + 6 * 4 + 4) * R
+        self._hblock = torch.zeros(self._block_bytes, dtype=torch.uint8, pin_memory=self._pin)
+        self._dblock = torch.zeros(self._block_bytes, dtype=torch.uint8, device=self.device)
+
+        def views(block):
+            return (block[: 16 * R].view(torch.int64), block[16 * R : 40 * R].view(torch.float32),
+                    block[40 * R :].view(torch.int32))
+
+        self._hl, self._hf, self._hi = views(self._hblock)
+        self._dl, self._df, self._di = views(self._dblock)
+        # numpy views of the host block: assigning a Python list to a slice of them costs a few microseconds,
+        # a torch.tensor() per field cost ten times that
+        self._nl, self._nf, self._ni = self._hl.numpy().reshape(2, R), self._hf.numpy().reshape(6, R), self._hi.numpy()
         self._out = torch.zeros(R, dtype=torch.int32, device=self.device)
         self._out_host = torch.zeros(R, dtype=torch.int32, pin_memory=self._pin)
         self.max_history = 0
@@ -111,20 +119,18 @@ class Sampler:
         Rm = self.max_rows
         # a batch of plain greedy rows needs no upload while the device rows it uses are known to be greedy
         if not (all_greedy and R <= self._greedy_rows):
-            hf = self._hf.view(6, Rm)
-            hf[0, :R] = torch.tensor([p.temperature for p in params], dtype=torch.float32)
-            hf[1, :R] = torch.tensor([p.top_p for p in params], dtype=torch.float32)
-            hf[2, :R] = torch.tensor([p.min_p for p in params], dtype=torch.float32)
-            hf[3, :R] = torch.tensor([p.repeat_penalty for p in params], dtype=torch.float32)
-            hf[4, :R] = torch.tensor([p.frequency_penalty for p in params], dtype=torch.float32)
-            hf[5, :R] = torch.tensor([p.presence_penalty for p in params], dtype=torch.float32)
-            self._hi[:R] = torch.tensor([p.top_k for p in params], dtype=torch.int32)
-            self._hl[:R] = torch.tensor([int(s) & 0x7FFFFFFFFFFFFFFF for s in seeds], dtype=torch.int64)
-            self._hl[Rm : Rm + R] = torch.tensor([int(c) for c in counters], dtype=torch.int64)
-            self._df.view(6, Rm)[:, :R].copy_(hf[:, :R], non_blocking=True)
-            self._di[:R].copy_(self._hi[:R], non_blocking=True)
-            self._dl.view(2, Rm)[:, :R].copy_(self._hl.view(2, Rm)[:, :R], non_blocking=True)
-            self.h2d_bytes += (6 * 4 + 4 + 16) * R
+            nf = self._nf
+            nf[0, :R] = [p.temperature for p in params]
+            nf[1, :R] = [p.top_p for p in params]
+            nf[2, :R] = [p.min_p for p in params]
+            nf[3, :R] = [p.repeat_penalty for p in params]
+            nf[4, :R] = [p.frequency_penalty for p in params]
+            nf[5, :R] = [p.presence_penalty for p in params]
+            self._ni[:R] = [p.top_k for p in params]
+            self._nl[0, :R] = [int(s) & 0x7FFFFFFFFFFFFFFF for s in seeds]
+            self._nl[1, :R] = [int(c) for c in counters]
+            self._dblock.copy_(self._hblock, non_blocking=True)
+            self.h2d_bytes += self._block_bytes
             # rows beyond R keep what an earlier batch left: greedy only if they were and this batch is
             self._greedy_rows = max(R, self._greedy_rows) if all_greedy else 0
         if any(p.has_penalties() for p in params):
@@ -134,11 +140,12 @@ class Sampler:
             self._grow_history(need)
             n_hist = max(1, need)
             hist = self._hh.view(-1)[: R * n_hist].view(R, n_hist)
-            hist.fill_(-1)
+            nh = hist.numpy()
+            nh.fill(-1)
             for i, (p, h) in enumerate(zip(params, histories)):
                 n = min(p.repeat_last_n, len(h)) if p.has_penalties() else 0
                 if n:
-                    hist[i, :n] = torch.tensor(list(h[len(h) - n :]), dtype=torch.int32)
+                    nh[i, :n] = h[len(h) - n :]
             dh = self._dh.view(-1)[: R * n_hist].view(R, n_hist)
             dh.copy_(hist, non_blocking=True)
             self.h2d_bytes += 4 * R * n_hist
