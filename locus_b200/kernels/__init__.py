@@ -1049,6 +1049,12 @@ def apply_penalties(logits: torch.Tensor, history: torch.Tensor, repeat: torch.T
     _check(code, "apply_penalties")
 
 
+def sample_use_cluster(on: bool) -> None:
+    """Let rows of 8,192 to 163,840 tokens be sampled by a cluster of eight blocks per row (the default), or keep
+    every row on the one-block kernel.  Both give the same tokens; for tests and measurements."""
+    _lib("sampling").locus_sample_use_cluster(I(1 if on else 0))
+
+
 def sample(logits: torch.Tensor, *, temperature: torch.Tensor, top_k: torch.Tensor,
            top_p: torch.Tensor, min_p: torch.Tensor, seeds: torch.Tensor, counters: torch.Tensor,
            out: torch.Tensor, kept_count: Optional[torch.Tensor] = None) -> None:

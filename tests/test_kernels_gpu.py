@@ -806,6 +806,47 @@ def test_sample_greedy_and_filters(V):
     assert out.cpu().tolist() == first
 
 
+@pytest.mark.parametrize("V", [8192, 20001, 151936, 163840])
+def test_sample_cluster_kernel_gives_the_one_block_kernels_tokens(V):
+    """Rows of 8,192 to 163,840 tokens are sampled by a cluster of eight blocks per row that holds the row in
+    registers; the one-block kernel takes every other size.  Same filters, same fixed-point sums, same draw: the
+    same token and the same number of kept tokens, row by row, draw by draw."""
+    R = 9
+    g = torch.Generator().manual_seed(V)
+    logits = torch.randn(R, V, generator=g) * 2.5
+    logits[1, 17] = logits[1, V - 1] = logits[1].max() + 1          # a tie of maxima: the first wins
+    logits[7] = 0.25                                                 # every token alike
+    logits[8, : V // 2] = -200.0                                     # half the row weighs nothing at all
+    dl = logits.to(DEV)
+    f32 = lambda v: torch.tensor(v, dtype=torch.float32, device=DEV)
+    temp = f32([0.0, 0.0, 0.8, 1.0, 1.3, 0.7, 0.05, 1.0, 0.9])
+    top_k = torch.tensor([0, 0, 1, 50, 0, 40, 0, 0, 7000], dtype=torch.int32, device=DEV)
+    top_p = f32([1.0, 1.0, 1.0, 1.0, 0.6, 0.9, 0.95, 0.5, 0.999])
+    min_p = f32([0.0, 0.0, 0.0, 0.0, 0.0, 0.05, 0.0, 0.0, 0.0])
+    seeds = torch.arange(R, dtype=torch.int64, device=DEV) * 77 + 5
+    res = {}
+    try:
+        for cluster in (True, False):
+            K.sample_use_cluster(cluster)
+            toks, kept_all = [], []
+            for c in range(40):
+                out = torch.full((R,), -1, dtype=torch.int32, device=DEV)
+                kept = torch.full((R,), -1, dtype=torch.int32, device=DEV)
+                K.sample(dl, temperature=temp, top_k=top_k, top_p=top_p, min_p=min_p, seeds=seeds,
+                         counters=torch.full((R,), c, dtype=torch.int64, device=DEV), out=out, kept_count=kept)
+                toks.append(out.cpu().tolist())
+                kept_all.append(kept.cpu().tolist())
+            res[cluster] = (toks, kept_all)
+    finally:
+        K.sample_use_cluster(True)
+    assert res[True] == res[False]
+    toks = res[True][0]
+    assert all(0 <= t < V for row in toks for t in row)
+    assert toks[0][1] == 17 and toks[0][0] == int(torch.argmax(logits[0]))
+    assert len({row[7] for row in toks}) > 5            # the flat row is drawn from all over
+    assert all(row[8] >= V // 2 for row in toks)        # nothing without weight is drawn
+
+
 def test_penalties():
     import plain_qwen2moe as plain
     V, R = 50, 3
