@@ -871,7 +871,7 @@ def router_topk(h: torch.Tensor, w_router: torch.Tensor, w_gate: Optional[torch.
 
 def router_logits(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor) -> None:
     """logits[t, e] = w_all[e] . h[t] in float32 with the weight-streaming tensor-core kernel,
-    for ANY number of tokens (tiles of up to 32): one kernel, and one order of the sum, for
+    for ANY number of tokens (tiles of up to 16): one kernel, and one order of the sum, for
     every batch shape.  bfloat16 ``h`` [T, H] and ``w_all`` [E (+1), H]; ``logits`` [T, >= E (+1)]."""
     _cuda_c(h, "h")
     _cuda_c(w_all, "w_all")
@@ -880,7 +880,9 @@ def router_logits(h: torch.Tensor, w_all: torch.Tensor, logits: torch.Tensor) ->
     _need(h.dtype == torch.bfloat16 and w_all.dtype == torch.bfloat16 and H % 8 == 0, "router_logits: bfloat16, H % 8 == 0")
     _need(logits.dtype == torch.float32 and logits.shape[0] >= T and logits.shape[1] >= n and logits.stride(1) == 1,
           "router_logits: logits must be float32 [T, >= rows of w_all]")
-    tile = 8 if T <= 8 else (16 if T <= 16 else 32)
+    # tiles of 16 tokens from 9 tokens on: with 32 a block's chain is twice as long (64 tokens: 9.1 us against 4.2,
+    # 8,192 tokens: 60 against 34), and the order of a sum does not depend on the tile
+    tile = 8 if T <= 8 else 16
     code = _lib("gemm_skinny").locus_gemm_skinny(
         _p(h), _p(w_all), None, None, I(0), _p(logits), I(0), I(0), None, None, None, I(1), I(T), I(n), I(H),
         LL(h.stride(0)), LL(logits.stride(0)), I(tile), None, None, None, None, I(0), LL(0), I(0), _stream()
