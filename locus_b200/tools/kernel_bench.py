@@ -193,9 +193,32 @@ def bench_attn_chunk(args) -> None:
           f"{f'tcgen05, {n_splits} key ranges' if tc else (f'mma.sync, {n_splits} key ranges' if mma else 'cuda cores')}: {us:.1f} us/call  {flops / us / 1e6:.1f} TFLOP/s (causal flops)")
 
 
+def bench_sample(args) -> None:
+    """The sampling kernel on --rows rows of --vocab random float32 logits: greedy, temperature 0.8 alone, with
+    top-k 50, with top-p 0.9, with top-k 50 + top-p 0.9 + min-p 0.05.  --one-block keeps every row on the one-block
+    kernel (up to 16 rows of 8,192 to 163,840 tokens otherwise go to the cluster kernel)."""
+    dev = "cuda:0"
+    R, V = args.rows, args.vocab
+    K.sample_use_cluster(not args.one_block)
+    logits = torch.randn(R, V, device=dev, generator=torch.Generator(dev).manual_seed(1)) * 3
+    full = lambda v, dt: torch.full((R,), v, dtype=dt, device=dev)
+    out = torch.zeros(R, dtype=torch.int32, device=dev)
+    seeds, ctr = torch.arange(R, dtype=torch.int64, device=dev), torch.zeros(R, dtype=torch.int64, device=dev)
+    for name, t, k, p, m in (("greedy", 0.0, 0, 1.0, 0.0), ("temperature", 0.8, 0, 1.0, 0.0), ("top-k 50", 0.8, 50, 1.0, 0.0),
+                             ("top-p 0.9", 0.8, 0, 0.9, 0.0), ("top-k + top-p + min-p", 0.8, 50, 0.9, 0.05)):
+        kw = dict(temperature=full(t, torch.float32), top_k=full(k, torch.int32), top_p=full(p, torch.float32),
+                  min_p=full(m, torch.float32), seeds=seeds, counters=ctr, out=out)
+        us = _time(lambda: K.sample(logits, **kw), args.iters, args.graph)
+        print(f"sample rows={R} vocab={V} {'one block a row' if args.one_block else 'default'} {name}: {us:.1f} us/call")
+    K.sample_use_cluster(True)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="kernel_bench")
-    ap.add_argument("kernel", choices=["linear", "attn_decode", "attn_chunk", "experts"])
+    ap.add_argument("kernel", choices=["linear", "attn_decode", "attn_chunk", "experts", "sample"])
+    ap.add_argument("--rows", type=int, default=8, help="sample: rows of logits")
+    ap.add_argument("--vocab", type=int, default=151936, help="sample: logits of a row")
+    ap.add_argument("--one-block", action="store_true", help="sample: never the cluster kernel")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--graph", action="store_true", help="time a CUDA graph of the calls")
@@ -236,7 +259,7 @@ def main(argv=None) -> int:
         print("kernel_bench: no CUDA device", file=sys.stderr)
         return 1
     {"linear": bench_linear, "attn_decode": bench_attn_decode, "attn_chunk": bench_attn_chunk,
-     "experts": bench_experts}[args.kernel](args)
+     "experts": bench_experts, "sample": bench_sample}[args.kernel](args)
     return 0
 
 
