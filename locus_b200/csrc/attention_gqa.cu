@@ -144,8 +144,9 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // HD: head size (64 or 128).  WIDE: groups of more than 8 heads (a second tile of heads).
-template <int HD, bool WIDE>
-__global__ void __launch_bounds__(32 * GQ_WARPS, 1) attn_decode_gqa_kernel(GqaArgs a, int n_items, long long max_units,
+// GQW warps of a block, GQS chunks of 16 keys in flight per warp (10 x 2 for many pairs, 6 x 4 for few: see above).
+template <int HD, bool WIDE, int GQW, int GQS>
+__global__ void __launch_bounds__(32 * GQW, 1) attn_decode_gqa_kernel(GqaArgs a, int n_items, long long max_units,
                                                                            int cost_range, int cost_merge) {
     pdl_trigger();  // every block of this grid is resident from the start
     constexpr int KS = HD / 16;      // k-steps of a score tile
@@ -162,17 +163,17 @@ __global__ void __launch_bounds__(32 * GQ_WARPS, 1) attn_decode_gqa_kernel(GqaAr
     const int P = a.page_tokens, G = a.nh / a.nkv;
 
     __shared__ KeyRanges kr;
-    __shared__ __align__(8) unsigned long long gq_bars[GQ_WARPS * GQ_STAGES];
-    const uint32_t bars = smem_u32(gq_bars) + warp * (GQ_STAGES * 8);  // this warp's barriers, one per stage
+    __shared__ __align__(8) unsigned long long gq_bars[GQW * GQS];
+    const uint32_t bars = smem_u32(gq_bars) + warp * (GQS * 8);  // this warp's barriers, one per stage
     if (lane == 0) {
 #pragma unroll
-        for (int i = 0; i < GQ_STAGES; ++i) mbar_init(bars + 8 * i, 1);
+        for (int i = 0; i < GQS; ++i) mbar_init(bars + 8 * i, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     __syncwarp();
     uint32_t parity = 0;  // bit i: the phase of stage i's barrier that the next wait on it looks for
-    const int n_warps = gridDim.x * GQ_WARPS;
+    const int n_warps = gridDim.x * GQW;
     // a unit (range, kv head) leaves G partial results: the scratch holds max_units of them
     const int len = plan_key_ranges(kr, a.items, a.seg_ctx, a.seg_q0, a.window, n_items, a.nkv, max_units / G, n_warps,
                                     cost_range, cost_merge);
@@ -184,7 +185,7 @@ __global__ void __launch_bounds__(32 * GQ_WARPS, 1) attn_decode_gqa_kernel(GqaAr
     const float qscale = a.scale * 1.4426950408889634f;  // scores in base 2
     const size_t plane = static_cast<size_t>(a.nkv) * P * HD;  // elements of the K (or V) half of a page
 
-    for (long long u = static_cast<long long>(blockIdx.x) * GQ_WARPS + warp; u < n_units; u += n_warps) {
+    for (long long u = static_cast<long long>(blockIdx.x) * GQW + warp; u < n_units; u += n_warps) {
         const int kvh = static_cast<int>(u % a.nkv);
         const int r = static_cast<int>(u / a.nkv);
         int item = 0;
@@ -226,7 +227,7 @@ __global__ void __launch_bounds__(32 * GQ_WARPS, 1) attn_decode_gqa_kernel(GqaAr
         }
 
         // A stage of the warp's ring: the K tile [16 keys][hd], then the V tile, rows as they lie in the page.
-        const uint32_t ring = smem_u32(gq_smem) + warp * (GQ_STAGES * STAGE_BYTES);
+        const uint32_t ring = smem_u32(gq_smem) + warp * (GQS * STAGE_BYTES);
         auto issue = [&](int k0, int st) {
             if (k0 < k_end && lane == 0) {
                 const int page = table[k0 / P];
@@ -242,14 +243,14 @@ __global__ void __launch_bounds__(32 * GQ_WARPS, 1) attn_decode_gqa_kernel(GqaAr
         const int k_start = max(k_begin, t_lo & ~15);
         bool ok = true;
 #pragma unroll
-        for (int c = 0; c < GQ_STAGES - 1; ++c) issue(k_start + 16 * c, c);
+        for (int c = 0; c < GQS - 1; ++c) issue(k_start + 16 * c, c);
         int st = 0;
         for (int k0 = k_start; k0 < k_end; k0 += 16) {
             __syncwarp();  // every lane has read the chunk before this one: its slot may be overwritten
             {
-                int st_new = st + GQ_STAGES - 1;
-                if (st_new >= GQ_STAGES) st_new -= GQ_STAGES;
-                issue(k0 + 16 * (GQ_STAGES - 1), st_new);
+                int st_new = st + GQS - 1;
+                if (st_new >= GQS) st_new -= GQS;
+                issue(k0 + 16 * (GQS - 1), st_new);
             }
             if (!mbar_wait(bars + 8 * st, (parity >> st) & 1u)) {  // the copies of chunk k0 have landed
                 ok = false;
@@ -257,7 +258,7 @@ __global__ void __launch_bounds__(32 * GQ_WARPS, 1) attn_decode_gqa_kernel(GqaAr
             }
             parity ^= 1u << st;
             const uint32_t src = ring + st * STAGE_BYTES;
-            if (++st == GQ_STAGES) st = 0;
+            if (++st == GQS) st = 0;
             if (k0 < t_lo || k0 + 16 > k_end) {
                 // a chunk with dead keys: their V rows become zeros (two lanes per row, 8 x 16 bytes of its 2 hd each)
                 const int r = lane >> 1, t = k0 + r;
@@ -437,6 +438,12 @@ extern "C" int locus_attn_decode_gqa_takes(int dt, int nh, int nkv, int hd, int 
     return (G >= 2 && G <= 16 && (hd == 64 || hd == 128) && page_tokens % 16 == 0 && n_items <= DS_MAX_ITEMS) ? 1 : 0;
 }
 
+// Up to this many (request, key/value head) pairs the 6 x 4 shape runs; g_gqa_deep forces it on (1) or off (0) for
+// tests and measurements (-1: by the number of pairs).
+#define GQ_DEEP_PAIRS 48
+static int g_gqa_deep = -1;
+extern "C" void locus_attn_decode_gqa_set_deep(int deep) { g_gqa_deep = deep; }
+
 // Scratch as for locus_attn_decode: part_o holds max_units partial results of hd floats (at least
 // n_items * nh), part_ml two floats each, counters n_items * nh ints that are zero before and after the call.
 extern "C" int locus_attn_decode_gqa(const void* q, const void* pool, void* out, const int* seg_q0, const int* seg_ctx,
@@ -466,18 +473,28 @@ extern "C" int locus_attn_decode_gqa(const void* q, const void* pool, void* out,
     a.part_o = part_o; a.part_ml = part_ml; a.counters = counters;
     const dim3 grid(n_sm);
     const bool wide = nh / nkv > 8;
-    const size_t smem = static_cast<size_t>(GQ_WARPS) * GQ_STAGES * 2 * 16 * hd * 2;
-#define GQA_LAUNCH(HD_, WIDE_)                                                                                         \
+    // few (request, key/value head) pairs: fewer warps with a deeper ring (a warp's chain of chunks sets the time);
+    // many: more warps.  28 heads on 4 at 8,192 tokens, 6 x 4 against 10 x 2: 8 requests (32 pairs) 45.8 against
+    // 54.5 us, 16 requests (64 pairs) 66.7 against 65.8, 64 requests 230 against 184; 16 heads on 2 at 4,000 tokens:
+    // 16 requests (32 pairs) 35.7 against 42.6 us, 32 requests (64 pairs) 44.6 against 45.0
+    const bool few = g_gqa_deep >= 0 ? g_gqa_deep != 0 : static_cast<long long>(n_items) * nkv <= GQ_DEEP_PAIRS;
+#define GQA_LAUNCH_WS(HD_, WIDE_, W_, S_)                                                                              \
     do {                                                                                                               \
+        const size_t smem = static_cast<size_t>(W_) * S_ * 2 * 16 * hd * 2;                                            \
         static bool attr_set = false;                                                                                  \
         if (!attr_set) {                                                                                               \
-            if (cudaFuncSetAttribute(attn_decode_gqa_kernel<HD_, WIDE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                     static_cast<int>(smem)) != cudaSuccess)                                           \
+            if (cudaFuncSetAttribute(attn_decode_gqa_kernel<HD_, WIDE_, W_, S_>,                                       \
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) \
                 return static_cast<int>(cudaGetLastError());                                                           \
             attr_set = true;                                                                                           \
         }                                                                                                              \
-        locus_launch(attn_decode_gqa_kernel<HD_, WIDE_>, grid, 32 * GQ_WARPS, smem, stream, a, n_items, max_units,     \
+        locus_launch(attn_decode_gqa_kernel<HD_, WIDE_, W_, S_>, grid, 32 * W_, smem, stream, a, n_items, max_units,   \
                      cost_range, cost_merge);                                                                          \
+    } while (0)
+#define GQA_LAUNCH(HD_, WIDE_)                                                                                         \
+    do {                                                                                                               \
+        if (few) GQA_LAUNCH_WS(HD_, WIDE_, 6, 4);                                                                      \
+        else GQA_LAUNCH_WS(HD_, WIDE_, GQ_WARPS, GQ_STAGES);                                                           \
     } while (0)
     if (hd == 128) {
         if (wide) GQA_LAUNCH(128, true);
@@ -486,6 +503,7 @@ extern "C" int locus_attn_decode_gqa(const void* q, const void* pool, void* out,
         if (wide) GQA_LAUNCH(64, true);
         else GQA_LAUNCH(64, false);
     }
+#undef GQA_LAUNCH_WS
 #undef GQA_LAUNCH
     return locus_launch_status();
 }

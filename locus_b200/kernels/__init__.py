@@ -759,6 +759,13 @@ def decode_units(max_items: int, n_heads: int, head_dim: int, dtype: torch.dtype
     return max_items * n_heads * max_splits
 
 
+def attn_decode_gqa_variant(few: Optional[bool]) -> None:
+    """Force the grouped-query decode kernel's shape for few (request, key/value head) pairs (six warps a block,
+    four chunks in flight per warp) on (True) or off (False: ten warps, two chunks), or leave the choice to the
+    library (None).  For tests and measurements."""
+    _lib("attention_gqa").locus_attn_decode_gqa_set_deep(I(-1 if few is None else 1 if few else 0))
+
+
 def attn_decode_variant(deep: Optional[bool]) -> None:
     """Force the streaming decode kernel's variant with two chunks in flight per warp on (True) or off (False), or
     leave the choice to the library (None: by the number of (request, head) pairs and the longest context).  For

@@ -654,8 +654,9 @@ def test_attn_decode_grouped_queries(nh, nkv, hd, P, window, monkeypatch):
     EK.attn_decode(q, pool, ref, items=items, n_items=len(segs), part_o=None, part_ml=None, counters=None,
                    max_splits=max_splits, **meta, **kw)
     outs = {}
-    for gqa in (True, False):
+    for gqa, few in ((True, True), (True, False), (False, None)):   # both shapes of the group kernel, then per head
         K.USE_GQA_DECODE = gqa
+        K.attn_decode_gqa_variant(few)
         try:
             for again in range(2):
                 out = torch.zeros(T, nh * hd, dtype=dtype, device=DEV)
@@ -663,11 +664,12 @@ def test_attn_decode_grouped_queries(nh, nkv, hd, P, window, monkeypatch):
                 pm = part_ml if gqa else torch.full((2 * len(segs) * nh * max_splits,), float("nan"), device=DEV)
                 K.attn_decode(q.to(DEV), pool.to(DEV), out, items=items.to(DEV), n_items=len(segs), part_o=pu,
                               part_ml=pm, counters=counters, max_splits=max_splits, **_dev(meta), **kw)
-                close(out, ref, dtype, f"attn_decode, grouped queries ({'group' if gqa else 'per head'} kernel)")
+                close(out, ref, dtype, f"attn_decode, grouped queries ({'group' if gqa else 'per head'} kernel, few pairs: {few})")
                 assert int(counters.abs().sum()) == 0
             outs[gqa] = out
         finally:
             K.USE_GQA_DECODE = True
+            K.attn_decode_gqa_variant(None)
     # a scratch that holds just one partial result per (request, head): one range each, still right
     tight_o = torch.full((len(segs) * nh * hd,), float("nan"), device=DEV)
     tight_ml = torch.full((2 * len(segs) * nh,), float("nan"), device=DEV)
