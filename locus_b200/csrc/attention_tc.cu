@@ -10,13 +10,15 @@
 //   softmax warps: the threads of a query row read its row of S (tcgen05.ld), mask (causal, window,
 //           end of the sequence), keep the running maximum and denominator (base 2), write
 //           P = exp2(s - m) as bfloat16 into shared memory in the swizzled K-major operand layout
-//   MMA 2:  PV[q, d] = sum_t P[q, t] V[t, d]       (A = P, B = V read MN-major: V lies [t][d] in the
-//           cache, which is the transposed operand; 128 x 128 in TMEM, a fresh sum per tile)
-//   the row's thread adds PV into its 128 output registers: O = O * exp2(m_old - m_new) + PV.
+//   MMA 2:  O[q, d] += sum_t P[q, t] V[t, d]      (A = P, B = V read MN-major: V lies [t][d] in the
+//           cache, which is the transposed operand; 128 x 128 in TMEM, ONE sum from the first tile to the last)
+//   The row's threads rescale O in tensor memory (tcgen05.ld, multiply, tcgen05.st) only when the row's maximum
+//   has run ahead of the reference its probabilities are formed against by more than 2^8, and read it once at
+//   the end: O / denominator.  (Adding every tile's P V into registers cost 400 cycles a tile.)
 //
-// S and PV are double-buffered in tensor memory (4 x 128 columns), so the tensor pipe computes the
-// scores of the next tile while the softmax warps work on this one, and the sum of a tile is added
-// one tile late, while the tensor pipe multiplies the next P (two buffers) by its V.  Warp 0: TMA; warp 1: MMA issue (one thread);
+// S is double-buffered in tensor memory (2 x 128 columns beside the 128 of O), so the tensor pipe computes the
+// scores of the next tile while the softmax warps work on this one; P has two buffers in shared memory.
+// Warp 0: TMA; warp 1: MMA issue (one thread);
 // warps 2-9: softmax and output, two threads per query row (64 keys and 64 output dimensions each).  Head size 128 only (other sizes and pages that are not a multiple
 // of 64 tokens go to the mma.sync kernel).
 //
@@ -166,6 +168,54 @@ __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Packed float32 pairs (one instruction for two lanes of arithmetic) and a three-way maximum: the softmax
+// warps are bound by instruction issue as much as by the special-function unit.
+__device__ __forceinline__ unsigned long long at_pair(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void at_unpair(unsigned long long v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long at_fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ unsigned long long at_add2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ unsigned long long at_mul2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ float at_max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ void at_st32(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,"
+        "%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+          "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+          "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+          "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+
+// The weighted sum of V stays in tensor memory from a block's first key tile to its last: the MMAs of every tile add
+// to it.  A row's probabilities are formed against a reference maximum that follows the row's true running maximum
+// only when that has run ahead by more than 2^AT_LAG_LOG2; then, and only then, the row's sum is read, rescaled
+// and written back.  Probabilities reach 2^8 at most, far inside bfloat16's and float32's range, and the quotient
+// sum / denominator is the same number whatever reference it was formed with.
+#define AT_LAG_LOG2 8.0f
+
 __global__ void __launch_bounds__(320, 1)
 attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv, TcAttnArgs a) {
     extern __shared__ __align__(1024) uint8_t at_raw[];
@@ -202,7 +252,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t sQ = base, sK = sQ + AT_TILE_BYTES, sV = sK + 2 * AT_TILE_BYTES, sP = sV + 2 * AT_TILE_BYTES;
     const uint32_t bars = sP + 2 * AT_TILE_BYTES;
     const uint32_t q_full = bars, k_full = bars + 8, v_full = bars + 24, k_free = bars + 40, v_free = bars + 56;
-    const uint32_t s_full = bars + 72, s_free = bars + 88, pv_full = bars + 104, pv_free = bars + 120, p_ready = bars + 136;
+    const uint32_t s_full = bars + 72, s_free = bars + 88, pv_done = bars + 104, p_ready = bars + 136;
     const uint32_t slot = bars + 144;
     volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(at_raw + (slot - at_smem(at_raw)));
 
@@ -215,8 +265,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             at_bar_init(v_free + 8 * b, 1);
             at_bar_init(s_full + 8 * b, 1);
             at_bar_init(s_free + 8 * b, 8);    // one arrival per softmax warp
-            at_bar_init(pv_full + 8 * b, 1);
-            at_bar_init(pv_free + 8 * b, 8);
+            at_bar_init(pv_done + 8 * b, 1);
         }
         at_bar_init(p_ready, 8);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -230,7 +279,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *slot_ptr;
-    const uint32_t tS = tmem, tPV = tmem + 2 * AT_MK;  // S0, S1, PV0, PV1: 128 columns each
+    const uint32_t tS = tmem, tO = tmem + 2 * AT_MK;  // S0, S1, O: 128 columns each
 
     if (warp == 0) {
         if (lane == 0) {
@@ -291,19 +340,18 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             for (int j = 0; j < n_tiles && ok; ++j) {
                 const int b = j & 1;
                 if (j + 1 < n_tiles && !scores(j + 1)) break;
-                // PV_j = P_j V_j
+                // O += P_j V_j: the sum stays in tensor memory from the first tile to the last
                 if (!at_wait(p_ready, j & 1, 6)) break;
                 if (!at_wait(v_full + 8 * b, (j >> 1) & 1, 7)) break;
-                if (!at_wait(pv_free + 8 * b, ((j >> 1) & 1) ^ 1, 8)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int ks = 0; ks < AT_MK / 16; ++ks) {
                     const uint64_t dp = at_desc_k(sP + b * AT_TILE_BYTES + (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32);
                     const uint64_t dv = at_desc_mn(sV + b * AT_TILE_BYTES + ks * (16 * 128), AT_HALF_BYTES);
-                    at_mma(tPV + b * AT_HD, dp, dv, idesc2, ks > 0);
+                    at_mma(tO, dp, dv, idesc2, (j > 0 || ks > 0) ? 1u : 0u);  // O += P_j V_j
                 }
-                at_commit(pv_full + 8 * b);
-                at_commit(v_free + 8 * b);
+                at_commit(pv_done + 8 * b);  // tells the softmax warps (P's buffer is free, the sum may be touched) ...
+                at_commit(v_free + 8 * b);   // ... and the loader (the stage's V is free)
             }
         }
     } else {
@@ -314,34 +362,15 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const int pq = p0 + r;              // its position
         const uint32_t lane_bits = static_cast<uint32_t>(quarter * 32) << 16;
         const float scale_log2 = a.scale * 1.4426950408889634f;
-        float o[64];
-#pragma unroll
-        for (int d = 0; d < 64; ++d) o[d] = 0.f;
-        float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+        const unsigned long long scale2 = at_pair(scale_log2, scale_log2);
+        float m_run = -INFINITY, l_run = 0.f;  // the row's reference maximum (base 2, scaled); this thread's part of the denominator
         uint8_t* at_generic = at_raw + (base - at_smem(at_raw));
         uint8_t* gP0 = at_generic + (sP - base) + half * AT_HALF_BYTES + r * 128;
         float* xch = reinterpret_cast<float*>(at_generic + (slot + 16 - base));  // [2 tile parities][2 halves][128 rows]
         bool ok = true;
         const int lo = a.window > 0 ? max(0, pq - a.window + 1) : 0;  // first key this row sees
+        const uint32_t tOmine = tO + lane_bits + 64 * half;           // this thread's 64 columns of the row's sum
 
-        auto add_sum = [&](int j, float alpha) -> bool {  // O = O * alpha + PV_j (this thread's 64 dimensions)
-            const int b = j & 1;
-            if (!at_wait(pv_full + 8 * b, (j >> 1) & 1, 9)) return false;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t v0[32], v1[32];
-            at_ld32(tPV + b * AT_HD + lane_bits + 64 * half, v0);
-            at_ld32(tPV + b * AT_HD + lane_bits + 64 * half + 32, v1);
-            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                o[i] = fmaf(o[i], alpha, __uint_as_float(v0[i]));
-                o[32 + i] = fmaf(o[32 + i], alpha, __uint_as_float(v1[i]));
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) at_arrive(pv_free + 8 * b);
-            return true;
-        };
         // the two threads of a row exchange a value through shared memory (a barrier of their two warps)
         auto with_partner = [&](int parity, float mine) -> float {
             float* slot_f = xch + parity * 256;
@@ -375,24 +404,58 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
             }
 #pragma unroll
-            for (int i = 0; i < 32; ++i) mx = fmaxf(mx, fmaxf(__uint_as_float(s0[i]), __uint_as_float(s1[i])));
+            for (int i = 0; i < 32; ++i) mx = at_max3(mx, __uint_as_float(s0[i]), __uint_as_float(s1[i]));
             mx = fmaxf(mx, with_partner(b, mx)) * scale_log2;  // the scale is positive: the maximum can be scaled last
-            mx = fmaxf(mx, m_run);
-            const float m_ref = mx == -INFINITY ? 0.f : mx;       // exp2(-inf - 0) = 0 for a row without keys so far
-            const float alpha = mx == -INFINITY ? 1.f : at_exp2(m_run - mx);
-            // P = exp2(s * scale - m) as bfloat16 into shared memory (K-major operand, 128-byte swizzle); the
-            // buffer of tile j - 2 is free: its MMA finished before the sum of tile j - 2 was added (below)
+            const float m_new = fmaxf(mx, m_run);               // the same in both threads of the row
+            // The buffer of P_{j-2} is free when its product is finished (the same barrier frees the stage's V).
+            if (j > 1 && !at_wait(pv_done + 8 * b, ((j >> 1) & 1) ^ 1, 9)) ok = false;
+            // Does the reference maximum follow?  Only when some row of the warp has run ahead of its reference by
+            // more than 2^AT_LAG_LOG2 (always at a row's first key: -inf is infinitely far; -inf - -inf is not a
+            // number and compares false, so a row without a key yet keeps -inf).  Both warps of a row hold the same
+            // rows and the same maxima, so they decide alike.  Then every row of the warp moves its reference and
+            // rescales its sum, which needs the product of the tile before this one finished.
+            if (__any_sync(0xffffffffu, m_new - m_run > AT_LAG_LOG2)) {
+                if (j > 0) {
+                    if (!at_wait(pv_done + 8 * (b ^ 1), ((j - 1) >> 1) & 1, 12)) ok = false;
+                    const float f = m_run == -INFINITY ? 1.f : at_exp2(m_run - m_new);
+                    const unsigned long long f2 = at_pair(f, f);
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t v[32];
+                        at_ld32(tOmine + 32 * c, v);
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int d = 0; d < 32; d += 2) {
+                            float x, y;
+                            at_unpair(at_mul2(at_pair(__uint_as_float(v[d]), __uint_as_float(v[d + 1])), f2), x, y);
+                            v[d] = __float_as_uint(x);
+                            v[d + 1] = __float_as_uint(y);
+                        }
+                        at_st32(tOmine + 32 * c, v);
+                    }
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    l_run *= f;
+                }
+                m_run = m_new;
+            }
+            const float m_ref = m_run == -INFINITY ? 0.f : m_run;  // exp2(-inf - 0) = 0 for a row without keys so far
+            const unsigned long long neg_m2 = at_pair(-m_ref, -m_ref);
+            // P = exp2(s * scale - m_ref) as bfloat16 into shared memory (K-major operand, 128-byte swizzle)
             uint8_t* gP = gP0 + b * AT_TILE_BYTES;
-            float sum = 0.f;
+            unsigned long long sum2 = at_pair(0.f, 0.f);
 #pragma unroll
             for (int q8 = 0; q8 < 8; ++q8) {  // 16-byte pieces of 8 probabilities
                 float pr[8];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint32_t raw = q8 < 4 ? s0[8 * q8 + i] : s1[8 * (q8 - 4) + i];
-                    const float x = fmaf(__uint_as_float(raw), scale_log2, -m_ref);
+                for (int i = 0; i < 8; i += 2) {
+                    const uint32_t r0 = q8 < 4 ? s0[8 * q8 + i] : s1[8 * (q8 - 4) + i];
+                    const uint32_t r1 = q8 < 4 ? s0[8 * q8 + i + 1] : s1[8 * (q8 - 4) + i + 1];
+                    float x, y;
+                    at_unpair(at_fma2(at_pair(__uint_as_float(r0), __uint_as_float(r1)), scale2, neg_m2), x, y);
                     pr[i] = at_exp2(x);
-                    sum += pr[i];
+                    pr[i + 1] = at_exp2(y);
+                    sum2 = at_add2(sum2, at_pair(pr[i], pr[i + 1]));
                 }
                 uint4 pk;
                 pk.x = at_pack_prob(pr[0], pr[1]);
@@ -401,8 +464,11 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 pk.w = at_pack_prob(pr[6], pr[7]);
                 *reinterpret_cast<uint4*>(gP + ((q8 ^ (r & 7)) << 4)) = pk;
             }
-            l_run = l_run * alpha + sum;
-            m_run = mx;
+            {
+                float x, y;
+                at_unpair(sum2, x, y);
+                l_run += x + y;
+            }
             // the last tile may hold rows of V behind the sequence's end (never written, any bit pattern): zero them
             if (tile_first + AT_MK - 1 > t_hi) {
                 if (!at_wait(v_full + 8 * b, (j >> 1) & 1, 11)) ok = false;
@@ -412,7 +478,7 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     for (int q8 = 0; q8 < 8; ++q8) *reinterpret_cast<uint4*>(gV + q8 * 16) = make_uint4(0, 0, 0, 0);
                 }
             }
-            // S_j is read, P_j is written: tell the MMA warp
+            // S_j is read, P_j is written, the sum is where the MMAs may add to it: tell the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
@@ -420,33 +486,38 @@ attn_chunk_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 at_arrive(s_free + 8 * b);
                 at_arrive(p_ready);
             }
-            // the sum of the tile before this one (its P used the maximum of then), while the tensor pipe
-            // multiplies this tile's P by V
-            if (j > 0 && !add_sum(j - 1, alpha_prev)) ok = false;
-            alpha_prev = alpha;  // the factor that takes O from the maximum of tile j - 1 to that of tile j
         }
-        if (!add_sum(n_tiles - 1, alpha_prev)) ok = false;
+        // the sum is complete when the last product is
+        if (!at_wait(pv_done + 8 * ((n_tiles - 1) & 1), ((n_tiles - 1) >> 1) & 1, 13)) ok = false;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         {
             const float l = l_run + with_partner(n_tiles & 1, l_run);
-            if (a.n_splits > 1) {
-                if (ok && r < nq) {
-                    const size_t unit = (static_cast<size_t>(row0 + r) * a.nh + h) * a.n_splits + split;
-                    float* po = a.part_o + unit * AT_HD + 64 * half;
+            const float inv = 1.0f / l;
 #pragma unroll
-                    for (int d = 0; d < 64; d += 4) *reinterpret_cast<float4*>(po + d) = make_float4(o[d], o[d + 1], o[d + 2], o[d + 3]);
-                    if (half == 0) *reinterpret_cast<float2*>(a.part_ml + unit * 2) = make_float2(m_run, l);
-                }
-            } else if (ok && r < nq) {
-                const float inv = 1.0f / l;
-                bf16* dst = a.out + (static_cast<size_t>(row0 + r) * a.nh + h) * AT_HD + 64 * half;
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+                at_ld32(tOmine + 32 * c, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (a.n_splits > 1) {
+                    if (ok && r < nq) {
+                        const size_t unit = (static_cast<size_t>(row0 + r) * a.nh + h) * a.n_splits + split;
+                        float* po = a.part_o + unit * AT_HD + 64 * half + 32 * c;
 #pragma unroll
-                for (int d = 0; d < 64; d += 8) {
-                    uint4 pk;
-                    pk.x = at_pack(o[d] * inv, o[d + 1] * inv);
-                    pk.y = at_pack(o[d + 2] * inv, o[d + 3] * inv);
-                    pk.z = at_pack(o[d + 4] * inv, o[d + 5] * inv);
-                    pk.w = at_pack(o[d + 6] * inv, o[d + 7] * inv);
-                    *reinterpret_cast<uint4*>(dst + d) = pk;
+                        for (int d = 0; d < 32; d += 4)
+                            *reinterpret_cast<uint4*>(po + d) = make_uint4(v[d], v[d + 1], v[d + 2], v[d + 3]);
+                        if (half == 0 && c == 0) *reinterpret_cast<float2*>(a.part_ml + unit * 2) = make_float2(m_run, l);
+                    }
+                } else if (ok && r < nq) {
+                    bf16* dst = a.out + (static_cast<size_t>(row0 + r) * a.nh + h) * AT_HD + 64 * half + 32 * c;
+#pragma unroll
+                    for (int d = 0; d < 32; d += 8) {
+                        uint4 pk;
+                        pk.x = at_pack(__uint_as_float(v[d]) * inv, __uint_as_float(v[d + 1]) * inv);
+                        pk.y = at_pack(__uint_as_float(v[d + 2]) * inv, __uint_as_float(v[d + 3]) * inv);
+                        pk.z = at_pack(__uint_as_float(v[d + 4]) * inv, __uint_as_float(v[d + 5]) * inv);
+                        pk.w = at_pack(__uint_as_float(v[d + 6]) * inv, __uint_as_float(v[d + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + d) = pk;
+                    }
                 }
             }
         }

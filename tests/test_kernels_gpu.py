@@ -598,6 +598,36 @@ def test_attn_chunk_tcgen05_one_far_key_among_thousands_in_ranges():
         close(out, ref, dtype, f"far key, {n_splits} key ranges")
 
 
+@pytest.mark.parametrize("slope", [0.1, 0.01, -0.02])
+def test_attn_chunk_tcgen05_scores_that_rise_or_fall_along_the_keys(slope):
+    """The kernel keeps a row's weighted sum in tensor memory and rescales it only when the row's maximum has run
+    ahead of the reference its probabilities are formed against by more than 2^8.  Scores that rise by 0.1 a key
+    (18 powers of two a tile: a rescale at every tile), by 0.01 (a rescale every few tiles, probabilities above 1
+    in between) and scores that fall (the first tile's maximum stands to the end), whole and in key ranges."""
+    dtype, hd, nh, nkv, P = torch.bfloat16, 128, 2, 2, 64
+    segs = [(3000, 256), (0, 300)]
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=11, n_pages=60)
+    pool = (pool.float() * 0.2).to(dtype)
+    q = (q.float() * 0.2).to(dtype)
+    q.view(T, nh, hd)[:, :, 0] = math.sqrt(hd)                      # score = slope * position + small noise
+    for s, (c, n) in enumerate(segs):
+        for t in range(c + n):
+            page, off = int(meta["block_table"][s, t // P]), t % P
+            pool[page, 0, :, off, 0] = slope * t
+    items_t = torch.tensor([(s, o) for s, (c, n) in enumerate(segs) for o in range(0, n, K.MMA_QUERY_TILE)], dtype=torch.int32)
+    kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=0, scale=1 / math.sqrt(hd))
+    ref = torch.zeros(T, nh * hd, dtype=torch.float64)
+    EK.attn_chunk(q, pool, ref, items=items_t, n_items=len(items_t), **meta, **kw)
+    for n_splits in (1, 5):
+        part_o = torch.full((T * nh * n_splits * hd,), float("nan"), device=DEV)
+        part_ml = torch.full((T * nh * n_splits * 2,), float("nan"), device=DEV)
+        out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device=DEV)
+        K.attn_chunk_tc(q.to(DEV), pool.to(DEV), out, items=items_t.to(DEV), n_items=len(items_t), n_splits=n_splits,
+                        part_o=part_o, part_ml=part_ml, **_dev(meta), **kw)
+        assert K.attn_tc_error() == 0
+        close(out, ref, dtype, f"scores with slope {slope}, {n_splits} key ranges")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkv,hd,P,window", [(4, 4, 16, 16, 0), (6, 2, 32, 64, 0), (5, 1, 48, 16, 0),
                                                 (16, 16, 128, 64, 0), (2, 1, 256, 64, 0), (4, 2, 64, 16, 300),
