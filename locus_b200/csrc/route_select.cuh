@@ -181,6 +181,64 @@ __device__ __forceinline__ void route_small_block(float* rs_smem, const float* _
         select_token(logits + static_cast<size_t>(t) * ld, rs_smem + wid * 2 * E, t, lane, ids, wts, gamma, s_ids, E,
                      has_gate, o);
     __syncthreads();
+    if (n_pairs <= 32 && E <= 64) {
+        // A handful of pairs (a decode step of up to 8 requests): one warp lays them out with votes instead of loops
+        // and block barriers.  Lane p holds pair p; the lanes of an expert find each other, the first of them counts.
+        if (wid != 0) return;
+        const int id = lane < n_pairs ? s_ids[lane] : -1 - lane;  // lanes without a pair match nobody
+        const unsigned peers = __match_any_sync(0xffffffffu, id);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        for (int e = lane; e < E; e += 32) s_cnt[e] = 0;
+        __syncwarp();
+        if (lane < n_pairs && rank == 0) s_cnt[id] = __popc(peers);
+        __syncwarp();
+        // exclusive prefix sums of rows and tiles over the experts, two experts a lane
+        const int e0 = 2 * lane, e1 = 2 * lane + 1;
+        const int c0 = e0 < E ? s_cnt[e0] : 0, c1 = e1 < E ? s_cnt[e1] : 0;
+        const int t0 = (c0 + tile_m - 1) / tile_m, t1 = (c1 + tile_m - 1) / tile_m;
+        int rows_incl = c0 + c1, tiles_incl = t0 + t1;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int rr = __shfl_up_sync(0xffffffffu, rows_incl, d);
+            const int tt = __shfl_up_sync(0xffffffffu, tiles_incl, d);
+            if (lane >= d) {
+                rows_incl += rr;
+                tiles_incl += tt;
+            }
+        }
+        const int rows_before = rows_incl - c0 - c1, tiles_before = tiles_incl - t0 - t1;
+        if (e0 < E) {
+            s_off[e0] = rows_before;
+            lo.counts[e0] = c0;
+            lo.offsets[e0] = rows_before;
+            for (int i = 0; i < t0; ++i) {
+                lo.tile_expert[tiles_before + i] = e0;
+                lo.tile_row0[tiles_before + i] = rows_before + i * tile_m;
+                lo.tile_rows[tiles_before + i] = min(tile_m, c0 - i * tile_m);
+            }
+        }
+        if (e1 < E) {
+            s_off[e1] = rows_before + c0;
+            lo.counts[e1] = c1;
+            lo.offsets[e1] = rows_before + c0;
+            for (int i = 0; i < t1; ++i) {
+                lo.tile_expert[tiles_before + t0 + i] = e1;
+                lo.tile_row0[tiles_before + t0 + i] = rows_before + c0 + i * tile_m;
+                lo.tile_rows[tiles_before + t0 + i] = min(tile_m, c1 - i * tile_m);
+            }
+        }
+        if (lane == 31) {
+            lo.offsets[E] = rows_incl;
+            *lo.n_tiles = tiles_incl;
+        }
+        __syncwarp();
+        if (lane < n_pairs) {
+            const int at = s_off[id] + rank;   // pairs of an expert in ascending pair order
+            lo.sorted_pair[at] = lane;
+            lo.pair_pos[lane] = at;
+        }
+        return;
+    }
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
         int c = 0;
         for (int p = 0; p < n_pairs; ++p) c += (s_ids[p] == e);
