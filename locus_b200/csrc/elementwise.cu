@@ -100,15 +100,24 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x,
                                                           const int* __restrict__ rows, int H,
                                                           const void* __restrict__ add_src, int add_bf16,
                                                           const int* __restrict__ add_pos, int add_k, int vec_io) {
-    pdl_entry();
-    pdl_trigger();
     __shared__ float warp_part[8];
     __shared__ float scale_s;
     const int i = blockIdx.x;
+    const int n4 = H >> 2;
+    const bool wide = vec_io;
+    // The norm's weights do not depend on the kernel in front: under programmatic dependent launch they are asked
+    // for before the wait for it (the row itself is what that kernel writes).
+    float4 g[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int j = threadIdx.x + u * 256;
+        g[u] = (wide && j < n4) ? load4(w + (j << 2)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_entry();
+    pdl_trigger();
     const int r = rows ? rows[i] : i;
     float4* src = reinterpret_cast<float4*>(x + static_cast<size_t>(r) * H);
     const bool write_back = rows == nullptr;
-    const int n4 = H >> 2;
     auto fetch = [&](int j) -> float4 {
         float4 t = src[j];
         if (add_src != nullptr) {
@@ -160,11 +169,16 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(float* __restrict__ x,
     const float scale = scale_s;
     TO* dst = out + static_cast<size_t>(i) * H;
     // four weights in, four results out, each as one access where the rows are aligned for it (checked by the host)
-    const bool wide = vec_io;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
         const int j = threadIdx.x + u * 256;
-        if (j < n4) store4(dst, w, j << 2, v[u], scale, wide);
+        if (j >= n4) continue;
+        if (wide) {
+            const int c = j << 2;
+            put4(dst + c, v[u].x * scale * g[u].x, v[u].y * scale * g[u].y, v[u].z * scale * g[u].z, v[u].w * scale * g[u].w);
+        } else {
+            store4(dst, w, j << 2, v[u], scale, false);
+        }
     }
     for (int j = threadIdx.x + 1024; j < n4; j += 256) store4(dst, w, j << 2, fetch_again(j), scale, wide);
 }
