@@ -296,20 +296,22 @@ __global__ void __launch_bounds__(256) rope_kv_write_bf16_kernel(
     const bf16* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ inv_freq,
     bf16* __restrict__ q_out, bf16* __restrict__ pool, const int* __restrict__ slots, int nh, int nkv, int hd,
     int page_tokens, int write_kv) {
-    pdl_entry();
-    pdl_trigger();
+    // Positions, slots and frequencies were on the device before the step's first kernel: under programmatic
+    // dependent launch the angles' sines and cosines are ready before the wait for the kernel that writes q, k, v.
     __shared__ float cs_c[128], cs_s[128];
     const int t = blockIdx.x;
     const int half = hd / 2;
     const float pos = static_cast<float>(positions[t]);
+    const int slot = slots[t];
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         const float theta = pos * inv_freq[i];
         cs_c[i] = cosf(theta);
         cs_s[i] = sinf(theta);
     }
     __syncthreads();
+    pdl_entry();
+    pdl_trigger();
     const bf16* src = qkv + static_cast<size_t>(t) * (nh + 2 * nkv) * hd;
-    const int slot = slots[t];
     const int page = slot / page_tokens, off = slot % page_tokens;
     bf16* kbase = pool + static_cast<size_t>(page) * 2 * nkv * page_tokens * hd + static_cast<size_t>(off) * hd;
     const int cpb = half / 8;  // 16-byte chunks per half head
