@@ -572,17 +572,17 @@ def test_attn_chunk_tcgen05(nh, nkv, P, window):
 
 
 def test_attn_chunk_tcgen05_one_far_key_among_thousands_in_ranges():
-    """A portion of 256 tokens behind 6,000 cached ones, the keys cut into ranges: one key far back (in an early
+    """A portion of 128 tokens behind 3,900 cached ones, the keys cut into ranges: one key far back (in an early
     range) is made to carry nearly all the weight of some queries, so that a range whose maximum or denominator
     were lost in the merge would show."""
     dtype, hd, nh, nkv, P = torch.bfloat16, 128, 2, 1, 64
-    segs = [(6000, 256)]
-    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=5, n_pages=100)
+    segs = [(3900, 128)]
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=5, n_pages=66)
     far = 777
     page, off = int(meta["block_table"][0, far // P]), far % P
     pool[page, 0, 0, off] = pool[page, 0, 0, off] * 0 + 4.0      # a large key ...
     q[::3] = q[::3] * 0 + 0.5                                     # ... that every third query points at
-    items_t = torch.tensor([(0, o) for o in range(0, 256, K.MMA_QUERY_TILE)], dtype=torch.int32)
+    items_t = torch.tensor([(0, o) for o in range(0, 128, K.MMA_QUERY_TILE)], dtype=torch.int32)
     kw = dict(n_heads=nh, n_kv_heads=nkv, head_dim=hd, page_tokens=P, window=0, scale=1 / math.sqrt(hd))
     ref = torch.zeros(T, nh * hd, dtype=torch.float64)
     EK.attn_chunk(q, pool, ref, items=items_t, n_items=len(items_t), **meta, **kw)
@@ -605,8 +605,8 @@ def test_attn_chunk_tcgen05_scores_that_rise_or_fall_along_the_keys(slope):
     (18 powers of two a tile: a rescale at every tile), by 0.01 (a rescale every few tiles, probabilities above 1
     in between) and scores that fall (the first tile's maximum stands to the end), whole and in key ranges."""
     dtype, hd, nh, nkv, P = torch.bfloat16, 128, 2, 2, 64
-    segs = [(3000, 256), (0, 300)]
-    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=11, n_pages=60)
+    segs = [(1500, 128), (0, 200)]
+    pool, q, meta, T = _paged_case(dtype, nh, nkv, hd, P, segs, seed=11, n_pages=32)
     pool = (pool.float() * 0.2).to(dtype)
     q = (q.float() * 0.2).to(dtype)
     q.view(T, nh, hd)[:, :, 0] = math.sqrt(hd)                      # score = slope * position + small noise
