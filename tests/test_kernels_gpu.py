@@ -879,6 +879,33 @@ def test_sample_cluster_kernel_gives_the_one_block_kernels_tokens(V):
     assert all(row[8] >= V // 2 for row in toks)        # nothing without weight is drawn
 
 
+def test_sampler_front_end_at_the_full_vocabulary():
+    """Sampler.sample (packed parameter upload, penalties, then the sampling kernel) on 5 rows of 151,936 logits:
+    the same tokens whether the rows go to the cluster kernel or to the one-block kernel, and the same again for the
+    same seeds and counters."""
+    from locus_b200.sampling.sampler import GREEDY, Sampler, SamplingParams
+
+    V, R = 151936, 5
+    logits = (torch.randn(R, V, generator=torch.Generator().manual_seed(7)) * 2.0).to(DEV)
+    params = [GREEDY, SamplingParams(temperature=0.8), SamplingParams(temperature=1.0, top_k=40, top_p=0.9),
+              SamplingParams(temperature=0.7, top_p=0.8, min_p=0.02),
+              SamplingParams(temperature=0.9, top_p=0.95, repeat_penalty=1.2, presence_penalty=0.3, repeat_last_n=16)]
+    hist = [[1, 2, 3], [], [5], [7, 7], list(range(100, 140))]
+    seeds = [11, 12, 13, 14, 15]
+    runs = {}
+    try:
+        for cluster in (True, False, True):
+            K.sample_use_cluster(cluster)
+            s = Sampler(DEV, 8)
+            runs.setdefault(cluster, []).append([s.sample(logits.clone(), params, seeds, [c] * R, hist) for c in range(12)])
+    finally:
+        K.sample_use_cluster(True)
+    assert runs[True][0] == runs[False][0] == runs[True][1]
+    toks = runs[True][0]
+    assert all(row[0] == int(torch.argmax(logits[0])) for row in toks)
+    assert len({row[1] for row in toks}) > 3 and all(0 <= t < V for row in toks for t in row)
+
+
 def test_penalties():
     import plain_qwen2moe as plain
     V, R = 50, 3
