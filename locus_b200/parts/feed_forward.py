@@ -61,6 +61,8 @@ class DenseMlp(FeedForward):
 # (decode steps of the 2.7B sizes at 4,096 tokens of context: 1.995 -> 1.81 ms at one request, 4.14 -> 3.97 at 8,
 # 6.83 -> 6.40 at 16, 9.00 -> 8.88 at 32; at 64 the router and the product get in each other's way: 13.27 -> 13.37).
 SHARED_EARLY_TOKENS = 32
+SHARED_OVERLAP_FROM = 1024   # steps of at least this many tokens ...
+SHARED_OVERLAP_ROWS = 192    # ... and at most this many rows per routed expert run the shared expert on the side stream
 
 
 class SparseMoe(FeedForward):
@@ -167,9 +169,16 @@ class SparseMoe(FeedForward):
         sorted_already = False
         # The shared expert needs only h for its first product: for a few tokens, where no kernel fills the GPU, it
         # starts on the side stream beside the router; its second product waits for the router's gate (below).
-        overlap = self.shared is not None and T <= 64
+        # Long portions, too, while the routed experts wait for their weights rather than for the tensor cores
+        # (fewer than about 190 rows per expert: flops / peak < bytes / bandwidth): the shared expert's products,
+        # which are bound by the tensor cores, then run beside the router, the selection, the layout and the gather
+        # and fill what the routed products leave idle.  (2,048 tokens of the 2.7B sizes in one step 12.6 -> 11.7 ms,
+        # in two steps of 1,024 17.5 -> 15.2 ms; steps of 512 tokens lose, 27.6 -> 28.7 ms, and so do the 57B sizes'
+        # steps of 4,096 and 8,192 tokens, whose experts are bound by the tensor cores: 1,254 -> 1,289 ms.)
+        long_overlap = T >= SHARED_OVERLAP_FROM and n_pairs <= SHARED_OVERLAP_ROWS * self.E
+        overlap = self.shared is not None and (T <= 64 or long_overlap)
         shared_act = None
-        if overlap and T <= SHARED_EARLY_TOKENS:
+        if overlap and (T <= SHARED_EARLY_TOKENS or long_overlap):
             with rt.side():
                 shared_act = self.shared.forward_up(h, rt)
         if self._router_all is not None and K.USE_TENSOR_CORES:
