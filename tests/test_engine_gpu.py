@@ -234,6 +234,42 @@ def test_short_portions_behind_a_long_context_with_head_size_128(tmp_path_factor
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_long_portion_with_the_shared_expert_beside_the_router(dtype, tmp_path_factory):
+    """A step of more than 1,024 tokens on a model with enough experts that each gets fewer than 192 rows: the
+    shared expert then starts on the side stream before the router and runs beside the selection, the layout, the
+    gather and the routed products.  Run once with the picked experts read back after every router (which waits for
+    the device there) and once without a wait anywhere in the step; shorter steps of the same requests take the
+    other orders."""
+    import locus_b200.parts.feed_forward as FF
+    from tiny_configs import config
+
+    raw = config("D")
+    raw["num_experts"], raw["max_position_embeddings"] = 16, 2048
+    case = Case("D", tmp_path_factory.mktemp("models_d_wide"), raw=raw, requests=[(1190, 4), (60, 5)])
+    beside = []
+    orig = FF.DenseMlp.forward_up
+
+    def forward_up(self, h, rt):
+        beside.append((h.shape[0], rt.side_stream is not None and torch.cuda.current_stream() == rt.side_stream))
+        return orig(self, h, rt)
+
+    FF.DenseMlp.forward_up = forward_up
+    try:
+        for observe in (True, False):
+            runner, cache = make_runner(case, dtype, page_tokens=64, n_pages=24, max_tokens=1280, max_seq=2048)
+            steps = [[("r0", 1100), ("r1", 30)], [("r0", 88), ("r1", 29)], [("r0", 1), ("r1", 1)], [("r0", 1)]]
+            got = run_trace(runner, cache, case, steps, observe=observe)
+            check(case, got, dtype, f"shared expert beside the router (routing read back: {observe})")
+            assert cache.free_pages() == cache.total_pages()
+    finally:
+        FF.DenseMlp.forward_up = orig
+    n_layers = raw["num_hidden_layers"]
+    assert beside.count((1130, True)) == 2 * n_layers and (1130, False) not in beside
+    assert beside.count((117, False)) == 2 * n_layers and (117, True) not in beside   # 65 to 1,023 tokens: no overlap
+    assert beside.count((2, True)) == 2 * n_layers                                    # up to 32 tokens: early as well
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_last_32_tokens_one_by_one(case, dtype):
     runner, cache = make_runner(case, dtype)
     steps = []
