@@ -163,6 +163,11 @@ class SparseMoe(FeedForward):
         widths_ok = self.I % 8 == 0 and self.hidden % 8 == 0
         all_bf16 = (K.tensor_cores_take(h, self.params["gate_exps"]) and widths_ok
                     and self.params["down_exps"].dtype == torch.bfloat16)
+        if not all_bf16 and widths_ok and n_pairs <= K.FEW_ROWS * self.E:
+            # No tensor-core form (float32) and a handful of rows per expert: tiles of 8 rows on the row-streaming
+            # kernel read an expert's weights once per tile, where the CUDA-core product would compute a 64-row
+            # tile for every expert that has a row.
+            tile = K.FEW_ROWS
         streamed = (all_bf16 and tile <= K.SKINNY_TILE_ROWS) or (widths_ok and tile <= K.FEW_ROWS)
         if not streamed and not all_bf16:
             tile = 64

@@ -110,7 +110,7 @@ def _moe_step(part, W, cfg, dtype, rt, T, seed):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("E,k,norm,I,Is,T", [(8, 2, False, 32, 64, 5), (12, 3, True, 48, 0, 70), (60, 4, False, 40, 96, 300),
-                                            (60, 4, True, 24, 56, 1100)])
+                                            (60, 4, True, 24, 56, 1100), (60, 4, False, 40, 96, 100)])
 def test_sparse_moe_part(dtype, E, k, norm, I, Is, T):
     H = 72
     part = make_part("feed_forward", PartSpec("sparse_moe", {"hidden": H, "n_experts": E, "top_k": k, "norm_topk": norm,
