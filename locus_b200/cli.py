@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 import time
 from typing import List
@@ -90,6 +91,11 @@ def build_parser() -> argparse.ArgumentParser:
                     help="write a random-weights model folder from --config into <model_dir> first")
     ap.add_argument("--config", default="", help="config.json for --random-weights")
     ap.add_argument("--stats", action="store_true", help="print engine counters at exit")
+    ap.add_argument("--moe-stats", action="store_true",
+                    help="count the picked experts per layer and print the reference's moe-stats line at exit "
+                         "(also switched on by the environment variable LOCUS_MOE_STATS)")
+    ap.add_argument("--kernel-times", action="store_true",
+                    help="run every step eagerly and print, at exit, the time per kernel entry point")
     return ap
 
 
@@ -145,6 +151,16 @@ def main(argv=None) -> int:
               f"embd={plan.hidden_size} heads={getattr(cfg, 'num_attention_heads', '?')}/"
               f"{getattr(cfg, 'num_key_value_heads', '?')} vocab={plan.vocab_size}", file=sys.stderr)
         ids = _parse_prompt(args.prompt, plan.vocab_size, args.seed)
+        moe_stats = kernel_times = None
+        if args.moe_stats or os.environ.get("LOCUS_MOE_STATS") is not None:   # moe_stats.cpp:23-27
+            from .engine.moe_stats import MoeStats
+
+            moe_stats = MoeStats(eng.model)
+        if args.kernel_times:
+            from . import kernels as K
+
+            kernel_times = K.kernel_times()
+            kernel_times.__enter__()
         sp = SamplingParams(temperature=args.temperature, top_k=args.top_k, top_p=args.top_p, min_p=args.min_p,
                             repeat_penalty=args.repeat_penalty, frequency_penalty=args.frequency_penalty,
                             presence_penalty=args.presence_penalty, repeat_last_n=args.repeat_last_n)
@@ -170,6 +186,15 @@ def main(argv=None) -> int:
                   f"(batch_decode=1 batch_prefill={0 if args.no_batch_prefill else 1})", file=sys.stderr)
         if args.stats:
             print(json.dumps(eng.stats()), file=sys.stderr)
+        if kernel_times is not None:
+            kernel_times.__exit__(None, None, None)
+            table = kernel_times.table()
+            total = sum(ms for _, ms in table.values()) or 1.0
+            print("kernel-times: entry point, launches, ms, share (eager steps)", file=sys.stderr)
+            for what, (n, ms) in sorted(table.items(), key=lambda kv: -kv[1][1]):
+                print(f"kernel-times: {what:<20} {n:>8} {ms:>10.3f} {100.0 * ms / total:>5.1f}%", file=sys.stderr)
+        if moe_stats is not None:
+            print(moe_stats.report(), file=sys.stderr)
     except Exception as e:  # the reference prints "error: <what>" and returns 1 (run_main.cpp:133-136)
         print(f"error: {e}", file=sys.stderr)
         return 1

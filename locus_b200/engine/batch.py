@@ -102,6 +102,7 @@ class _SideScope:
         self._ctx.__enter__()
         self._scope = K.stream_scope()
         self._scope.__enter__()
+        K.timing_restart()
         return self
 
     def __exit__(self, *exc):

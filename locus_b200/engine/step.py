@@ -262,7 +262,7 @@ class ModelRunner:
         rows in the order of the entries and of their ``want``; valid until the next step).
         The requests' token counts are advanced."""
         decode_only = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
-        graphed = self.use_graphs and decode_only and self.device.type == "cuda"
+        graphed = self.use_graphs and decode_only and self.device.type == "cuda" and not K.timing_active()
         batch = self._build(entries, fixed_shapes=graphed)
         before = K.launches
         if graphed:

@@ -90,6 +90,71 @@ class stream_scope:
         return False
 
 
+class kernel_times:
+    """Opt-in table of where the time of eager steps goes, by entry point of this module (the reference has no
+    profiler of its own: it prints counters at exit and is timed from outside).  Inside the scope an event is
+    recorded behind every entry point's launch, on the stream it went to, and the launch is charged the time from
+    the event before it on that stream (the scope's start, for the first launch on the stream that opened the
+    scope) to its own: its run and whatever the stream waited for in front of it.  ``ModelRunner.step`` replays no
+    graph meanwhile.  ``table()`` waits for the device and returns {entry point: (launches, milliseconds)}; the
+    first launch on another stream is counted without a time."""
+
+    def __enter__(self):
+        global _TIMES
+        _need(_TIMES is None, "kernel_times: scopes do not nest")
+        self._spans = []   # (entry point, event before, event behind)
+        self._counts = {}
+        self._last = {}    # stream -> the event behind its latest launch
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+        self._last[torch.cuda.current_stream().cuda_stream] = start
+        _TIMES = self
+        return self
+
+    def __exit__(self, *exc):
+        global _TIMES
+        _TIMES = None
+        return False
+
+    def _mark(self, what: str) -> None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        key = torch.cuda.current_stream().cuda_stream
+        before = self._last.get(key)
+        if before is not None:
+            self._spans.append((what, before, ev))
+        self._counts[what] = self._counts.get(what, 0) + 1
+        self._last[key] = ev
+
+    def restart(self) -> None:
+        """The current stream starts a stretch of work of its own (a side stream that has just been told to wait
+        for the main one): its next launch is charged from here, not from its last launch long ago."""
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        self._last[torch.cuda.current_stream().cuda_stream] = ev
+
+    def table(self) -> dict:
+        torch.cuda.synchronize()
+        ms = {}
+        for what, a, b in self._spans:
+            ms[what] = ms.get(what, 0.0) + a.elapsed_time(b)
+        return {what: (n, ms.get(what, 0.0)) for what, n in self._counts.items()}
+
+
+_TIMES: Optional[kernel_times] = None
+
+
+def timing_active() -> bool:
+    """Whether a :class:`kernel_times` scope is open (steps then run eagerly)."""
+    return _TIMES is not None
+
+
+def timing_restart() -> None:
+    """See :meth:`kernel_times.restart`; nothing without an open scope."""
+    if _TIMES is not None:
+        _TIMES.restart()
+
+
 # kernels launched through this module since import (some entry points launch two and count the second themselves)
 launches = 0
 _LAUNCHES_OF = {}
@@ -105,6 +170,8 @@ def _check(code: int, what: str, detail: str = "") -> None:
     global launches
     if code == 0:
         launches += _LAUNCHES_OF.get(what, 1)
+        if _TIMES is not None:
+            _TIMES._mark(what)
         return
     if code == ERR_UNSUPPORTED:
         raise KernelError(f"{what}: sizes or element types outside what the kernel takes {detail}")

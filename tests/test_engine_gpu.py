@@ -700,3 +700,50 @@ def test_released_midway_and_fed_again_from_the_start(case, dtype):
         scale = float(ref.abs().max())
         assert float(err.max()) <= tol_max * scale, f"{name}: max error {float(err.max()):.3e} at {int(err.max(dim=1).values.argmax())}"
         assert float(err.mean()) <= tol_mean * scale, name
+
+
+def test_expert_counters_through_graphs_and_the_kernel_time_table(tmp_path_factory):
+    """The expert counters count once per executed step, also when decode steps are replayed from their CUDA graph
+    (the counting is one more launch of the graph); the opt-in kernel time table makes steps run eagerly, names the
+    entry points that ran and charges them times that fit into the wall clock of the scope."""
+    import time
+
+    import locus_b200.kernels as K
+    from locus_b200.engine.moe_stats import MoeStats
+    from locus_b200.engine.step import StepEntry
+
+    case = Case("B", tmp_path_factory.mktemp("models_telemetry"))
+    runner, cache = make_runner(case, torch.bfloat16, use_graphs=True)
+    stats = MoeStats(runner.model)
+    toks = case.tokens["r5"]
+    seq = cache.open("a")
+
+    def feed(a, n):
+        assert cache.ensure_capacity(seq, n)
+        return runner.step([StepEntry(seq, toks[a : a + n], [n - 1])])
+
+    feed(0, 60)
+    for i in range(60, 72):
+        feed(i, 1)
+    replays = runner.stats["graph_replays"]
+    assert replays >= 10
+    k, n_moe = case.cfg["num_experts_per_tok"], len(stats.counts)
+    assert n_moe > 0 and stats.summary()["activations"] == 72 * k * n_moe
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    with K.kernel_times() as kt:
+        assert K.timing_active()
+        for i in range(72, 76):
+            feed(i, 1)
+        feed(76, 24)
+        table = kt.table()
+    wall_ms = (time.perf_counter() - t0) * 1e3
+    assert not K.timing_active() and runner.stats["graph_replays"] == replays   # nothing was replayed inside
+    for what in ("embed_rows", "rmsnorm", "linear", "rope_kv_write", "attn_decode"):
+        assert what in table and table[what][0] > 0, (what, sorted(table))
+    total = sum(ms for _, ms in table.values())
+    assert all(ms >= 0.0 for _, ms in table.values()) and 0.0 < total <= 2.0 * wall_ms + 1.0   # two streams at most
+    feed(100, 1)
+    assert runner.stats["graph_replays"] == replays + 1                          # and graphs again afterwards
+    assert stats.summary()["activations"] == 101 * k * n_moe
+    cache.release(seq)

@@ -120,6 +120,44 @@ def test_generation_through_the_engine_matches_plain_greedy(name, tmp_path):
     assert len(c[0]) == 5
 
 
+def test_moe_stats_count_every_pick_and_word_the_reference_line(tmp_path):
+    """The expert counters against the plain implementation's routing of the same tokens: every (layer, expert)
+    count, the number of activations and the reference's one-line report."""
+    from locus_b200.engine.moe_stats import MoeStats
+
+    cfg, W, model, cache, runner = setup("B", tmp_path, n_pages=16)
+    stats = MoeStats(model)
+    toks = random_tokens(40, cfg["vocab_size"], 3)
+    s = cache.open("a")
+    fed = 0
+    for n in (23, 16, 1):   # two portions and a single token
+        assert cache.ensure_capacity(s, n)
+        runner.step([StepEntry(s, toks[fed : fed + n], [n - 1])])
+        fed += n
+    aux = {}
+    plain.forward(cfg, W, toks, torch.float64, aux=aux)
+    table = stats.table()
+    assert set(table) == set(aux) and len(table) > 0
+    k = cfg["num_experts_per_tok"]
+    for prefix, rows in aux.items():
+        want = [0] * cfg["num_experts"]
+        for ids, _ in rows:
+            for e in ids:
+                want[int(e)] += 1
+        assert table[prefix] == want, prefix
+    sm = stats.summary()
+    assert sm["activations"] == 40 * k * len(table) and sm["slots"] == cfg["num_experts"] * len(table)
+    assert 1 <= sm["min_unique"] <= sm["max_unique"] <= cfg["num_experts"]
+    line = stats.report()
+    assert line.startswith(f"moe-stats: {sm['activations']} activations; experts touched per moe layer min ")
+    assert f"{sm['touched']} of {sm['slots']} (" in line and line.endswith("layer-expert slots touched")
+    stats.detach()
+    assert all(p.observer is None for p in stats.parts)
+    assert cache.ensure_capacity(s, 1)
+    runner.step([StepEntry(s, [1], [0])])
+    assert stats.summary()["activations"] == sm["activations"]   # detached: counts no more
+
+
 def plain_descriptors(cache, entries, chunk_tile, mma_tile):
     """The descriptors of a step, written down from their definitions with lists."""
     P, W = cache.page_tokens, cache.table_width
