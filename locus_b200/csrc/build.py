@@ -36,7 +36,9 @@ NVCC_FLAGS = [
     "-fPIC",
 ]
 
-HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"]
+# Flags of the host modules; $LOCUS_HOST_FLAGS adds to them (for instance "-fsanitize=address,undefined -g" for a
+# checked build of the cache's and the scheduler's bookkeeping; the flags are part of the library's name).
+HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-Wall"] + os.environ.get("LOCUS_HOST_FLAGS", "").split()
 
 _INCLUDE = re.compile(r'^\s*#\s*include\s+"([^"]+)"', re.M)
 
